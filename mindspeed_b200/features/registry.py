@@ -1,0 +1,616 @@
+"""All feature classes, in application order (reference: mindspeed/features_manager/__init__.py:377-409).
+
+Every class owns its flags.  Flag names are the reference's (including its historical spellings such
+as ``--pre-tockens``) so launch scripts carry over; vendor-specific names that users already have in
+scripts (``--use-ascend-mc2``, ``--use-ascend-coc``, ``--hccl-*``) are kept as aliases of the
+hardware-neutral ones (``--use-fused-tp-comm``, ``--use-chunked-tp-comm``, ``--nccl-*``).
+"""
+from __future__ import annotations
+
+from .feature import Feature, add_arg
+
+
+# ======================================================================================
+# level-0 basics
+# ======================================================================================
+class RequirementsBasicFeature(Feature):
+    def __init__(self):
+        super().__init__("requirements-basic", optimization_level=0)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--optimization-level", type=int, choices=[0, 1, 2], default=2,
+                help="0: library GEMM + NCCL paths; 1: + fused single-GPU kernels; 2: + fused compute/communication kernels")
+        add_arg(g, "--optimizer-selection", type=str, default="fused_adamw",
+                choices=["fused_adamw", "fused_torch_adamw", "fused_ema_adamw"])
+        add_arg(g, "--ai-framework", type=str, default="pytorch", choices=["pytorch", "mindspore"])
+
+    def validate_args(self, args):
+        if args.ai_framework != "pytorch":
+            raise AssertionError("only the pytorch framework layer exists in this build")
+
+
+class MegatronBasicFeature(Feature):
+    def __init__(self):
+        super().__init__("megatron-basic", optimization_level=0)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--use-fused-rmsnorm", action="store_true")
+        add_arg(g, "--use-fused-swiglu", action="store_true")
+        add_arg(g, "--use-fused-rotary-pos-emb", action="store_true")
+        add_arg(g, "--use-fused-moe-token-permute-and-unpermute", action="store_true")
+        add_arg(g, "--use-fused-ring-attention-update", action="store_true")
+        add_arg(g, "--gemm-gradient-accumulation-fusion", action="store_true")
+
+    def post_validate_args(self, args):
+        if args.optimization_level >= 1:
+            for k in ("use_fused_rmsnorm", "use_fused_swiglu", "use_fused_rotary_pos_emb",
+                      "use_fused_moe_token_permute_and_unpermute", "use_fused_ring_attention_update"):
+                setattr(args, k, True)
+
+
+class TransformerEngineBasicFeature(Feature):
+    """fp8 recipes and the TE-compatible module options
+    (reference: mindspeed/features_manager/megatron_basic/transformer_engine_basic.py:41-272)."""
+
+    def __init__(self):
+        super().__init__("transformer-engine-basic", optimization_level=0)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--fp8-format", type=str, default=None, choices=["e4m3", "hybrid", "hif8"])
+        add_arg(g, "--fp8-recipe", type=str, default="delayed",
+                choices=["delayed", "tensorwise", "mxfp8", "mxfp8-32x32", "blockwise"])
+        add_arg(g, "--no-use-gmm-fp8", action="store_false", dest="use_gmm_fp8")
+        add_arg(g, "--te-comparison-with-cpu", action="store_true")
+        add_arg(g, "--te-comparison-with-bf16", action="store_true")
+        add_arg(g, "--te-gmm-mode", type=str, default="performance", choices=["performance", "compatible"])
+        add_arg(g, "--fp8-reuse-quantized-weight", action="store_true")
+        add_arg(g, "--qat-scheme", type=str, default=None, choices=[None, "w4a16", "w8a16", "w4a4"])
+        add_arg(g, "--qat-quant-block-size", type=int, default=128)
+        add_arg(g, "--no-qad-enable", action="store_false", dest="qad_enable")
+        add_arg(g, "--kl-loss-reduction", type=str, default="batchmean")
+
+    def validate_args(self, args):
+        if args.fp8_format == "hif8":
+            raise AssertionError("hif8 is an Ascend number format with no Blackwell tensor-core mode; use e4m3/hybrid")
+        if args.fp8_format and args.fp8_recipe == "delayed" and getattr(args, "moe_grouped_gemm", False):
+            pass
+
+
+class ProfileFeature(Feature):
+    def __init__(self):
+        super().__init__("profile", optimization_level=0)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--profile", action="store_true")
+        add_arg(g, "--profile-step-start", type=int, default=10)
+        add_arg(g, "--profile-step-end", type=int, default=12)
+        add_arg(g, "--profile-level", type=str, default="level0", choices=["level0", "level1", "level2"])
+        add_arg(g, "--profile-with-cpu", action="store_true")
+        add_arg(g, "--profile-with-stack", action="store_true")
+        add_arg(g, "--profile-with-memory", action="store_true")
+        add_arg(g, "--profile-record-shapes", action="store_true")
+        add_arg(g, "--profile-save-path", type=str, default="./profile_dir")
+        add_arg(g, "--profile-ranks", nargs="+", type=int, default=[-1])
+
+
+class TflopsCalculateFeature(Feature):
+    def __init__(self):
+        super().__init__("op-cal-tflops", optimization_level=0)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--op-cal-tflops", action="store_true", help="count FLOPs per step and log MFU / HFU")
+
+
+class DeterministicFeature(Feature):
+    def __init__(self):
+        super().__init__("npu-deterministic", optimization_level=0)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--npu-deterministic", "--deterministic", dest="npu_deterministic", action="store_true")
+        add_arg(g, "--npu-datadump", "--tensor-dump", dest="npu_datadump", action="store_true")
+        add_arg(g, "--jit-compile", action="store_true")
+
+    def configure(self, manager, args):
+        if getattr(args, "npu_deterministic", False):
+            from ..utils.determinism import enable_determinism
+            enable_determinism(getattr(args, "seed", 1234))
+
+
+class TokenizerFeature(Feature):
+    def __init__(self):
+        super().__init__("tokenizer", optimization_level=0)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--tokenizer-name-or-path", type=str, default=None)
+        add_arg(g, "--tokenizer-not-use-fast", action="store_false", dest="tokenizer_use_fast")
+
+
+# ======================================================================================
+# tensor parallel
+# ======================================================================================
+class FusedTPCommFeature(Feature):
+    """Fused all-gather->GEMM and GEMM->reduce-scatter kernels (the reference's MC2,
+    mindspeed/features_manager/tensor_parallel/mc2.py:15-32)."""
+
+    def __init__(self):
+        super().__init__("use-ascend-mc2", optimization_level=2)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--use-ascend-mc2", "--use-fused-tp-comm", dest="use_ascend_mc2", action="store_true")
+
+    def validate_args(self, args):
+        self.incompatible_check(args, "use_ascend_coc")
+        if args.use_ascend_mc2:
+            if not getattr(args, "sequence_parallel", False) or getattr(args, "tensor_model_parallel_size", 1) <= 1:
+                raise AssertionError("fused TP communication needs --sequence-parallel and tensor parallel size > 1")
+
+    def configure(self, manager, args):
+        manager.set_slot("tp_comm_ops", "fused", owner=self.feature_name)
+
+
+class ChunkedTPCommFeature(Feature):
+    """Chunk-pipelined GEMM / collective (the reference's CoC, features_manager/tensor_parallel/locl_coc.py:14-27)."""
+
+    def __init__(self):
+        super().__init__("use-ascend-coc", optimization_level=2)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--use-ascend-coc", "--use-chunked-tp-comm", dest="use_ascend_coc", action="store_true")
+        add_arg(g, "--coc-mode", type=int, default=-1, choices=[-1, 0, 1, 2])
+        add_arg(g, "--coc-parallel-num", type=int, default=1, choices=[1, 2, 4, 8])
+        add_arg(g, "--coc-fused-kernel", action="store_true")
+
+    def validate_args(self, args):
+        if args.use_ascend_coc and args.coc_fused_kernel and not getattr(args, "sequence_parallel", False):
+            raise AssertionError("--coc-fused-kernel needs --sequence-parallel")
+
+    def configure(self, manager, args):
+        manager.set_slot("tp_comm_ops", "fused" if args.coc_fused_kernel else "chunked", owner=self.feature_name)
+
+
+class TP2DFeature(Feature):
+    def __init__(self):
+        super().__init__("tp-2d", optimization_level=2)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--tp-2d", action="store_true")
+        add_arg(g, "--tp-x", type=int, default=1)
+        add_arg(g, "--tp-y", type=int, default=1)
+        add_arg(g, "--enable-overlap-ag-with-matmul", action="store_true")
+        add_arg(g, "--enable-overlap-matmul-with-rs", action="store_true")
+        add_arg(g, "--enable-backward-overlap-ag-with-matmul", action="store_true")
+
+    def validate_args(self, args):
+        if not args.tp_2d:
+            return
+        if args.tp_x * args.tp_y != args.tensor_model_parallel_size:
+            raise AssertionError("tp_x * tp_y must equal --tensor-model-parallel-size")
+        for bad in ("sequence_parallel", "use_ascend_coc"):
+            if getattr(args, bad, False):
+                raise AssertionError(f"--tp-2d is incompatible with {bad}")
+        if getattr(args, "num_experts", None):
+            raise AssertionError("--tp-2d does not support MoE")
+        if getattr(args, "context_parallel_size", 1) > 1 and args.context_parallel_algo not in ("megatron_cp_algo", "ulysses_cp_algo"):
+            raise AssertionError("--tp-2d supports ring or Ulysses context parallelism only")
+
+
+class UnalignedLinearFeature(Feature):
+    def __init__(self):
+        super().__init__("unaligned-linear", optimization_level=2)
+
+    def register_args(self, parser):
+        add_arg(parser.add_argument_group(title=self.feature_name), "--unaligned-linear", action="store_true")
+
+    def validate_args(self, args):
+        if args.unaligned_linear and getattr(args, "use_ascend_mc2", False):
+            raise AssertionError("--unaligned-linear is incompatible with the fused TP communication kernels")
+
+
+# ======================================================================================
+# context parallel / attention
+# ======================================================================================
+class ContextParallelFeature(Feature):
+    def __init__(self):
+        super().__init__("context-parallel-size", optimization_level=2)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--context-parallel-algo", type=str, default="megatron_cp_algo",
+                choices=["megatron_cp_algo", "ulysses_cp_algo", "hybrid_cp_algo", "hybrid_adaptive_cp_algo",
+                         "adaptive_cp_algo", "kvallgather_cp_algo"])
+        add_arg(g, "--cp-window-size", type=int, default=1)
+        add_arg(g, "--attention-mask-type", type=str, default="causal", choices=["causal", "general"])
+        add_arg(g, "--use-cp-send-recv-overlap", action="store_true")
+        add_arg(g, "--megatron-cp-in-bnsd", action="store_true")
+        add_arg(g, "--ulysses-degree-in-cp", type=int, default=None)
+        add_arg(g, "--context-parallel-kv-cache-policy", type=str, default=None, choices=[None, "full", "half"])
+        add_arg(g, "--context-parallel-cache-interval", type=int, default=0)
+        add_arg(g, "--use-ulysses-allgather-kv", action="store_true")
+        add_arg(g, "--attention-mask-on-cpu", action="store_true")
+        add_arg(g, "--adaptive-cp-without-coarse", action="store_true")
+        add_arg(g, "--adaptive-cp-dynamic-attn-mask", action="store_true")
+        add_arg(g, "--adaptive-cp-only-reschedule", action="store_true")
+        add_arg(g, "--adaptive-cp-manually-set-mask-list", action="store_true")
+
+    def is_need_apply(self, args):
+        return getattr(args, "context_parallel_size", 1) > 1 and self.optimization_level <= getattr(args, "optimization_level", 2) \
+            or getattr(args, "context_parallel_size", 1) > 1
+
+    def validate_args(self, args):
+        cp = args.context_parallel_size
+        if cp <= 1:
+            return
+        algo = args.context_parallel_algo
+        seq = args.seq_length
+        if algo == "megatron_cp_algo":
+            if seq % (2 * cp) != 0:
+                raise AssertionError("ring context parallel needs seq_length divisible by 2 * cp")
+            w = args.cp_window_size
+            if not (1 <= w < cp) and cp > 1 and w != 1:
+                raise AssertionError("cp_window_size must satisfy 1 <= window < cp")
+            if cp % w != 0:
+                raise AssertionError("cp must be divisible by cp_window_size")
+        if algo == "ulysses_cp_algo":
+            heads = args.num_attention_heads
+            if heads % (cp * args.tensor_model_parallel_size) != 0:
+                raise AssertionError("Ulysses needs num_attention_heads divisible by cp * tp")
+            if seq % cp != 0:
+                raise AssertionError("Ulysses needs seq_length divisible by cp")
+        if algo in ("hybrid_cp_algo", "hybrid_adaptive_cp_algo"):
+            u = args.ulysses_degree_in_cp
+            if u is None or cp % u != 0 or not (1 < u < cp):
+                raise AssertionError("hybrid context parallel needs 1 < ulysses_degree_in_cp < cp dividing cp")
+            ring = cp // u
+            if seq % (2 * ring * u) != 0:
+                raise AssertionError("hybrid context parallel needs seq_length divisible by 2 * cp")
+        if algo == "kvallgather_cp_algo" and args.attention_mask_type != "causal":
+            raise AssertionError("KV-allgather context parallel supports causal attention only")
+
+
+class FlashAttentionFeature(Feature):
+    def __init__(self):
+        super().__init__("use-flash-attn", optimization_level=2)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--pre-tockens", type=int, default=65536)
+        add_arg(g, "--next-tockens", type=int, default=0)
+        add_arg(g, "--sparse-mode", type=int, default=0, choices=[0, 1, 2, 3, 4])
+        add_arg(g, "--use-fusion-attn-v2", action="store_true")
+        add_arg(g, "--square-alibi-mask", action="store_true")
+        add_arg(g, "--fill-neg-inf", action="store_true")
+        add_arg(g, "--alibi-fusion-attn-type", type=int, default=None, choices=[None, 0, 2, 3])
+        add_arg(g, "--alibi-diagonal-opposite", action="store_true")
+        add_arg(g, "--reset-attention-mask", action="store_true")
+        add_arg(g, "--fix-sub-seq-length", type=int, default=None)
+        add_arg(g, "--experimental-attention-variant", type=str, default=None, choices=[None, "dsa"])
+        add_arg(g, "--use-dsa-absorb", action="store_true")
+        add_arg(g, "--use-fused-lightning-indexer", action="store_true")
+        add_arg(g, "--use-fused-sparse-flash-attention", action="store_true")
+        add_arg(g, "--use-fused-lightning-indexer-kl-loss", action="store_true")
+
+
+class MLAFeature(Feature):
+    def __init__(self):
+        super().__init__("multi-head-latent-attention", optimization_level=2)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--multi-head-latent-attention", "--multi-latent-attention", dest="multi_head_latent_attention",
+                action="store_true")
+        add_arg(g, "--q-lora-rank", type=int, default=None)
+        add_arg(g, "--kv-lora-rank", type=int, default=512)
+        add_arg(g, "--v-head-dim", type=int, default=128)
+        add_arg(g, "--qk-rope-head-dim", type=int, default=64)
+        add_arg(g, "--qk-nope-head-dim", type=int, default=128)
+        add_arg(g, "--rope-scaling-type", type=str, default=None, choices=[None, "yarn"])
+        add_arg(g, "--rope-scaling-factor", type=float, default=1.0)
+        add_arg(g, "--rope-scaling-original-max-position-embeddings", type=int, default=4096)
+        add_arg(g, "--rope-scaling-beta-fast", type=int, default=32)
+        add_arg(g, "--rope-scaling-beta-slow", type=int, default=1)
+        add_arg(g, "--rope-scaling-mscale", type=float, default=1.0)
+        add_arg(g, "--rope-scaling-mscale-all-dim", type=float, default=0.0)
+
+
+# ======================================================================================
+# pipeline parallel
+# ======================================================================================
+class DualpipeVFeature(Feature):
+    def __init__(self):
+        super().__init__("schedules-method", optimization_level=2)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--schedules-method", type=str, default=None, choices=[None, "dualpipev", "dualpipe", "chimera"])
+        add_arg(g, "--dualpipev-dw-detach", action="store_true")
+
+    def validate_args(self, args):
+        if args.schedules_method in ("dualpipev", "dualpipe"):
+            pp = args.pipeline_model_parallel_size
+            if pp < 2:
+                raise AssertionError("DualPipe schedules need pipeline parallel size >= 2")
+            if args.num_layers % (2 * pp) != 0:
+                raise AssertionError("number of layers must be divisible by 2 * pipeline parallel size")
+            nmb = args.global_batch_size // (args.micro_batch_size * max(1, args.data_parallel_size))
+            if nmb < 2 * pp:
+                raise AssertionError("DualPipe schedules need at least 2 * pp micro-batches")
+            for bad in ("num_layers_per_virtual_pipeline_stage", "swap_attention", "tp_2d"):
+                if getattr(args, bad, None):
+                    raise AssertionError(f"dualpipe schedules are incompatible with {bad}")
+            if getattr(args, "context_parallel_size", 1) > 1:
+                raise AssertionError("dualpipe schedules are incompatible with context parallelism")
+
+    def configure(self, manager, args):
+        manager.set_slot("schedule", args.schedules_method, owner=self.feature_name)
+
+
+class PipelineMiscFeature(Feature):
+    def __init__(self):
+        super().__init__("pipeline-misc", optimization_level=0)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--recompute-in-bubble", action="store_true")
+        add_arg(g, "--recompute-in-advance", action="store_true")
+        add_arg(g, "--noop-layers", type=str, default=None)
+        add_arg(g, "--optimize-send-recv-comm", action="store_true")
+        add_arg(g, "--use-multiparameter-pipeline-model-parallel", action="store_true")
+        add_arg(g, "--pipeline-model-parallel-layout", type=str, default=None)
+        add_arg(g, "--pipeline-num-transformer-layers", type=str, default=None)
+        add_arg(g, "--automated-pipeline", action="store_true")
+        add_arg(g, "--automated-pipeline-perf", action="store_true")
+        add_arg(g, "--recompute-module-list", type=str, default=None)
+
+    def validate_args(self, args):
+        if args.recompute_in_bubble and args.recompute_in_advance:
+            raise AssertionError("--recompute-in-bubble and --recompute-in-advance are exclusive")
+        if (args.recompute_in_bubble or args.recompute_in_advance) and \
+                not getattr(args, "num_layers_per_virtual_pipeline_stage", None):
+            raise AssertionError("RiPipe recompute scheduling needs the interleaved schedule")
+        if isinstance(args.noop_layers, str):
+            args.noop_layers = sorted({int(x) for x in args.noop_layers.split(",") if x != ""})
+        if isinstance(args.pipeline_num_transformer_layers, str):
+            import ast
+            args.pipeline_num_transformer_layers = ast.literal_eval(args.pipeline_num_transformer_layers)
+
+
+# ======================================================================================
+# MoE
+# ======================================================================================
+class MoEFeature(Feature):
+    def __init__(self):
+        super().__init__("moe", optimization_level=0)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--moe-tp-extend-ep", action="store_true")
+        add_arg(g, "--moe-permutation-async-comm", action="store_true")
+        add_arg(g, "--moe-alltoall-overlap-comm", action="store_true")
+        add_arg(g, "--moe-allgather-overlap-comm", action="store_true")
+        add_arg(g, "--moe-alltoall-mc2", "--moe-alltoall-fused", dest="moe_alltoall_mc2", action="store_true")
+        add_arg(g, "--moe-fb-overlap", action="store_true")
+        add_arg(g, "--moe-unperm2-mem-optim-swap", action="store_true")
+        add_arg(g, "--moe-zero-memory", type=str, default="disable", choices=["disable", "level0", "level1"])
+        add_arg(g, "--moe-zero-memory-num-layers", type=int, default=None)
+        add_arg(g, "--n-shared-experts", type=int, default=None)
+        add_arg(g, "--fix-router", action="store_true")
+        add_arg(g, "--balanced-moe-experts", action="store_true")
+        add_arg(g, "--balanced-moe-hot-expert-num", type=int, default=3)
+        add_arg(g, "--trans-hot-expert-group-num", type=int, default=3)
+        add_arg(g, "--enable-expert-placement", action="store_true")
+        add_arg(g, "--expert-placement-freq", type=int, default=50)
+        add_arg(g, "--enable-fine-grained-expert-placement", action="store_true")
+        add_arg(g, "--fine-grained-expert-placement-thre", type=float, default=0.08)
+        add_arg(g, "--print-expert-load", action="store_true")
+        add_arg(g, "--moe-bmm-mc2", action="store_true")
+        # legacy deepspeed-style MoE
+        add_arg(g, "--moe-model-type", type=str, default="megatron_moe", choices=["deepspeed_moe", "megatron_moe"])
+        add_arg(g, "--moe-train-capacity-factor", type=float, default=1.0)
+        add_arg(g, "--noisy-gate-policy", type=str, default=None)
+        add_arg(g, "--moe-no-drop", action="store_true")
+        add_arg(g, "--moe-dynamic-padding", action="store_true")
+        add_arg(g, "--moe-use-sinkhorn", action="store_true")
+        add_arg(g, "--use-pipe-experts", action="store_true")
+        add_arg(g, "--pipe-experts-multi-data", type=int, default=1)
+        add_arg(g, "--pipe-experts-multi-stream", action="store_true")
+        add_arg(g, "--ampipe-degree", type=int, default=0)
+
+    def validate_args(self, args):
+        ne = getattr(args, "num_experts", None)
+        if args.moe_alltoall_overlap_comm or args.moe_alltoall_mc2:
+            if getattr(args, "expert_model_parallel_size", 1) <= 1:
+                raise AssertionError("the overlapped / fused alltoall dispatcher needs expert parallel size > 1")
+            if not getattr(args, "moe_grouped_gemm", False):
+                raise AssertionError("the overlapped / fused alltoall dispatcher needs --moe-grouped-gemm")
+            if getattr(args, "moe_token_dispatcher_type", "alltoall") not in ("alltoall", "alltoall_seq"):
+                raise AssertionError("alltoall overlap needs --moe-token-dispatcher-type alltoall")
+        if args.moe_fb_overlap:
+            if getattr(args, "moe_token_dispatcher_type", "") != "alltoall" or not getattr(args, "moe_grouped_gemm", False):
+                raise AssertionError("--moe-fb-overlap needs the alltoall dispatcher and grouped GEMM")
+            if (getattr(args, "expert_tensor_parallel_size", None) or 1) != 1:
+                raise AssertionError("--moe-fb-overlap needs expert tensor parallel size 1")
+            if getattr(args, "moe_pad_expert_input_to_capacity", False):
+                raise AssertionError("--moe-fb-overlap does not support drop-and-pad")
+        if args.moe_alltoall_mc2 and getattr(args, "use_ascend_mc2", False) and ne:
+            pass
+        if args.moe_tp_extend_ep and ne and ne % (getattr(args, "tensor_model_parallel_size", 1) *
+                                                   getattr(args, "expert_model_parallel_size", 1)) != 0:
+            raise AssertionError("--moe-tp-extend-ep needs num_experts divisible by tp * ep")
+
+    def configure(self, manager, args):
+        if args.moe_alltoall_mc2:
+            manager.set_slot("moe_dispatcher", "fused", owner=self.feature_name)
+        elif args.moe_alltoall_overlap_comm:
+            manager.set_slot("moe_dispatcher", "overlap", owner=self.feature_name)
+
+
+# ======================================================================================
+# memory
+# ======================================================================================
+class MemoryFeature(Feature):
+    def __init__(self):
+        super().__init__("memory", optimization_level=0)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--recompute-activation-function", action="store_true")
+        add_arg(g, "--recompute-activation-function-num-layers", type=int, default=None)
+        add_arg(g, "--recompute-norm", action="store_true")
+        add_arg(g, "--recompute-norm-num-layers", type=int, default=None)
+        add_arg(g, "--enable-recompute-layers-per-pp-rank", action="store_true")
+        add_arg(g, "--swap-attention", action="store_true")
+        add_arg(g, "--swap-modules", type=str, default="input_norm,self_attention,post_attention_norm")
+        add_arg(g, "--swap-layer-input", action="store_true")
+        add_arg(g, "--smart-swap", action="store_true")
+        add_arg(g, "--reuse-fp32-param", action="store_true")
+        add_arg(g, "--compress-dense", type=str, default="disable", choices=["disable", "level0", "level1"])
+        add_arg(g, "--compress-activation", action="store_true")
+        add_arg(g, "--compress-optimizer", action="store_true")
+        add_arg(g, "--adaptive-recompute-device-size", type=int, default=-1)
+        add_arg(g, "--adaptive-recompute-profiling-step", type=int, default=10)
+        add_arg(g, "--adaptive-recompute-device-swap", action="store_true")
+        add_arg(g, "--adaptive-memory-optimization", action="store_true")
+
+    def validate_args(self, args):
+        if args.swap_attention and getattr(args, "schedules_method", None) in ("dualpipev", "dualpipe"):
+            raise AssertionError("--swap-attention is incompatible with dualpipe schedules")
+        if args.reuse_fp32_param and getattr(args, "optimizer_selection", "") == "fused_ema_adamw":
+            raise AssertionError("--reuse-fp32-param is incompatible with fused_ema_adamw")
+        if args.reuse_fp32_param and not getattr(args, "bf16", False):
+            raise AssertionError("--reuse-fp32-param needs --bf16")
+        if args.smart_swap and (args.swap_attention or args.adaptive_memory_optimization):
+            raise AssertionError("--smart-swap excludes --swap-attention / --adaptive-memory-optimization")
+
+
+# ======================================================================================
+# optimizer
+# ======================================================================================
+class OptimizerFeature(Feature):
+    def __init__(self):
+        super().__init__("optimizer", optimization_level=0)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--swap-optimizer", action="store_true")
+        add_arg(g, "--swap-optimizer-times", type=int, default=16)
+        add_arg(g, "--virtual-optimizer", nargs="+", type=float, default=None)
+        add_arg(g, "--quant-states", type=str, default=None, choices=[None, "fp8", "hif8", "mxfp8"])
+        add_arg(g, "--quant-grads", action="store_true")
+        add_arg(g, "--ema-decay", type=float, default=0.9999)
+        add_arg(g, "--use-ema", action="store_true")
+        for name, typ, default in (("--muon-momentum", float, 0.95), ("--muon-num-ns-steps", int, 5),
+                                   ("--muon-extra-scale-factor", float, 1.0)):
+            add_arg(g, name, type=typ, default=default)
+        add_arg(g, "--muon-nesterov", action="store_true")
+        add_arg(g, "--muon-scale-mode", type=str, default="spectral", choices=["spectral", "unit_rms_norm", "shape_scaling"])
+        add_arg(g, "--muon-tp-mode", type=str, default="blockwise", choices=["blockwise", "duplicated", "distributed"])
+        add_arg(g, "--muon-coefficient-type", type=str, default="quintic", choices=["simple", "quintic", "polar_express"])
+        add_arg(g, "--muon-fp32-matmul-prec", type=str, default="medium", choices=["low", "medium", "high"])
+        add_arg(g, "--muon-scalar-optimizer", type=str, default="adam")
+        add_arg(g, "--muon-no-split-qkv", action="store_false", dest="muon_split_qkv")
+        add_arg(g, "--apply-wd-to-qk-layernorm", action="store_true")
+
+    def validate_args(self, args):
+        if args.swap_optimizer and args.quant_states:
+            raise AssertionError("--swap-optimizer is incompatible with the low-precision optimizer")
+        if args.quant_states == "hif8":
+            raise AssertionError("hif8 optimizer states are Ascend-specific; use fp8 or mxfp8")
+
+
+# ======================================================================================
+# distributed
+# ======================================================================================
+class DistributedFeature(Feature):
+    def __init__(self):
+        super().__init__("distributed", optimization_level=0)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--param-and-grad-buffer-pad", type=int, default=None)
+        add_arg(g, "--reset-bucket-group-order", action="store_true")
+        add_arg(g, "--layerzero", action="store_true")
+        add_arg(g, "--layerzero-config", type=str, default=None)
+        add_arg(g, "--fsdp2-config-path", type=str, default=None)
+        add_arg(g, "--disable-gloo-group", action="store_true")
+        add_arg(g, "--hccl-slice-size", "--nccl-slice-size", dest="hccl_slice_size", type=int, default=10 * 1024 * 1024)
+        add_arg(g, "--hccl-group-buffer", "--nccl-group-buffer", dest="hccl_group_buffer", type=str, default=None)
+        add_arg(g, "--hccl-group-buffer-adaptive", action="store_true")
+        add_arg(g, "--hccl-ep-group-buffer-adaptive-factor", type=float, default=-1.0)
+        add_arg(g, "--hccl-op-mode", type=str, default=None)
+        add_arg(g, "--async-log-allreduce", action="store_true")
+        add_arg(g, "--dist-train", action="store_true")
+        add_arg(g, "--aiqos", action="store_true")
+        add_arg(g, "--aiqos-mode", type=str, default="auto")
+        add_arg(g, "--aiqos-schedule", type=str, default=None)
+        add_arg(g, "--aiqos-enable-roce", action="store_true")
+
+    def validate_args(self, args):
+        if args.param_and_grad_buffer_pad is not None and args.param_and_grad_buffer_pad <= 0:
+            raise AssertionError("--param-and-grad-buffer-pad must be positive")
+        if args.layerzero and getattr(args, "use_distributed_optimizer", False):
+            raise AssertionError("--layerzero replaces --use-distributed-optimizer")
+
+
+class AutoSettingsFeature(Feature):
+    def __init__(self):
+        super().__init__("auto-settings", optimization_level=0)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--auto-settings", action="store_true")
+        add_arg(g, "--auto-settings-work-dir", type=str, default="./auto_settings_dir")
+        add_arg(g, "--auto-settings-ranks", type=int, default=8)
+        add_arg(g, "--auto-settings-log-level", type=str, default="info", choices=["debug", "info", "warning"])
+        add_arg(g, "--auto-settings-type", type=str, default="white", choices=["white", "black", "mixed"])
+        add_arg(g, "--target-nnodes", type=int, default=1)
+        add_arg(g, "--nnodes", type=int, default=1)
+        add_arg(g, "--nproc-per-node", type=int, default=8)
+        add_arg(g, "--node-rank", type=int, default=0)
+        add_arg(g, "--master-addr", type=str, default="127.0.0.1")
+        add_arg(g, "--master-port", type=int, default=12345)
+        add_arg(g, "--prof-file", type=str, default=None)
+
+
+class TTPFeature(Feature):
+    def __init__(self):
+        super().__init__("ttp-enabled", optimization_level=0)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--ttp-enabled", action="store_true")
+        add_arg(g, "--ttp-server-ip", type=str, default="127.0.0.1")
+        add_arg(g, "--ttp-server-port", type=int, default=29500)
+        add_arg(g, "--ttp-dump-dir", type=str, default=None)
+        add_arg(g, "--ttp-max-dump-ckpt-to-keep", type=int, default=1)
+        add_arg(g, "--ttp-save-optimizer", action="store_true")
+        add_arg(g, "--ttp-save-rng", action="store_true")
+        add_arg(g, "--ttp-dump-timeout-seconds", type=int, default=60)
+        add_arg(g, "--ttp-wait-dump-file-timeout", type=int, default=60)
+        add_arg(g, "--ttp-heartbeat-interval-ms", type=int, default=1000)
+        add_arg(g, "--ttp-heartbeat-timeout-ms", type=int, default=3000)
+        add_arg(g, "--ttp-max-missed-count", type=int, default=3)
+
+    def validate_args(self, args):
+        if args.ttp_enabled and not args.ttp_dump_dir:
+            raise AssertionError("--ttp-enabled needs --ttp-dump-dir")
+
+
+def create_features_list():
+    return [
+        RequirementsBasicFeature(), MegatronBasicFeature(), TransformerEngineBasicFeature(), ProfileFeature(),
+        TflopsCalculateFeature(), DeterministicFeature(), TokenizerFeature(),
+        FusedTPCommFeature(), ChunkedTPCommFeature(), TP2DFeature(), UnalignedLinearFeature(),
+        ContextParallelFeature(), FlashAttentionFeature(), MLAFeature(),
+        DualpipeVFeature(), PipelineMiscFeature(), MoEFeature(), MemoryFeature(), OptimizerFeature(),
+        DistributedFeature(), AutoSettingsFeature(), TTPFeature(),
+    ]

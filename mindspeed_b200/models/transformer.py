@@ -1,0 +1,240 @@
+"""Transformer layer / block.
+
+Layer = pre-norm -> attention -> residual -> pre-norm -> MLP or MoE -> residual.
+Block adds activation recompute (full: block / uniform; per-pipeline-rank counts), no-op layers for
+pipeline balancing (reference: mindspeed/core/transformer/transformer_block.py:20-246,
+mindspeed/core/pipeline_parallel/noop_layers/*) and the final norm.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from ..parallel import parallel_state as ps
+from ..parallel.random import checkpoint as tp_checkpoint, get_cuda_rng_tracker, CheckpointWithoutOutput
+from .attention import MLASelfAttention, SelfAttention
+from .mlp import MLP
+from .norms import IdentityOp, build_norm
+
+
+def _bda(x, bias, residual, p, training):
+    if bias is not None:
+        x = x + bias
+    if p > 0.0 and training:
+        x = torch.nn.functional.dropout(x, p=p, training=True)
+    return residual + x
+
+
+class NoopTransformerLayer(nn.Module):
+    """Placeholder that forwards its input; lets the layer count be padded so stages balance."""
+
+    def __init__(self, layer_number):
+        super().__init__()
+        self.layer_number = layer_number
+
+    def forward(self, hidden_states, *args, **kwargs):
+        return hidden_states.clone(), None
+
+
+def get_num_layers_to_build(config) -> int:
+    pp = ps.get_pipeline_model_parallel_world_size()
+    layout = getattr(config, "pipeline_model_parallel_layout", None)
+    if layout:
+        from ..parallel.pipeline.layout import PipelineLayout
+        vp = ps.get_virtual_pipeline_model_parallel_rank() or 0
+        return PipelineLayout.parse(layout, pp).num_decoder_layers(ps.get_pipeline_model_parallel_rank(), vp)
+    per_stage = getattr(config, "pipeline_num_transformer_layers", None)
+    if per_stage:
+        vp = ps.get_virtual_pipeline_model_parallel_rank() or 0
+        return per_stage[ps.get_pipeline_model_parallel_rank()][vp] if isinstance(per_stage[0], (list, tuple)) \
+            else per_stage[ps.get_pipeline_model_parallel_rank()]
+    if getattr(config, "schedules_method", None) == "dualpipev":
+        return config.num_layers // pp // 2
+    first, last = config.first_pipeline_num_layers, config.last_pipeline_num_layers
+    if first is not None or last is not None:
+        r = ps.get_pipeline_model_parallel_rank()
+        middle = pp - (first is not None) - (last is not None)
+        rest = config.num_layers - (first or 0) - (last or 0)
+        if r == 0 and first is not None:
+            n = first
+        elif r == pp - 1 and last is not None:
+            n = last
+        else:
+            n = rest // max(middle, 1)
+    else:
+        n = config.num_layers // pp
+    vpp = ps.get_virtual_pipeline_model_parallel_world_size()
+    if vpp is not None:
+        n //= vpp
+    return n
+
+
+def get_transformer_layer_offset(config, vp_stage: Optional[int] = None) -> int:
+    pp = ps.get_pipeline_model_parallel_world_size()
+    r = ps.get_pipeline_model_parallel_rank()
+    layout = getattr(config, "pipeline_model_parallel_layout", None)
+    if layout:
+        from ..parallel.pipeline.layout import PipelineLayout
+        vp = vp_stage if vp_stage is not None else (ps.get_virtual_pipeline_model_parallel_rank() or 0)
+        return PipelineLayout.parse(layout, pp).layer_offset(r, vp)
+    if getattr(config, "schedules_method", None) == "dualpipev":
+        per = config.num_layers // pp // 2
+        chunk = vp_stage if vp_stage is not None else (ps.get_virtual_pipeline_model_parallel_rank() or 0)
+        # chunk 0 holds layers [r*per, ...), chunk 1 holds the mirror slice counted from the end
+        # (reference: mindspeed/core/pipeline_parallel/dualpipev/dualpipev_chunks.py:43-53)
+        return r * per if chunk == 0 else config.num_layers - (r + 1) * per
+    n = get_num_layers_to_build(config)
+    vpp = ps.get_virtual_pipeline_model_parallel_world_size()
+    if vpp is not None:
+        vp = vp_stage if vp_stage is not None else ps.get_virtual_pipeline_model_parallel_rank()
+        total_per_vp = config.num_layers // vpp
+        return vp * total_per_vp + r * n
+    first = config.first_pipeline_num_layers
+    if first is not None and r > 0:
+        return first + (r - 1) * n
+    return r * n
+
+
+class TransformerLayer(nn.Module):
+    def __init__(self, config, layer_number=1, hidden_dropout=None, is_moe=None):
+        super().__init__()
+        self.config = config
+        self.layer_number = layer_number + get_transformer_layer_offset(config)
+        self.hidden_dropout = config.hidden_dropout if hidden_dropout is None else hidden_dropout
+        self.input_layernorm = build_norm(config, config.hidden_size)
+        attn_cls = MLASelfAttention if config.multi_latent_attention else SelfAttention
+        self.self_attention = attn_cls(config, self.layer_number, attn_mask_type=getattr(config, "attention_mask_type", "causal"))
+        self.pre_mlp_layernorm = build_norm(config, config.hidden_size)
+        if is_moe is None:
+            is_moe = _is_moe_layer(config, self.layer_number)
+        self.is_moe = is_moe
+        if is_moe:
+            from ..parallel.moe.moe_layer import MoELayer
+            self.mlp = MoELayer(config, layer_number=self.layer_number)
+        else:
+            self.mlp = MLP(config)
+        self.recompute_norm = bool(getattr(config, "recompute_norm", False))
+
+    def _norm(self, norm, x):
+        return norm(x)
+
+    def forward(self, hidden_states, attention_mask=None, rotary_pos_emb=None, packed_seq_params=None, **kwargs):
+        residual = hidden_states
+        if self.recompute_norm and self.training and hidden_states.requires_grad:
+            ck = CheckpointWithoutOutput()
+            ln = ck.checkpoint(self.input_layernorm, False, hidden_states)
+            attn_out, attn_bias = self.self_attention(ln, attention_mask=attention_mask, rotary_pos_emb=rotary_pos_emb,
+                                                      packed_seq_params=packed_seq_params)
+            ck.discard_output()
+            attn_out.register_hook(ck.recompute)
+        else:
+            ln = self.input_layernorm(hidden_states)
+            attn_out, attn_bias = self.self_attention(ln, attention_mask=attention_mask, rotary_pos_emb=rotary_pos_emb,
+                                                      packed_seq_params=packed_seq_params)
+        if self.config.apply_residual_connection_post_layernorm:
+            residual = ln
+        hidden_states = _bda(attn_out, attn_bias, residual, self.hidden_dropout, self.training)
+        residual = hidden_states
+        if self.recompute_norm and self.training and hidden_states.requires_grad and not self.is_moe:
+            ck2 = CheckpointWithoutOutput()
+            ln2 = ck2.checkpoint(self.pre_mlp_layernorm, False, hidden_states)
+            mlp_out, mlp_bias = self.mlp(ln2)
+            ck2.discard_output()
+            mlp_out.register_hook(ck2.recompute)
+        else:
+            ln2 = self.pre_mlp_layernorm(hidden_states)
+            mlp_out, mlp_bias = self.mlp(ln2)
+        if self.config.apply_residual_connection_post_layernorm:
+            residual = ln2
+        hidden_states = _bda(mlp_out, mlp_bias, residual, self.hidden_dropout, self.training)
+        return hidden_states, None
+
+
+def _is_moe_layer(config, layer_number) -> bool:
+    if config.num_moe_experts is None:
+        return False
+    if layer_number <= getattr(config, "first_k_dense_replace", 0):
+        return False
+    freq = config.moe_layer_freq
+    if isinstance(freq, int):
+        return (layer_number - 1) % freq == 0 if freq > 1 else True
+    return bool(freq[layer_number - 1])
+
+
+class TransformerBlock(nn.Module):
+    def __init__(self, config, pre_process=True, post_process=True, post_layer_norm=True, vp_stage=None):
+        super().__init__()
+        self.config, self.pre_process, self.post_process = config, pre_process, post_process
+        self.input_tensor = None
+        n = get_num_layers_to_build(config)
+        offset = get_transformer_layer_offset(config, vp_stage)
+        noop = set(getattr(config, "noop_layers", None) or [])
+        layers = []
+        for i in range(n):
+            if (offset + i) in noop:
+                layers.append(NoopTransformerLayer(offset + i + 1))
+            else:
+                layers.append(TransformerLayer(config, layer_number=i + 1))
+        self.layers = nn.ModuleList(layers)
+        self.num_layers_per_pipeline_rank = n
+        self.final_layernorm = build_norm(config, config.hidden_size) if (post_process and post_layer_norm) else None
+
+    def set_input_tensor(self, t):
+        self.input_tensor = t
+
+    def _recompute_count(self):
+        cfg = self.config
+        n = cfg.recompute_num_layers
+        if getattr(cfg, "enable_recompute_layers_per_pp_rank", False) and isinstance(n, (list, tuple)):
+            # per pipeline rank (and virtual stage) layer counts
+            # (reference: mindspeed/core/transformer/transformer_block.py:20-156)
+            vp = ps.get_virtual_pipeline_model_parallel_rank() or 0
+            n = n[ps.get_pipeline_model_parallel_rank()]
+            if isinstance(n, (list, tuple)):
+                n = n[vp]
+        return n
+
+    def _checkpointed_forward(self, hidden_states, attention_mask, rotary_pos_emb, packed_seq_params):
+        def custom(start, end):
+            def run(h, mask, cos, sin):
+                rpe = None if cos is None else (cos, sin)
+                for i in range(start, end):
+                    h, _ = self.layers[i](h, attention_mask=mask, rotary_pos_emb=rpe, packed_seq_params=packed_seq_params)
+                return h
+            return run
+        cos, sin = (None, None) if rotary_pos_emb is None else rotary_pos_emb
+        n = len(self.layers)
+        cnt = self._recompute_count()
+        if self.config.recompute_method == "uniform":
+            i = 0
+            while i < n:
+                j = min(i + cnt, n)
+                hidden_states = tp_checkpoint(custom(i, j), self.config.distribute_saved_activations, hidden_states,
+                                              attention_mask, cos, sin)
+                i = j
+        else:  # block: checkpoint the first `cnt` real layers, run the rest normally
+            done = 0
+            for i in range(n):
+                is_noop = isinstance(self.layers[i], NoopTransformerLayer)
+                if done < cnt and not is_noop:
+                    hidden_states = tp_checkpoint(custom(i, i + 1), self.config.distribute_saved_activations,
+                                                  hidden_states, attention_mask, cos, sin)
+                    done += 1
+                else:
+                    hidden_states = custom(i, i + 1)(hidden_states, attention_mask, cos, sin)
+        return hidden_states
+
+    def forward(self, hidden_states, attention_mask=None, rotary_pos_emb=None, packed_seq_params=None, **kwargs):
+        if not self.pre_process:
+            hidden_states = self.input_tensor
+        if self.config.recompute_granularity == "full" and self.training:
+            hidden_states = self._checkpointed_forward(hidden_states, attention_mask, rotary_pos_emb, packed_seq_params)
+        else:
+            for layer in self.layers:
+                hidden_states, _ = layer(hidden_states, attention_mask=attention_mask, rotary_pos_emb=rotary_pos_emb,
+                                         packed_seq_params=packed_seq_params)
+        if self.final_layernorm is not None:
+            hidden_states = self.final_layernorm(hidden_states)
+        return hidden_states

@@ -1,0 +1,70 @@
+"""RMSNorm (and the eager LayerNorm wrapper).
+
+``rms_norm(x, weight, eps)`` is an autograd function over csrc/kernels/norm.cu on a GPU and
+the eager restatement on CPU (reference semantics: mindspeed/core/fusions/fused_rms_norm.py:7-42).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import loader
+from ._dtypes import code
+
+
+def rms_norm_ref(x, weight, eps=1e-5, zero_centered=False):
+    xf = x.float()
+    rstd = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    w = weight.float() + 1.0 if zero_centered else weight.float()
+    return (xf * rstd * w).to(x.dtype)
+
+
+_scratch = {}
+
+
+def _get_scratch(dev, elems):
+    buf = _scratch.get(dev)
+    if buf is None or buf.numel() < elems:
+        buf = torch.empty(elems, dtype=torch.float32, device=dev)
+        _scratch[dev] = buf
+    return buf
+
+
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps, zero_centered):
+        L = loader.require_lib()
+        xc = x.contiguous()
+        cols = xc.shape[-1]
+        rows = xc.numel() // cols
+        y = torch.empty_like(xc)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        loader.check(L.msb_rmsnorm_fwd(loader.p(xc), loader.p(weight), loader.p(y), loader.p(rstd), rows, cols,
+                                       ctypes.c_float(eps), int(zero_centered), code(x.dtype),
+                                       ctypes.c_void_p(loader.stream_ptr())), "rmsnorm_fwd")
+        ctx.save_for_backward(xc, weight, rstd)
+        ctx.zero_centered = zero_centered
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        L = loader.require_lib()
+        x, weight, rstd = ctx.saved_tensors
+        dy = dy.contiguous()
+        cols = x.shape[-1]
+        rows = x.numel() // cols
+        dx = torch.empty_like(x)
+        dw = torch.empty_like(weight)
+        L.msb_rmsnorm_bwd_scratch_elems.restype = ctypes.c_size_t
+        scratch = _get_scratch(x.device, L.msb_rmsnorm_bwd_scratch_elems(rows, cols))
+        loader.check(L.msb_rmsnorm_bwd(loader.p(dy), loader.p(x), loader.p(weight), loader.p(rstd), loader.p(dx),
+                                       loader.p(dw), loader.p(scratch), rows, cols, int(ctx.zero_centered), 0,
+                                       code(x.dtype), ctypes.c_void_p(loader.stream_ptr())), "rmsnorm_bwd")
+        return dx, dw, None, None
+
+
+def rms_norm(x, weight, eps=1e-5, zero_centered=False, fused=True):
+    if fused and x.is_cuda and loader.use_kernels(x) and weight.dtype == x.dtype:
+        return _RMSNormFn.apply(x, weight, eps, zero_centered)
+    return rms_norm_ref(x, weight, eps, zero_centered)

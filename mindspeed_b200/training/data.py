@@ -1,0 +1,57 @@
+"""Synthetic and indexed token datasets.
+
+``SyntheticGPTDataset`` draws token ids i.i.d. uniform from a seeded generator; labels are the ids
+shifted by one (the layout the benchmark configs prescribe).  ``get_batch`` slices the batch for this
+context-parallel rank.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..parallel import parallel_state as ps
+from ..parallel.context_parallel.batch_utils import get_batch_on_this_cp_rank
+
+
+class SyntheticGPTDataset(torch.utils.data.Dataset):
+    def __init__(self, vocab_size, seq_length, num_samples, seed=1234):
+        self.vocab_size, self.seq_length, self.num_samples, self.seed = vocab_size, seq_length, num_samples, seed
+
+    def __len__(self):
+        return self.num_samples
+
+    def __getitem__(self, idx):
+        g = torch.Generator().manual_seed(self.seed * 1000003 + idx)
+        text = torch.randint(0, self.vocab_size, (self.seq_length + 1,), generator=g, dtype=torch.int64)
+        return {"tokens": text[:-1], "labels": text[1:], "loss_mask": torch.ones(self.seq_length),
+                "position_ids": torch.arange(self.seq_length)}
+
+
+class BatchIterator:
+    """Yields micro-batches for this data-parallel rank in global-sample order."""
+
+    def __init__(self, dataset, micro_batch_size, dp_rank, dp_size, start=0, pin=False, device=None):
+        self.ds, self.mbs, self.r, self.n = dataset, micro_batch_size, dp_rank, dp_size
+        self.cursor, self.pin, self.device = start, pin, device
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        items = []
+        for i in range(self.mbs):
+            idx = (self.cursor + self.r * self.mbs + i) % len(self.ds)
+            items.append(self.ds[idx])
+        self.cursor += self.mbs * self.n
+        batch = {k: torch.stack([it[k] for it in items]) for k in items[0]}
+        if self.pin and torch.cuda.is_available():
+            batch = {k: v.pin_memory() for k, v in batch.items()}
+        return batch
+
+
+def get_batch(data_iterator, device=None):
+    """tokens, labels, loss_mask, attention_mask(None: causal), position_ids for this cp rank."""
+    batch = next(data_iterator)
+    if device is not None:
+        batch = {k: v.to(device, non_blocking=True) for k, v in batch.items()}
+    batch = get_batch_on_this_cp_rank(batch)
+    return batch["tokens"], batch["labels"], batch["loss_mask"], None, batch["position_ids"]

@@ -1,0 +1,229 @@
+"""pretrain() / train() / train_step() (Megatron ``training`` surface).
+
+reference: mindspeed/training.py:78-160 (train_step with EMA update), :163-384 (pretrain),
+mindspeed/functional/profile/adaptor.py:13-78 (profiler wrapping), tflops logging
+mindspeed/functional/tflops_calculate/adaptor.py:196-231.
+"""
+from __future__ import annotations
+
+import math
+import time
+from typing import Callable, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..optimizer import OptimizerConfig, get_megatron_optimizer
+from ..parallel import parallel_state as ps
+from ..parallel.distributed import DistributedDataParallel, DistributedDataParallelConfig, finalize_model_grads
+from ..parallel.pipeline.schedules import get_forward_backward_func
+from ..utils.logging import print_rank_0, print_rank_last
+from . import flops as flops_mod
+from .global_vars import get_args, get_num_microbatches, get_timers
+from .initialize import initialize_megatron
+
+
+class OptimizerParamScheduler:
+    """Learning-rate schedule: warmup then constant / linear / cosine / inverse-sqrt decay."""
+
+    def __init__(self, optimizer, max_lr, min_lr, warmup_steps, decay_steps, style):
+        self.opt, self.max_lr, self.min_lr = optimizer, max_lr, min_lr
+        self.warmup, self.decay, self.style, self.num_steps = warmup_steps, decay_steps, style, 0
+        self.step(0)
+
+    def get_lr(self):
+        n = self.num_steps
+        if self.warmup > 0 and n <= self.warmup:
+            return self.max_lr * n / self.warmup
+        if self.style == "constant" or not self.decay:
+            return self.max_lr
+        if n > self.decay:
+            return self.min_lr
+        r = (n - self.warmup) / max(1, self.decay - self.warmup)
+        if self.style == "linear":
+            c = 1.0 - r
+        elif self.style == "cosine":
+            c = 0.5 * (math.cos(math.pi * r) + 1.0)
+        elif self.style == "inverse-square-root":
+            return max(self.min_lr, self.max_lr * math.sqrt(max(self.warmup, 1)) / math.sqrt(max(n, 1)))
+        else:
+            c = 1.0
+        return self.min_lr + c * (self.max_lr - self.min_lr)
+
+    def step(self, increment=1):
+        self.num_steps += increment
+        lr = self.get_lr()
+        for g in self.opt.param_groups:
+            g["lr"] = lr
+
+    def state_dict(self):
+        return {"num_steps": self.num_steps}
+
+    def load_state_dict(self, sd):
+        self.num_steps = sd["num_steps"]
+        self.step(0)
+
+
+def get_model(model_provider_func, wrap_with_ddp=True):
+    args = get_args()
+    vpp = ps.get_virtual_pipeline_model_parallel_world_size()
+    models = []
+    if ps.get_pipeline_model_parallel_world_size() > 1 and (vpp is not None or args.schedules_method in ("dualpipev",)):
+        n = vpp if vpp is not None else 2
+        if vpp is None:
+            ps.set_virtual_pipeline_model_parallel_world_size(2)
+        for i in range(n):
+            ps.set_virtual_pipeline_model_parallel_rank(i)
+            if args.schedules_method == "dualpipev":
+                # V shape: chunk 0 is the head on pp rank 0, chunk 1 is the tail on pp rank 0
+                pre = ps.get_pipeline_model_parallel_rank() == 0 and i == 0
+                post = ps.get_pipeline_model_parallel_rank() == 0 and i == 1
+            else:
+                pre, post = ps.is_pipeline_first_stage(), ps.is_pipeline_last_stage()
+            models.append(model_provider_func(pre_process=pre, post_process=post))
+        ps.set_virtual_pipeline_model_parallel_rank(0)
+    else:
+        models.append(model_provider_func(pre_process=ps.is_pipeline_first_stage(), post_process=ps.is_pipeline_last_stage()))
+    for m in models:
+        if torch.cuda.is_available() and dist.get_backend() != "gloo":
+            m.cuda(torch.cuda.current_device())
+    if not wrap_with_ddp:
+        return models
+    cfg = models[0].config
+    ddp_cfg = DistributedDataParallelConfig(
+        grad_reduce_in_fp32=args.accumulate_allreduce_grads_in_fp32, overlap_grad_reduce=args.overlap_grad_reduce,
+        overlap_param_gather=args.overlap_param_gather, use_distributed_optimizer=args.use_distributed_optimizer,
+        check_for_nan_in_grad=args.check_for_nan_in_loss_and_grad, bucket_size=args.ddp_bucket_size,
+        average_in_collective=args.ddp_average_in_collective, param_and_grad_buffer_pad=args.param_and_grad_buffer_pad,
+        num_distributed_optimizer_instances=args.num_distributed_optimizer_instances)
+    models = [DistributedDataParallel(cfg, ddp_cfg, m, disable_bucketing=(i > 0)) for i, m in enumerate(models)]
+    return models
+
+
+def setup_model_and_optimizer(model_provider_func, no_wd_decay_cond=None, scale_lr_cond=None, lr_mult=1.0):
+    args = get_args()
+    model = get_model(model_provider_func)
+    ocfg = OptimizerConfig(optimizer=args.optimizer, lr=args.lr, min_lr=args.min_lr, weight_decay=args.weight_decay,
+                           bf16=args.bf16, fp16=args.fp16, params_dtype=args.params_dtype, adam_beta1=args.adam_beta1,
+                           adam_beta2=args.adam_beta2, adam_eps=args.adam_eps, clip_grad=args.clip_grad,
+                           use_distributed_optimizer=args.use_distributed_optimizer,
+                           optimizer_selection=args.optimizer_selection, use_ema=args.use_ema, ema_decay=args.ema_decay,
+                           swap_optimizer=args.swap_optimizer, swap_optimizer_times=args.swap_optimizer_times,
+                           quant_states=args.quant_states, reuse_fp32_param=args.reuse_fp32_param)
+    optimizer = get_megatron_optimizer(ocfg, model, no_wd_decay_cond, scale_lr_cond, lr_mult)
+    sched = OptimizerParamScheduler(optimizer, args.lr, args.min_lr, args.lr_warmup_iters,
+                                    args.lr_decay_iters or args.train_iters, args.lr_decay_style)
+    cfg = model[0].module.config
+    cfg.finalize_model_grads_func = finalize_model_grads
+    if args.swap_attention:
+        from ..memory.swap_attention import install_swap_attention
+        install_swap_attention(model, args)
+    if args.load:
+        from ..checkpointing import load_checkpoint
+        args.iteration = load_checkpoint(model, optimizer, sched)
+    else:
+        args.iteration = 0
+    return model, optimizer, sched
+
+
+def train_step(forward_step_func, data_iterator, model, optimizer, opt_param_scheduler, config=None):
+    """One optimizer step over ``num_microbatches`` micro-batches."""
+    args = get_args()
+    for m in model:
+        m.zero_grad_buffer()
+    optimizer.zero_grad()
+    fb = get_forward_backward_func()
+    losses_reduced = fb(forward_step_func=forward_step_func, data_iterator=data_iterator, model=model,
+                        num_microbatches=get_num_microbatches(), seq_length=args.seq_length,
+                        micro_batch_size=args.micro_batch_size, decoder_seq_length=None, forward_only=False)
+    ok, grad_norm, num_zeros = optimizer.step()
+    if ok:
+        opt_param_scheduler.step(1)
+        skipped = 0
+    else:
+        skipped = 1
+    loss_reduced = {}
+    if ps.is_pipeline_last_stage(ignore_virtual=True) and losses_reduced:
+        for key in losses_reduced[0]:
+            vals = [x[key] for x in losses_reduced]
+            if torch.is_tensor(vals[0]) and vals[0].numel() == 2:
+                t = torch.stack(vals).sum(0)
+                loss_reduced[key] = t[0] / t[1]
+            else:
+                loss_reduced[key] = sum(vals) / len(vals)
+    return loss_reduced, skipped, grad_norm, num_zeros
+
+
+def training_log(loss_dict, iteration, elapsed, grad_norm, skipped, lr):
+    args = get_args()
+    bs = args.global_batch_size
+    tokens = bs * args.seq_length
+    world = args.world_size
+    msg = f" iteration {iteration:8d}/{args.train_iters:8d} | elapsed time per iteration (ms): {elapsed * 1000:.1f}"
+    msg += f" | learning rate: {lr:.3E} | global batch size: {bs:5d}"
+    for k, v in loss_dict.items():
+        msg += f" | {k}: {float(v):.6E}"
+    if grad_norm is not None:
+        msg += f" | grad norm: {float(grad_norm):.3f}"
+    msg += f" | tokens/sec/GPU: {tokens / elapsed / world:.1f}"
+    if args.op_cal_tflops or args.log_throughput:
+        f = flops_mod.num_floating_point_operations(args, bs)
+        hf = f + flops_mod.recompute_extra_flops(args, bs)
+        peak = flops_mod.measured_peaks()["bf16_tflops"] * 1e12
+        msg += f" | throughput per GPU (TFLOP/s/GPU): {f / elapsed / world / 1e12:.1f}"
+        msg += f" | MFU: {f / elapsed / world / peak:.4f} | HFU: {hf / elapsed / world / peak:.4f}"
+    print_rank_last(msg)
+
+
+def train(forward_step_func, model, optimizer, opt_param_scheduler, train_data_iterator, process_non_loss_data_func=None):
+    args = get_args()
+    for m in model:
+        m.train()
+    iteration = args.iteration
+    prof = None
+    if args.profile and (args.profile_ranks == [-1] or args.rank in args.profile_ranks):
+        from ..utils.profiler import build_profiler
+        prof = build_profiler(args)
+        prof.__enter__()
+    history = []
+    while iteration < args.train_iters:
+        t0 = time.time()
+        loss_dict, skipped, grad_norm, _ = train_step(forward_step_func, train_data_iterator, model, optimizer,
+                                                      opt_param_scheduler)
+        iteration += 1
+        if torch.cuda.is_available() and next(model[0].parameters()).is_cuda:
+            torch.cuda.synchronize()
+        elapsed = time.time() - t0
+        if prof is not None:
+            prof.step()
+        if iteration % args.log_interval == 0:
+            training_log(loss_dict, iteration, elapsed, grad_norm, skipped, optimizer.param_groups[0]["lr"])
+        history.append({k: float(v) for k, v in loss_dict.items()})
+        if args.save and args.save_interval and iteration % args.save_interval == 0:
+            from ..checkpointing import save_checkpoint
+            save_checkpoint(iteration, model, optimizer, opt_param_scheduler)
+        if args.exit_interval and iteration % args.exit_interval == 0:
+            break
+    if prof is not None:
+        prof.__exit__(None, None, None)
+    args.iteration = iteration
+    return history
+
+
+def pretrain(train_valid_test_dataset_provider, model_provider, model_type=None, forward_step_func=None,
+             process_non_loss_data_func=None, extra_args_provider=None, args_defaults=None, args_list=None):
+    """Full entry: initialise, (optionally) run the auto-settings search and return, build, train, save."""
+    args = initialize_megatron(extra_args_provider, args_defaults, args_list=args_list)
+    if args.auto_settings:
+        from ..auto_settings import AutoSettings
+        return AutoSettings().auto_setting_fun(args)
+    if args.ttp_enabled:
+        from ..ttp import install_ttp
+        install_ttp(args)
+    model, optimizer, sched = setup_model_and_optimizer(model_provider)
+    train_iter = train_valid_test_dataset_provider(args)
+    history = train(forward_step_func, model, optimizer, sched, train_iter, process_non_loss_data_func)
+    if args.save:
+        from ..checkpointing import save_checkpoint
+        save_checkpoint(args.iteration, model, optimizer, sched)
+    return history
