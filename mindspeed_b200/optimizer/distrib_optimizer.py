@@ -50,7 +50,7 @@ class _BucketState:
         self.grad = buf.grad_data[self.lo:self.hi]
         self.param16 = buf.param_data[self.lo:self.hi] if buf.param_data is not None else None
         if use_master:
-            self.master = self.param16.float().clone()
+            self.master = self.param16.float()
         else:
             self.master = self.param16  # fp32 params: update in place
             self.param16 = None

@@ -201,7 +201,7 @@ class CheckpointWithoutOutput:
         if self.cuda:
             torch.cuda.set_rng_state(self.cuda_state)
         get_cuda_rng_tracker().set_states(self.tracker_states)
-        detached = [a.detach().requires_grad_(a.requires_grad) for a in args]
+        detached = [a.detach().requires_grad_(r) for a, r in zip(args, self.ctx.req)]
         with torch.enable_grad():
             outs = self.run_function(*detached)
         torch.set_rng_state(cpu)

@@ -1,0 +1,137 @@
+"""sm_100a elementwise / reduction kernels against fp32 PyTorch references."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 1e-4, torch.float16: 1e-3, torch.bfloat16: 5e-3}
+
+
+def _close(a, b, dtype, scale=1.0):
+    tol = TOL[dtype] * scale
+    torch.testing.assert_close(a.float(), b.float(), atol=tol * max(1.0, b.float().abs().max().item()), rtol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,cols", [(64, 4096), (33, 512), (7, 520), (4, 12288)])
+def test_rmsnorm(dtype, rows, cols):
+    from mindspeed_b200.ops.norm import rms_norm, rms_norm_ref
+    torch.manual_seed(0)
+    x = torch.randn(rows, cols, device="cuda", dtype=dtype, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(cols, device="cuda")).to(dtype).requires_grad_(True)
+    y = rms_norm(x, w, 1e-5)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = rms_norm_ref(xr, wr, 1e-5)
+    _close(y, yr, dtype)
+    g = torch.randn_like(y)
+    y.backward(g)
+    yr.backward(g.float())
+    _close(x.grad, xr.grad, dtype, 2)
+    _close(w.grad, wr.grad, dtype, 4)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_swiglu(dtype):
+    from mindspeed_b200.ops.activation import swiglu, swiglu_ref
+    torch.manual_seed(1)
+    x = torch.randn(129, 2 * 1792, device="cuda", dtype=dtype, requires_grad=True)
+    y = swiglu(x)
+    xr = x.detach().float().requires_grad_(True)
+    yr = swiglu_ref(xr)
+    _close(y, yr, dtype)
+    g = torch.randn_like(y)
+    y.backward(g)
+    yr.backward(g.float())
+    _close(x.grad, xr.grad, dtype, 2)
+
+
+def test_swiglu_weighted():
+    from mindspeed_b200.ops.activation import swiglu, swiglu_ref
+    torch.manual_seed(2)
+    x = torch.randn(77, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    sc = torch.rand(77, device="cuda", requires_grad=True)
+    y = swiglu(x, sc)
+    xr, sr = x.detach().float().requires_grad_(True), sc.detach().clone().requires_grad_(True)
+    yr = swiglu_ref(xr, sr)
+    _close(y, yr, torch.bfloat16)
+    g = torch.randn_like(y)
+    y.backward(g)
+    yr.backward(g.float())
+    _close(x.grad, xr.grad, torch.bfloat16, 2)
+    _close(sc.grad, sr.grad, torch.bfloat16, 4)
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_rope(interleaved):
+    from mindspeed_b200.ops.rope import apply_rope, apply_rope_ref, rope_packed_qkv_
+    torch.manual_seed(3)
+    s, b, n, d = 96, 2, 6, 128
+    ang = torch.outer(torch.arange(s, device="cuda").float(), 1.0 / (10000 ** (torch.arange(0, d, 2, device="cuda").float() / d)))
+    emb = torch.stack((ang, ang), -1).reshape(s, d) if interleaved else torch.cat((ang, ang), -1)
+    cos, sin = emb.cos().contiguous(), emb.sin().contiguous()
+    t = torch.randn(s, b, n, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = apply_rope(t, cos, sin, interleaved)
+    tr = t.detach().float().requires_grad_(True)
+    yr = apply_rope_ref(tr, cos, sin, interleaved)
+    _close(y, yr, torch.bfloat16)
+    g = torch.randn_like(y)
+    y.backward(g)
+    yr.backward(g.float())
+    _close(t.grad, tr.grad, torch.bfloat16)
+    # packed qkv in place: groups=2, 3 q heads per group
+    groups, qpg = 2, 3
+    qkv = torch.randn(s, b, groups * (qpg + 2) * d, device="cuda", dtype=torch.bfloat16)
+    ref = qkv.clone().view(s, b, groups, qpg + 2, d)
+    part = ref[:, :, :, :qpg + 1].reshape(s, b, groups * (qpg + 1), d)
+    ref[:, :, :, :qpg + 1] = apply_rope_ref(part.float(), cos, sin, interleaved).to(torch.bfloat16).view(s, b, groups, qpg + 1, d)
+    rope_packed_qkv_(qkv, cos, sin, groups, qpg, d, interleaved)
+    _close(qkv.view_as(ref), ref, torch.bfloat16)
+
+
+def test_adam_flat_matches_torch_adamw():
+    from mindspeed_b200.ops.adam import adam_flat
+    torch.manual_seed(4)
+    n = 100003
+    p = torch.randn(n, device="cuda")
+    ref = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref], lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    for step in range(1, 4):
+        g = torch.randn(n, device="cuda")
+        ref.grad = g.clone()
+        opt.step()
+        adam_flat(p, g, m, v, p16, 1e-3, 0.9, 0.95, 1e-8, 0.1, step)
+    torch.testing.assert_close(p, ref.data, atol=1e-6, rtol=1e-5)
+    torch.testing.assert_close(p16.float(), p.bfloat16().float())
+
+
+def test_l2norm_and_clip():
+    from mindspeed_b200.ops import adam as A
+    g = torch.randn(1 << 20, device="cuda")
+    out = A.l2norm_sq(g)
+    torch.testing.assert_close(out.item(), g.double().pow(2).sum().item(), rtol=1e-4, atol=0)
+    coef = torch.zeros(1, device="cuda"); inf = torch.zeros(1, device="cuda"); nrm = torch.zeros(1, device="cuda")
+    A.clip_coef(out, 1.0, coef, inf, nrm)
+    assert abs(coef.item() - 1.0 / (g.norm().item() + 1e-6)) < 1e-6 and inf.item() == 0
+
+
+@pytest.mark.parametrize("vocab", [4096, 16032, 1000])
+def test_fused_cross_entropy(vocab):
+    from mindspeed_b200.ops.cross_entropy import fused_vocab_parallel_cross_entropy
+    torch.manual_seed(5)
+    rows = 257
+    logits = (3 * torch.randn(rows, 1, vocab, device="cuda")).bfloat16().requires_grad_(True)
+    tgt = torch.randint(0, vocab, (rows, 1), device="cuda")
+    ref_in = logits.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(ref_in.view(rows, vocab), tgt.view(-1), reduction="none")
+    x = logits.detach().clone().requires_grad_(True)
+    y = x * 1.0
+    loss = fused_vocab_parallel_cross_entropy(y, tgt)
+    torch.testing.assert_close(loss.view(-1), ref, atol=2e-2, rtol=1e-2)
+    w = torch.rand(rows, 1, device="cuda")
+    (loss * w).sum().backward()
+    (ref * w.view(-1)).sum().backward()
+    torch.testing.assert_close(x.grad.float(), ref_in.grad, atol=5e-3, rtol=5e-2)
