@@ -236,3 +236,67 @@ MSB_API int msb_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, co
   });
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm backward for callers that must not allocate (declared in include/msb_noalloc.h).
+//
+// Same math and kernels as msb_rmsnorm_bwd, but the fp32 partial-sum scratch is a fixed array that
+// lives inside this library instead of a buffer the caller provides.
+// ---------------------------------------------------------------------------------------------
+#define MSB_NOALLOC_SCRATCH_FLOATS (512 * 1024)  // 2 MiB per GPU that loads the library
+static __device__ __align__(256) float g_noalloc_scratch[MSB_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+
+// Device address of the scratch array for the current device. In host code the array's name is only a
+// stand-in symbol, not something a kernel can dereference, so it is translated once per device.
+int noalloc_scratch(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) {
+    msb_set_error("rmsnorm_bwd_noalloc: cannot identify the current device");
+    return 1;
+  }
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      msb_set_error("rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return 1;
+    }
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+MSB_API size_t msb_rmsnorm_bwd_noalloc_max_cols() { return (size_t)BWD_MAX_COLS; }
+
+MSB_API int msb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* gamma, const float* rstd, void* dx,
+                                    void* dgamma, int rows, int cols, int zero_centered, int accumulate_dgamma,
+                                    int dtype, cudaStream_t s) {
+  if (rows == 0) return 0;
+  MSB_REQUIRE(rows > 0 && cols > 0, "rmsnorm_bwd_noalloc: rows=%d cols=%d must be positive", rows, cols);
+  MSB_REQUIRE(cols % 8 == 0 && cols <= BWD_MAX_COLS,
+              "rmsnorm_bwd_noalloc: cols=%d is not supported (multiple of 8, at most %d); use msb_rmsnorm_bwd with "
+              "caller-provided scratch instead", cols, BWD_MAX_COLS);
+  float* scratch = nullptr;
+  if (noalloc_scratch(&scratch) != 0) return 1;
+  int grid = msb::num_sms() * 2;
+  if (grid > rows) grid = rows;
+  const int fit = MSB_NOALLOC_SCRATCH_FLOATS / cols;  // >= 64 because cols <= 8192
+  if (grid > fit) grid = fit;
+  // every one of the grid*cols partial sums is overwritten by the first kernel before the second reads it,
+  // so nothing left over from an earlier call needs clearing
+  MSB_DISPATCH_FLOAT(dtype, T, {
+    int th = pick_threads(cols / 8, 256);
+    if (zero_centered) rmsnorm_bwd_kernel<T, true><<<grid, th, 0, s>>>((const T*)dy, (const T*)x, (const T*)gamma, rstd, (T*)dx, scratch, rows, cols);
+    else rmsnorm_bwd_kernel<T, false><<<grid, th, 0, s>>>((const T*)dy, (const T*)x, (const T*)gamma, rstd, (T*)dx, scratch, rows, cols);
+    MSB_CHECK_LAUNCH("rmsnorm_bwd_noalloc");
+    colsum_partials_kernel<T><<<(cols + 255) / 256, 256, 0, s>>>(scratch, (T*)dgamma, grid, cols, accumulate_dgamma);
+    MSB_CHECK_LAUNCH("rmsnorm_bwd_noalloc_reduce");
+  });
+  return 0;
+}
