@@ -9,6 +9,7 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <string.h>
 
 #define MSB_API extern "C" __attribute__((visibility("default")))
 

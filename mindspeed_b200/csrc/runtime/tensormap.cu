@@ -1,0 +1,45 @@
+// Host-side construction of TMA tensor maps. The driver entry point is resolved at run time through the CUDA
+// runtime, so the library has no link-time dependency on libcuda.
+#include "msb_common.cuh"
+#include "msb_sm100.cuh"
+#include <mutex>
+
+namespace msb {
+
+PFN_encodeTiled get_encode_tiled() {
+  static PFN_encodeTiled fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (PFN_encodeTiled)p;
+  });
+  return fn;
+}
+
+int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows, uint64_t cols,
+                 uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
+  PFN_encodeTiled enc = get_encode_tiled();
+  if (!enc) { msb_set_error("cuTensorMapEncodeTiled is not available from this driver"); return 1; }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) { msb_set_error("tensor map base %p is not 16-byte aligned", base); return 2; }
+  if ((ld * elem_bytes) % 16 != 0) { msb_set_error("tensor map row pitch %llu bytes is not a multiple of 16", (unsigned long long)(ld * elem_bytes)); return 2; }
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstr[1] = {ld * (uint64_t)elem_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapSwizzle sw = (box_cols * elem_bytes == 128) ? CU_TENSOR_MAP_SWIZZLE_128B
+                          : (box_cols * elem_bytes == 64) ? CU_TENSOR_MAP_SWIZZLE_64B
+                          : (box_cols * elem_bytes == 32) ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE;
+  CUresult r = enc(out, dt, 2, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    msb_set_error("cuTensorMapEncodeTiled failed (%d) rows=%llu cols=%llu ld=%llu box=%ux%u", (int)r, (unsigned long long)rows,
+                  (unsigned long long)cols, (unsigned long long)ld, box_rows, box_cols);
+    return 1;
+  }
+  return 0;
+}
+
+}  // namespace msb

@@ -150,6 +150,50 @@ class ChunkedOps(DefaultOps):
         return torch.cat(outs, dim=0)
 
 
+class Sm100Ops(DefaultOps):
+    """Library collectives, hand-written tcgen05 GEMMs (optimisation level >= 1 on a GPU)."""
+    name = "sm100"
+
+    @staticmethod
+    def _ok(x, w):
+        from ..ops import gemm as G
+        return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and G.supported(x, w)
+                and w.is_contiguous() and G.shapes_ok(x.numel() // x.shape[-1], w.shape[0], w.shape[1]))
+
+    @classmethod
+    def matmul(cls, x, w, nt=True):
+        from ..ops import gemm as G
+        if cls._ok(x, w):
+            return G.linear_fwd(x, w) if nt else G.linear_dgrad(x, w)
+        return DefaultOps.matmul(x, w, nt)
+
+    @classmethod
+    def allgather_matmul(cls, x, w, group, nt=True, need_gathered=False):
+        total = M.all_gather_first_dim(x, group)
+        return cls.matmul(total, w, nt), (total if need_gathered else None)
+
+    @classmethod
+    def matmul_reduce_scatter(cls, x, w, group, nt=True):
+        return M.reduce_scatter_first_dim(cls.matmul(x, w, nt), group)
+
+    @classmethod
+    def matmul_all_reduce(cls, x, w, group, nt=True):
+        y = cls.matmul(x, w, nt).contiguous()
+        M.all_reduce(y, group)
+        return y
+
+    @classmethod
+    def wgrad(cls, dy, x, main_grad=None):
+        from ..ops import gemm as G
+        dy2, x2 = _flat2d(dy), _flat2d(x)
+        ok = (dy2.is_cuda and dy2.dtype == torch.bfloat16 and x2.dtype == torch.bfloat16 and G.supported(dy2, x2, main_grad)
+              and G.shapes_ok(dy2.shape[0], dy2.shape[1], x2.shape[1])
+              and (main_grad is None or (main_grad.dtype == torch.float32 and main_grad.is_contiguous())))
+        if ok:
+            return G.linear_wgrad(dy2, x2, main_grad)
+        return DefaultOps.wgrad(dy, x, main_grad)
+
+
 _ACTIVE = {"ops": DefaultOps}
 
 
@@ -170,6 +214,8 @@ def select_ops(optimization_level: int = 0, use_fused: bool = False, use_chunked
     elif use_chunked:
         ChunkedOps.parallel_num = parallel_num
         set_ops(ChunkedOps)
+    elif optimization_level >= 1 and torch.cuda.is_available():
+        set_ops(Sm100Ops)
     else:
         set_ops(DefaultOps)
     return get_ops()
