@@ -303,6 +303,366 @@ __global__ void __launch_bounds__(192, 1) gemm_sm100_kernel(const __grid_constan
   }
 }
 
+
+// =====================================================================================================
+// Fused GEMM + collective over NVLink peer memory (one kernel, four extra "copy" warps per CTA).
+//
+// MODE_AG  all-gather -> GEMM.  The A operand is the all-gathered activation [M, K]; rank r owns rows
+//          [r*rows_per_rank, (r+1)*rows_per_rank) of it and has written them into slab r of its own symmetric
+//          buffer before the launch.  Copy warps pull the other ranks' slabs over NVLink (plain peer loads,
+//          16 B per thread, 8 in flight) into this GPU's buffer in 16-row pieces and bump a per-m-tile counter;
+//          the TMA producer waits (bounded) for an m-tile's counter before loading it from LOCAL memory, so a
+//          remote tile crosses NVLink exactly once and every MMA operand read is a local TMA load.  Tiles are
+//          visited m-major starting at the local slab, so compute starts at once.  The filled local buffer is
+//          also the "gathered input" the backward pass needs.
+// MODE_RS  GEMM -> reduce-scatter.  Each finished 128 x BN tile is stored to a local partial buffer; the copy
+//          warps of the same CTA then push its rows (coalesced 512 B segments) into the owner rank's staging
+//          slab [src rank][rows_per_rank, N].  Tiles are visited starting at the next rank's rows, own rows last.
+//          When a GPU has pushed everything its last CTA publishes an exit flag to every peer; the separate
+//          msb_rs_reduce kernel on the owner waits (bounded) for all exit flags and sums the slabs in rank order
+//          (deterministic).
+// Both modes begin with an all-to-all flag handshake (epoch counter) that proves every peer has finished the
+// previous use of the shared buffers and has written its inputs.
+// =====================================================================================================
+enum CommMode : int { MODE_AG = 1, MODE_RS = 2 };
+constexpr int AG_SUB = 8;   // pieces per 128-row m-tile pulled independently
+
+struct CommParams {
+  GemmParams g;
+  // AG
+  const uint4* ag_peer[MAX_SRC];   // peer r's symmetric gathered buffer (base)
+  uint4* ag_local;                 // this GPU's gathered buffer (also the A operand)
+  unsigned int* ready;             // [num_m_tiles] counters in local memory
+  unsigned int ready_target;
+  int rows_per_rank;
+  // RS
+  uint4* rs_stage_peer[MAX_SRC];   // owner o's staging base
+  const uint4* rs_partial;         // local partial [M, N] bf16 (== g.D[0])
+};
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+__device__ __forceinline__ uint4 ld_cg_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool wait_counter_ge(const unsigned int* ctr, unsigned int value, unsigned int* status,
+                                                unsigned int code, uint64_t limit_ns) {
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+    if ((int)(v - value) >= 0) return true;
+    if (globaltimer_ns() - t0 > limit_ns) { atomicCAS(status, 0u, code); return false; }
+    if (*((volatile unsigned int*)status) != 0u) return false;
+    __nanosleep(100);
+  }
+}
+
+template <int BN, int NSTAGE, int MODE, bool B_MN>
+__global__ void __launch_bounds__(320, 1) gemm_comm_sm100_kernel(const __grid_constant__ CommParams cp) {
+  const GemmParams& p = cp.g;
+  using L = SmemLayout<BN, NSTAGE>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + L::BAR_OFFSET;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (NSTAGE + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * NSTAGE + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * NSTAGE + 2 + a); };
+  auto pfull_bar = [&](int a) { return bar_base + 8u * (2 * NSTAGE + 4 + a); };
+  auto pempty_bar = [&](int a) { return bar_base + 8u * (2 * NSTAGE + 6 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * NSTAGE + 8);
+  uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int tiles_per_rank = cp.rows_per_rank / BM;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+  // m-major tile order with rotation: t -> (m, n)
+  auto tile_mn = [&](int t, int& m, int& n) { m = ((t / num_n) + p.m_tile_rot) % num_m; n = t % num_n; };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NSTAGE; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 128);
+      mbar_init(pfull_bar(a), 128); mbar_init(pempty_bar(a), 128);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  // ---- entry handshake ----
+  bool alive = true;
+  {
+    if (blockIdx.x == 0 && threadIdx.x < p.world) {
+      __threadfence_system();
+      unsigned int* dst = p.flag_peer[threadIdx.x] + p.rank;
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(p.epoch) : "memory");
+    }
+    if (threadIdx.x < p.world)
+      alive = wait_flag_ge(p.flag_local + threadIdx.x, p.epoch, p.status, 0x100u + threadIdx.x, 10000000000ull);
+    alive = __syncthreads_and(alive);
+  }
+
+  if (alive) {
+    if (warp == 0) {
+      // ===================== TMA producer =====================
+      if (lane == 0) {
+        int stage = 0; uint32_t phase = 0;
+        for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+          int m_blk, n_blk;
+          tile_mn(t, m_blk, n_blk);
+          if (MODE == MODE_AG && (m_blk / tiles_per_rank) != p.rank) {
+            if (!wait_counter_ge(cp.ready + m_blk, cp.ready_target, p.status, 0x40u, 10000000000ull)) { alive = false; break; }
+            asm volatile("fence.proxy.async.global;" ::: "memory");   // generic-proxy peer copies -> TMA (async proxy) reads
+          }
+          const int m0 = m_blk * BM, n0 = n_blk * BN;
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, 0x10u)) { alive = false; break; }
+            const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
+            const uint32_t sb = sa + L::A_BYTES;
+            mbar_arrive_expect_tx(full_bar(stage), L::STAGE_BYTES);
+            const int k0 = kb * BK;
+            tma_load_2d(sa, &p.tmA[0], full_bar(stage), k0, m0);
+            if (!B_MN) {
+              tma_load_2d(sb, &p.tmB, full_bar(stage), k0, n0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), &p.tmB, full_bar(stage), n0 + j * 64, k0);
+            }
+            if (++stage == NSTAGE) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+    } else if (warp == 1) {
+      // ===================== MMA issuer =====================
+      if (lane == 0) {
+        constexpr uint32_t idesc = make_idesc_f16(BM, BN, 1, 0, B_MN ? 1 : 0);
+        int stage = 0; uint32_t phase = 0;
+        int acc = 0; uint32_t acc_phase = 0;
+        for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+          if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, p.status, 0x20u)) { alive = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (!mbar_wait(full_bar(stage), phase, p.status, 0x21u, 12000000000ull)) { alive = false; break; }
+            tc_fence_after();
+            const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
+            const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t adesc = make_smem_desc(sa + k * (UMMA_K * 2), 0, 1024);
+              const uint64_t bdesc = B_MN ? make_smem_desc(sb + k * (UMMA_K * 128), BK * 128, 1024)
+                                          : make_smem_desc(sb + k * (UMMA_K * 2), 0, 1024);
+              umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(empty_bar(stage));
+            if (++stage == NSTAGE) { stage = 0; phase ^= 1u; }
+          }
+          if (!alive) break;
+          umma_commit(tfull_bar(acc));
+          if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+      }
+    } else if (warp < 6) {
+      // ===================== epilogue (warps 2..5) =====================
+      const int q = warp & 3;
+      int acc = 0; uint32_t acc_phase = 0;
+      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+        int m_blk, n_blk;
+        tile_mn(t, m_blk, n_blk);
+        if (!mbar_wait(tfull_bar(acc), acc_phase, p.status, 0x30u, 14000000000ull)) { alive = false; break; }
+        tc_fence_after();
+        if (MODE == MODE_RS) {
+          // the push of the tile that used this slot two tiles ago must have been picked up
+          if (!mbar_wait(pempty_bar(acc), acc_phase ^ 1u, p.status, 0x31u, 14000000000ull)) { alive = false; break; }
+        }
+        const int row = m_blk * BM + q * 32 + lane;
+        const bool row_ok = row < p.M;
+        const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + (uint32_t)c, r);
+          tmem_ld_wait();
+          const int col0 = n_blk * BN + c;
+          if (row_ok && col0 < p.N) {
+            __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D[0]) + (long long)row * p.ldd + col0;
+            if (col0 + 32 <= p.N) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+                  pk[j] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(drow + v * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) drow[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            }
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(tempty_bar(acc));
+        if (MODE == MODE_RS) mbar_arrive(pfull_bar(acc));      // tile is in the local partial buffer (CTA-scope release)
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    } else {
+      // ===================== copy warps (6..9): NVLink traffic =====================
+      const int ct = threadIdx.x - 192;   // 0..127
+      if (MODE == MODE_AG) {
+        // work items in consumption order: shard (rank+1), (rank+2), ...; inside a shard m-tile by m-tile; AG_SUB pieces each
+        const int items = (p.world - 1) * tiles_per_rank * AG_SUB;
+        const size_t piece_v4 = (size_t)(BM / AG_SUB) * (size_t)p.K * 2 / 16;   // uint4 per piece (contiguous rows)
+        for (int it = blockIdx.x; it < items; it += gridDim.x) {
+          const int sub = it % AG_SUB;
+          const int mt_lin = it / AG_SUB;
+          const int s = mt_lin / tiles_per_rank + 1;
+          const int src = (p.rank + s) % p.world;
+          const int mt = src * tiles_per_rank + (mt_lin % tiles_per_rank);
+          const size_t base = ((size_t)mt * AG_SUB + sub) * piece_v4;
+          const uint4* from = cp.ag_peer[src] + base;
+          uint4* to = cp.ag_local + base;
+          size_t i = ct;
+          for (; i + 7 * 128 < piece_v4; i += 8 * 128) {
+            uint4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = ld_cg_v4(from + i + j * 128);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) to[i + j * 128] = v[j];
+          }
+          for (; i < piece_v4; i += 128) to[i] = ld_cg_v4(from + i);
+          __threadfence();
+          named_bar_sync(1, 128);
+          if (ct == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cp.ready + mt) : "memory");
+        }
+      } else {
+        int acc = 0; uint32_t acc_phase = 0;
+        const int cwarp = ct >> 5;
+        for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+          int m_blk, n_blk;
+          tile_mn(t, m_blk, n_blk);
+          if (!mbar_wait(pfull_bar(acc), acc_phase, p.status, 0x50u, 16000000000ull)) { alive = false; break; }
+          const int owner = m_blk / tiles_per_rank;
+          if (owner != p.rank) {
+            const int n0 = n_blk * BN;
+            const int ncols = min(BN, p.N - n0);
+            const int v4_per_row = ncols / 8;                      // N is a multiple of 8
+            const long long ld_v4 = p.ldd / 8;
+            const uint4* src_base = cp.rs_partial + (long long)(m_blk * BM) * ld_v4 + n0 / 8;
+            // owner's staging: [src rank][rows_per_rank][N]
+            uint4* dst_base = cp.rs_stage_peer[owner] + ((long long)p.rank * cp.rows_per_rank + (m_blk % tiles_per_rank) * BM) * ld_v4 + n0 / 8;
+            for (int r0 = cwarp; r0 < BM; r0 += 4 * 4) {
+              uint4 v[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int r = r0 + 4 * j;
+                if (lane < v4_per_row && r < BM) v[j] = ld_cg_v4(src_base + (long long)r * ld_v4 + lane);
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int r = r0 + 4 * j;
+                if (lane < v4_per_row && r < BM) dst_base[(long long)r * ld_v4 + lane] = v[j];
+              }
+            }
+          }
+          mbar_arrive(pempty_bar(acc));
+          if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+        __threadfence_system();
+      }
+    }
+  }
+
+  // ---- teardown ----
+  tc_fence_before();
+  __syncthreads();
+  if (MODE == MODE_RS) {
+    __shared__ unsigned int is_last;
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      unsigned int prev = atomicAdd(p.flag_local + 2 * MAX_SRC, 1u);
+      is_last = (prev == gridDim.x - 1) ? 1u : 0u;
+    }
+    __syncthreads();
+    if (is_last && threadIdx.x < p.world) {
+      if (threadIdx.x == 0) p.flag_local[2 * MAX_SRC] = 0u;
+      __threadfence_system();
+      unsigned int* dstf = p.flag_peer[threadIdx.x] + MAX_SRC + p.rank;
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dstf), "r"(p.epoch) : "memory");
+    }
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// Owner-side reduction of the reduce-scatter: out[rows, N] = sum over ranks of slab_r (own slab read from the
+// local partial buffer), fixed rank order, fp32 accumulation.  Waits (bounded) for every peer's exit flag.
+__global__ void __launch_bounds__(256) rs_reduce_kernel(const uint4* __restrict__ stage, const uint4* __restrict__ own_partial,
+                                                         uint4* __restrict__ out, const __nv_bfloat16* __restrict__ residual,
+                                                         long long n_v4, long long slab_v4, int world, int rank,
+                                                         const unsigned int* flag_local, unsigned int epoch,
+                                                         unsigned int* status, unsigned long long limit_ns) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (threadIdx.x < world && threadIdx.x != rank) {
+    if (!wait_flag_ge(flag_local + MAX_SRC + threadIdx.x, epoch, status, 0x200u + threadIdx.x, limit_ns)) ok = 0;
+  }
+  __syncthreads();
+  if (!ok) return;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_v4; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int r = 0; r < world; ++r) {
+      uint4 v = (r == rank) ? ld_cg_v4(own_partial + i) : ld_cg_v4(stage + (long long)r * slab_v4 + i);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(h[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+    }
+    if (residual) {
+      uint4 v = *reinterpret_cast<const uint4*>(residual + i * 8);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(h[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+    }
+    uint4 o;
+    __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ho[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    out[i] = o;
+  }
+}
+
+template <int BN, int NSTAGE, int MODE, bool B_MN>
+int launch_comm_variant(const CommParams& cp, int grid, cudaStream_t s) {
+  using L = SmemLayout<BN, NSTAGE>;
+  auto kern = gemm_comm_sm100_kernel<BN, NSTAGE, MODE, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) { msb_set_error("gemm_comm_sm100: cannot set %d bytes of dynamic shared memory: %s", L::TOTAL, cudaGetErrorString(e)); return 1; }
+    attr_set = true;
+  }
+  kern<<<grid, 320, L::TOTAL, s>>>(cp);
+  MSB_CHECK_LAUNCH("gemm_comm_sm100");
+  return 0;
+}
+
 template <int BN, int NSTAGE, int EPI, bool A_MN, bool B_MN>
 int launch_variant(const GemmParams& p, int grid, cudaStream_t s) {
   using L = SmemLayout<BN, NSTAGE>;
@@ -432,4 +792,103 @@ MSB_API int msb_gemm_bf16(const void* A, const void* B, void* D, const void* bia
   a.a_mn_major = a_mn_major; a.b_mn_major = b_mn_major; a.epilogue = epilogue;
   a.status = status; a.world = 1;
   return msb_gemm_bf16_ex(&a, s);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Fused GEMM + collective launchers
+// ---------------------------------------------------------------------------------------------------------
+struct MsbCommArgs {
+  const void* A;                 // AG: this GPU's gathered buffer [M, K]; RS: local activation [M, K]
+  const void* B;                 // weight, K-major [N, K] (b_mn_major = 0) or MN-major [K, N] (1)
+  void* D;                       // AG: output [M, N]; RS: local partial buffer [M, N]
+  const void* peer_buf[MAX_SRC]; // AG: every rank's gathered buffer; RS: every rank's staging [world][rows_per_rank, N]
+  int M, N, K;
+  int b_mn_major;
+  int world, rank;
+  unsigned int epoch;
+  unsigned int* flag_local;
+  unsigned int* flag_peer[MAX_SRC];
+  unsigned int* ready;           // AG: [M/128] counters, zeroed by the launcher
+  unsigned int* status;
+};
+
+static int fill_comm(CommParams& cp, const MsbCommArgs* a, int mode, int bn) {
+  memset(&cp, 0, sizeof(cp));
+  GemmParams& p = cp.g;
+  int rc = make_tmap_2d(&p.tmA[0], a->A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->M, a->K, a->K, BM, BK);
+  if (rc) return rc;
+  if (!a->b_mn_major) rc = make_tmap_2d(&p.tmB, a->B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->N, a->K, a->K, bn, BK);
+  else rc = make_tmap_2d(&p.tmB, a->B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->K, a->N, a->N, BK, 64);
+  if (rc) return rc;
+  p.D[0] = a->D;
+  p.M = a->M; p.N = a->N; p.K = a->K; p.ldd = a->N;
+  p.status = a->status; p.world = a->world; p.rank = a->rank; p.epoch = a->epoch;
+  p.flag_local = a->flag_local;
+  for (int i = 0; i < MAX_SRC; ++i) p.flag_peer[i] = a->flag_peer[i];
+  cp.rows_per_rank = a->M / a->world;
+  const int tiles_per_rank = cp.rows_per_rank / BM;
+  if (mode == MODE_AG) {
+    p.m_tile_rot = a->rank * tiles_per_rank;
+    for (int i = 0; i < a->world; ++i) cp.ag_peer[i] = reinterpret_cast<const uint4*>(a->peer_buf[i]);
+    cp.ag_local = reinterpret_cast<uint4*>(const_cast<void*>(a->A));
+    cp.ready = a->ready; cp.ready_target = AG_SUB;
+  } else {
+    p.m_tile_rot = ((a->rank + 1) % a->world) * tiles_per_rank;
+    for (int i = 0; i < a->world; ++i) cp.rs_stage_peer[i] = reinterpret_cast<uint4*>(const_cast<void*>(a->peer_buf[i]));
+    cp.rs_partial = reinterpret_cast<const uint4*>(a->D);
+  }
+  return 0;
+}
+
+static int check_comm(const MsbCommArgs* a, const char* what) {
+  MSB_REQUIRE(a->world >= 2 && a->world <= MAX_SRC, "%s: world size %d not in [2, %d]", what, a->world, MAX_SRC);
+  MSB_REQUIRE(a->M % (a->world * BM) == 0, "%s: M=%d must be a multiple of world*128", what, a->M);
+  MSB_REQUIRE(a->N % 8 == 0 && a->K % 8 == 0, "%s: N=%d and K=%d must be multiples of 8", what, a->N, a->K);
+  MSB_REQUIRE(a->status && a->flag_local, "%s: status and flags are required", what);
+  return 0;
+}
+
+// Y[M, N] = allgather(x)[M, K] * B.  Every rank has already stored its rows into slab `rank` of its own gathered buffer.
+MSB_API int msb_gemm_allgather(const MsbCommArgs* a, cudaStream_t s) {
+  int rc = check_comm(a, "gemm_allgather");
+  if (rc) return rc;
+  MSB_REQUIRE((a->K * 2 * (BM / AG_SUB)) % 16 == 0, "gemm_allgather: K=%d too small", a->K);
+  const int bn = pick_bn(a->M, a->N, msb::num_sms());
+  CommParams cp;
+  rc = fill_comm(cp, a, MODE_AG, bn);
+  if (rc) return rc;
+  if (cudaMemsetAsync(a->ready, 0, sizeof(unsigned int) * (a->M / BM), s) != cudaSuccess) { msb_set_error("gemm_allgather: memset failed"); return 1; }
+  const int grid = msb::num_sms();
+  if (bn == 256) return a->b_mn_major ? launch_comm_variant<256, 4, MODE_AG, true>(cp, grid, s) : launch_comm_variant<256, 4, MODE_AG, false>(cp, grid, s);
+  return a->b_mn_major ? launch_comm_variant<128, 6, MODE_AG, true>(cp, grid, s) : launch_comm_variant<128, 6, MODE_AG, false>(cp, grid, s);
+}
+
+// partial[M, N] = x[M, K] * B, rows pushed to their owners' staging; follow with msb_rs_reduce on every rank.
+MSB_API int msb_gemm_reduce_scatter(const MsbCommArgs* a, cudaStream_t s) {
+  int rc = check_comm(a, "gemm_reduce_scatter");
+  if (rc) return rc;
+  const int bn = pick_bn(a->M, a->N, msb::num_sms());
+  CommParams cp;
+  rc = fill_comm(cp, a, MODE_RS, bn);
+  if (rc) return rc;
+  const long long tiles = (long long)(a->M / BM) * ((a->N + bn - 1) / bn);
+  const int sms = msb::num_sms();
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  if (bn == 256) return a->b_mn_major ? launch_comm_variant<256, 4, MODE_RS, true>(cp, grid, s) : launch_comm_variant<256, 4, MODE_RS, false>(cp, grid, s);
+  return a->b_mn_major ? launch_comm_variant<128, 6, MODE_RS, true>(cp, grid, s) : launch_comm_variant<128, 6, MODE_RS, false>(cp, grid, s);
+}
+
+// out[rows, N] = sum_r slab_r (+ residual); slab `rank` comes from own_partial, the others from `stage`.
+MSB_API int msb_rs_reduce(const void* stage, const void* own_partial, void* out, const void* residual, long long rows, int N,
+                          int world, int rank, const unsigned int* flag_local, unsigned int epoch, unsigned int* status,
+                          int wait_limit_ms, cudaStream_t s) {
+  MSB_REQUIRE(N % 8 == 0, "rs_reduce: N=%d must be a multiple of 8", N);
+  const long long n_v4 = rows * N / 8;
+  int grid = (int)((n_v4 + 255) / 256);
+  if (grid > msb::num_sms() * 8) grid = msb::num_sms() * 8;
+  rs_reduce_kernel<<<grid, 256, 0, s>>>((const uint4*)stage, (const uint4*)own_partial, (uint4*)out, (const __nv_bfloat16*)residual,
+                                        n_v4, n_v4, world, rank, flag_local, epoch, status,
+                                        wait_limit_ms > 0 ? (unsigned long long)wait_limit_ms * 1000000ull : 10000000000ull);
+  MSB_CHECK_LAUNCH("rs_reduce");
+  return 0;
 }

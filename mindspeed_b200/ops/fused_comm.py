@@ -1,0 +1,149 @@
+"""Fused GEMM + collective back end (optimisation level 2): drives csrc/kernels/gemm_sm100.cu in its
+all-gather and reduce-scatter modes over a symmetric heap.
+
+  allgather_matmul:      y = allgather(x) @ W^T  (or @ W)   one kernel: peer pulls + tcgen05 tiles
+  matmul_reduce_scatter: y = reduce_scatter(x @ W^T)        one kernel (tiles + pushes) + the owner-side reduction
+
+Both are numerically interchangeable with the library path within bf16 rounding: partial sums cross NVLink in bf16
+and are added in fp32 in a fixed rank order, so results are run-to-run deterministic.
+reference semantics: npu_all_gather_base_mm / npu_mm_reduce_scatter_base as used by
+mindspeed/core/tensor_parallel/mc2_feature/linear_function.py:23-246.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from . import loader
+from . import gemm as G
+from ..parallel.comm_ops import Sm100Ops
+from ..parallel.symm_mem import READY_OFFSET_WORDS, SymmetricHeap, get_heap
+
+MAX_SRC = 8
+
+
+class _CommArgs(ctypes.Structure):
+    _fields_ = [("A", ctypes.c_void_p), ("B", ctypes.c_void_p), ("D", ctypes.c_void_p),
+                ("peer_buf", ctypes.c_void_p * MAX_SRC), ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int),
+                ("b_mn_major", ctypes.c_int), ("world", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_uint),
+                ("flag_local", ctypes.c_void_p), ("flag_peer", ctypes.c_void_p * MAX_SRC), ("ready", ctypes.c_void_p),
+                ("status", ctypes.c_void_p)]
+
+
+def _heap_bytes(default_mib=640):
+    return int(os.environ.get("MSB200_SYMM_HEAP_MIB", default_mib)) * 1024 * 1024
+
+
+def _buf_bytes(request):
+    """Named buffers are sized once; reserve a floor so later, somewhat larger shapes still fit."""
+    return max(request, int(os.environ.get("MSB200_SYMM_BUF_MIB", 128)) * 1024 * 1024)
+
+
+class _Ctx:
+    """Per-process-group state: heap, buffer offsets, call parity."""
+
+    def __init__(self, group):
+        self.heap: SymmetricHeap = get_heap(group, _heap_bytes())
+        self.ag_calls = 0
+
+    def fill_common(self, a: _CommArgs, epoch: int, dev):
+        h = self.heap
+        a.world, a.rank, a.epoch = h.world, h.rank, epoch
+        a.flag_local = h.ptr(h.rank, 0)
+        for r in range(h.world):
+            a.flag_peer[r] = h.ptr(r, 0)
+        a.ready = h.ptr(h.rank, 4 * READY_OFFSET_WORDS)
+        a.status = G.status_word(dev).data_ptr()
+
+
+_CTX = {}
+
+
+def _ctx(group) -> _Ctx:
+    c = _CTX.get(id(group))
+    if c is None:
+        c = _Ctx(group)
+        _CTX[id(group)] = c
+    return c
+
+
+def reset():
+    _CTX.clear()
+
+
+class FusedOps(Sm100Ops):
+    name = "fused"
+    gathered_is_view = True   # the gathered input returned by allgather_matmul lives in a recycled symmetric buffer
+
+    @staticmethod
+    def _eligible(x, w, group, rows_total, n_out, k):
+        if group is None or not x.is_cuda or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+            return False
+        ws = dist.get_world_size(group)
+        return 2 <= ws <= MAX_SRC and rows_total % (ws * 128) == 0 and n_out % 8 == 0 and k % 8 == 0 and w.is_contiguous()
+
+    @classmethod
+    def allgather_matmul(cls, x, w, group, nt=True, need_gathered=False):
+        ws = dist.get_world_size(group) if group is not None else 1
+        x2 = x.reshape(-1, x.shape[-1])
+        rows, k = x2.shape
+        m = rows * ws
+        n = w.shape[0] if nt else w.shape[1]
+        if not cls._eligible(x, w, group, m, n, k):
+            return Sm100Ops.allgather_matmul(x, w, group, nt, need_gathered)
+        L = loader.require_lib()
+        c = _ctx(group)
+        h = c.heap
+        parity = c.ag_calls & 1
+        c.ag_calls += 1
+        off = h.alloc(f"ag{parity}", _buf_bytes(m * k * 2))
+        gathered = h.tensor(off, (m, k), torch.bfloat16)
+        gathered[h.rank * rows:(h.rank + 1) * rows].copy_(x2)
+        y = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+        a = _CommArgs()
+        a.A, a.B, a.D = h.ptr(h.rank, off), w.data_ptr(), y.data_ptr()
+        for r in range(ws):
+            a.peer_buf[r] = h.ptr(r, off)
+        a.M, a.N, a.K, a.b_mn_major = m, n, k, 0 if nt else 1
+        c.fill_common(a, h.next_epoch(), x.device)
+        loader.check(L.msb_gemm_allgather(ctypes.byref(a), ctypes.c_void_p(loader.stream_ptr())), "gemm_allgather")
+        lead = (x.shape[0] * ws,) + tuple(x.shape[1:-1])
+        total = gathered.view(*lead, k) if need_gathered else None
+        return y.view(*lead, n), total
+
+    @classmethod
+    def matmul_reduce_scatter(cls, x, w, group, nt=True):
+        ws = dist.get_world_size(group) if group is not None else 1
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        m, k = x2.shape
+        n = w.shape[0] if nt else w.shape[1]
+        if not cls._eligible(x, w, group, m, n, k) or x2.data_ptr() % 16 != 0:
+            return Sm100Ops.matmul_reduce_scatter(x, w, group, nt)
+        L = loader.require_lib()
+        c = _ctx(group)
+        h = c.heap
+        rows = m // ws
+        off_partial = h.alloc("rs_partial", _buf_bytes(m * n * 2))
+        off_stage = h.alloc("rs_stage", _buf_bytes(m * n * 2))
+        a = _CommArgs()
+        a.A, a.B, a.D = x2.data_ptr(), w.data_ptr(), h.ptr(h.rank, off_partial)
+        for r in range(ws):
+            a.peer_buf[r] = h.ptr(r, off_stage)
+        a.M, a.N, a.K, a.b_mn_major = m, n, k, 0 if nt else 1
+        epoch = h.next_epoch()
+        c.fill_common(a, epoch, x.device)
+        st = ctypes.c_void_p(loader.stream_ptr())
+        loader.check(L.msb_gemm_reduce_scatter(ctypes.byref(a), st), "gemm_reduce_scatter")
+        out = torch.empty(rows, n, dtype=torch.bfloat16, device=x.device)
+        own = h.ptr(h.rank, off_partial + h.rank * rows * n * 2)
+        loader.check(L.msb_rs_reduce(ctypes.c_void_p(h.ptr(h.rank, off_stage)), ctypes.c_void_p(own), loader.p(out), None,
+                                     ctypes.c_longlong(rows), n, ws, h.rank, ctypes.c_void_p(h.ptr(h.rank, 0)),
+                                     ctypes.c_uint(epoch), ctypes.c_void_p(G.status_word(x.device).data_ptr()), 0, st),
+                     "rs_reduce")
+        lead = (x.shape[0] // ws,) + tuple(x.shape[1:-1])
+        return out.view(*lead, n)

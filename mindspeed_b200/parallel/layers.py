@@ -157,6 +157,8 @@ class _RowLinearFn(torch.autograd.Function):
         dw = None
         if need_wgrad:
             if ctx.defer and WeightGradStore.enabled():
+                if getattr(ops, "gathered_is_view", False) and ctx.sp:
+                    dy_total = dy_total.clone()  # the fused op's gathered buffer is recycled two calls later
                 WeightGradStore.put(x, dy_total, weight, False, ctx.group, ctx.fusion)
             else:
                 dw = _wgrad(ops, dy_total, x, weight, ctx.fusion)
