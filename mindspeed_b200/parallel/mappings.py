@@ -114,12 +114,24 @@ def all_to_all_single(x, group, output_split_sizes=None, input_split_sizes=None,
     else:
         out = x.new_empty([sum(output_split_sizes)] + list(x.shape[1:]))
     if _is_gloo(group):
-        # gloo has no all_to_all_single for uneven splits on every build: use list form
+        # gloo has no all-to-all: exchange pairwise with non-blocking send / receive
         ins = list(x.split(input_split_sizes if input_split_sizes is not None else x.shape[0] // n, dim=0))
         outs = list(out.split(output_split_sizes if output_split_sizes is not None else out.shape[0] // n, dim=0))
-        outs = [o.contiguous() for o in outs]
-        dist.all_to_all(outs, [i.contiguous() for i in ins], group=group)
-        out = torch.cat(outs, dim=0)
+        me = _rk(group)
+        recv_bufs = [torch.empty_like(o) for o in outs]
+        reqs = []
+        for p in range(n):
+            if p == me:
+                recv_bufs[p].copy_(ins[p])
+                continue
+            peer = dist.get_global_rank(group, p)
+            if ins[p].numel() > 0:
+                reqs.append(dist.isend(ins[p].contiguous(), peer, group=group))
+            if recv_bufs[p].numel() > 0:
+                reqs.append(dist.irecv(recv_bufs[p], peer, group=group))
+        for r in reqs:
+            r.wait()
+        out = torch.cat(recv_bufs, dim=0)
         return (out, None) if async_op else out
     h = dist.all_to_all_single(out, x, output_split_sizes=output_split_sizes, input_split_sizes=input_split_sizes,
                                group=group, async_op=async_op)

@@ -17,6 +17,18 @@ def _free_port():
         return s.getsockname()[1]
 
 
+def _plain(o):
+    """Tensors travel back as numpy arrays (torch's shared-memory pickling needs the sender to stay alive)."""
+    import torch
+    if torch.is_tensor(o):
+        return o.detach().cpu().numpy()
+    if isinstance(o, (list, tuple)):
+        return type(o)(_plain(x) for x in o)
+    if isinstance(o, dict):
+        return {k: _plain(v) for k, v in o.items()}
+    return o
+
+
 def _entry(rank, world, port, fn, args, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank))
@@ -24,7 +36,7 @@ def _entry(rank, world, port, fn, args, q):
         import torch
         torch.set_num_threads(1)
         out = fn(rank, world, *args)
-        q.put((rank, "ok", out))
+        q.put((rank, "ok", _plain(out)))
     except Exception:
         q.put((rank, "err", traceback.format_exc()))
 
