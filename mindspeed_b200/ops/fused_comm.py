@@ -102,7 +102,8 @@ class FusedOps(Sm100Ops):
         off = h.alloc(f"ag{parity}", _buf_bytes(m * k * 2))
         gathered = h.tensor(off, (m, k), torch.bfloat16)
         gathered[h.rank * rows:(h.rank + 1) * rows].copy_(x2)
-        y = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+        lead = (x.shape[0] * ws,) + tuple(x.shape[1:-1])
+        y = torch.empty(*lead, n, dtype=torch.bfloat16, device=x.device)   # final shape: custom Functions must not return views
         a = _CommArgs()
         a.A, a.B, a.D = h.ptr(h.rank, off), w.data_ptr(), y.data_ptr()
         for r in range(ws):
@@ -110,9 +111,8 @@ class FusedOps(Sm100Ops):
         a.M, a.N, a.K, a.b_mn_major = m, n, k, 0 if nt else 1
         c.fill_common(a, h.next_epoch(), x.device)
         loader.check(L.msb_gemm_allgather(ctypes.byref(a), ctypes.c_void_p(loader.stream_ptr())), "gemm_allgather")
-        lead = (x.shape[0] * ws,) + tuple(x.shape[1:-1])
         total = gathered.view(*lead, k) if need_gathered else None
-        return y.view(*lead, n), total
+        return y, total
 
     @classmethod
     def matmul_reduce_scatter(cls, x, w, group, nt=True):
@@ -139,11 +139,11 @@ class FusedOps(Sm100Ops):
         c.fill_common(a, epoch, x.device)
         st = ctypes.c_void_p(loader.stream_ptr())
         loader.check(L.msb_gemm_reduce_scatter(ctypes.byref(a), st), "gemm_reduce_scatter")
-        out = torch.empty(rows, n, dtype=torch.bfloat16, device=x.device)
+        lead = (x.shape[0] // ws,) + tuple(x.shape[1:-1])
+        out = torch.empty(*lead, n, dtype=torch.bfloat16, device=x.device)
         own = h.ptr(h.rank, off_partial + h.rank * rows * n * 2)
         loader.check(L.msb_rs_reduce(ctypes.c_void_p(h.ptr(h.rank, off_stage)), ctypes.c_void_p(own), loader.p(out), None,
                                      ctypes.c_longlong(rows), n, ws, h.rank, ctypes.c_void_p(h.ptr(h.rank, 0)),
                                      ctypes.c_uint(epoch), ctypes.c_void_p(G.status_word(x.device).data_ptr()), 0, st),
                      "rs_reduce")
-        lead = (x.shape[0] // ws,) + tuple(x.shape[1:-1])
-        return out.view(*lead, n)
+        return out
