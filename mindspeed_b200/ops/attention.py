@@ -90,3 +90,86 @@ def flash_attention(q, k, v, causal=True, softmax_scale=None, return_lse=False, 
     if be == "library" and q.is_cuda:
         return _library(q, k, v, causal, softmax_scale, return_lse)
     return attention_ref(q, k, v, causal, softmax_scale, return_lse=return_lse)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Block primitives for ring / KV-allgather attention: forward returning LSE, backward taking the GLOBAL output
+# and LSE (so partial blocks of one softmax row can be differentiated independently).
+# ---------------------------------------------------------------------------------------------------------
+def attn_bwd_ref(dout, q, k, v, out, lse, causal, softmax_scale=None, q_offset=0):
+    """fp32 reference backward. Shapes as the forward; lse [b, n, sq] is the global log-sum-exp of each row."""
+    sq, b, nq, d = q.shape
+    sk, nkv = k.shape[0], k.shape[2]
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
+    rep = nq // nkv
+    qf = q.permute(1, 2, 0, 3).float()
+    kf = k.permute(1, 2, 0, 3).float().repeat_interleave(rep, dim=1)
+    vf = v.permute(1, 2, 0, 3).float().repeat_interleave(rep, dim=1)
+    do = dout.permute(1, 2, 0, 3).float()
+    of = out.permute(1, 2, 0, 3).float()
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        qi = torch.arange(sq, device=q.device).view(sq, 1) + q_offset
+        kj = torch.arange(sk, device=q.device).view(1, sk)
+        s = s.masked_fill((kj > qi).view(1, 1, sq, sk), float("-inf"))
+    p = torch.exp(s - lse.float().unsqueeze(-1))
+    p = torch.nan_to_num(p, nan=0.0, posinf=0.0)
+    dv = torch.matmul(p.transpose(-1, -2), do)
+    dp = torch.matmul(do, vf.transpose(-1, -2))
+    delta = (do * of).sum(-1, keepdim=True)
+    ds = p * (dp - delta) * scale
+    dq = torch.matmul(ds, kf)
+    dk = torch.matmul(ds.transpose(-1, -2), qf)
+    if rep > 1:
+        dk = dk.view(b, nkv, rep, sk, -1).sum(2)
+        dv = dv.view(b, nkv, rep, sk, -1).sum(2)
+    back = lambda t, ref: t.permute(2, 0, 1, 3).contiguous().to(ref.dtype)
+    return back(dq, q), back(dk, k), back(dv, v)
+
+
+def attn_fwd_block(q, k, v, causal, softmax_scale=None):
+    """(out [sq,b,nq,dv], lse [b,nq,sq] fp32, ctx) for one (Q block, KV block) pair; causal = top-left aligned."""
+    if q.is_cuda and get_backend(q) != "ref":
+        sq, b, nq, d = q.shape
+        nkv = k.shape[2]
+        rep = nq // nkv
+        qb = q.permute(1, 2, 0, 3)
+        kb = k.permute(1, 2, 0, 3)
+        vb = v.permute(1, 2, 0, 3)
+        if rep > 1:
+            kb, vb = kb.repeat_interleave(rep, 1), vb.repeat_interleave(rep, 1)
+        res = torch.ops.aten._scaled_dot_product_flash_attention(qb, kb, vb, 0.0, causal, False, scale=softmax_scale)
+        out, lse = res[0], res[1]
+        ctx = (res[6], res[7])  # philox seed / offset
+        return out.permute(2, 0, 1, 3), lse, ctx
+    out, lse = attention_ref(q, k, v, causal, softmax_scale, return_lse=True)
+    return out, lse, None
+
+
+def attn_bwd_block(dout, q, k, v, out, lse, causal, softmax_scale=None, ctx=None):
+    if q.is_cuda and get_backend(q) != "ref" and ctx is not None:
+        sq, b, nq, d = q.shape
+        sk, nkv = k.shape[0], k.shape[2]
+        rep = nq // nkv
+        qb, kb, vb = q.permute(1, 2, 0, 3), k.permute(1, 2, 0, 3), v.permute(1, 2, 0, 3)
+        if rep > 1:
+            kb, vb = kb.repeat_interleave(rep, 1), vb.repeat_interleave(rep, 1)
+        dq, dk, dv = torch.ops.aten._scaled_dot_product_flash_attention_backward(
+            dout.permute(1, 2, 0, 3), qb, kb, vb, out.permute(1, 2, 0, 3), lse.contiguous(), None, None, sq, sk, 0.0, causal,
+            ctx[0], ctx[1], scale=softmax_scale)
+        if rep > 1:
+            dk = dk.view(b, nkv, rep, sk, -1).sum(2)
+            dv = dv.view(b, nkv, rep, sk, -1).sum(2)
+        return dq.permute(2, 0, 1, 3), dk.permute(2, 0, 1, 3), dv.permute(2, 0, 1, 3)
+    return attn_bwd_ref(dout, q, k, v, out, lse, causal, softmax_scale)
+
+
+def merge_lse(out1, lse1, out2, lse2):
+    """Online-softmax merge of two partial attention results over disjoint key sets
+    (reference math: mindspeed/core/context_parallel/utils.py:77-119; here in LSE form).
+    out [s,b,n,d]; lse [b,n,s]."""
+    lse = torch.logaddexp(lse1, lse2)
+    w1 = torch.exp(lse1 - lse).permute(2, 0, 1).unsqueeze(-1)
+    w2 = torch.exp(lse2 - lse).permute(2, 0, 1).unsqueeze(-1)
+    out = out1.float() * w1 + out2.float() * w2
+    return out.to(out1.dtype), lse

@@ -1,0 +1,51 @@
+"""Ulysses context parallelism: all-to-all sequence <-> heads around ordinary attention.
+
+q/k/v arrive [s/p, b, n, d]; an all-to-all makes them [s, b, n/p, d]; attention runs on the full sequence with a
+head subset; a second all-to-all restores [s/p, b, n*d]
+(reference: mindspeed/core/context_parallel/ulysses_context_parallel/ulysses_context_parallel.py:83-108,127-221).
+GQA with fewer KV heads than ranks repeats KV heads up to the group size first (:186-190).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ...ops import attention as A
+from .. import mappings as M
+
+
+def seq_to_heads(x, group):
+    """[s/p, b, n, d] -> [s, b, n/p, d]"""
+    p = dist.get_world_size(group)
+    if p == 1:
+        return x
+    sl, b, n, d = x.shape
+    t = x.reshape(sl, b, p, n // p, d).permute(2, 0, 1, 3, 4).contiguous()  # [p, s/p, b, n/p, d]
+    t = M.all_to_all(group, t.reshape(p * sl, b, n // p, d))
+    return t  # rows are now ordered by source rank = sequence chunk
+
+
+def heads_to_seq(x, group):
+    """[s, b, n/p, d] -> [s/p, b, n, d]"""
+    p = dist.get_world_size(group)
+    if p == 1:
+        return x
+    s, b, nl, d = x.shape
+    t = M.all_to_all(group, x.contiguous())                                   # [p * s/p, b, n/p, d] by source = head group
+    t = t.reshape(p, s // p, b, nl, d).permute(1, 2, 0, 3, 4).contiguous()    # [s/p, b, p, n/p, d]
+    return t.reshape(s // p, b, p * nl, d)
+
+
+def ulysses_attention(q, k, v, config, group, causal=True, softmax_scale=None, layer_number=1, inner=None):
+    p = dist.get_world_size(group)
+    nkv = k.shape[2]
+    if nkv < p:
+        rep = p // nkv
+        k, v = k.repeat_interleave(rep, dim=2), v.repeat_interleave(rep, dim=2)
+    qh, kh, vh = seq_to_heads(q, group), seq_to_heads(k, group), seq_to_heads(v, group)
+    if inner is not None:
+        o = inner(qh, kh, vh)
+    else:
+        backend = "sm100" if (config is not None and config.optimization_level >= 1 and config.use_flash_attn) else None
+        o = A.flash_attention(qh, kh, vh, causal=causal, softmax_scale=softmax_scale, backend=backend)
+    return heads_to_seq(o, group)

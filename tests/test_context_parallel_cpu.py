@@ -1,0 +1,68 @@
+"""Context-parallel attention on CPU/gloo against full-sequence attention on one rank (out, dq, dk, dv)."""
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from dist_utils import run_distributed  # noqa: E402
+
+
+def _full(seed, s, b, nq, nkv, d):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(s, b, nq, d, generator=g)
+    k = torch.randn(s, b, nkv, d, generator=g)
+    v = torch.randn(s, b, nkv, d, generator=g)
+    w = torch.randn(s, b, nq, d, generator=g)
+    return q, k, v, w
+
+
+def _run(rank, world, algo, nq, nkv, causal, extra):
+    import torch.distributed as dist
+    from mindspeed_b200.config import TransformerConfig
+    from mindspeed_b200.ops.attention import attention_ref
+    from mindspeed_b200.parallel import parallel_state as ps
+    from mindspeed_b200.parallel.context_parallel import dispatch_context_parallel_attention
+    from mindspeed_b200.parallel.context_parallel.batch_utils import slice_for_cp
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    kw = dict(context_parallel_size=world, use_cp_send_recv_overlap=extra.get("overlap", False))
+    if algo == "hybrid_cp_algo":
+        kw["ulysses_degree_in_cp"] = 2
+    ps.initialize_model_parallel(**kw)
+    cfg = TransformerConfig(num_layers=1, hidden_size=nq * 16, num_attention_heads=nq, num_query_groups=nkv,
+                            context_parallel_size=world, use_cpu_initialization=True, optimization_level=0)
+    cfg.context_parallel_algo = algo
+    cfg.context_parallel_kv_cache_policy = extra.get("cache")
+    cfg.context_parallel_cache_interval = 0
+    s, b, d = 32 * world, 2, 16
+    q, k, v, w = _full(3, s, b, nq, nkv, d)
+    qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
+    ref = attention_ref(qf, kf, vf, causal=causal)
+    (ref * w).sum().backward()
+    sl = lambda t: slice_for_cp(t, 0, algo).clone()
+    ql, kl, vl = (sl(t).requires_grad_(True) for t in (q, k, v))
+    out = dispatch_context_parallel_attention(ql, kl, vl, cfg, causal=causal)
+    (out * sl(w)).sum().backward()
+    res = {}
+    res["out"] = (out.detach() - sl(ref.detach())).abs().max().item()
+    res["dq"] = (ql.grad - sl(qf.grad)).abs().max().item()
+    res["dk"] = (kl.grad - sl(kf.grad)).abs().max().item()
+    res["dv"] = (vl.grad - sl(vf.grad)).abs().max().item()
+    ps.destroy_model_parallel()
+    dist.destroy_process_group()
+    return res
+
+
+@pytest.mark.parametrize("algo,world,nq,nkv,causal,extra", [
+    ("megatron_cp_algo", 2, 4, 2, True, {}),
+    ("megatron_cp_algo", 4, 4, 4, True, {"overlap": True, "cache": "full"}),
+    ("ulysses_cp_algo", 2, 4, 2, True, {}),
+    ("ulysses_cp_algo", 4, 4, 2, True, {}),
+    ("kvallgather_cp_algo", 2, 4, 2, True, {}),
+    ("hybrid_cp_algo", 4, 4, 4, True, {}),
+])
+def test_cp_attention_matches_full(algo, world, nq, nkv, causal, extra):
+    for r in run_distributed(_run, world, algo, nq, nkv, causal, extra):
+        for key, err in r.items():
+            assert err < 2e-4, (algo, key, err, r)
