@@ -327,7 +327,7 @@ class MLAFeature(Feature):
 # ======================================================================================
 class DualpipeVFeature(Feature):
     def __init__(self):
-        super().__init__("schedules-method", optimization_level=2)
+        super().__init__("schedules-method", optimization_level=0)
 
     def register_args(self, parser):
         g = parser.add_argument_group(title=self.feature_name)

@@ -614,13 +614,26 @@ def set_virtual_pipeline_model_parallel_world_size(v):
     _S.vpp_world = v
 
 
+_STAGE_OVERRIDE = {"first": None, "last": None}
+
+
+def set_stage_override(first, last):
+    """Schedules whose chunk placement is not ``chunk*pp + rank`` (V-shaped, bidirectional) tell the model code
+    explicitly whether the chunk being run is the first / last model stage."""
+    _STAGE_OVERRIDE["first"], _STAGE_OVERRIDE["last"] = first, last
+
+
 def is_pipeline_first_stage(ignore_virtual=False):
+    if not ignore_virtual and _STAGE_OVERRIDE["first"] is not None:
+        return _STAGE_OVERRIDE["first"]
     if not ignore_virtual and _S.vpp_world is not None and _S.vpp_rank != 0:
         return False
     return get_pipeline_model_parallel_rank() == 0
 
 
 def is_pipeline_last_stage(ignore_virtual=False):
+    if not ignore_virtual and _STAGE_OVERRIDE["last"] is not None:
+        return _STAGE_OVERRIDE["last"]
     if not ignore_virtual and _S.vpp_world is not None and _S.vpp_rank != _S.vpp_world - 1:
         return False
     return get_pipeline_model_parallel_rank() == get_pipeline_model_parallel_world_size() - 1

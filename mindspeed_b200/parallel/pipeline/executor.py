@@ -1,0 +1,151 @@
+"""Executes a pipeline ``Plan`` (plan.py) on this rank: lockstep slots, one batched send/receive group per slot.
+
+Every tensor is sent in the slot after it was produced and received in that same slot, so both ends always put
+the matching operations into the same ``batch_isend_irecv`` group and the order inside a group is canonical
+(sorted by direction, chunk and micro-batch) on both sides.  Communication stays on NCCL point-to-point
+(gloo on CPU); the next slot's receives are not posted early, which keeps memory bounded by the plan itself.
+
+B / W split: when the plan contains W operations for a chunk, its B runs with the weight-gradient store enabled
+(linear layers queue their weight-gradient GEMMs, reference: mindspeed/core/weight_grad_store.py:63-240) and the W
+operation pops that micro-batch's queue.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import parallel_state as ps
+from ..weight_grad_store import WeightGradStore
+from . import schedules as S
+from .plan import Message, Op, Plan
+
+_CURRENT = S._CURRENT
+current_microbatch = S.current_microbatch
+
+
+def _set_linear_deferral(module, flag: bool):
+    for m in module.modules():
+        if hasattr(m, "wgrad_deferral"):
+            m.wgrad_deferral = flag
+
+
+def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microbatches, seq_length, micro_batch_size,
+             forward_only=False, collect_non_loss_data=False):
+    if not isinstance(model, list):
+        model = [model]
+    if not isinstance(data_iterator, list):
+        data_iterator = [data_iterator] * len(model)
+    config = S._cfg(model)
+    pp_group = ps.get_pipeline_model_parallel_group()
+    pp_ranks = ps._ranks("pp")
+    rank = ps.get_pipeline_model_parallel_rank()
+    pl = plan.placement
+    Sn = pl.num_stages
+    shape = S.get_tensor_shapes(seq_length=seq_length, micro_batch_size=micro_batch_size, config=config)[0]
+    dev = next(model[0].parameters()).device
+    dtype = config.pipeline_dtype
+    has_w = any(op.kind == "W" for ops in plan.table[rank] for op in ops)
+    inputs: Dict[Tuple[int, int], Optional[torch.Tensor]] = {}
+    outputs: Dict[Tuple[int, int], torch.Tensor] = {}
+    inbox: Dict[Tuple[str, int, int], torch.Tensor] = {}
+    outbox: Dict[Tuple[str, int, int], torch.Tensor] = {}
+    store: List = []
+    total_tokens = torch.zeros([], dtype=torch.int)
+    saved_vpp = (ps.get_virtual_pipeline_model_parallel_rank(), ps.get_virtual_pipeline_model_parallel_world_size())
+    ctxs = []
+    if not forward_only:
+        for m in model:
+            if hasattr(m, "no_sync"):
+                c = m.no_sync()
+                c.__enter__()
+                ctxs.append(c)
+    if has_w:
+        for m in model:
+            _set_linear_deferral(m, True)
+    key = lambda m: (m.kind, m.src, m.dst, m.src_chunk, m.mb)
+    try:
+        for t in range(plan.num_slots):
+            sends = sorted(plan.sends.get((rank, t), []), key=key)
+            recvs = sorted(plan.recvs.get((rank, t), []), key=key)
+            if forward_only:
+                sends = [m for m in sends if m.kind == "act"]
+                recvs = [m for m in recvs if m.kind == "act"]
+            ops, bufs = [], []
+            allm = sorted(sends + recvs, key=key)
+            for m in allm:
+                if m.src == rank and m in sends:
+                    ten = outbox.pop((m.kind, m.src_chunk, m.mb))
+                    ops.append(dist.P2POp(dist.isend, ten.contiguous(), pp_ranks[m.dst], pp_group))
+                else:
+                    buf = torch.empty(shape, dtype=dtype, device=dev)
+                    bufs.append((m, buf))
+                    ops.append(dist.P2POp(dist.irecv, buf, pp_ranks[m.src], pp_group))
+            if ops:
+                for r in dist.batch_isend_irecv(ops):
+                    r.wait()
+            for m, buf in bufs:
+                inbox[(m.kind, m.dst_chunk, m.mb)] = buf
+            for op in plan.table[rank][t]:
+                if forward_only and op.kind != "F":
+                    continue
+                pipe, stage = pl.stage_of[(rank, op.chunk)]
+                _CURRENT.update(chunk=op.chunk, mb=op.mb, pipe=pipe)
+                ps.set_virtual_pipeline_model_parallel_world_size(None)
+                ps.set_stage_override(stage == 0, stage == Sn - 1)
+                chunk = model[op.chunk]
+                if op.kind == "F":
+                    inp = None
+                    if stage > 0:
+                        inp = inbox.pop(("act", op.chunk, op.mb))
+                        inp.requires_grad_(not forward_only)
+                    out, nt = S.forward_step(forward_step_func, data_iterator[op.chunk], chunk, num_microbatches, inp,
+                                             store, config, collect_non_loss_data, current_microbatch=op.mb)
+                    total_tokens += nt.cpu() if torch.is_tensor(nt) else nt
+                    if not forward_only:
+                        inputs[(op.chunk, op.mb)] = inp
+                        outputs[(op.chunk, op.mb)] = out
+                    if stage < Sn - 1:
+                        dr, dc = pl.holder(pipe, stage + 1)
+                        if dr == rank:
+                            inbox[("act", dc, op.mb)] = out.detach().clone()
+                        else:
+                            outbox[("act", op.chunk, op.mb)] = out.detach()
+                elif op.kind == "B":
+                    inp = inputs.pop((op.chunk, op.mb))
+                    out = outputs.pop((op.chunk, op.mb))
+                    og = None if stage == Sn - 1 else inbox.pop(("grad", op.chunk, op.mb))
+                    if has_w:
+                        WeightGradStore.enable(True)
+                    g = S.backward_step(inp, out, og, None, config)
+                    if has_w:
+                        WeightGradStore.flush()
+                        WeightGradStore.enable(False)
+                    if stage > 0:
+                        dr, dc = pl.holder(pipe, stage - 1)
+                        if dr == rank:
+                            inbox[("grad", dc, op.mb)] = g
+                        else:
+                            outbox[("grad", op.chunk, op.mb)] = g
+                else:  # W
+                    WeightGradStore.pop()
+    finally:
+        ps.set_stage_override(None, None)
+        ps.set_virtual_pipeline_model_parallel_rank(saved_vpp[0])
+        ps.set_virtual_pipeline_model_parallel_world_size(saved_vpp[1])
+        if has_w:
+            WeightGradStore.pop_all()
+            WeightGradStore.enable(False)
+            for m in model:
+                _set_linear_deferral(m, False)
+        for c in ctxs:
+            c.__exit__(None, None, None)
+    if not forward_only:
+        if pl.replicas > 1:
+            from .chimera import allreduce_replica_grads
+            allreduce_replica_grads(model)
+        fin = getattr(config, "finalize_model_grads_func", None)
+        if fin is not None:
+            fin(model, total_tokens if config.calculate_per_token_loss else None)
+    return store

@@ -1,0 +1,23 @@
+"""Interleaved 1F1B (virtual pipeline): v chunks per rank, stage = chunk * pp + rank."""
+from .. import parallel_state as ps
+from .executor import run_plan
+from .plan import build_plan
+
+_CACHE = {}
+
+
+def _plan(name, pp, n, vpp=None, split_w=True):
+    k = (name, pp, n, vpp, split_w)
+    if k not in _CACHE:
+        _CACHE[k] = build_plan(name, pp, n, vpp=vpp, split_w=split_w)
+    return _CACHE[k]
+
+
+def forward_backward_interleaved(*, forward_step_func, data_iterator, model, num_microbatches, seq_length, micro_batch_size,
+                                 forward_only=False, collect_non_loss_data=False, **_):
+    pp = ps.get_pipeline_model_parallel_world_size()
+    vpp = len(model)
+    plan = _plan("interleaved", pp, num_microbatches, vpp)
+    return run_plan(plan, forward_step_func=forward_step_func, data_iterator=data_iterator, model=model,
+                    num_microbatches=num_microbatches, seq_length=seq_length, micro_batch_size=micro_batch_size,
+                    forward_only=forward_only, collect_non_loss_data=collect_non_loss_data)

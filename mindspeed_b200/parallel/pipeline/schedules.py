@@ -21,6 +21,12 @@ from .. import parallel_state as ps
 from . import p2p
 
 _SCHEDULE_OVERRIDE = {"name": None}
+_CURRENT = {"chunk": 0, "mb": 0, "pipe": 0}   # the (chunk, micro-batch, pipeline) being executed
+
+
+def current_microbatch():
+    """Lets a forward_step_func or data iterator see which micro-batch the schedule is running."""
+    return dict(_CURRENT)
 
 
 def set_schedule(name: Optional[str]):
@@ -77,6 +83,8 @@ def forward_step(forward_step_func, data_iterator, model, num_microbatches, inpu
     """One micro-batch forward.  ``forward_step_func(data_iterator, model) -> (output, loss_func)``;
     on the last stage ``loss_func(output) -> (loss, {name: value})`` or ``(loss, num_tokens, {...})``."""
     set_input_tensor(model, input_tensor)
+    if current_microbatch is not None:
+        _CURRENT["mb"] = current_microbatch
     ctx = torch.autocast("cuda", dtype=config.autocast_dtype) if getattr(config, "enable_autocast", False) else contextlib.nullcontext()
     with ctx:
         output_tensor, loss_func = forward_step_func(data_iterator, model)

@@ -65,6 +65,7 @@ class WeightGradStore:
         return M.all_gather_first_dim(x, group), None
 
     @classmethod
+    @torch.no_grad()
     def pop(cls, num: int = -1) -> int:
         """Run the weight-gradient GEMMs of one flushed micro-batch (or ``num`` entries of it)."""
         from .comm_ops import get_ops
@@ -96,7 +97,14 @@ class WeightGradStore:
             x, dy, weight, sp, group, fusion = e
             dw = _wgrad(ops, dy, total, weight, fusion)
             if dw is not None:
-                weight.grad = dw if weight.grad is None else weight.grad + dw
+                # autograd is not involved here, so the data-parallel hook will not fire: add to the buffer directly
+                if hasattr(weight, "main_grad"):
+                    weight.main_grad.add_(dw.to(weight.main_grad.dtype))
+                    cb = getattr(weight, "_main_grad_ready_cb", None)
+                    if cb is not None:
+                        cb(weight)
+                else:
+                    weight.grad = dw if weight.grad is None else weight.grad + dw
         return len(entries)
 
     @classmethod

@@ -68,7 +68,17 @@ def get_model(model_provider_func, wrap_with_ddp=True):
     args = get_args()
     vpp = ps.get_virtual_pipeline_model_parallel_world_size()
     models = []
-    if ps.get_pipeline_model_parallel_world_size() > 1 and (vpp is not None or args.schedules_method in ("dualpipev",)):
+    pp = ps.get_pipeline_model_parallel_world_size()
+    if pp > 1 and args.schedules_method in ("dualpipe", "chimera"):
+        # bidirectional: chunk 0 is stage r of the "down" replica, chunk 1 is stage pp-1-r of the "up" replica
+        r = ps.get_pipeline_model_parallel_rank()
+        models.append(model_provider_func(pre_process=(r == 0), post_process=(r == pp - 1)))
+        ps.set_pipeline_model_parallel_rank(pp - 1 - r)
+        try:
+            models.append(model_provider_func(pre_process=(pp - 1 - r == 0), post_process=(pp - 1 - r == pp - 1)))
+        finally:
+            ps.set_pipeline_model_parallel_rank(None)
+    elif pp > 1 and (vpp is not None or args.schedules_method in ("dualpipev",)):
         n = vpp if vpp is not None else 2
         if vpp is None:
             ps.set_virtual_pipeline_model_parallel_world_size(2)
@@ -143,7 +153,7 @@ def train_step(forward_step_func, data_iterator, model, optimizer, opt_param_sch
     else:
         skipped = 1
     loss_reduced = {}
-    if ps.is_pipeline_last_stage(ignore_virtual=True) and losses_reduced:
+    if losses_reduced:   # whichever rank holds a loss stage (the last rank; rank 0 for V-shaped schedules; both ends for bidirectional)
         for key in losses_reduced[0]:
             vals = [x[key] for x in losses_reduced]
             if torch.is_tensor(vals[0]) and vals[0].numel() == 2:

@@ -1,0 +1,134 @@
+"""Pipeline schedules: plan validity for every schedule, and gloo multi-rank numerics against no pipelining."""
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from dist_utils import run_distributed  # noqa: E402
+
+
+@pytest.mark.parametrize("name,vpp", [("1f1b", None), ("interleaved", 2), ("interleaved", 4), ("dualpipev", None),
+                                      ("dualpipev_greedy", None), ("dualpipe", None), ("chimera", None)])
+@pytest.mark.parametrize("pp", [2, 4, 8])
+def test_plans_are_valid_and_matched(name, vpp, pp):
+    from mindspeed_b200.parallel.pipeline.plan import build_plan, validate
+    for n in (2 * pp, 4 * pp):
+        plan = build_plan(name, pp, n, vpp=vpp)
+        validate(plan)
+        # every message is received in the slot it is sent, and its consumer runs no earlier than that slot
+        for m in plan.messages:
+            ops = plan.table[m.dst][m.slot:]
+            kind = "F" if m.kind == "act" else "B"
+            assert any(o.kind == kind and o.chunk == m.dst_chunk and o.mb == m.mb for slot in ops for o in slot), m
+        for (r, t), sends in plan.sends.items():
+            for m in sends:
+                assert m in plan.recvs[(m.dst, t)]
+
+
+def test_1f1b_bubble_matches_theory():
+    from mindspeed_b200.parallel.pipeline.plan import order_1f1b, placement_1f1b, simulate_orders, greedy_orders, placement_v
+    for pp, n in ((4, 8), (8, 32)):
+        _, bub = simulate_orders(placement_1f1b(pp), order_1f1b(pp, n), {"F": 1, "B": 2, "W": 0})
+        assert abs(bub - (pp - 1) / (n + pp - 1)) < 1e-6
+        # the V schedule with split weight gradients must beat 1F1B's bubble
+        _, bub_v = simulate_orders(placement_v(pp), greedy_orders(placement_v(pp), n, True), {"F": 1, "B": 1, "W": 1})
+        assert bub_v < 0.5 * bub
+
+
+BASE = ["--num-layers", "4", "--hidden-size", "64", "--num-attention-heads", "4", "--ffn-hidden-size", "128", "--seq-length", "32",
+        "--max-position-embeddings", "32", "--micro-batch-size", "1", "--global-batch-size", "8", "--vocab-size", "128",
+        "--make-vocab-size-divisible-by", "1", "--train-iters", "3", "--lr", "1e-3", "--lr-decay-style", "constant",
+        "--hidden-dropout", "0", "--attention-dropout", "0", "--seed", "1234", "--distributed-backend", "gloo",
+        "--optimization-level", "0", "--use-cpu-initialization", "--weight-decay", "0.0", "--clip-grad", "0.0",
+        "--untie-embeddings-and-output-weights", "--swiglu", "--normalization", "RMSNorm", "--position-embedding-type", "rope",
+        "--disable-bias-linear", "--no-gradient-accumulation-fusion"]
+
+
+def _canonical_init(model):
+    """Give every parameter a value that depends only on its global name, so any pipeline layout holds the same model."""
+    import hashlib
+    for chunk in model:
+        inner = chunk.module if hasattr(chunk, "module") else chunk
+        for name, p in inner.named_parameters():
+            parts = name.split(".")
+            if "layers" in parts:
+                i = parts.index("layers")
+                layer = inner.decoder.layers[int(parts[i + 1])]
+                parts[i + 1] = str(layer.layer_number)
+            key = ".".join(parts)
+            seed = int(hashlib.sha256(key.encode()).hexdigest()[:8], 16)
+            g = torch.Generator().manual_seed(seed)
+            with torch.no_grad():
+                if p.dim() == 1:
+                    p.copy_(1.0 + 0.01 * torch.randn(p.shape, generator=g))
+                else:
+                    p.copy_(0.05 * torch.randn(p.shape, generator=g))
+
+
+def _train(rank, world, extra, bidirectional):
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import pretrain_gpt as pg
+    from mindspeed_b200.parallel import parallel_state as ps
+    from mindspeed_b200.parallel.pipeline.executor import current_microbatch
+    from mindspeed_b200.training import get_args, initialize_megatron, setup_model_and_optimizer, train_step
+    from mindspeed_b200.training.data import SyntheticGPTDataset
+    args = initialize_megatron(args_list=BASE + list(extra))
+    model, opt, sched = setup_model_and_optimizer(pg.model_provider)
+    _canonical_init(model)
+    if bidirectional:
+        from mindspeed_b200.parallel.pipeline.chimera import sync_replica_params
+        sync_replica_params(model)
+    opt.reload_model_params()
+    ds = SyntheticGPTDataset(args.padded_vocab_size, args.seq_length, 4096, seed=args.seed)
+    nmb = args.global_batch_size // args.micro_batch_size
+    state = {"step": 0}
+
+    class It:
+        """Data keyed by (step, pipeline, micro-batch) so every layout sees the same global batch."""
+        def __iter__(self):
+            return self
+
+        def __next__(self):
+            cur = current_microbatch()
+            mb = cur["mb"] + (cur["pipe"] * (nmb // 2) if bidirectional else 0)
+            item = ds[state["step"] * nmb + mb]
+            return {k: v.unsqueeze(0) for k, v in item.items()}
+
+    class Plain:
+        def __init__(self):
+            self.i = 0
+
+        def __iter__(self):
+            return self
+
+        def __next__(self):
+            item = ds[self.i]
+            self.i += 1
+            return {k: v.unsqueeze(0) for k, v in item.items()}
+
+    it = It() if ps.get_pipeline_model_parallel_world_size() > 1 else Plain()
+    out = []
+    for _ in range(3):
+        ld, *_ = train_step(pg.forward_step, [it] * len(model) if len(model) > 1 else it, model, opt, sched)
+        state["step"] += 1
+        out.append(float(ld["lm loss"]) if "lm loss" in ld else None)
+    return out
+
+
+@pytest.mark.parametrize("world,extra,bidir", [
+    (2, ["--pipeline-model-parallel-size", "2"], False),
+    (2, ["--pipeline-model-parallel-size", "2", "--num-layers-per-virtual-pipeline-stage", "1"], False),
+    (2, ["--pipeline-model-parallel-size", "2", "--schedules-method", "dualpipev"], False),
+    (2, ["--pipeline-model-parallel-size", "2", "--schedules-method", "chimera"], True),
+    (2, ["--pipeline-model-parallel-size", "2", "--schedules-method", "dualpipe"], True),
+])
+def test_pipeline_matches_no_pipeline(world, extra, bidir):
+    ref = run_distributed(_train, 1, [], False)[0]
+    res = run_distributed(_train, world, extra, bidir)
+    have = [r for r in res if r[0] is not None]
+    # bidirectional schedules compute half of the micro-batches' losses at each end of the pipeline
+    got = [sum(v) / len(v) for v in zip(*have)] if bidir else have[0]
+    for a, b in zip(ref, got):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (ref, got)
