@@ -222,4 +222,8 @@ PFN_encodeTiled get_encode_tiled();  // defined in runtime/tensormap.cu
 // box = [box_rows, box_cols]; 128-byte swizzle when box_cols * elem_bytes == 128, none otherwise.
 int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows, uint64_t cols,
                  uint64_t ld, uint32_t box_rows, uint32_t box_cols);
+// General tiled tensor map: `rank` dims (innermost first), byte strides for dims 1..rank-1, box per dim.
+// 128-byte swizzle when the innermost box extent is 128 bytes.
+int make_tmap_nd(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes, int rank, const uint64_t* dims,
+                 const uint64_t* strides_bytes, const uint32_t* box);
 }  // namespace msb

@@ -42,4 +42,24 @@ int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int
   return 0;
 }
 
+int make_tmap_nd(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes, int rank, const uint64_t* dims,
+                 const uint64_t* strides_bytes, const uint32_t* box) {
+  PFN_encodeTiled enc = get_encode_tiled();
+  if (!enc) { msb_set_error("cuTensorMapEncodeTiled is not available from this driver"); return 1; }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) { msb_set_error("tensor map base %p is not 16-byte aligned", base); return 2; }
+  cuuint64_t gdim[5]; cuuint64_t gstr[4]; cuuint32_t bx[5]; cuuint32_t es[5];
+  for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+  for (int i = 0; i + 1 < rank; ++i) {
+    if (strides_bytes[i] % 16 != 0) { msb_set_error("tensor map stride %llu is not a multiple of 16 bytes", (unsigned long long)strides_bytes[i]); return 2; }
+    gstr[i] = strides_bytes[i];
+  }
+  const uint32_t inner = box[0] * (uint32_t)elem_bytes;
+  CUtensorMapSwizzle sw = inner == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : inner == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                          : inner == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE;
+  CUresult r = enc(out, dt, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { msb_set_error("cuTensorMapEncodeTiled (rank %d) failed (%d)", rank, (int)r); return 1; }
+  return 0;
+}
+
 }  // namespace msb
