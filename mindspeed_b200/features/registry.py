@@ -283,6 +283,8 @@ class FlashAttentionFeature(Feature):
 
     def register_args(self, parser):
         g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--attention-backend", type=str, default="auto", choices=["auto", "library", "sm100"],
+                help="sm100: hand-written tcgen05 flash attention; library: cuDNN/flash via torch; auto: the faster of the two")
         add_arg(g, "--pre-tockens", type=int, default=65536)
         add_arg(g, "--next-tockens", type=int, default=0)
         add_arg(g, "--sparse-mode", type=int, default=0, choices=[0, 1, 2, 3, 4])

@@ -66,7 +66,9 @@ class CoreAttention(nn.Module):
         elif attention_mask is not None and not self.causal:
             out = attn_ops.attention_ref(q, k, v, causal=False, softmax_scale=self.softmax_scale, mask=attention_mask)
         else:
-            backend = "sm100" if (self.config.optimization_level >= 1 and self.config.use_flash_attn) else None
+            # "auto" keeps the library kernel while it is the faster one on this shape; "sm100" forces the hand-written one
+            want = getattr(self.config, "attention_backend", "auto")
+            backend = "sm100" if (want == "sm100" and self.config.optimization_level >= 1) else None
             out = attn_ops.flash_attention(q, k, v, causal=self.causal, softmax_scale=self.softmax_scale, backend=backend)
         if self.dropout_p > 0 and self.training:
             with get_cuda_rng_tracker().fork():
