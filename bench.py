@@ -148,8 +148,11 @@ def main():
         if a.level >= 2:
             args_list += ["--use-fused-tp-comm"]
     rl = a.recompute_layers
+    if n == 1:
+        # one GPU holds the whole model: keep the master weights as (bf16 parameter + 16-bit residual) to free 16 GB for activations
+        args_list += ["--reuse-fp32-param"]
     if rl < 0:
-        rl = {1: 18}.get(n, 0)
+        rl = {1: 8}.get(n, 0)
     if rl > 0:
         args_list += ["--recompute-granularity", "full", "--recompute-method", "block", "--recompute-num-layers", str(rl)]
     args = initialize_megatron(args_list=args_list)

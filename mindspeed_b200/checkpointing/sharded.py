@@ -123,7 +123,8 @@ def optimizer_sharded_state_dict(optimizer, sharding_type: str = "fully_sharded_
                 sl = slice(lo - st.lo, hi - st.lo)
                 replica = 0 if (split or tp_rank == 0) else tp_rank
                 replica += 0 if optimizer.sharded else st.buf.dp_rank
-                for kind, src in (("exp_avg", st.m), ("exp_avg_sq", st.v), ("master", st.master if st.param16 is not None else None),
+                for kind, src in (("exp_avg", st.m), ("exp_avg_sq", st.v), ("master", st.master if (st.param16 is not None and st.master is not None) else None),
+                                  ("residual", getattr(st, "residual", None)),
                                   ("ema", st.ema)):
                     if src is None:
                         continue

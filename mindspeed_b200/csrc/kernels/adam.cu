@@ -62,6 +62,35 @@ __global__ void adam_flat_kernel(float* __restrict__ p, const G* __restrict__ g,
   }
 }
 
+// AdamW on a master weight stored as (bf16 model parameter, 16-bit residual): the fp32 master never exists in memory.
+//   stored = bits(fp32) + 0x8000 (as integers);  hi = stored >> 16 is the bf16 parameter the model uses (round-half-up of
+//   the master), lo = stored & 0xffff is the residual;  bits(fp32) = ((hi << 16) | lo) - 0x8000 recovers the master exactly.
+// reference: mindspeed/optimizer/optimizer.py:249-280 (reuse-fp32-param: int32 add/sub of 32768 and a split in halves).
+template <typename G>
+__global__ void adam_flat_reuse_kernel(__nv_bfloat16* __restrict__ hi, unsigned short* __restrict__ lo, const G* __restrict__ g,
+                                       float* __restrict__ m, float* __restrict__ v, size_t n, float lr, float beta1, float beta2,
+                                       float eps, float wd, float bc1, float bc2_sqrt, float grad_scale, int adam_w_mode,
+                                       const float* __restrict__ found_inf, const float* __restrict__ grad_scale_dev) {
+  if (found_inf && *found_inf != 0.f) return;
+  if (grad_scale_dev) grad_scale *= *grad_scale_dev;
+  const unsigned short* hi_bits = reinterpret_cast<const unsigned short*>(hi);
+  unsigned short* hi_out = reinterpret_cast<unsigned short*>(hi);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const unsigned int stored = ((unsigned int)hi_bits[i] << 16) | (unsigned int)lo[i];
+    float pf = __uint_as_float(stored - 0x8000u);
+    float gf = to_f(g[i]) * grad_scale;
+    if (!adam_w_mode) gf += wd * pf;
+    float mf = beta1 * m[i] + (1.f - beta1) * gf;
+    float vf = beta2 * v[i] + (1.f - beta2) * gf * gf;
+    const float step = (mf / bc1) / (sqrtf(vf) / bc2_sqrt + eps);
+    pf = adam_w_mode ? pf * (1.f - lr * wd) - lr * step : pf - lr * step;
+    m[i] = mf; v[i] = vf;
+    const unsigned int out = __float_as_uint(pf) + 0x8000u;
+    hi_out[i] = (unsigned short)(out >> 16);
+    lo[i] = (unsigned short)(out & 0xffffu);
+  }
+}
+
 template <typename G>
 __global__ void l2norm_sq_partial(const G* __restrict__ g, size_t n, float* __restrict__ partial) {
   __shared__ float red[32];
@@ -144,5 +173,18 @@ MSB_API int msb_scale(void* x, long long n, float scale, const float* scale_dev,
 MSB_API int msb_clip_coef(const float* norm_sq, float max_norm, float* coef, float* found_inf, float* norm_out, cudaStream_t s) {
   clip_coef_kernel<<<1, 1, 0, s>>>(norm_sq, max_norm, coef, found_inf, norm_out);
   MSB_CHECK_LAUNCH("clip_coef");
+  return 0;
+}
+
+MSB_API int msb_adam_flat_reuse(void* hi, void* lo, const void* g, float* m, float* v, long long n, float lr, float beta1,
+                                float beta2, float eps, float wd, int step, float grad_scale, int adam_w_mode, int bias_correction,
+                                const float* found_inf, const float* grad_scale_dev, int grad_dtype, cudaStream_t s) {
+  if (n == 0) return 0;
+  float bc1 = 1.f, bc2s = 1.f;
+  if (bias_correction) { bc1 = 1.f - powf(beta1, (float)step); bc2s = sqrtf(1.f - powf(beta2, (float)step)); }
+  int grid = (int)(((size_t)n + 255) / 256); if (grid > msb::num_sms() * 16) grid = msb::num_sms() * 16;
+  MSB_DISPATCH_FLOAT(grad_dtype, G, adam_flat_reuse_kernel<G><<<grid, 256, 0, s>>>((__nv_bfloat16*)hi, (unsigned short*)lo, (const G*)g, m, v,
+      (size_t)n, lr, beta1, beta2, eps, wd, bc1, bc2s, grad_scale, adam_w_mode, found_inf, grad_scale_dev));
+  MSB_CHECK_LAUNCH("adam_flat_reuse");
   return 0;
 }

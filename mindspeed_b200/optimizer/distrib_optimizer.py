@@ -39,7 +39,7 @@ class _Segment:
 
 
 class _BucketState:
-    def __init__(self, buf, bucket, sharded, use_master, ema):
+    def __init__(self, buf, bucket, sharded, use_master, ema, reuse=False):
         self.buf, self.bucket = buf, bucket
         if sharded:
             self.lo, self.hi = buf.shard_range(bucket)
@@ -49,14 +49,22 @@ class _BucketState:
         dev = buf.grad_data.device
         self.grad = buf.grad_data[self.lo:self.hi]
         self.param16 = buf.param_data[self.lo:self.hi] if buf.param_data is not None else None
-        if use_master:
+        self.residual = None
+        if use_master and reuse and self.param16.dtype == torch.bfloat16:
+            # master = (bf16 parameter, 16-bit residual): the parameter already is the rounded master, residual starts at 0x8000-offset zero
+            from ..memory.reuse_param import split_fp32
+            hi, lo = split_fp32(self.param16.float())
+            self.param16.copy_(hi)
+            self.residual = lo
+            self.master = None
+        elif use_master:
             self.master = self.param16.float()
         else:
             self.master = self.param16  # fp32 params: update in place
             self.param16 = None
         self.m = torch.zeros(n, dtype=torch.float32, device=dev)
         self.v = torch.zeros(n, dtype=torch.float32, device=dev)
-        self.ema = self.master.clone() if ema else None
+        self.ema = self.master.clone() if (ema and self.master is not None) else None
         self.segments: List[_Segment] = []
 
 
@@ -87,7 +95,8 @@ class DistributedOptimizer:
                     self._dev = buf.grad_data.device
                     use_master = buf.param_dtype != torch.float32
                     for b in buf.buckets:
-                        st = _BucketState(buf, b, self.sharded and buf.dp_size > 1, use_master, config.use_ema)
+                        st = _BucketState(buf, b, self.sharded and buf.dp_size > 1, use_master, config.use_ema,
+                                          reuse=config.reuse_fp32_param)
                         # segments: walk params in buffer order (bucket.params is reverse layer order, ascending offset)
                         cur = None
                         for p in b.params:
@@ -130,7 +139,11 @@ class DistributedOptimizer:
 
     def reload_model_params(self):
         for st in self.states + self.expert_states:
-            if st.param16 is not None:
+            if st.residual is not None:
+                from ..memory.reuse_param import split_fp32
+                hi, lo = split_fp32(st.param16.float())
+                st.residual.copy_(lo)
+            elif st.param16 is not None:
                 st.master.copy_(st.param16)
 
     def _all_states(self):
@@ -175,6 +188,13 @@ class DistributedOptimizer:
         for st in self._all_states():
             for sg in st.segments:
                 sl = slice(sg.start, sg.end)
+                if st.residual is not None:
+                    from ..memory.reuse_param import adam_flat_reuse
+                    adam_flat_reuse(st.param16[sl], st.residual[sl], st.grad[sl], st.m[sl], st.v[sl], lr * sg.lr_mult,
+                                    cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps, wd * sg.wd_mult, self.step_count, coef_host,
+                                    True, found_inf=self._found_inf if (on_gpu and coef_dev is not None) else None,
+                                    grad_scale_dev=coef_dev)
+                    continue
                 adam_ops.adam_flat(st.master[sl], st.grad[sl], st.m[sl], st.v[sl],
                                    None if st.param16 is None else st.param16[sl], lr * sg.lr_mult, cfg.adam_beta1,
                                    cfg.adam_beta2, cfg.adam_eps, wd * sg.wd_mult, self.step_count, coef_host, True,
@@ -212,7 +232,9 @@ class DistributedOptimizer:
         out = {"step": self.step_count, "param_groups": [{k: v for k, v in g.items()} for g in self.param_groups], "buckets": []}
         for st in self._all_states():
             d = {"lo": st.lo, "hi": st.hi, "exp_avg": st.m, "exp_avg_sq": st.v}
-            if st.param16 is not None:
+            if st.residual is not None:
+                d["residual"] = st.residual
+            elif st.param16 is not None:
                 d["master"] = st.master
             if st.ema is not None:
                 d["ema"] = st.ema
@@ -226,7 +248,9 @@ class DistributedOptimizer:
         for st, d in zip(self._all_states(), sd["buckets"]):
             st.m.copy_(d["exp_avg"])
             st.v.copy_(d["exp_avg_sq"])
-            if "master" in d and st.param16 is not None:
+            if "residual" in d and st.residual is not None:
+                st.residual.copy_(d["residual"])
+            if "master" in d and st.param16 is not None and st.master is not None:
                 st.master.copy_(d["master"])
             if "ema" in d and st.ema is not None:
                 st.ema.copy_(d["ema"])

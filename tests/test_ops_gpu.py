@@ -135,3 +135,22 @@ def test_fused_cross_entropy(vocab):
     (loss * w).sum().backward()
     (ref * w.view(-1)).sum().backward()
     torch.testing.assert_close(x.grad.float(), ref_in.grad, atol=5e-3, rtol=5e-2)
+
+
+def test_reuse_fp32_param_split_merge_and_adam():
+    from mindspeed_b200.memory.reuse_param import adam_flat_reuse, merge_fp32, split_fp32
+    from mindspeed_b200.ops.adam import adam_flat
+    torch.manual_seed(6)
+    n = 70001
+    p = torch.randn(n, device="cuda")
+    hi, lo = split_fp32(p)
+    assert torch.equal(merge_fp32(hi, lo), p)                       # exact round trip
+    assert (hi.float() - p).abs().max() <= p.abs().max() * 2 ** -8  # hi is the rounded bf16 of the master
+    ref = p.clone()
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    m2, v2 = torch.zeros_like(p), torch.zeros_like(p)
+    for step in range(1, 4):
+        g = torch.randn(n, device="cuda")
+        adam_flat(ref, g, m, v, None, 1e-3, 0.9, 0.95, 1e-8, 0.1, step)
+        adam_flat_reuse(hi, lo, g, m2, v2, 1e-3, 0.9, 0.95, 1e-8, 0.1, step)
+    torch.testing.assert_close(merge_fp32(hi, lo), ref, atol=1e-6, rtol=1e-5)
