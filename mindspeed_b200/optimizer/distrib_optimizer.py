@@ -67,6 +67,12 @@ class _BucketState:
         self.ema = self.master.clone() if (ema and self.master is not None) else None
         self.segments: List[_Segment] = []
 
+    def param_view(self, sl):
+        """fp32 models: the parameter buffer itself is the master."""
+        return self.buf.param_data[self.lo:self.hi][sl]
+
+    master_fp32 = param_view
+
 
 def _default_wd_mult(name, p):
     no_wd = name.endswith(".bias") or p.dim() == 1
@@ -265,6 +271,14 @@ def get_megatron_optimizer(config: OptimizerConfig, model_chunks, no_weight_deca
     if config.optimizer == "muon":
         from .muon import build_muon_optimizer
         return build_muon_optimizer(config, model_chunks)
+    try:
+        from ..training.global_vars import get_args
+        virt = getattr(get_args(), "virtual_optimizer", None)
+    except RuntimeError:
+        virt = None
+    if virt:
+        from .virtual_adam import VirtualDistributedOptimizer
+        return VirtualDistributedOptimizer(config, model_chunks, virt, no_weight_decay_cond, scale_lr_cond, lr_mult)
     if config.swap_optimizer:
         from .swap_optimizer import SwapDistributedOptimizer
         return SwapDistributedOptimizer(config, model_chunks, no_weight_decay_cond, scale_lr_cond, lr_mult)
