@@ -66,3 +66,59 @@ def test_cp_attention_matches_full(algo, world, nq, nkv, causal, extra):
     for r in run_distributed(_run, world, algo, nq, nkv, causal, extra):
         for key, err in r.items():
             assert err < 2e-4, (algo, key, err, r)
+
+
+def _run_adaptive(rank, world):
+    import torch.distributed as dist
+    from mindspeed_b200.ops.attention import attention_ref
+    from mindspeed_b200.parallel import parallel_state as ps
+    from mindspeed_b200.parallel.context_parallel.adaptive import adaptive_attention
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ps.initialize_model_parallel(context_parallel_size=world)
+    s, b, n, d = 16 * world, 1, 2, 8
+    q, k, v, w = _full(5, s, b, n, n, d)
+    g = torch.Generator().manual_seed(11)
+    # band + a few global tokens, never fully masked rows
+    idx = torch.arange(s)
+    mask = ((idx.view(-1, 1) - idx.view(1, -1)).abs() > 12) & (idx.view(1, -1) > 1)
+    qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
+    ref = attention_ref(qf, kf, vf, causal=False, mask=mask.view(1, 1, s, s))
+    (ref * w).sum().backward()
+    per = s // world
+    sl = lambda t: t[rank * per:(rank + 1) * per].clone()
+    ql, kl, vl = (sl(t).requires_grad_(True) for t in (q, k, v))
+    out = adaptive_attention(ql, kl, vl, None, mask)
+    (out * sl(w)).sum().backward()
+    res = {"out": (out.detach() - sl(ref.detach())).abs().max().item(), "dq": (ql.grad - sl(qf.grad)).abs().max().item(),
+           "dk": (kl.grad - sl(kf.grad)).abs().max().item(), "dv": (vl.grad - sl(vf.grad)).abs().max().item()}
+    ps.destroy_model_parallel()
+    dist.destroy_process_group()
+    return res
+
+
+def test_adaptive_cp_matches_masked_attention():
+    for r in run_distributed(_run_adaptive, 4):
+        for key, err in r.items():
+            assert err < 2e-4, (key, err, r)
+
+
+def test_adaptive_cp_host_algorithms():
+    from mindspeed_b200.parallel.context_parallel.adaptive import coarsen_mask, schedule_rounds, search_kmeans
+    S, blk = 64, 8
+    idx = torch.arange(S)
+    visible = (idx.view(-1, 1) - idx.view(1, -1)).abs() < 10
+    c = coarsen_mask(visible, blk)
+    ref = visible.view(8, blk, 8, blk).any(dim=3).any(dim=1)
+    assert torch.equal(c.bool(), ref)
+    rounds, ro = schedule_rounds(c, comm_limit=1)
+    need = c.bool() & ~torch.eye(8, dtype=torch.bool)
+    assert ((ro >= 0) == need).all()
+    for rd in range(rounds):                      # per round: each rank receives <= 1 and sends <= 1
+        m = ro == rd
+        assert m.sum(1).max() <= 1 and m.sum(0).max() <= 1
+    # two interleaved document families: k-means should separate them
+    fam = torch.arange(8) % 2
+    c2 = (fam.view(-1, 1) == fam.view(1, -1)).to(torch.uint8)
+    order = search_kmeans(c2, 2)
+    assert sorted(order) == list(range(8))
+    assert len({int(fam[i]) for i in order[:4]}) == 1 and len({int(fam[i]) for i in order[4:]}) == 1
