@@ -52,10 +52,8 @@ class _BucketState:
         self.residual = None
         if use_master and reuse and self.param16.dtype == torch.bfloat16:
             # master = (bf16 parameter, 16-bit residual): the parameter already is the rounded master, residual starts at 0x8000-offset zero
-            from ..memory.reuse_param import split_fp32
-            hi, lo = split_fp32(self.param16.float())
-            self.param16.copy_(hi)
-            self.residual = lo
+            # a bf16 value widened to fp32 has zero low bits, so its stored form is (same bf16, 0x8000): no temporaries needed
+            self.residual = torch.full((n,), -32768, dtype=torch.int16, device=dev)
             self.master = None
         elif use_master:
             self.master = self.param16.float()
@@ -146,9 +144,7 @@ class DistributedOptimizer:
     def reload_model_params(self):
         for st in self.states + self.expert_states:
             if st.residual is not None:
-                from ..memory.reuse_param import split_fp32
-                hi, lo = split_fp32(st.param16.float())
-                st.residual.copy_(lo)
+                st.residual.fill_(-32768)
             elif st.param16 is not None:
                 st.master.copy_(st.param16)
 
