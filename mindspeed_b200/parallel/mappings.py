@@ -274,13 +274,25 @@ def all_to_all(group, x, output_split_sizes=None, input_split_sizes=None):
 
 
 # ---- uneven variants (unaligned TP / MoE with TP) -----------------------------------------
+def all_gather_uneven(x, group, sizes: List[int], dim: int = 0):
+    """All-gather of shards whose extent along ``dim`` differs per rank: pad to the largest, gather, trim."""
+    mx = max(sizes)
+    x = x.contiguous()
+    if x.shape[dim] < mx:
+        pad_shape = list(x.shape)
+        pad_shape[dim] = mx - x.shape[dim]
+        x = torch.cat((x, x.new_zeros(pad_shape)), dim=dim)
+    parts = [torch.empty_like(x) for _ in sizes]
+    dist.all_gather(parts, x, group=group)
+    return torch.cat([p.narrow(dim, 0, s) for p, s in zip(parts, sizes)], dim=dim)
+
+
+
 class _GatherUneven(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group, sizes):
         ctx.group, ctx.sizes = group, list(sizes)
-        parts = [x.new_empty([s] + list(x.shape[1:])) for s in sizes]
-        dist.all_gather(parts, x.contiguous(), group=group)
-        return torch.cat(parts, dim=0)
+        return all_gather_uneven(x, group, sizes, 0)
 
     @staticmethod
     def backward(ctx, g):
@@ -303,9 +315,7 @@ class _ReduceScatterUneven(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g):
-        parts = [g.new_empty([s] + list(g.shape[1:])) for s in ctx.sizes]
-        dist.all_gather(parts, g.contiguous(), group=ctx.group)
-        return torch.cat(parts, dim=0), None, None
+        return all_gather_uneven(g, ctx.group, ctx.sizes, 0), None, None
 
 
 def gather_uneven_first_dim(x, group, sizes: List[int]):
