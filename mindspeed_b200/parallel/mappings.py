@@ -233,7 +233,7 @@ class _AllToAll(torch.autograd.Function):
 
 
 def _tp(group):
-    return ps.get_tensor_model_parallel_group() if group is None else group
+    return ps.get_tensor_model_parallel_group(check_initialized=False) if group is None else group
 
 
 def copy_to_tensor_model_parallel_region(x, group=None):

@@ -154,3 +154,36 @@ def test_reuse_fp32_param_split_merge_and_adam():
         adam_flat(ref, g, m, v, None, 1e-3, 0.9, 0.95, 1e-8, 0.1, step)
         adam_flat_reuse(hi, lo, g, m2, v2, 1e-3, 0.9, 0.95, 1e-8, 0.1, step)
     torch.testing.assert_close(merge_fp32(hi, lo), ref, atol=1e-6, rtol=1e-5)
+
+
+def test_scaled_masked_softmax_and_ring_update_and_quant():
+    from mindspeed_b200.ops import misc
+    from mindspeed_b200.ops import quant as Q
+    torch.manual_seed(7)
+    x = torch.randn(2, 3, 64, 96, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    mask = torch.rand(2, 1, 64, 96, device="cuda") > 0.7
+    mask[..., 0] = False
+    y = misc.scaled_masked_softmax(x, mask, 0.5)
+    xr = x.detach().float().requires_grad_(True)
+    yr = misc.scaled_masked_softmax_ref(xr, mask, 0.5)
+    torch.testing.assert_close(y.float(), yr.float(), atol=1e-2, rtol=1e-2)
+    g = torch.randn_like(y)
+    y.backward(g); yr.backward(g.float())
+    torch.testing.assert_close(x.grad.float(), xr.grad, atol=2e-2, rtol=5e-2)
+    yc = misc.scaled_masked_softmax(x.detach(), None, 1.0, causal=True)
+    torch.testing.assert_close(yc.float(), misc.scaled_masked_softmax_ref(x.detach(), None, 1.0, True).float(), atol=1e-2, rtol=1e-2)
+    rows, d = 1000, 128
+    po, co = torch.randn(rows, d, device="cuda", dtype=torch.bfloat16), torch.randn(rows, d, device="cuda", dtype=torch.bfloat16)
+    pm, cm = torch.randn(rows, device="cuda"), torch.randn(rows, device="cuda")
+    ps_, cs = torch.rand(rows, device="cuda") + 0.1, torch.rand(rows, device="cuda") + 0.1
+    o, m, l = misc.ring_attention_update(po, pm, ps_, co, cm, cs)
+    ro, rm, rl = misc.ring_attention_update_ref(po, pm, ps_, co, cm, cs)
+    torch.testing.assert_close(o.float(), ro.float(), atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(m, rm); torch.testing.assert_close(l, rl, rtol=1e-4, atol=1e-5)
+    w = torch.randn(300, 512, device="cuda", dtype=torch.bfloat16) * 3
+    q, s = misc.quant_1x128(w)
+    qr, sr = Q.quant_1x128(w)
+    torch.testing.assert_close(s, sr, rtol=1e-5, atol=0)
+    assert (q.float() - qr.float()).abs().max() <= 32          # at most one fp8 step apart (rounding of the division)
+    h, yn = misc.add_rmsnorm(po, co, torch.ones(d, device="cuda", dtype=torch.bfloat16))
+    torch.testing.assert_close(h, po + co)
