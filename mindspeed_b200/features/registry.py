@@ -145,6 +145,8 @@ class FusedTPCommFeature(Feature):
     def register_args(self, parser):
         g = parser.add_argument_group(title=self.feature_name)
         add_arg(g, "--use-ascend-mc2", "--use-fused-tp-comm", dest="use_ascend_mc2", action="store_true")
+        add_arg(g, "--tp-recompute-all-gather", action="store_true",
+                help="re-gather the sequence-parallel input in backward instead of keeping the gathered copy from forward")
 
     def validate_args(self, args):
         self.incompatible_check(args, "use_ascend_coc")
@@ -154,6 +156,8 @@ class FusedTPCommFeature(Feature):
 
     def configure(self, manager, args):
         manager.set_slot("tp_comm_ops", "fused", owner=self.feature_name)
+        from ..parallel.layers import set_keep_gathered_input
+        set_keep_gathered_input(not args.tp_recompute_all_gather)
 
 
 class ChunkedTPCommFeature(Feature):

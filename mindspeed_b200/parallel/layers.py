@@ -90,16 +90,35 @@ def _init_sharded(weight, full_rows, full_cols, partition_dim, init_method, rank
         weight.copy_(torch.cat(mine, dim=partition_dim).to(params_dtype))
 
 
+# Keep the all-gathered input of sequence-parallel column linears for backward (memory for communication): the
+# reference's ``all_gather_recomputation_enabled = False`` setting (coc_feature/min_comm_cfg.py:44-54).
+_KEEP_GATHERED = {"on": False}
+
+
+def set_keep_gathered_input(flag: bool):
+    _KEEP_GATHERED["on"] = bool(flag)
+
+
 class _ColumnLinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, group, sequence_parallel, allreduce_dgrad, grad_accum_fusion, wgrad_deferral):
         ops = get_ops()
         ctx.group, ctx.sp, ctx.allreduce_dgrad = group, sequence_parallel, allreduce_dgrad
         ctx.fusion, ctx.defer, ctx.use_bias = grad_accum_fusion, wgrad_deferral, bias is not None
-        ctx.save_for_backward(x, weight)
+        keep = bool(sequence_parallel and _KEEP_GATHERED["on"] and ctx.needs_input_grad[1])
+        ctx.kept_total = keep
         if sequence_parallel:
-            y, _ = ops.allgather_matmul(x, weight, group, nt=True, need_gathered=False)
+            y, total = ops.allgather_matmul(x, weight, group, nt=True, need_gathered=keep)
+            if keep:
+                # the gathered activation is a by-product of the fused kernel: keeping it (one local copy out of the
+                # recycled symmetric buffer) removes the all-gather that backward would otherwise redo for dW
+                total = total.clone() if getattr(ops, "gathered_is_view", False) else total
+                ctx.save_for_backward(total, weight)
+            else:
+                ctx.save_for_backward(x, weight)
         else:
+            ctx.save_for_backward(x, weight)
+        if not sequence_parallel:
             y = ops.matmul(x, weight, nt=True)
         if bias is not None:
             y = y + bias
@@ -113,7 +132,7 @@ class _ColumnLinearFn(torch.autograd.Function):
         db = dy.reshape(-1, dy.shape[-1]).sum(0) if ctx.use_bias else None
         need_wgrad = weight.requires_grad
         total, ag_handle = x, None
-        if ctx.sp and need_wgrad and not ctx.defer:
+        if ctx.sp and need_wgrad and not ctx.defer and not ctx.kept_total:
             total, ag_handle = M.all_gather_first_dim(x, ctx.group, async_op=True)
         if ctx.sp:
             dx = ops.matmul_reduce_scatter(dy, weight, ctx.group, nt=False)
@@ -124,7 +143,7 @@ class _ColumnLinearFn(torch.autograd.Function):
         dw = None
         if need_wgrad:
             if ctx.defer and WeightGradStore.enabled():
-                WeightGradStore.put(x, dy, weight, ctx.sp, ctx.group, ctx.fusion)
+                WeightGradStore.put(x, dy, weight, ctx.sp and not ctx.kept_total, ctx.group, ctx.fusion)
             else:
                 if ag_handle is not None:
                     ag_handle.wait()
