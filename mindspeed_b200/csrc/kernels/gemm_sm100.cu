@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(192, 1) gemm_sm100_kernel(const __grid_constan
   const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
-  constexpr uint32_t TMEM_COLS = 2 * BN;  // 256 or 512: power of two
+  constexpr uint32_t TMEM_COLS = (BN <= 128) ? 256u : 512u;  // power of two >= 2 * BN
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NSTAGE; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -221,10 +221,15 @@ __global__ void __launch_bounds__(192, 1) gemm_sm100_kernel(const __grid_constan
         const bool row_ok = row < p.M;
         const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_row + (uint32_t)c, r);
+        for (int c2 = 0; c2 < BN; c2 += 64) {
+          uint32_t rr[2][32];
+          tmem_ld_32x32(t_row + (uint32_t)c2, rr[0]);          // two loads in flight per wait
+          tmem_ld_32x32(t_row + (uint32_t)(c2 + 32), rr[1]);
           tmem_ld_wait();
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+          uint32_t* r = rr[hh];
+          const int c = c2 + hh * 32;
           const int col0 = n_blk * BN + c;
           if (row_ok && col0 < p.N) {
             if (EPI == EPI_BF16) {
@@ -272,6 +277,7 @@ __global__ void __launch_bounds__(192, 1) gemm_sm100_kernel(const __grid_constan
             }
           }
         }
+          }
         tc_fence_before();
         mbar_arrive(tempty_bar(acc));
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
@@ -382,7 +388,7 @@ __global__ void __launch_bounds__(320, 1) gemm_comm_sm100_kernel(const __grid_co
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
   const int tiles_per_rank = cp.rows_per_rank / BM;
-  constexpr uint32_t TMEM_COLS = 2 * BN;
+  constexpr uint32_t TMEM_COLS = (BN <= 128) ? 256u : 512u;
   // m-major tile order with rotation: t -> (m, n)
   auto tile_mn = [&](int t, int& m, int& n) { m = ((t / num_n) + p.m_tile_rot) % num_m; n = t % num_n; };
 
@@ -698,15 +704,18 @@ int launch_epi(const GemmParams& p, int epi, int a_mn, int b_mn, int grid, cudaS
 }
 
 int pick_bn(int M, int N, int sms) {
-  // fewer, larger tiles unless the last wave would be mostly idle
-  auto eff = [&](int bn) {
-    long long tiles = (long long)((M + BM - 1) / BM) * ((N + bn - 1) / bn);
-    long long waves = (tiles + sms - 1) / sms;
-    return (double)tiles / (double)(waves * sms);
-  };
+  // modelled time = waves * (tile width + fixed per-tile overhead); candidates 256 / 192 / 128
   if (N <= 128) return 128;
-  double e256 = eff(256), e128 = eff(128);
-  return (e128 > e256 * 1.12) ? 128 : 256;
+  const int cands[3] = {256, 192, 128};
+  int best = 256; double best_t = 1e30;
+  for (int i = 0; i < 3; ++i) {
+    const int bn = cands[i];
+    const long long tiles = (long long)((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+    const long long waves = (tiles + sms - 1) / sms;
+    const double t = (double)waves * (bn + 40.0);
+    if (t < best_t * 0.97) { best_t = t; best = bn; }
+  }
+  return best;
 }
 
 }  // namespace
@@ -776,6 +785,7 @@ MSB_API int msb_gemm_bf16_ex(const MsbGemmArgs* a, cudaStream_t s) {
   int grid = (int)(tiles < sms ? tiles : sms);
   if (a->max_ctas > 0 && grid > a->max_ctas) grid = a->max_ctas;
   if (bn == 256) return launch_epi<256, 4>(p, a->epilogue, a->a_mn_major, a->b_mn_major, grid, s);
+  if (bn == 192) return launch_epi<192, 5>(p, a->epilogue, a->a_mn_major, a->b_mn_major, grid, s);
   return launch_epi<128, 6>(p, a->epilogue, a->a_mn_major, a->b_mn_major, grid, s);
 }
 
@@ -860,6 +870,7 @@ MSB_API int msb_gemm_allgather(const MsbCommArgs* a, cudaStream_t s) {
   if (cudaMemsetAsync(a->ready, 0, sizeof(unsigned int) * (a->M / BM), s) != cudaSuccess) { msb_set_error("gemm_allgather: memset failed"); return 1; }
   const int grid = msb::num_sms();
   if (bn == 256) return a->b_mn_major ? launch_comm_variant<256, 4, MODE_AG, true>(cp, grid, s) : launch_comm_variant<256, 4, MODE_AG, false>(cp, grid, s);
+  if (bn == 192) return a->b_mn_major ? launch_comm_variant<192, 5, MODE_AG, true>(cp, grid, s) : launch_comm_variant<192, 5, MODE_AG, false>(cp, grid, s);
   return a->b_mn_major ? launch_comm_variant<128, 6, MODE_AG, true>(cp, grid, s) : launch_comm_variant<128, 6, MODE_AG, false>(cp, grid, s);
 }
 
@@ -875,6 +886,7 @@ MSB_API int msb_gemm_reduce_scatter(const MsbCommArgs* a, cudaStream_t s) {
   const int sms = msb::num_sms();
   const int grid = (int)(tiles < sms ? tiles : sms);
   if (bn == 256) return a->b_mn_major ? launch_comm_variant<256, 4, MODE_RS, true>(cp, grid, s) : launch_comm_variant<256, 4, MODE_RS, false>(cp, grid, s);
+  if (bn == 192) return a->b_mn_major ? launch_comm_variant<192, 5, MODE_RS, true>(cp, grid, s) : launch_comm_variant<192, 5, MODE_RS, false>(cp, grid, s);
   return a->b_mn_major ? launch_comm_variant<128, 6, MODE_RS, true>(cp, grid, s) : launch_comm_variant<128, 6, MODE_RS, false>(cp, grid, s);
 }
 
