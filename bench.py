@@ -202,7 +202,9 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
+    h0 = time.perf_counter()
     run(a.steps, dev_iter, False)
+    host_enqueue_ms = (time.perf_counter() - h0) * 1e3     # host time to queue the steps; ~ device time means launch-bound
     e1.record()
     barrier()
     launches = loader.launch_count()
@@ -241,7 +243,7 @@ def main():
                           "micro_batch": args.micro_batch_size, "parallelism": f"tp{n}" + ("+sp" if n > 1 else "") + "+distopt",
                           "optimization_level": a.level, "recompute_layers": rl,
                           "l2": "per-step working set (>= 2 GB of weights per GPU) far exceeds the 126 MB L2"},
-               "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "impl": "ours"}
+               "clocks": clocks, "e2e": e2e, "host_enqueue_ms_per_step": host_enqueue_ms / a.steps, "gpu_launches": int(launches), "impl": "ours"}
         print(json.dumps(out))
     if world > 1:
         dist.barrier()

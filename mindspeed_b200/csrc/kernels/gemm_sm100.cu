@@ -389,8 +389,9 @@ __global__ void __launch_bounds__(320, 1) gemm_comm_sm100_kernel(const __grid_co
   const int num_kb = (p.K + BK - 1) / BK;
   const int tiles_per_rank = cp.rows_per_rank / BM;
   constexpr uint32_t TMEM_COLS = (BN <= 128) ? 256u : 512u;
-  // m-major tile order with rotation: t -> (m, n)
-  auto tile_mn = [&](int t, int& m, int& n) { m = ((t / num_n) + p.m_tile_rot) % num_m; n = t % num_n; };
+  // tile order: groups of `group_m` m-tiles (inside a group n-major, so concurrently running CTAs share both A and B
+  // tiles in L2), groups visited in rotated m order; group_m divides the per-rank slab, so a group never straddles ranks
+  auto tile_mn = [&](int t, int& m, int& n) { tile_coords(t, num_m, num_n, p.group_m, p.m_tile_rot, m, n); };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NSTAGE; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -496,26 +497,31 @@ __global__ void __launch_bounds__(320, 1) gemm_comm_sm100_kernel(const __grid_co
         const bool row_ok = row < p.M;
         const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_row + (uint32_t)c, r);
+        for (int c2 = 0; c2 < BN; c2 += 64) {
+          uint32_t rr[2][32];
+          tmem_ld_32x32(t_row + (uint32_t)c2, rr[0]);          // two loads in flight per wait
+          tmem_ld_32x32(t_row + (uint32_t)(c2 + 32), rr[1]);
           tmem_ld_wait();
-          const int col0 = n_blk * BN + c;
-          if (row_ok && col0 < p.N) {
-            __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D[0]) + (long long)row * p.ldd + col0;
-            if (col0 + 32 <= p.N) {
 #pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                uint32_t pk[4];
+          for (int hh = 0; hh < 2; ++hh) {
+            uint32_t* r = rr[hh];
+            const int col0 = n_blk * BN + c2 + hh * 32;
+            if (row_ok && col0 < p.N) {
+              __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D[0]) + (long long)row * p.ldd + col0;
+              if (col0 + 32 <= p.N) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
-                  pk[j] = *reinterpret_cast<uint32_t*>(&h);
+                for (int v = 0; v < 4; ++v) {
+                  uint32_t pk[4];
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+                    pk[j] = *reinterpret_cast<uint32_t*>(&h);
+                  }
+                  *reinterpret_cast<uint4*>(drow + v * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                 }
-                *reinterpret_cast<uint4*>(drow + v * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              } else {
+                for (int j = 0; j < 32 && col0 + j < p.N; ++j) drow[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
               }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j) drow[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
             }
           }
         }
@@ -541,12 +547,20 @@ __global__ void __launch_bounds__(320, 1) gemm_comm_sm100_kernel(const __grid_co
           const uint4* from = cp.ag_peer[src] + base;
           uint4* to = cp.ag_local + base;
           size_t i = ct;
-          for (; i + 7 * 128 < piece_v4; i += 8 * 128) {
-            uint4 v[8];
+          // 16 x 16 B per thread in flight: 32 KB per CTA, ~4.7 MB per GPU, about twice the NVLink bandwidth-delay product
+          for (; i + 15 * 128 < piece_v4; i += 16 * 128) {
+            uint4 v[16];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = ld_cg_v4(from + i + j * 128);
+            for (int j = 0; j < 16; ++j) v[j] = ld_cg_v4(from + i + j * 128);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) to[i + j * 128] = v[j];
+            for (int j = 0; j < 16; ++j) to[i + j * 128] = v[j];
+          }
+          for (; i + 3 * 128 < piece_v4; i += 4 * 128) {
+            uint4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = ld_cg_v4(from + i + j * 128);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) to[i + j * 128] = v[j];
           }
           for (; i < piece_v4; i += 128) to[i] = ld_cg_v4(from + i);
           __threadfence();
@@ -569,15 +583,15 @@ __global__ void __launch_bounds__(320, 1) gemm_comm_sm100_kernel(const __grid_co
             const uint4* src_base = cp.rs_partial + (long long)(m_blk * BM) * ld_v4 + n0 / 8;
             // owner's staging: [src rank][rows_per_rank][N]
             uint4* dst_base = cp.rs_stage_peer[owner] + ((long long)p.rank * cp.rows_per_rank + (m_blk % tiles_per_rank) * BM) * ld_v4 + n0 / 8;
-            for (int r0 = cwarp; r0 < BM; r0 += 4 * 4) {
-              uint4 v[4];
+            for (int r0 = cwarp; r0 < BM; r0 += 4 * 8) {
+              uint4 v[8];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
+              for (int j = 0; j < 8; ++j) {
                 const int r = r0 + 4 * j;
                 if (lane < v4_per_row && r < BM) v[j] = ld_cg_v4(src_base + (long long)r * ld_v4 + lane);
               }
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
+              for (int j = 0; j < 8; ++j) {
                 const int r = r0 + 4 * j;
                 if (lane < v4_per_row && r < BM) dst_base[(long long)r * ld_v4 + lane] = v[j];
               }
@@ -837,6 +851,8 @@ static int fill_comm(CommParams& cp, const MsbCommArgs* a, int mode, int bn) {
   for (int i = 0; i < MAX_SRC; ++i) p.flag_peer[i] = a->flag_peer[i];
   cp.rows_per_rank = a->M / a->world;
   const int tiles_per_rank = cp.rows_per_rank / BM;
+  p.group_m = 8;
+  while (tiles_per_rank % p.group_m != 0) p.group_m >>= 1;   // 8, 4, 2 or 1: a divisor of the per-rank slab
   if (mode == MODE_AG) {
     p.m_tile_rot = a->rank * tiles_per_rank;
     for (int i = 0; i < a->world; ++i) cp.ag_peer[i] = reinterpret_cast<const uint4*>(a->peer_buf[i]);

@@ -9,8 +9,9 @@ For each tensor-parallel linear of a Llama-3-8B-shape layer at TP = N it times, 
   library : NCCL all_gather_into_tensor + cuBLAS GEMM, or cuBLAS GEMM + NCCL reduce_scatter_tensor
 
 with CUDA events on the launching stream (3 warm-up launches, a 256 MB buffer rewritten between timed launches so
-that operands start outside L2, a barrier before each timed launch) and reports the maximum over ranks of the
-per-rank median.  The roofline for a fused kernel is the slower of
+that operands start outside L2, a barrier before each timed launch, and a short device-side delay in front of the
+first event so that the measured interval is device execution, not host launch latency) and reports the maximum
+over ranks of the per-rank median.  The roofline for a fused kernel is the slower of
 
   FLOPs / measured cuBLAS bf16 peak           and           bytes that must cross NVLink per GPU / 770 GB/s
 
@@ -42,6 +43,7 @@ def _timed(fn, group, flush_buf, L, loader, iters=8, warmup=3):
         dist.barrier(group)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(1_000_000)   # ~0.5 ms of device idle so the host has queued everything before e0 is reached
         e0.record()
         fn()
         e1.record()

@@ -109,8 +109,9 @@ class SymmetricHeap:
 _HEAPS: Dict[int, SymmetricHeap] = {}
 
 
-def get_heap(group, nbytes: int) -> SymmetricHeap:
-    key = id(group)
+def get_heap(group, nbytes: int, tag: str = "tp") -> SymmetricHeap:
+    """One heap per (group, tag): kernel families with their own flag words and buffers keep separate heaps."""
+    key = (id(group), tag)
     h = _HEAPS.get(key)
     if h is None:
         h = SymmetricHeap(group, nbytes)
