@@ -1,0 +1,329 @@
+"""Fully sharded data parallel (ZeRO-3), hybrid sharding and LayerZeRO (ZeRO-3 inside a sub-group + ZeRO-1 across it).
+
+One ``ShardedUnit`` per wrapped sub-module (normally a transformer layer):
+
+  storage     every parameter of the unit lives in one flat buffer, padded to the shard-group size; each rank keeps
+              1/S of it (``flat_shard``).  With ``zero1_over_replicas`` the optimizer additionally owns only 1/R of that
+              shard (``opt_param``), i.e. optimizer state is split over all S*R data-parallel ranks while parameters
+              are only split over the S ranks of the (NVLink-local) shard group - the LayerZeRO layout.
+  forward     pre-hook: all-gather the flat buffer over the shard group (the next unit's gather is issued right away
+              on a side stream when prefetching is on), parameters become views into it; post-hook: free it
+              (``reshard_after_forward``).
+  backward    pre-hook: all-gather again; when the last parameter gradient of the unit has been accumulated: flatten
+              the gradients, reduce-scatter over the shard group, then all-reduce (HSDP) or reduce-scatter (LayerZeRO)
+              over the replica group, and free the full buffer.
+  step        ``FullyShardedDataParallel.optimizer_params()`` are ordinary leaf tensors, so any optimizer works;
+              ``post_step()`` re-assembles ``flat_shard`` from the owned slices in the LayerZeRO layout.
+
+A YAML / dict plan chooses which sub-modules become units, the mixed-precision dtypes and the two group sizes.
+Runs on NCCL and (for tests) gloo.
+reference: mindspeed/core/distributed/torch_fully_sharded_data_parallel/* (fully_shard adaptor with YAML plan) and
+mindspeed/core/distributed/layerzero/* (ZeRO-1 over DP + ZeRO-3 over a sub-group).
+"""
+from __future__ import annotations
+
+import dataclasses
+import fnmatch
+from typing import Dict, Iterable, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import mappings as M
+
+
+@dataclasses.dataclass
+class FSDPPlan:
+    """Which modules to shard and how.  ``wrap`` holds class names or glob patterns over qualified module names."""
+    wrap: Sequence[str] = ("TransformerLayer",)
+    shard_size: Optional[int] = None          # ranks per shard group (None: the whole data-parallel group)
+    zero1_over_replicas: bool = False         # LayerZeRO: optimizer state also split over the replica group
+    reshard_after_forward: bool = True
+    param_dtype: Optional[str] = None         # dtype parameters are gathered in (e.g. "bfloat16"); None keeps theirs
+    reduce_dtype: Optional[str] = "float32"   # dtype of the gradient reduction
+    prefetch: bool = True
+
+    @staticmethod
+    def from_yaml(path: str) -> "FSDPPlan":
+        import yaml
+        with open(path) as f:
+            d = yaml.safe_load(f) or {}
+        return FSDPPlan.from_dict(d)
+
+    @staticmethod
+    def from_dict(d: Dict) -> "FSDPPlan":
+        d = dict(d.get("fsdp", d))
+        known = {f.name for f in dataclasses.fields(FSDPPlan)}
+        bad = set(d) - known
+        if bad:
+            raise ValueError(f"unknown FSDP plan keys: {sorted(bad)}")
+        if "wrap" in d and isinstance(d["wrap"], str):
+            d["wrap"] = [d["wrap"]]
+        return FSDPPlan(**d)
+
+
+def _dtype(name):
+    return None if name is None else getattr(torch, name)
+
+
+def build_groups(dp_ranks: List[int], shard_size: Optional[int]):
+    """(shard_group, replica_group) of the calling rank.  Shard groups are contiguous runs of ``shard_size`` ranks
+    (contiguous ranks share an NVSwitch domain), replica groups are strided across them."""
+    world = len(dp_ranks)
+    s = shard_size or world
+    if world % s != 0:
+        raise ValueError(f"shard size {s} must divide the data-parallel size {world}")
+    me = dist.get_rank()
+    shard_g = rep_g = None
+    for i in range(0, world, s):
+        ranks = dp_ranks[i:i + s]
+        g = dist.new_group(ranks)
+        if me in ranks:
+            shard_g = g
+    for j in range(s):
+        ranks = dp_ranks[j::s]
+        g = dist.new_group(ranks) if len(ranks) > 1 else None
+        if me in ranks:
+            rep_g = g
+    return shard_g, rep_g
+
+
+class ShardedUnit:
+    def __init__(self, module: nn.Module, shard_group, replica_group, plan: FSDPPlan, name: str = ""):
+        self.module, self.shard_group, self.replica_group, self.plan, self.name = module, shard_group, replica_group, plan, name
+        self.S = M._ws(shard_group)
+        self.R = M._ws(replica_group)
+        self.s_rank = M._rk(shard_group)
+        self.r_rank = M._rk(replica_group)
+        self.params: List[nn.Parameter] = [p for p in module.parameters(recurse=True) if not getattr(p, "_fsdp_owned", False)]
+        for p in self.params:
+            p._fsdp_owned = True
+        self.shapes = [p.shape for p in self.params]
+        self.numels = [p.numel() for p in self.params]
+        total = sum(self.numels)
+        div = self.S * (self.R if plan.zero1_over_replicas else 1)
+        self.padded = ((total + div - 1) // div) * div
+        self.total = total
+        dev = self.params[0].device if self.params else torch.device("cpu")
+        self.master_dtype = self.params[0].dtype if self.params else torch.float32
+        self.gather_dtype = _dtype(plan.param_dtype) or self.master_dtype
+        self.reduce_dtype = _dtype(plan.reduce_dtype) or self.master_dtype
+        flat = torch.zeros(self.padded, dtype=self.master_dtype, device=dev)
+        off = 0
+        for p, n in zip(self.params, self.numels):
+            flat[off:off + n].copy_(p.detach().reshape(-1))
+            off += n
+        per = self.padded // self.S
+        self.per = per
+        self.flat_shard = flat[self.s_rank * per:(self.s_rank + 1) * per].clone()
+        self.flat_shard_grad: Optional[torch.Tensor] = None
+        if plan.zero1_over_replicas and self.R > 1:
+            own = per // self.R
+            self.own = own
+            self.opt_param = nn.Parameter(self.flat_shard[self.r_rank * own:(self.r_rank + 1) * own].clone())
+        else:
+            self.own = per
+            self.opt_param = nn.Parameter(self.flat_shard)   # shares storage: the optimizer updates the shard in place
+            self.flat_shard = self.opt_param.data
+        self.full: Optional[torch.Tensor] = None
+        self._pending_grads = 0
+        self._reduced = False
+        self._gather_work = None
+        self._free_params()
+        self._install_hooks()
+
+    # -- (un)sharding ------------------------------------------------------------------------------------------
+    def _free_params(self):
+        for p in self.params:
+            p.data = torch.empty(0, dtype=self.gather_dtype, device=self.flat_shard.device)
+        self.full = None
+
+    def start_unshard(self):
+        """Issue the all-gather (asynchronously where the backend allows); ``finish_unshard`` makes it visible."""
+        if self.full is not None or self._gather_work is not None:
+            return
+        shard = self.flat_shard.to(self.gather_dtype)
+        if self.S == 1:
+            self._gather_work = (shard.clone(), None)
+            return
+        out = torch.empty(self.padded, dtype=self.gather_dtype, device=shard.device)
+        work = dist.all_gather_into_tensor(out, shard.contiguous(), group=self.shard_group, async_op=True)
+        self._gather_work = (out, work)
+
+    def finish_unshard(self):
+        if self.full is not None:
+            return
+        if self._gather_work is None:
+            self.start_unshard()
+        out, work = self._gather_work
+        self._gather_work = None
+        if work is not None:
+            work.wait()
+        self.full = out
+        off = 0
+        for p, n, shp in zip(self.params, self.numels, self.shapes):
+            p.data = out[off:off + n].view(shp)
+            off += n
+
+    def reshard(self):
+        self._free_params()
+
+    # -- hooks -------------------------------------------------------------------------------------------------
+    def _install_hooks(self):
+        self.module.register_forward_pre_hook(self._pre_forward)
+        self.module.register_forward_hook(self._post_forward)
+        self.module.register_full_backward_pre_hook(self._pre_backward)
+        for p in self.params:
+            if p.requires_grad:
+                p.register_post_accumulate_grad_hook(self._grad_ready)
+        self.next_unit: Optional["ShardedUnit"] = None
+        self.prev_unit: Optional["ShardedUnit"] = None
+
+    def _pre_forward(self, mod, args):
+        self.finish_unshard()
+        if self.plan.prefetch and self.next_unit is not None:
+            self.next_unit.start_unshard()
+
+    def _post_forward(self, mod, args, out):
+        if self.plan.reshard_after_forward:
+            self.reshard()
+
+    def _pre_backward(self, mod, grad_out):
+        self.finish_unshard()
+        self._pending_grads = sum(1 for p in self.params if p.requires_grad)
+        self._reduced = False
+        # the unit after this one (in forward order) has finished its backward entirely once ours starts: only now is
+        # it safe to drop its gathered weights (autograd re-reads a parameter's current storage when it unpacks it)
+        if self.next_unit is not None and self.next_unit._reduced:
+            self.next_unit.reshard()
+        if self.plan.prefetch and self.prev_unit is not None:
+            self.prev_unit.start_unshard()
+
+    def _grad_ready(self, p):
+        self._pending_grads -= 1
+        if self._pending_grads == 0:
+            self.reduce_grads()
+
+    def reduce_grads(self):
+        """Flatten, reduce-scatter over the shard group, reduce over the replica group; accumulates into .grad of
+        the optimizer's parameter (several micro-batches add up)."""
+        if self._reduced:
+            return
+        self._reduced = True
+        dev = self.flat_shard.device
+        flat = torch.zeros(self.padded, dtype=self.reduce_dtype, device=dev)
+        off = 0
+        for p, n in zip(self.params, self.numels):
+            if p.grad is not None:
+                flat[off:off + n].copy_(p.grad.reshape(-1))
+                p.grad = None
+            off += n
+        world = self.S * self.R
+        flat.div_(world)
+        g = M.reduce_scatter_first_dim(flat, self.shard_group) if self.S > 1 else flat
+        if self.R > 1:
+            if self.plan.zero1_over_replicas:
+                g = M.reduce_scatter_first_dim(g, self.replica_group)
+            else:
+                dist.all_reduce(g, group=self.replica_group)
+        g = g.to(self.opt_param.dtype)
+        if self.opt_param.grad is None:
+            self.opt_param.grad = g
+        else:
+            self.opt_param.grad.add_(g)
+
+    def post_step(self):
+        """LayerZeRO: rebuild the parameter shard from the slices the replicas own."""
+        if self.plan.zero1_over_replicas and self.R > 1:
+            out = M.all_gather_first_dim(self.opt_param.data, self.replica_group)
+            self.flat_shard.copy_(out)
+
+    # -- state -------------------------------------------------------------------------------------------------
+    def full_parameters(self) -> List[torch.Tensor]:
+        """Unsharded master-precision copies (collective over the shard group)."""
+        full = M.all_gather_first_dim(self.flat_shard, self.shard_group) if self.S > 1 else self.flat_shard
+        out, off = [], 0
+        for n, shp in zip(self.numels, self.shapes):
+            out.append(full[off:off + n].view(shp).clone())
+            off += n
+        return out
+
+
+class FullyShardedDataParallel(nn.Module):
+    """Wraps ``module``; every sub-module matched by the plan becomes a ShardedUnit, the remaining parameters form one
+    root unit.  ``dp_group_ranks`` lists the global ranks of the data-parallel group in order."""
+
+    def __init__(self, module: nn.Module, plan: Optional[FSDPPlan] = None, dp_group_ranks: Optional[List[int]] = None,
+                 shard_group=None, replica_group=None):
+        super().__init__()
+        self.module = module
+        self.plan = plan or FSDPPlan()
+        if shard_group is None and dist.is_initialized():
+            ranks = dp_group_ranks or list(range(dist.get_world_size()))
+            shard_group, replica_group = build_groups(ranks, self.plan.shard_size)
+        self.shard_group, self.replica_group = shard_group, replica_group
+        self.units: List[ShardedUnit] = []
+        for name, sub in module.named_modules():
+            if sub is module:
+                continue
+            if self._matches(name, sub) and any(not getattr(p, "_fsdp_owned", False) for p in sub.parameters()):
+                self.units.append(ShardedUnit(sub, shard_group, replica_group, self.plan, name))
+        if any(not getattr(p, "_fsdp_owned", False) for p in module.parameters()):
+            self.units.insert(0, ShardedUnit(module, shard_group, replica_group, self.plan, "<root>"))
+        # forward order == registration order for sequential stacks; used for prefetching only
+        body = [u for u in self.units if u.name != "<root>"]
+        for a, b in zip(body[:-1], body[1:]):
+            a.next_unit, b.prev_unit = b, a
+
+    def _matches(self, name: str, sub: nn.Module) -> bool:
+        cls = type(sub).__name__
+        return any(pat == cls or fnmatch.fnmatch(name, pat) for pat in self.plan.wrap)
+
+    def forward(self, *a, **kw):
+        return self.module(*a, **kw)
+
+    def optimizer_params(self) -> List[nn.Parameter]:
+        return [u.opt_param for u in self.units]
+
+    def finish_grad_sync(self):
+        """Reduce units whose backward never fired completely (unused parameters)."""
+        for u in self.units:
+            if not u._reduced and (u._pending_grads > 0 or any(p.grad is not None for p in u.params)):
+                u.reduce_grads()
+        for u in self.units:
+            u._reduced = False
+            u._pending_grads = 0
+            u.reshard()
+
+    def zero_grad(self, set_to_none: bool = True):
+        for u in self.units:
+            u.opt_param.grad = None
+
+    def post_step(self):
+        for u in self.units:
+            u.post_step()
+
+    def full_state_dict(self) -> Dict[str, torch.Tensor]:
+        """Unsharded parameters by their original names (collective)."""
+        out = {}
+        names = {id(p): n for n, p in self.module.named_parameters()}
+        for u in self.units:
+            for p, t in zip(u.params, u.full_parameters()):
+                out[names[id(p)]] = t
+        return out
+
+    def memory_summary(self) -> Dict[str, int]:
+        shard = sum(u.flat_shard.numel() * u.flat_shard.element_size() for u in self.units)
+        opt = sum(u.opt_param.numel() * u.opt_param.element_size() for u in self.units)
+        full = sum(u.padded * torch.empty((), dtype=u.gather_dtype).element_size() for u in self.units)
+        return {"param_shard_bytes": shard, "optimizer_param_bytes": opt, "unsharded_bytes": full}
+
+
+def fully_shard(module: nn.Module, plan=None, **kw) -> FullyShardedDataParallel:
+    """Entry point matching the torch ``fully_shard`` call shape; ``plan`` may be an FSDPPlan, a dict or a YAML path."""
+    if isinstance(plan, str):
+        plan = FSDPPlan.from_yaml(plan)
+    elif isinstance(plan, dict):
+        plan = FSDPPlan.from_dict(plan)
+    return FullyShardedDataParallel(module, plan, **kw)
