@@ -23,7 +23,6 @@ mindspeed/core/distributed/layerzero/* (ZeRO-1 over DP + ZeRO-3 over a sub-group
 from __future__ import annotations
 
 import dataclasses
-import fnmatch
 from typing import Dict, Iterable, List, Optional, Sequence
 
 import torch
@@ -31,6 +30,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from .. import mappings as M
+from ...utils.patterns import match as _match
 
 
 @dataclasses.dataclass
@@ -67,31 +67,35 @@ def _dtype(name):
     return None if name is None else getattr(torch, name)
 
 
-def build_groups(dp_ranks: List[int], shard_size: Optional[int]):
+def build_groups(dp_ranks: List[int], shard_size: Optional[int], all_dp_rank_lists: Optional[List[List[int]]] = None):
     """(shard_group, replica_group) of the calling rank.  Shard groups are contiguous runs of ``shard_size`` ranks
-    (contiguous ranks share an NVSwitch domain), replica groups are strided across them."""
-    world = len(dp_ranks)
-    s = shard_size or world
-    if world % s != 0:
-        raise ValueError(f"shard size {s} must divide the data-parallel size {world}")
+    (contiguous ranks share an NVSwitch domain), replica groups are strided across them.  Group creation is a
+    collective over the whole job: when several data-parallel groups exist (one per tensor-parallel index) pass all
+    of them in ``all_dp_rank_lists`` so that every rank creates every group in the same order."""
     me = dist.get_rank()
     shard_g = rep_g = None
-    for i in range(0, world, s):
-        ranks = dp_ranks[i:i + s]
-        g = dist.new_group(ranks)
-        if me in ranks:
-            shard_g = g
-    for j in range(s):
-        ranks = dp_ranks[j::s]
-        g = dist.new_group(ranks) if len(ranks) > 1 else None
-        if me in ranks:
-            rep_g = g
+    for ranks_all in (all_dp_rank_lists or [dp_ranks]):
+        world = len(ranks_all)
+        s = shard_size or world
+        if world % s != 0:
+            raise ValueError(f"shard size {s} must divide the data-parallel size {world}")
+        for i in range(0, world, s):
+            ranks = ranks_all[i:i + s]
+            g = dist.new_group(ranks)
+            if me in ranks:
+                shard_g = g
+        for j in range(s):
+            ranks = ranks_all[j::s]
+            g = dist.new_group(ranks) if len(ranks) > 1 else None
+            if me in ranks:
+                rep_g = g
     return shard_g, rep_g
 
 
 class ShardedUnit:
-    def __init__(self, module: nn.Module, shard_group, replica_group, plan: FSDPPlan, name: str = ""):
+    def __init__(self, module: nn.Module, shard_group, replica_group, plan: FSDPPlan, name: str = "", grad_scale: float = 1.0):
         self.module, self.shard_group, self.replica_group, self.plan, self.name = module, shard_group, replica_group, plan, name
+        self.grad_scale = grad_scale
         self.S = M._ws(shard_group)
         self.R = M._ws(replica_group)
         self.s_rank = M._rk(shard_group)
@@ -220,7 +224,7 @@ class ShardedUnit:
                 p.grad = None
             off += n
         world = self.S * self.R
-        flat.div_(world)
+        flat.mul_(self.grad_scale / world)
         g = M.reduce_scatter_first_dim(flat, self.shard_group) if self.S > 1 else flat
         if self.R > 1:
             if self.plan.zero1_over_replicas:
@@ -255,22 +259,28 @@ class FullyShardedDataParallel(nn.Module):
     root unit.  ``dp_group_ranks`` lists the global ranks of the data-parallel group in order."""
 
     def __init__(self, module: nn.Module, plan: Optional[FSDPPlan] = None, dp_group_ranks: Optional[List[int]] = None,
-                 shard_group=None, replica_group=None):
+                 shard_group=None, replica_group=None, grad_scale: float = 1.0, root_unit: bool = True,
+                 all_dp_rank_lists: Optional[List[List[int]]] = None):
+        """``grad_scale`` multiplies the averaged gradients (expert parameters under expert parallelism need 1/ep:
+        their owner already holds the sum over the expert-parallel ranks' tokens).  ``root_unit=False`` leaves the
+        parameters outside the matched sub-modules alone (another wrapper owns them)."""
         super().__init__()
         self.module = module
         self.plan = plan or FSDPPlan()
-        if shard_group is None and dist.is_initialized():
+        if shard_group == "local":          # explicit single-rank sharding (no communication at all)
+            shard_group = replica_group = None
+        elif shard_group is None and dist.is_initialized():
             ranks = dp_group_ranks or list(range(dist.get_world_size()))
-            shard_group, replica_group = build_groups(ranks, self.plan.shard_size)
+            shard_group, replica_group = build_groups(ranks, self.plan.shard_size, all_dp_rank_lists)
         self.shard_group, self.replica_group = shard_group, replica_group
         self.units: List[ShardedUnit] = []
         for name, sub in module.named_modules():
             if sub is module:
                 continue
             if self._matches(name, sub) and any(not getattr(p, "_fsdp_owned", False) for p in sub.parameters()):
-                self.units.append(ShardedUnit(sub, shard_group, replica_group, self.plan, name))
-        if any(not getattr(p, "_fsdp_owned", False) for p in module.parameters()):
-            self.units.insert(0, ShardedUnit(module, shard_group, replica_group, self.plan, "<root>"))
+                self.units.append(ShardedUnit(sub, shard_group, replica_group, self.plan, name, grad_scale))
+        if root_unit and any(not getattr(p, "_fsdp_owned", False) for p in module.parameters()):
+            self.units.insert(0, ShardedUnit(module, shard_group, replica_group, self.plan, "<root>", grad_scale))
         # forward order == registration order for sequential stacks; used for prefetching only
         body = [u for u in self.units if u.name != "<root>"]
         for a, b in zip(body[:-1], body[1:]):
@@ -278,7 +288,7 @@ class FullyShardedDataParallel(nn.Module):
 
     def _matches(self, name: str, sub: nn.Module) -> bool:
         cls = type(sub).__name__
-        return any(pat == cls or fnmatch.fnmatch(name, pat) for pat in self.plan.wrap)
+        return any(pat == cls or _match(name, pat) for pat in self.plan.wrap)
 
     def forward(self, *a, **kw):
         return self.module(*a, **kw)
@@ -310,7 +320,8 @@ class FullyShardedDataParallel(nn.Module):
         names = {id(p): n for n, p in self.module.named_parameters()}
         for u in self.units:
             for p, t in zip(u.params, u.full_parameters()):
-                out[names[id(p)]] = t
+                if id(p) in names:
+                    out[names[id(p)]] = t
         return out
 
     def memory_summary(self) -> Dict[str, int]:
