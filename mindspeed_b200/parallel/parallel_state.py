@@ -145,6 +145,7 @@ class _State:
     override_world: Dict[str, Optional[int]] = field(default_factory=dict)
     rank: int = 0
     world: int = 1
+    rank_offset: int = 0          # first global rank of this (sub-)world; generators work in sub-world-local ranks
     global_memory_buffer: object = None
     moe_tracker: dict = field(default_factory=dict)
     disable_gloo: bool = False
@@ -179,6 +180,8 @@ def _new_group(ranks, backend=None, timeout=None, pg_options=None):
 
 def _register(name: str, all_ranks: List[List[int]], backend=None, timeout=None, make_group=True):
     """Create one process group per rank list; remember the one this rank is in."""
+    if _S.rank_offset:
+        all_ranks = [[r + _S.rank_offset for r in ranks] for ranks in all_ranks]
     _S.all_groups[name] = all_ranks
     mine = None
     for ranks in all_ranks:
@@ -237,11 +240,16 @@ def initialize_model_parallel(
     optimize_send_recv_comm: bool = False,
     world_size: Optional[int] = None,
     rank: Optional[int] = None,
+    rank_offset: int = 0,
+    sub_world_size: Optional[int] = None,
 ) -> None:
     """Build every parallel group.  Signature follows Megatron-core 0.12 ``initialize_model_parallel``.
 
     ``world_size``/``rank`` may be passed explicitly to evaluate the topology in a
     single process without ``torch.distributed`` (no communicators are created then).
+    ``rank_offset``/``sub_world_size`` lay the grid over the global ranks ``[offset, offset + size)`` only (one
+    sub-model of a multi-model job); every rank of the job still has to make the call, because group creation is
+    collective, and ranks outside the range simply end up without groups.
     """
     import datetime
 
@@ -250,6 +258,9 @@ def initialize_model_parallel(
     r, w = _world_info()
     _S.rank = r if rank is None else rank
     _S.world = w if world_size is None else world_size
+    if sub_world_size is not None:
+        _S.world = sub_world_size
+    _S.rank_offset = rank_offset
     make = dist.is_available() and dist.is_initialized() and world_size is None
     _S.disable_gloo = not create_gloo_process_groups
     timeout = datetime.timedelta(minutes=distributed_timeout_minutes) if make else None
@@ -362,8 +373,9 @@ def initialize_model_parallel(
             p = _default_position_embedding_ranks(ranks, pipeline_model_parallel_split_rank)
         emb_all.append(e)
         pos_all.append(p)
-        if _S.rank in ranks:
-            _S.embedding_ranks, _S.position_embedding_ranks = e, p
+        if _S.rank - _S.rank_offset in ranks:
+            _S.embedding_ranks = [x + _S.rank_offset for x in e]
+            _S.position_embedding_ranks = [x + _S.rank_offset for x in p]
     reg("embd", emb_all)
     reg("pos_embd", pos_all)
 
@@ -443,6 +455,15 @@ def _default_position_embedding_ranks(pp_ranks, split_rank=None):
     if split_rank is not None and len(pp_ranks) > 1 and pp_ranks[split_rank] != pp_ranks[0]:
         return [pp_ranks[0], pp_ranks[split_rank]]
     return [pp_ranks[0]]
+
+
+def swap_state(new_state=None):
+    """Install ``new_state`` (a fresh empty one when None) as the module's parallel state and return the previous
+    one.  Multi-model jobs build one state per sub-model and keep the one of the sub-model this rank belongs to."""
+    global _S
+    old = _S
+    _S = new_state if new_state is not None else _State()
+    return old
 
 
 def destroy_model_parallel() -> None:
