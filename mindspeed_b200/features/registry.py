@@ -380,14 +380,24 @@ class PipelineMiscFeature(Feature):
     def validate_args(self, args):
         if args.recompute_in_bubble and args.recompute_in_advance:
             raise AssertionError("--recompute-in-bubble and --recompute-in-advance are exclusive")
-        if (args.recompute_in_bubble or args.recompute_in_advance) and \
-                not getattr(args, "num_layers_per_virtual_pipeline_stage", None):
-            raise AssertionError("RiPipe recompute scheduling needs the interleaved schedule")
+        if (args.recompute_in_bubble or args.recompute_in_advance):
+            if getattr(args, "pipeline_model_parallel_size", 1) < 2:
+                raise AssertionError("recompute scheduling (--recompute-in-bubble / --recompute-in-advance) needs pipeline parallelism")
+            if getattr(args, "schedules_method", None):
+                raise AssertionError("recompute scheduling applies to the 1F1B and interleaved schedules only")
+            if getattr(args, "recompute_granularity", None):
+                raise AssertionError("scheduler-placed recompute replaces --recompute-granularity; do not set both")
         if isinstance(args.noop_layers, str):
             args.noop_layers = sorted({int(x) for x in args.noop_layers.split(",") if x != ""})
         if isinstance(args.pipeline_num_transformer_layers, str):
             import ast
             args.pipeline_num_transformer_layers = ast.literal_eval(args.pipeline_num_transformer_layers)
+
+    def configure(self, manager, args):
+        if args.recompute_in_bubble:
+            manager.set_slot("schedule", "ripipe_bubble", owner=self.feature_name, force=True)
+        elif args.recompute_in_advance:
+            manager.set_slot("schedule", "ripipe_advance", owner=self.feature_name, force=True)
 
 
 # ======================================================================================

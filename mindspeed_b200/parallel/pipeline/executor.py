@@ -31,6 +31,38 @@ def _set_linear_deferral(module, flag: bool):
             m.wgrad_deferral = flag
 
 
+class _Replay:
+    """Iterator wrapper that remembers what it handed out, so a scheduler-placed recompute sees the same batch."""
+
+    def __init__(self, it):
+        self.it, self.taken = it, []
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        b = next(self.it)
+        self.taken.append(b)
+        return b
+
+
+def _rng_capture():
+    st = {"cpu": torch.get_rng_state()}
+    if torch.cuda.is_available():
+        st["cuda"] = torch.cuda.get_rng_state()
+        from ..random import get_cuda_rng_tracker
+        st["tracker"] = get_cuda_rng_tracker().get_states()
+    return st
+
+
+def _rng_restore(st):
+    torch.set_rng_state(st["cpu"])
+    if "cuda" in st:
+        torch.cuda.set_rng_state(st["cuda"])
+        from ..random import get_cuda_rng_tracker
+        get_cuda_rng_tracker().set_states(st["tracker"])
+
+
 def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microbatches, seq_length, micro_batch_size,
              forward_only=False, collect_non_loss_data=False):
     if not isinstance(model, list):
@@ -47,6 +79,8 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
     dev = next(model[0].parameters()).device
     dtype = config.pipeline_dtype
     has_w = any(op.kind == "W" for ops in plan.table[rank] for op in ops)
+    lazy = {(op.chunk, op.mb) for ops in plan.table[rank] for op in ops if op.kind == "R"}   # forwards that drop activations
+    stash: Dict[Tuple[int, int], tuple] = {}
     inputs: Dict[Tuple[int, int], Optional[torch.Tensor]] = {}
     outputs: Dict[Tuple[int, int], torch.Tensor] = {}
     inbox: Dict[Tuple[str, int, int], torch.Tensor] = {}
@@ -100,10 +134,20 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
                     if stage > 0:
                         inp = inbox.pop(("act", op.chunk, op.mb))
                         inp.requires_grad_(not forward_only)
-                    out, nt = S.forward_step(forward_step_func, data_iterator[op.chunk], chunk, num_microbatches, inp,
-                                             store, config, collect_non_loss_data, current_microbatch=op.mb)
+                    drop = (op.chunk, op.mb) in lazy and not forward_only
+                    if drop:
+                        # RiPipe: run without building a graph, remember (input, batch, RNG) for the R op
+                        rng = _rng_capture()
+                        it = _Replay(data_iterator[op.chunk]) if data_iterator[op.chunk] is not None else None
+                        with torch.no_grad():
+                            out, nt = S.forward_step(forward_step_func, it, chunk, num_microbatches, inp, store, config,
+                                                     collect_non_loss_data, current_microbatch=op.mb)
+                        stash[(op.chunk, op.mb)] = (inp, it.taken if it is not None else None, rng)
+                    else:
+                        out, nt = S.forward_step(forward_step_func, data_iterator[op.chunk], chunk, num_microbatches, inp,
+                                                 store, config, collect_non_loss_data, current_microbatch=op.mb)
                     total_tokens += nt.cpu() if torch.is_tensor(nt) else nt
-                    if not forward_only:
+                    if not forward_only and not drop:
                         inputs[(op.chunk, op.mb)] = inp
                         outputs[(op.chunk, op.mb)] = out
                     if stage < Sn - 1:
@@ -112,6 +156,15 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
                             inbox[("act", dc, op.mb)] = out.detach().clone()
                         else:
                             outbox[("act", op.chunk, op.mb)] = out.detach()
+                elif op.kind == "R":
+                    inp, batches, rng = stash.pop((op.chunk, op.mb))
+                    now = _rng_capture()
+                    _rng_restore(rng)
+                    out, _ = S.forward_step(forward_step_func, iter(batches) if batches is not None else None, chunk,
+                                            num_microbatches, inp, [], config, collect_non_loss_data, current_microbatch=op.mb)
+                    _rng_restore(now)
+                    inputs[(op.chunk, op.mb)] = inp
+                    outputs[(op.chunk, op.mb)] = out
                 elif op.kind == "B":
                     inp = inputs.pop((op.chunk, op.mb))
                     out = outputs.pop((op.chunk, op.mb))

@@ -27,7 +27,7 @@ from typing import Callable, Dict, List, Optional, Tuple
 
 @dataclass(frozen=True)
 class Op:
-    kind: str   # "F", "B", "W"
+    kind: str   # "F", "B", "W", "R" (scheduler-placed recompute of a forward whose activations were dropped)
     chunk: int
     mb: int
 
@@ -300,7 +300,7 @@ class Plan:
     recvs: Dict[Tuple[int, int], List[Message]] = field(default_factory=dict)
 
     def bubble_fraction(self, cost: Dict[str, float] = None) -> float:
-        cost = cost or {"F": 1.0, "B": 2.0, "W": 0.0}
+        cost = dict({"F": 1.0, "B": 2.0, "W": 0.0, "R": 1.0}, **(cost or {}))
         busy = [sum(cost[o.kind] for ops in rank for o in ops) for rank in self.table]
         slot_cost = [max((sum(cost[o.kind] for o in self.table[r][t]) for r in range(len(self.table))), default=0)
                      for t in range(self.num_slots)]
@@ -334,6 +334,8 @@ def assign_slots(placement: Placement, orders: List[List[Op]], n_mb: int, pair_f
                         ok = done.get((pipe, stage + 1, "B", op.mb), 1 << 30) < t
                 elif op.kind == "W":
                     ok = (pipe, stage, "B", op.mb) in done
+                elif op.kind == "R":
+                    ok = done.get((pipe, stage, "F", op.mb), 1 << 30) < t
                 if ok:
                     ops_here.append(op)
                     finished_now.append((pipe, stage, op.kind, op.mb, r))
@@ -405,6 +407,8 @@ def simulate_orders(placement: Placement, orders: List[List[Op]], cost: Dict[str
                         deps.append((pipe, st + 1, "B", op.mb))
                 if op.kind == "W":
                     deps.append((pipe, st, "B", op.mb))
+                if op.kind == "R":
+                    deps.append((pipe, st, "F", op.mb))
                 if any(d not in fin for d in deps):
                     break
                 start = max([clock[r]] + [fin[d] for d in deps])
@@ -443,7 +447,46 @@ def validate(plan: Plan) -> None:
                     assert b < seen[((pipe, s - 1), "B", mb)]
 
 
-def build_plan(name: str, pp: int, n_mb: int, vpp: Optional[int] = None, split_w: bool = True) -> Plan:
+def insert_recompute(orders: List[List[Op]], mode: str = "bubble") -> List[List[Op]]:
+    """Scheduler-placed recompute (RiPipe): the forward of (chunk, mb) drops its activations and an ``R`` op rebuilds
+    them before the backward.
+
+      * a forward whose backward follows it directly keeps its activations: no R (this removes the recompute of
+        the last stage's steady state and of every stage's final micro-batches);
+      * mode "bubble":  R sits directly in front of its B.  R needs nothing from other ranks, so in the slot table it
+        runs while the rank would otherwise wait for the gradient from downstream - inside the bubble when there is
+        one;
+      * mode "advance": R is moved one operation earlier than that, so the rebuilt activations are already there when
+        the gradient arrives and the recompute never sits between the arrival of a gradient and its backward.
+    reference: mindspeed/core/pipeline_parallel/ripipe_schedules.py:41-799 (--recompute-in-bubble / --recompute-in-advance).
+    """
+    if mode not in ("bubble", "advance"):
+        raise ValueError("recompute mode must be 'bubble' or 'advance'")
+    out = []
+    for ops in orders:
+        new: List[Op] = []
+        for i, op in enumerate(ops):
+            if op.kind == "B":
+                prev = ops[i - 1] if i > 0 else None
+                keep = prev is not None and prev.kind == "F" and (prev.chunk, prev.mb) == (op.chunk, op.mb)
+                if not keep:
+                    r = Op("R", op.chunk, op.mb)
+                    if mode == "advance" and new and not (new[-1].kind == "F" and (new[-1].chunk, new[-1].mb) == (op.chunk, op.mb)):
+                        new.insert(len(new) - 1, r)
+                    else:
+                        new.append(r)
+            new.append(op)
+        out.append(new)
+    return out
+
+
+def recomputed_forwards(orders: List[List[Op]]) -> List[set]:
+    """Per rank: the (chunk, mb) pairs whose forward must not keep activations (they have an R op)."""
+    return [{(o.chunk, o.mb) for o in ops if o.kind == "R"} for ops in orders]
+
+
+def build_plan(name: str, pp: int, n_mb: int, vpp: Optional[int] = None, split_w: bool = True,
+               recompute: Optional[str] = None) -> Plan:
     if name == "1f1b":
         pl, orders = placement_1f1b(pp), order_1f1b(pp, n_mb)
     elif name == "interleaved":
@@ -461,4 +504,6 @@ def build_plan(name: str, pp: int, n_mb: int, vpp: Optional[int] = None, split_w
         orders = greedy_orders(pl, n_mb, split_w and name == "dualpipe")
     else:
         raise ValueError(name)
+    if recompute:
+        orders = insert_recompute(orders, recompute)
     return assign_slots(pl, orders, n_mb)

@@ -30,7 +30,7 @@ def current_microbatch():
 
 
 def set_schedule(name: Optional[str]):
-    """``--schedules-method``: None | 'dualpipev' | 'dualpipe' | 'chimera'."""
+    """``--schedules-method``: None | 'dualpipev' | 'dualpipe' | 'chimera' | 'ripipe_bubble' | 'ripipe_advance'."""
     _SCHEDULE_OVERRIDE["name"] = name
 
 
@@ -47,6 +47,12 @@ def get_forward_backward_func():
         if name == "chimera":
             from .chimera import forward_backward_chimera
             return forward_backward_chimera
+        if name == "ripipe_bubble":
+            from .ripipe import forward_backward_recompute_in_bubble
+            return forward_backward_recompute_in_bubble
+        if name == "ripipe_advance":
+            from .ripipe import forward_backward_recompute_in_advance
+            return forward_backward_recompute_in_advance
         if ps.get_virtual_pipeline_model_parallel_world_size() is not None:
             return forward_backward_pipelining_with_interleaving
         return forward_backward_pipelining_without_interleaving

@@ -27,6 +27,33 @@ def test_plans_are_valid_and_matched(name, vpp, pp):
                 assert m in plan.recvs[(m.dst, t)]
 
 
+@pytest.mark.parametrize("mode", ["bubble", "advance"])
+def test_recompute_ops_fill_bubbles(mode):
+    from mindspeed_b200.parallel.pipeline.plan import build_plan, validate
+    pp, n = 4, 8
+    base = build_plan("1f1b", pp, n)
+    plan = build_plan("1f1b", pp, n, recompute=mode)
+    validate(plan)
+    for r in range(pp):
+        ops = [o for slot in plan.table[r] for o in slot]
+        rs = {(o.chunk, o.mb) for o in ops if o.kind == "R"}
+        # the last stage runs B right after F: it never recomputes; earlier stages recompute the micro-batches in flight
+        assert (len(rs) == 0) == (r == pp - 1)
+        for (c, mb) in rs:
+            i_f = ops.index(next(o for o in ops if o.kind == "F" and (o.chunk, o.mb) == (c, mb)))
+            i_r = ops.index(next(o for o in ops if o.kind == "R" and (o.chunk, o.mb) == (c, mb)))
+            i_b = ops.index(next(o for o in ops if o.kind == "B" and (o.chunk, o.mb) == (c, mb)))
+            assert i_f < i_r < i_b
+    # timed simulation: scheduler-placed recompute must beat recompute inside every backward (B = 2 + 1), because it
+    # skips the forwards that are followed directly by their backward and runs the rest while waiting for gradients
+    from mindspeed_b200.parallel.pipeline.plan import insert_recompute, order_1f1b, placement_1f1b, simulate_orders
+    pl, orders = placement_1f1b(pp), order_1f1b(pp, n)
+    t_none, _ = simulate_orders(pl, orders, {"F": 1, "B": 2, "W": 0})
+    t_naive, _ = simulate_orders(pl, orders, {"F": 1, "B": 3, "W": 0})
+    t_ri, _ = simulate_orders(pl, insert_recompute(orders, mode), {"F": 1, "B": 2, "W": 0, "R": 1})
+    assert t_none <= t_ri < t_naive, (t_none, t_ri, t_naive)
+
+
 def test_1f1b_bubble_matches_theory():
     from mindspeed_b200.parallel.pipeline.plan import order_1f1b, placement_1f1b, simulate_orders, greedy_orders, placement_v
     for pp, n in ((4, 8), (8, 32)):
@@ -121,6 +148,8 @@ def _train(rank, world, extra, bidirectional):
     (2, ["--pipeline-model-parallel-size", "2"], False),
     (2, ["--pipeline-model-parallel-size", "2", "--num-layers-per-virtual-pipeline-stage", "1"], False),
     (2, ["--pipeline-model-parallel-size", "2", "--schedules-method", "dualpipev"], False),
+    (2, ["--pipeline-model-parallel-size", "2", "--recompute-in-bubble"], False),
+    (2, ["--pipeline-model-parallel-size", "2", "--num-layers-per-virtual-pipeline-stage", "1", "--recompute-in-advance"], False),
     (2, ["--pipeline-model-parallel-size", "2", "--schedules-method", "chimera"], True),
     (2, ["--pipeline-model-parallel-size", "2", "--schedules-method", "dualpipe"], True),
 ])
