@@ -1,0 +1,111 @@
+"""Smart swap (profile -> policy -> execute), adaptive recompute (profile -> knapsack -> apply), auto pipeline split."""
+import torch
+import torch.nn as nn
+
+from mindspeed_b200.memory import adaptive_recompute as AR
+from mindspeed_b200.memory import auto_pipeline as AP
+from mindspeed_b200.memory import smart_swap as SS
+
+
+class Blk(nn.Module):
+    def __init__(self, h):
+        super().__init__()
+        self.a, self.b = nn.Linear(h, 4 * h), nn.Linear(4 * h, h)
+
+    def forward(self, x):
+        return x + self.b(torch.tanh(self.a(x)))
+
+
+def _net(n=4, h=64):
+    torch.manual_seed(0)
+    return nn.Sequential(*[Blk(h) for _ in range(n)])
+
+
+def test_smart_swap_phases_and_numerics():
+    net = _net()
+    x = torch.randn(256, 64, requires_grad=True)
+    ref = net(x).pow(2).sum()
+    ref.backward()
+    gref = [p.grad.clone() for p in net.parameters()]
+    net.zero_grad()
+    mgr = SS.SmartSwapManager(budget_bytes=300_000, warmup_steps=1, min_bytes=1 << 12, op_time=1e-3, d2h_gbs=1.0, h2d_gbs=1.0)
+    with mgr.step_context():
+        loss = net(x).pow(2).sum()
+    loss.backward()
+    net.zero_grad()
+    prof = mgr.profiler
+    assert prof.lives and all(l.use_op >= 0 for l in prof.lives)
+    gen = SS.PolicyGenerator(prof.lives, prof.num_forward_ops, prof.num_backward_ops, op_time=1e-3, d2h_gbs=1.0, h2d_gbs=1.0)
+    base_peak = max(gen.timeline())
+    mgr.end_step()
+    assert mgr.phase == "stable" and mgr.policy.swap_keys
+    assert mgr.policy.expected_peak < base_peak
+    # tensors alive at the peak and with long idle time are preferred: the earliest big saves
+    first = min(prof.lives, key=lambda l: l.save_op)
+    assert first.key in mgr.policy.swap_keys
+    with mgr.step_context() as ex:
+        loss = net(x).pow(2).sum()
+    loss.backward()
+    assert ex.n_swapped == len(mgr.policy.swap_keys) and ex.bytes_swapped > 0
+    assert torch.allclose(loss, ref)
+    for p, g in zip(net.parameters(), gref):
+        assert torch.allclose(p.grad, g, atol=1e-6)
+
+
+def test_policy_respects_copy_bandwidth():
+    lives = [SS.TensorLife(0, 100 << 20, 0, 99), SS.TensorLife(1, 100 << 20, 48, 51)]
+    gen = SS.PolicyGenerator(lives, 50, 100, op_time=1e-3, d2h_gbs=10.0, h2d_gbs=10.0)
+    pol = gen.generate(budget_bytes=150 << 20)
+    assert pol.swap_keys == [0]          # tensor 1 lives too briefly around the peak for its copies to hide
+
+
+def test_knapsack_prefers_cheap_bytes():
+    P = AR.ModuleProfile
+    profs = [P("l0", 3.0, 100 << 20, 10 << 20, 1), P("l0.attn", 1.0, 70 << 20, 10 << 20, 1, "l0"), P("l0.mlp", 1.5, 20 << 20, 10 << 20, 1, "l0"),
+             P("l1", 3.0, 100 << 20, 10 << 20, 1), P("l1.attn", 1.0, 70 << 20, 10 << 20, 1, "l1"), P("l1.mlp", 1.5, 20 << 20, 10 << 20, 1, "l1")]
+    assert AR.solve_recompute(profs, 0) == []
+    assert sorted(AR.solve_recompute(profs, 50 << 20)) in (["l0.attn"], ["l1.attn"])
+    assert sorted(AR.solve_recompute(profs, 120 << 20)) == ["l0.attn", "l1.attn"]
+    assert sorted(AR.solve_recompute(profs, 170 << 20)) == ["l0", "l1"] or len(AR.solve_recompute(profs, 170 << 20)) >= 2
+    assert sorted(AR.solve_recompute(profs, 10_000 << 20)) == ["l0", "l1"]
+
+
+def test_adaptive_recompute_end_to_end():
+    net = _net(3)
+    x = torch.randn(128, 64, requires_grad=True)
+    names = ["0", "1", "2"]
+    ar = AR.AdaptiveRecompute(net, candidates=names, profiling_steps=1, device_budget_bytes=200_000)
+    with ar.step_context():
+        loss = net(x).pow(2).sum()
+    loss.backward()
+    gref = [p.grad.clone() for p in net.parameters()]
+    net.zero_grad()
+    ar.end_step(static_bytes=0)
+    assert all(ar.profiles[n].saved_bytes > 0 and ar.profiles[n].forward_time > 0 for n in names)
+    assert ar.chosen and all(isinstance(getattr(net, n), AR._Ckpt) for n in ar.chosen)
+    with ar.step_context():
+        loss2 = net(x).pow(2).sum()
+    loss2.backward()
+    assert torch.allclose(loss, loss2)
+    got = [p.grad for p in net.parameters()]
+    assert all(torch.allclose(a, b, atol=1e-6) for a, b in zip(got, gref))
+
+
+def test_auto_pipeline_balances_time_under_memory():
+    LP = AP.LayerProfile
+    layers = [LP(1.0, 2.0, 100, 10, 50) for _ in range(8)]
+    plan = AP.solve_pipeline(layers, pp=4, n_mb=8, budget_bytes=10_000)
+    assert plan.feasible and plan.layers_per_stage == [2, 2, 2, 2] and plan.recompute_per_stage == [0, 0, 0, 0]
+    # a tight budget: early stages hold more micro-batches in flight, so they must recompute (or take fewer layers)
+    tight = AP.solve_pipeline(layers, pp=4, n_mb=8, budget_bytes=2 * 50 + 4 * 120)
+    assert tight.feasible and tight.recompute_per_stage[0] >= tight.recompute_per_stage[-1]
+    assert all(b <= 2 * 50 + 4 * 120 for b in tight.stage_bytes)
+    # heterogeneous layers: the split follows time, not count
+    layers2 = [LP(1.0, 2.0, 10, 1, 5)] * 4 + [LP(3.0, 6.0, 10, 1, 5)] * 4
+    p2 = AP.solve_pipeline(layers2, pp=2, n_mb=4, budget_bytes=10_000)
+    assert p2.layers_per_stage == [5, 3]
+    none = AP.solve_pipeline(layers, pp=4, n_mb=8, budget_bytes=10)
+    assert not none.feasible
+    mbs, plan = AP.search_micro_batch(lambda m: [LP(1.0 * m ** 0.9, 2.0 * m ** 0.9, 100 * m, 10 * m, 50) for _ in range(8)],
+                                      [1, 2, 4], global_batch=32, dp=1, pp=4, budget_bytes=3000)
+    assert mbs in (1, 2, 4) and plan.feasible
