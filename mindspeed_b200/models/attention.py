@@ -18,7 +18,7 @@ import torch.nn as nn
 from ..ops import attention as attn_ops
 from ..ops.rope import apply_rope, rope_packed_qkv_
 from ..parallel import parallel_state as ps
-from ..parallel.layers import ColumnParallelLinear, RowParallelLinear, divide
+from ..parallel.layers import ColumnParallelLinear, RowParallelLinear, divide, linear_classes
 from ..parallel.random import get_cuda_rng_tracker
 from .norms import build_norm
 
@@ -88,11 +88,12 @@ class SelfAttention(nn.Module):
         self.ng = divide(self.ng_total, tp)
         self.qpg = self.nq // self.ng
         qkv_out = (self.nq_total + 2 * self.ng_total) * self.d
-        self.linear_qkv = ColumnParallelLinear(config.hidden_size, qkv_out, config=config, init_method=config.init_method,
+        Col, Row = linear_classes(config)
+        self.linear_qkv = Col(config.hidden_size, qkv_out, config=config, init_method=config.init_method,
                                                bias=config.add_bias_linear or config.add_qkv_bias, gather_output=False,
                                                skip_bias_add=False)
         self.core_attention = CoreAttention(config, layer_number, attn_mask_type)
-        self.linear_proj = RowParallelLinear(self.nq_total * self.d, config.hidden_size, config=config,
+        self.linear_proj = Row(self.nq_total * self.d, config.hidden_size, config=config,
                                              init_method=config.output_layer_init_method, bias=config.add_bias_linear,
                                              input_is_parallel=True, skip_bias_add=True)
         if config.qk_layernorm:

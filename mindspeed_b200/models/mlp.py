@@ -6,7 +6,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops.activation import swiglu
-from ..parallel.layers import ColumnParallelLinear, RowParallelLinear
+from ..parallel.layers import ColumnParallelLinear, RowParallelLinear, linear_classes
 from ..parallel.random import CheckpointWithoutOutput
 
 
@@ -17,10 +17,11 @@ class MLP(nn.Module):
         ffn = ffn_hidden_size or config.ffn_hidden_size
         inp = input_size or config.hidden_size
         fc1_out = ffn * 2 if config.gated_linear_unit else ffn
-        self.linear_fc1 = ColumnParallelLinear(inp, fc1_out, config=config, init_method=config.init_method,
+        Col, Row = linear_classes(config)
+        self.linear_fc1 = Col(inp, fc1_out, config=config, init_method=config.init_method,
                                                bias=config.add_bias_linear, skip_bias_add=True, is_expert=is_expert,
                                                stride=2 if config.gated_linear_unit else 1)
-        self.linear_fc2 = RowParallelLinear(ffn, config.hidden_size, config=config,
+        self.linear_fc2 = Row(ffn, config.hidden_size, config=config,
                                             init_method=config.output_layer_init_method, bias=config.add_bias_linear,
                                             input_is_parallel=True, skip_bias_add=True, is_expert=is_expert)
         self.activation_func = config.activation_func

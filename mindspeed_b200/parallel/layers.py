@@ -383,3 +383,12 @@ class VocabParallelEmbedding(nn.Module):
         from ..checkpointing.sharded import make_tp_sharded_tensors
         return make_tp_sharded_tensors(self.state_dict(prefix="", keep_vars=True), prefix, {"weight": 0},
                                        sharded_offsets, self.rank, self.world)
+
+
+def linear_classes(config):
+    """(column, row) linear classes for model code: the fp8-capable subclasses when an fp8 format is configured
+    (they behave exactly like the plain ones outside an fp8 autocast region)."""
+    if getattr(config, "fp8", None) or getattr(config, "fp8_format", None):
+        from ..models.te_compat import TEColumnParallelLinear, TERowParallelLinear
+        return TEColumnParallelLinear, TERowParallelLinear
+    return ColumnParallelLinear, RowParallelLinear

@@ -143,10 +143,19 @@ def train_step(forward_step_func, data_iterator, model, optimizer, opt_param_sch
         m.zero_grad_buffer()
     optimizer.zero_grad()
     fb = get_forward_backward_func()
-    losses_reduced = fb(forward_step_func=forward_step_func, data_iterator=data_iterator, model=model,
-                        num_microbatches=get_num_microbatches(), seq_length=args.seq_length,
-                        micro_batch_size=args.micro_batch_size, decoder_seq_length=None, forward_only=False)
+    fp8_recipe = None
+    if getattr(args, "fp8_format", None):
+        from ..models.te_compat import fp8_autocast, recipe_from_args
+        fp8_recipe = recipe_from_args(args)
+    import contextlib
+    with (fp8_autocast(True, fp8_recipe) if fp8_recipe is not None else contextlib.nullcontext()):
+        losses_reduced = fb(forward_step_func=forward_step_func, data_iterator=data_iterator, model=model,
+                            num_microbatches=get_num_microbatches(), seq_length=args.seq_length,
+                            micro_batch_size=args.micro_batch_size, decoder_seq_length=None, forward_only=False)
     ok, grad_norm, num_zeros = optimizer.step()
+    if fp8_recipe is not None:
+        from ..models.te_compat import clear_fp8_weight_cache
+        clear_fp8_weight_cache()       # weights moved: cached quantised copies are stale
     if ok:
         opt_param_scheduler.step(1)
         skipped = 0

@@ -45,6 +45,7 @@ def test_training_step_on_native_allocator():
         assert any(e["phase"] == 1 for e in ev) and any(e["is_free"] for e in ev)
         # soft limit + pressure callback: the callback drops a big tensor so the next allocation fits
         held = [torch.empty(256 << 20, dtype=torch.uint8, device=dev)]
+        A.empty_cache()            # otherwise the allocator makes room by returning cached segments first
         A.set_limit(A.device_stats()["reserved_bytes"] + (64 << 20))
         calls = []
         def on_pressure(need, d):
