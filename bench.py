@@ -41,6 +41,8 @@ def parse():
     p.add_argument("--seq", type=int, default=8192)
     p.add_argument("--recompute-layers", type=int, default=-1, help="-1: pick by GPU count")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--profile-dir", type=str, default=None,
+                   help="run one extra, untimed step under the step-window profiler on rank 0 and write its kernel table here")
     return p.parse_args()
 
 
@@ -194,6 +196,13 @@ def main():
         return last
 
     run(a.warmup, dev_iter, False)
+    if a.profile_dir and int(os.environ["RANK"]) == 0:
+        from mindspeed_b200.utils.profiler import StepWindowProfiler
+        with StepWindowProfiler(start=0, end=1, save_path=a.profile_dir, rank=0, level="level0") as prof:
+            run(1, dev_iter, False)
+            prof.step()
+    elif a.profile_dir:
+        run(1, dev_iter, False)          # the other ranks take part in the profiled step's collectives
     sampler = ClockSampler(torch.cuda.current_device())
     barrier()
     if int(os.environ["RANK"]) == 0:

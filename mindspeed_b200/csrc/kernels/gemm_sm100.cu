@@ -368,7 +368,7 @@ __device__ __forceinline__ bool wait_counter_ge(const unsigned int* ctr, unsigne
 }
 
 template <int BN, int NSTAGE, int MODE, bool B_MN>
-__global__ void __launch_bounds__(320, 1) gemm_comm_sm100_kernel(const __grid_constant__ CommParams cp) {
+__global__ void __launch_bounds__(448, 1) gemm_comm_sm100_kernel(const __grid_constant__ CommParams cp) {
   const GemmParams& p = cp.g;
   using L = SmemLayout<BN, NSTAGE>;
   extern __shared__ uint8_t smem_raw[];
@@ -532,12 +532,14 @@ __global__ void __launch_bounds__(320, 1) gemm_comm_sm100_kernel(const __grid_co
       }
     } else {
       // ===================== copy warps (6..9): NVLink traffic =====================
-      const int ct = threadIdx.x - 192;   // 0..127
+      // two independent copy groups of four warps each (warps 6-9 and 10-13): twice the loads in flight per SM
+      const int cgrp = (threadIdx.x - 192) >> 7;   // 0 or 1
+      const int ct = (threadIdx.x - 192) & 127;    // 0..127 inside the group
       if (MODE == MODE_AG) {
         // work items in consumption order: shard (rank+1), (rank+2), ...; inside a shard m-tile by m-tile; AG_SUB pieces each
         const int items = (p.world - 1) * tiles_per_rank * AG_SUB;
         const size_t piece_v4 = (size_t)(BM / AG_SUB) * (size_t)p.K * 2 / 16;   // uint4 per piece (contiguous rows)
-        for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        for (int it = blockIdx.x * 2 + cgrp; it < items; it += 2 * gridDim.x) {
           const int sub = it % AG_SUB;
           const int mt_lin = it / AG_SUB;
           const int s = mt_lin / tiles_per_rank + 1;
@@ -564,16 +566,19 @@ __global__ void __launch_bounds__(320, 1) gemm_comm_sm100_kernel(const __grid_co
           }
           for (; i < piece_v4; i += 128) to[i] = ld_cg_v4(from + i);
           __threadfence();
-          named_bar_sync(1, 128);
+          named_bar_sync(1 + cgrp, 128);
           if (ct == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cp.ready + mt) : "memory");
         }
       } else {
-        int acc = 0; uint32_t acc_phase = 0;
+        // group g pushes the tiles that used accumulator slot g (slots alternate tile by tile), so each group owns one
+        // pfull/pempty barrier pair and its phase flips once per tile it handles
+        int acc = 0; uint32_t my_phase = 0;
         const int cwarp = ct >> 5;
-        for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+        for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x, acc ^= 1) {
+          if (acc != cgrp) continue;
           int m_blk, n_blk;
           tile_mn(t, m_blk, n_blk);
-          if (!mbar_wait(pfull_bar(acc), acc_phase, p.status, 0x50u, 16000000000ull)) { alive = false; break; }
+          if (!mbar_wait(pfull_bar(acc), my_phase, p.status, 0x50u, 16000000000ull)) { alive = false; break; }
           const int owner = m_blk / tiles_per_rank;
           if (owner != p.rank) {
             const int n0 = n_blk * BN;
@@ -598,7 +603,7 @@ __global__ void __launch_bounds__(320, 1) gemm_comm_sm100_kernel(const __grid_co
             }
           }
           mbar_arrive(pempty_bar(acc));
-          if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+          my_phase ^= 1u;
         }
         __threadfence_system();
       }
@@ -678,7 +683,7 @@ int launch_comm_variant(const CommParams& cp, int grid, cudaStream_t s) {
     if (e != cudaSuccess) { msb_set_error("gemm_comm_sm100: cannot set %d bytes of dynamic shared memory: %s", L::TOTAL, cudaGetErrorString(e)); return 1; }
     attr_set = true;
   }
-  kern<<<grid, 320, L::TOTAL, s>>>(cp);
+  kern<<<grid, 448, L::TOTAL, s>>>(cp);
   MSB_CHECK_LAUNCH("gemm_comm_sm100");
   return 0;
 }
@@ -757,6 +762,12 @@ struct MsbGemmArgs {
   int wait_peers_before, signal_peers_after;
 };
 
+// Process-wide cap on the number of CTAs the persistent GEMM-class kernels launch (0 = no cap).  Two such kernels
+// on different streams share the GPU by SM count when each is capped (one CTA occupies a whole SM here).
+static int g_cta_limit = 0;
+MSB_API void msb_gemm_set_cta_limit(int n) { g_cta_limit = n > 0 ? n : 0; }
+MSB_API int msb_gemm_get_cta_limit() { return g_cta_limit; }
+
 MSB_API int msb_gemm_bf16_ex(const MsbGemmArgs* a, cudaStream_t s) {
   MSB_REQUIRE(a->M > 0 && a->N > 0 && a->K > 0, "gemm: empty problem %dx%dx%d", a->M, a->N, a->K);
   MSB_REQUIRE(a->nsrc >= 1 && a->nsrc <= MAX_SRC && a->ndst >= 1 && a->ndst <= MAX_SRC, "gemm: bad source/destination count");
@@ -798,6 +809,7 @@ MSB_API int msb_gemm_bf16_ex(const MsbGemmArgs* a, cudaStream_t s) {
   const long long tiles = (long long)num_m * ((a->N + bn - 1) / bn);
   int grid = (int)(tiles < sms ? tiles : sms);
   if (a->max_ctas > 0 && grid > a->max_ctas) grid = a->max_ctas;
+  if (g_cta_limit > 0 && grid > g_cta_limit) grid = g_cta_limit;
   if (bn == 256) return launch_epi<256, 4>(p, a->epilogue, a->a_mn_major, a->b_mn_major, grid, s);
   if (bn == 192) return launch_epi<192, 5>(p, a->epilogue, a->a_mn_major, a->b_mn_major, grid, s);
   return launch_epi<128, 6>(p, a->epilogue, a->a_mn_major, a->b_mn_major, grid, s);
@@ -884,7 +896,8 @@ MSB_API int msb_gemm_allgather(const MsbCommArgs* a, cudaStream_t s) {
   rc = fill_comm(cp, a, MODE_AG, bn);
   if (rc) return rc;
   if (cudaMemsetAsync(a->ready, 0, sizeof(unsigned int) * (a->M / BM), s) != cudaSuccess) { msb_set_error("gemm_allgather: memset failed"); return 1; }
-  const int grid = msb::num_sms();
+  int grid = msb::num_sms();
+  if (g_cta_limit > 0 && grid > g_cta_limit) grid = g_cta_limit;
   if (bn == 256) return a->b_mn_major ? launch_comm_variant<256, 4, MODE_AG, true>(cp, grid, s) : launch_comm_variant<256, 4, MODE_AG, false>(cp, grid, s);
   if (bn == 192) return a->b_mn_major ? launch_comm_variant<192, 5, MODE_AG, true>(cp, grid, s) : launch_comm_variant<192, 5, MODE_AG, false>(cp, grid, s);
   return a->b_mn_major ? launch_comm_variant<128, 6, MODE_AG, true>(cp, grid, s) : launch_comm_variant<128, 6, MODE_AG, false>(cp, grid, s);
@@ -900,7 +913,8 @@ MSB_API int msb_gemm_reduce_scatter(const MsbCommArgs* a, cudaStream_t s) {
   if (rc) return rc;
   const long long tiles = (long long)(a->M / BM) * ((a->N + bn - 1) / bn);
   const int sms = msb::num_sms();
-  const int grid = (int)(tiles < sms ? tiles : sms);
+  int grid = (int)(tiles < sms ? tiles : sms);
+  if (g_cta_limit > 0 && grid > g_cta_limit) grid = g_cta_limit;
   if (bn == 256) return a->b_mn_major ? launch_comm_variant<256, 4, MODE_RS, true>(cp, grid, s) : launch_comm_variant<256, 4, MODE_RS, false>(cp, grid, s);
   if (bn == 192) return a->b_mn_major ? launch_comm_variant<192, 5, MODE_RS, true>(cp, grid, s) : launch_comm_variant<192, 5, MODE_RS, false>(cp, grid, s);
   return a->b_mn_major ? launch_comm_variant<128, 6, MODE_RS, true>(cp, grid, s) : launch_comm_variant<128, 6, MODE_RS, false>(cp, grid, s);

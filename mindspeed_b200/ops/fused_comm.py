@@ -77,6 +77,29 @@ def reset():
 class FusedOps(Sm100Ops):
     name = "fused"
     gathered_is_view = True   # the gathered input returned by allgather_matmul lives in a recycled symmetric buffer
+    # backward of a column-parallel linear: the weight-gradient GEMM (pure compute) runs on a side stream on
+    # ``wgrad_ctas`` SMs while the GEMM->reduce-scatter kernel (mostly waiting on NVLink) runs on the remaining ones
+    concurrent_wgrad = os.environ.get("MSB200_CONCURRENT_WGRAD", "0") != "0"   # opt-in: pays only when the dgrad kernel is NVLink-bound
+    wgrad_ctas = int(os.environ.get("MSB200_WGRAD_CTAS", "96"))
+    _side_stream = None
+
+    @classmethod
+    def dgrad_reduce_scatter_with_wgrad(cls, dy, w, total, main_grad, group):
+        """dx = reduce_scatter(dy @ w) and main_grad += dy^T @ total, issued so that the two overlap on the GPU."""
+        if cls._side_stream is None:
+            cls._side_stream = torch.cuda.Stream()
+        side, cur = cls._side_stream, torch.cuda.current_stream()
+        n_sm = torch.cuda.get_device_properties(dy.device).multi_processor_count
+        k = max(8, min(cls.wgrad_ctas, n_sm - 16))
+        side.wait_stream(cur)
+        with torch.cuda.stream(side), G.cta_limit(k):
+            cls.wgrad(dy, total, main_grad)
+        dy.record_stream(side)
+        total.record_stream(side)
+        with G.cta_limit(n_sm - k):
+            dx = cls.matmul_reduce_scatter(dy, w, group, nt=False)
+        cur.wait_stream(side)
+        return dx
 
     @staticmethod
     def _eligible(x, w, group, rows_total, n_out, k):

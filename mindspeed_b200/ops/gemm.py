@@ -37,6 +37,24 @@ def check_status(device=None):
             raise RuntimeError(f"sm_100a kernel reported a bounded-wait time-out, code 0x{v:x} on {dev}")
 
 
+class cta_limit:
+    """``with cta_limit(n):`` GEMM-class kernels launched inside use at most ``n`` CTAs (= SMs).  Lets two persistent
+    kernels on different streams split the GPU between them."""
+
+    def __init__(self, n: int):
+        self.n = int(n)
+
+    def __enter__(self):
+        L = loader.require_lib()
+        self.prev = L.msb_gemm_get_cta_limit()
+        L.msb_gemm_set_cta_limit(self.n)
+        return self
+
+    def __exit__(self, *exc):
+        loader.require_lib().msb_gemm_set_cta_limit(self.prev)
+        return False
+
+
 def supported(*tensors) -> bool:
     if loader.lib() is None:
         return False

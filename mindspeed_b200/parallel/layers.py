@@ -134,6 +134,16 @@ class _ColumnLinearFn(torch.autograd.Function):
         total, ag_handle = x, None
         if ctx.sp and need_wgrad and not ctx.defer and not ctx.kept_total:
             total, ag_handle = M.all_gather_first_dim(x, ctx.group, async_op=True)
+        concurrent = (ctx.sp and need_wgrad and not ctx.defer and ctx.kept_total and ctx.fusion and hasattr(weight, "main_grad")
+                      and dy.is_cuda and getattr(ops, "concurrent_wgrad", False))
+        if concurrent:
+            # weight gradient on a side stream, sharing the SMs with the NVLink-bound GEMM->reduce-scatter kernel
+            dx = ops.dgrad_reduce_scatter_with_wgrad(dy, weight, total, weight.main_grad, ctx.group)
+            weight.grad_added_to_main_grad = True
+            cb = getattr(weight, "_main_grad_ready_cb", None)
+            if cb is not None:
+                cb(weight)
+            return dx, None, db, None, None, None, None, None
         if ctx.sp:
             dx = ops.matmul_reduce_scatter(dy, weight, ctx.group, nt=False)
         elif ctx.allreduce_dgrad:
