@@ -128,6 +128,13 @@ def setup_model_and_optimizer(model_provider_func, no_wd_decay_cond=None, scale_
     if args.swap_attention:
         from ..memory.swap_attention import install_swap_attention
         install_swap_attention(model, args)
+    if getattr(args, "qat_scheme", None):
+        from ..qat import QATConfig, apply_qat
+        qcfg = QATConfig(scheme=args.qat_scheme.upper(), weight_group=getattr(args, "qat_quant_block_size", 128))
+        for m in model:
+            apply_qat(m, qcfg)
+    _MEMORY_MANAGERS.clear()
+    _MEMORY_MANAGERS.extend(build_memory_managers(args, model))
     if args.load:
         from ..checkpointing import load_checkpoint
         args.iteration = load_checkpoint(model, optimizer, sched)
@@ -136,8 +143,43 @@ def setup_model_and_optimizer(model_provider_func, no_wd_decay_cond=None, scale_
     return model, optimizer, sched
 
 
+_MEMORY_MANAGERS = []   # objects with step_context() / end_step(): smart swap, adaptive recompute
+
+
+def build_memory_managers(args, model):
+    """Per-step memory policies selected by flags.  Each wraps the forward/backward of a step in a context manager
+    (profiling or executing its policy through saved-tensor hooks) and is told when the step ends."""
+    out = []
+    budget_mb = getattr(args, "adaptive_recompute_device_size", -1)
+    if budget_mb and budget_mb > 0 and not getattr(args, "smart_swap", False):
+        from ..memory.adaptive_recompute import AdaptiveRecompute
+        for m in model:
+            out.append(AdaptiveRecompute(m, profiling_steps=getattr(args, "adaptive_recompute_profiling_step", 10),
+                                         device_budget_bytes=budget_mb << 20))
+    if getattr(args, "smart_swap", False):
+        from ..memory.smart_swap import SmartSwapManager
+        if torch.cuda.is_available():
+            total = torch.cuda.get_device_properties(torch.cuda.current_device()).total_memory
+            budget = int(0.85 * total) if not (budget_mb and budget_mb > 0) else budget_mb << 20
+        else:
+            budget = (budget_mb << 20) if budget_mb and budget_mb > 0 else 1 << 40
+        out.append(SmartSwapManager(budget_bytes=budget, warmup_steps=2))
+    return out
+
+
 def train_step(forward_step_func, data_iterator, model, optimizer, opt_param_scheduler, config=None):
     """One optimizer step over ``num_microbatches`` micro-batches."""
+    import contextlib as _cl
+    with _cl.ExitStack() as _stack:
+        for mgr in _MEMORY_MANAGERS:
+            _stack.enter_context(mgr.step_context())
+        out = _train_step_inner(forward_step_func, data_iterator, model, optimizer, opt_param_scheduler, config)
+    for mgr in _MEMORY_MANAGERS:
+        mgr.end_step()
+    return out
+
+
+def _train_step_inner(forward_step_func, data_iterator, model, optimizer, opt_param_scheduler, config=None):
     args = get_args()
     for m in model:
         m.zero_grad_buffer()
