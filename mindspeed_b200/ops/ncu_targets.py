@@ -2,6 +2,8 @@
 
   python -m mindspeed_b200.ops.ncu_targets gemm        # 3 launches each of fwd / dgrad / wgrad, 8192^3 bf16
   python -m mindspeed_b200.ops.ncu_targets elementwise # rmsnorm / swiglu / rope / adam / cross-entropy once each
+  python -m mindspeed_b200.ops.ncu_targets fp8         # 3 launches of the block-scaled fp8 GEMM, 8192 x 8192 x 8192
+  python -m mindspeed_b200.ops.ncu_targets gemm_tp8    # the four forward GEMM shapes of a Llama-3-8B layer at TP8
 
 Inputs exceed the 126 MB L2 but stay well under 2 GB on the device; there are only a handful of launches, so a
 ``--set full`` capture ends by itself within a minute or two.
@@ -53,5 +55,41 @@ def elementwise():
     torch.cuda.synchronize()
 
 
+def fp8():
+    from . import gemm as G
+    from . import gemm_fp8 as F
+    from .quant import quant_128x128, quant_1x128
+    M = N = K = 8192
+    x = torch.randn(M, K, device="cuda")
+    w = torch.randn(N, K, device="cuda") * 0.05
+    xq, xs = quant_1x128(x)
+    wq, ws = quant_128x128(w)
+    del x, w
+    import time
+    for _ in range(3):
+        F.fp8_gemm(xq, xs, wq, ws)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        F.fp8_gemm(xq, xs, wq, ws)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 5
+    print(f"fp8 blockscaled 8192^3: {ms:.3f} ms  {2.0 * M * N * K / ms / 1e9:.1f} TFLOP/s (back-to-back launches, L2 warm)")
+    G.check_status()
+
+
+def gemm_tp8():
+    from . import gemm as G
+    for (M, N, K) in ((8192, 768, 4096), (8192, 3584, 4096), (8192, 4096, 1792), (8192, 4096, 512)):
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+        for _ in range(2):
+            G.linear_fwd(x, w)
+    torch.cuda.synchronize()
+    G.check_status()
+
+
 if __name__ == "__main__":
-    {"gemm": gemm, "elementwise": elementwise}[sys.argv[1] if len(sys.argv) > 1 else "gemm"]()
+    {"gemm": gemm, "elementwise": elementwise, "fp8": fp8, "gemm_tp8": gemm_tp8}[sys.argv[1] if len(sys.argv) > 1 else "gemm"]()

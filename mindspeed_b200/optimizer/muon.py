@@ -128,6 +128,62 @@ class Muon(torch.optim.Optimizer):
         return None
 
 
+class SwapMuon(Muon):
+    """Muon whose momentum buffers live in pinned host memory: each step copies a parameter's buffer to the device on a
+    side stream while the previous parameter is being orthogonalised, and writes it back afterwards, so the device
+    only ever holds two momentum buffers (reference: the swap variant of the reference's Muon, --swap-optimizer with
+    --optimizer-selection muon)."""
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self._stream = torch.cuda.Stream() if torch.cuda.is_available() else None
+
+    def _host_buffer(self, p):
+        st = self.state[p]
+        if "momentum_host" not in st:
+            st["momentum_host"] = torch.zeros(p.shape, dtype=torch.float32, device="cpu",
+                                              pin_memory=torch.cuda.is_available() and p.is_cuda)
+        return st["momentum_host"]
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        items = [(g, p) for g in self.param_groups for p in g["params"]
+                 if (p.grad is not None or getattr(p, "main_grad", None) is not None)]
+        if not items:
+            return None
+
+        def fetch(p):
+            h = self._host_buffer(p)
+            if not p.is_cuda:
+                return h
+            with torch.cuda.stream(self._stream):
+                return h.to(p.device, non_blocking=True)
+
+        nxt = fetch(items[0][1])
+        for i, (group, p) in enumerate(items):
+            if p.is_cuda:
+                torch.cuda.current_stream().wait_stream(self._stream)
+            buf = nxt
+            if i + 1 < len(items):
+                nxt = fetch(items[i + 1][1])          # prefetch overlaps this parameter's Newton-Schulz iterations
+            g = p.grad if p.grad is not None else p.main_grad
+            buf.mul_(group["momentum"]).add_(g.float())
+            u = g.float() + group["momentum"] * buf if group["nesterov"] else buf
+            u2 = u.reshape(u.shape[0], -1)
+            upd = self._orth(u2, p, group) * muon_scale(u2.shape, group["scale_mode"], group["extra_scale_factor"])
+            p.mul_(1.0 - group["lr"] * group["weight_decay"])
+            p.add_(upd.reshape(p.shape).to(p.dtype), alpha=-group["lr"])
+            h = self._host_buffer(p)
+            if p.is_cuda:
+                self._stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self._stream):
+                    h.copy_(buf, non_blocking=True)
+                buf.record_stream(self._stream)
+            elif buf is not h:
+                h.copy_(buf)
+        return None
+
+
 class ChainedOptimizer:
     """Several optimizers stepped together (Megatron ``ChainedOptimizer`` surface)."""
 

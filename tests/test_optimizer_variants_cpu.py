@@ -40,3 +40,18 @@ def test_quantised_states_and_ema_and_muon_train():
     assert ema == pytest.approx(base, abs=1e-6)            # EMA tracking does not change the trajectory
     mu = run_distributed(_run, 1, ["--optimizer", "muon", "--lr", "1e-3"])[0]
     assert all(x == x for x in mu)
+
+
+def test_swap_muon_matches_muon():
+    import torch
+    from mindspeed_b200.optimizer.muon import Muon, SwapMuon
+    torch.manual_seed(0)
+    w1 = torch.nn.Parameter(torch.randn(16, 24))
+    w2 = torch.nn.Parameter(w1.detach().clone())
+    a, b = Muon([w1], lr=0.05, weight_decay=0.01), SwapMuon([w2], lr=0.05, weight_decay=0.01)
+    for step in range(4):
+        g = torch.randn(16, 24, generator=torch.Generator().manual_seed(step))
+        w1.grad, w2.grad = g.clone(), g.clone()
+        a.step(); b.step()
+    assert torch.allclose(w1, w2, atol=1e-6)
+    assert b.state[w2]["momentum_host"].device.type == "cpu" and "momentum_buffer" not in b.state[w2]
