@@ -564,6 +564,9 @@ class DistributedFeature(Feature):
         add_arg(g, "--hccl-ep-group-buffer-adaptive-factor", type=float, default=-1.0)
         add_arg(g, "--hccl-op-mode", type=str, default=None)
         add_arg(g, "--async-log-allreduce", action="store_true")
+        add_arg(g, "--use-fused-dist-opt", action="store_true",
+                help="distributed-optimizer step as one peer-memory kernel (reduce-scatter + AdamW + all-gather); "
+                     "needs --use-distributed-optimizer, a data-parallel group of 2..8 GPUs in one NVSwitch domain and level 2")
         add_arg(g, "--dist-train", action="store_true")
         add_arg(g, "--aiqos", action="store_true")
         add_arg(g, "--aiqos-mode", type=str, default="auto")

@@ -187,6 +187,8 @@ class DistributedOptimizer:
                 if not math.isfinite(nrm):
                     return False, grad_norm, None
                 coef_host = min(1.0, cfg.clip_grad / (nrm + 1e-6)) if cfg.clip_grad > 0 else 1.0
+        if any(getattr(st.buf, "fused", False) for st in self._all_states()):
+            return self._step_fused(lr, wd)
         for st in self._all_states():
             for sg in st.segments:
                 sl = slice(sg.start, sg.end)
@@ -206,6 +208,79 @@ class DistributedOptimizer:
         if self.sharded:
             for chunk in self.model_chunks:
                 chunk.start_param_sync(force_sync=not chunk.ddp_config.overlap_param_gather)
+        return True, grad_norm, None
+
+    def _step_fused(self, lr, wd):
+        """Every (bucket, segment) as peer-memory kernel launches: pull-reduce gradients from the data-parallel peers,
+        AdamW on the owned shard, push the new bf16 weights to every peer.  With clipping the reduction (and the
+        squared norm) is a first pass, the update a second one that reads the clip coefficient on the device."""
+        import ctypes
+        from ..ops import gemm as G
+        from ..ops import loader
+        from ..ops.fused_dist_opt import _Args
+        cfg = self.config
+        L = loader.require_lib()
+        clip = cfg.clip_grad > 0.0
+        st_word = G.status_word(self._dev)
+
+        def launch(st, sg, pull, do_adam, push, use_clip):
+            buf = st.buf
+            h = buf.heap
+            a = _Args()
+            gsz = buf.grad_data.element_size()
+            for r in range(h.world):
+                a.peer_grad[r] = h.ptr(r, buf.grad_off)
+                a.peer_param[r] = h.ptr(r, buf.param_off)
+                a.flag_peer[r] = h.ptr(r, 0)
+            sl = slice(sg.start, sg.end)
+            a.reduced = st.reduced[sl].data_ptr()
+            a.master, a.m, a.v = st.master[sl].data_ptr(), st.m[sl].data_ptr(), st.v[sl].data_ptr()
+            a.sumsq = self._norm_sq.data_ptr() if (pull and sg.in_norm and clip) else None
+            a.clip_coef = self._coef.data_ptr() if use_clip else None
+            a.found_inf = self._found_inf.data_ptr() if use_clip else None
+            a.n, a.shard_offset = sg.end - sg.start, st.lo + sg.start
+            a.grad_scale = float(buf.gradient_scaling_factor) * (1.0 / h.world if buf.ddp_config.average_in_collective else 1.0)
+            a.lr, a.beta1, a.beta2, a.eps, a.wd = lr * sg.lr_mult, cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps, wd * sg.wd_mult
+            a.step, a.world, a.rank = self.step_count, h.world, h.rank
+            a.grad_is_bf16 = int(buf.grad_data.dtype == torch.bfloat16)
+            a.pull, a.do_adam, a.push = int(pull), int(do_adam), int(push)
+            a.epoch = h.next_epoch()
+            a.flag_local = h.ptr(h.rank, 0)
+            a.status = st_word.data_ptr()
+            loader.check(L.msb_dist_opt_fused(ctypes.byref(a), ctypes.c_void_p(loader.stream_ptr())), "dist_opt_fused")
+            st.last_epoch = a.epoch
+
+        states = [st for st in self._all_states()]
+        for st in states:
+            if not getattr(st.buf, "fused", False) or st.residual is not None or st.master is None:
+                raise RuntimeError("--use-fused-dist-opt needs bf16 parameters with fp32 masters in every buffer "
+                                   "(not --reuse-fp32-param) and a data-parallel group of 2..8 GPUs")
+            if not hasattr(st, "reduced"):
+                st.reduced = torch.zeros_like(st.m)
+        grad_norm = None
+        if clip:
+            self._norm_sq.zero_()
+            for st in states:
+                for sg in st.segments:
+                    launch(st, sg, True, False, False, False)
+            dist.all_reduce(self._norm_sq, group=ps.get_data_parallel_group(with_context_parallel=True))
+            mp = ps.get_model_parallel_group()
+            if mp is not None and dist.get_world_size(mp) > 1:
+                dist.all_reduce(self._norm_sq, group=mp)
+            adam_ops.clip_coef(self._norm_sq, cfg.clip_grad, self._coef, self._found_inf, self._norm)
+            grad_norm = self._norm
+            for st in states:
+                for sg in st.segments:
+                    launch(st, sg, False, True, True, True)
+        else:
+            for st in states:
+                for sg in st.segments:
+                    launch(st, sg, True, True, True, False)
+        for st in states:                    # the next forward reads the parameter buffer: wait (bounded) for every peer's pushes
+            h = st.buf.heap
+            loader.check(L.msb_dist_opt_wait_params(ctypes.c_void_p(h.ptr(h.rank, 0)), ctypes.c_uint(st.last_epoch), h.world,
+                                                    ctypes.c_void_p(st_word.data_ptr()), 0, ctypes.c_void_p(loader.stream_ptr())),
+                         "dist_opt_wait_params")
         return True, grad_norm, None
 
     # ---- EMA helpers (reference: fused_ema_adamw store/restore/copy_to) ----

@@ -79,10 +79,28 @@ class ParamAndGradBuffer:
             self.buckets.append(cur)
         self.numel = offset
         dev = device if device is not None else self.params[0].device
-        self.grad_data = torch.zeros(self.numel, dtype=grad_dtype, device=dev)
-        self.param_data = None
-        if ddp_config.use_distributed_optimizer or ddp_config.contiguous_params:
-            self.param_data = torch.zeros(self.numel, dtype=param_dtype, device=dev)
+        self.fused = bool(getattr(ddp_config, "fused_dist_opt", False) and ddp_config.use_distributed_optimizer
+                          and 2 <= self.dp_size <= 8 and dev.type == "cuda" and param_dtype == torch.bfloat16
+                          and grad_dtype in (torch.float32, torch.bfloat16))
+        self.heap = None
+        if self.fused:
+            # both buffers live in a symmetric heap over the data-parallel group: the optimizer's fused kernel pulls
+            # gradient shards from the peers and pushes updated parameters to them, so no NCCL collective touches them
+            from ..symm_mem import get_heap
+            gsz = torch.empty((), dtype=grad_dtype).element_size()
+            ParamAndGradBuffer._heap_seq = getattr(ParamAndGradBuffer, "_heap_seq", 0) + 1
+            self.heap = get_heap(dp_group, self.numel * (gsz + 2) + (1 << 20), tag=f"dp{ParamAndGradBuffer._heap_seq}")
+            self.grad_off = self.heap.alloc("grad", self.numel * gsz)
+            self.param_off = self.heap.alloc("param", self.numel * 2)
+            self.grad_data = self.heap.tensor(self.grad_off, (self.numel,), grad_dtype)
+            self.grad_data.zero_()
+            self.param_data = self.heap.tensor(self.param_off, (self.numel,), param_dtype)
+            self.param_data.zero_()
+        else:
+            self.grad_data = torch.zeros(self.numel, dtype=grad_dtype, device=dev)
+            self.param_data = None
+            if ddp_config.use_distributed_optimizer or ddp_config.contiguous_params:
+                self.param_data = torch.zeros(self.numel, dtype=param_dtype, device=dev)
         for p in self.params:
             s, e, _ = self.param_index[id(p)]
             if self.param_data is not None:
@@ -127,6 +145,9 @@ class ParamAndGradBuffer:
             self.start_grad_sync(b)
 
     def start_grad_sync(self, b: Bucket):
+        if self.fused:
+            b.handle = "done"          # the optimizer's fused kernel reduces (and scales) straight from the peers' buffers
+            return
         if b.handle is not None or self.dp_size == 1 and self.gradient_scaling_factor == 1.0:
             if self.dp_size == 1:
                 b.handle = "done"
@@ -169,7 +190,7 @@ class ParamAndGradBuffer:
 
     # ---- parameter all-gather (distributed optimizer) ----
     def start_param_sync(self, b: Bucket, async_op=False):
-        if self.dp_size == 1:
+        if self.dp_size == 1 or self.fused:      # fused: the optimizer kernel already pushed the new weights everywhere
             return
         s, e = self.shard_range(b)
         full = self.bucket_param(b)

@@ -32,6 +32,7 @@ class DistributedDataParallelConfig:
     contiguous_params: bool = True
     param_and_grad_buffer_pad: Optional[int] = None
     reset_bucket_group_order: bool = False
+    fused_dist_opt: bool = False      # gradient / parameter buffers in a symmetric heap; the optimizer's fused kernel moves the data
 
 
 class DistributedDataParallel(nn.Module):

@@ -105,7 +105,9 @@ def get_model(model_provider_func, wrap_with_ddp=True):
         overlap_param_gather=args.overlap_param_gather, use_distributed_optimizer=args.use_distributed_optimizer,
         check_for_nan_in_grad=args.check_for_nan_in_loss_and_grad, bucket_size=args.ddp_bucket_size,
         average_in_collective=args.ddp_average_in_collective, param_and_grad_buffer_pad=args.param_and_grad_buffer_pad,
-        num_distributed_optimizer_instances=args.num_distributed_optimizer_instances)
+        num_distributed_optimizer_instances=args.num_distributed_optimizer_instances,
+        fused_dist_opt=bool(getattr(args, "use_fused_dist_opt", False) and args.use_distributed_optimizer
+                            and getattr(args, "optimization_level", 0) >= 2 and torch.cuda.is_available()))
     models = [DistributedDataParallel(cfg, ddp_cfg, m, disable_bucketing=(i > 0)) for i, m in enumerate(models)]
     return models
 
