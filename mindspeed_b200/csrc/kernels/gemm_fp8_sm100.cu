@@ -13,7 +13,7 @@
 //
 // Why promotion in registers: the per-k-block scale differs per row, so partial sums of different k-blocks cannot
 // share one tensor-memory accumulator.  Each k-block (128 fp8 = one 128-byte swizzle row, four K=32 MMAs) is
-// accumulated into one of two TMEM buffers; while the tensor core works on the next k-block, the four epilogue warps
+// accumulated into one of four TMEM buffers; while the tensor core works on the next k-block, the eight epilogue warps
 // read the finished 128 x 128 partial sum from TMEM and fold it into fp32 registers with one FMA per element.
 // Per k-block the tensor core needs ~0.14 us at the fp8 peak and the promotion ~0.1 us, so the two overlap.
 //
@@ -21,7 +21,8 @@
 // `m_tile_group[m_tile]` names the expert of every 128-row tile (-1 = padding tile, skipped), and selects the row
 // offset g*N into B_q and sB.  With G = 1 and a null table the kernel is a plain GEMM.
 //
-// CTA = 6 warps (TMA producer, MMA issuer, 4 promotion/epilogue warps), tile 128 x 128 x 128, 6 stages of 32 KB.
+// CTA = 10 warps (TMA producer, MMA issuer, 8 promotion/epilogue warps: 4 lane quarters x 2 column halves), tile
+// 128 x 128 x 128, 6 stages of 32 KB.
 // All waits are bounded (status word), TMEM is freed on every exit path.
 #include "msb_common.cuh"
 #include "msb_sm100.cuh"
@@ -37,7 +38,8 @@ constexpr int F_UMMA_K = 32;
 constexpr int A_BYTES = FBM * FBK, B_BYTES = FBN * FBK, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int BAR_OFFSET = FSTAGES * STAGE_BYTES;
 constexpr int SMEM_TOTAL = BAR_OFFSET + 256 + 1024;
-constexpr uint32_t F_TMEM_COLS = 256;            // two 128-column accumulators
+constexpr int NACC = 4;                          // accumulator buffers in flight (k-blocks between MMA and promotion)
+constexpr uint32_t F_TMEM_COLS = 512;            // four 128-column accumulators: the whole tensor memory of the SM
 
 enum FEpi : int { FEPI_BF16 = 0, FEPI_F32 = 1, FEPI_F32_ACC = 2 };
 
@@ -55,15 +57,15 @@ struct Fp8Params {
 };
 
 template <int EPI>
-__global__ void __launch_bounds__(192, 1) gemm_fp8_blockscaled_kernel(const __grid_constant__ Fp8Params p) {
+__global__ void __launch_bounds__(320, 1) gemm_fp8_blockscaled_kernel(const __grid_constant__ Fp8Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + BAR_OFFSET;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (FSTAGES + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * FSTAGES + a); };
-  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * FSTAGES + 2 + a); };
-  const uint32_t tmem_slot = bar_base + 8u * (2 * FSTAGES + 4);
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * FSTAGES + NACC + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * FSTAGES + 2 * NACC);
   uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -82,7 +84,7 @@ __global__ void __launch_bounds__(192, 1) gemm_fp8_blockscaled_kernel(const __gr
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < FSTAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 128); }
+    for (int a = 0; a < NACC; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 256); }
     mbar_fence_init();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, F_TMEM_COLS); tmem_relinquish(); }
@@ -140,13 +142,16 @@ __global__ void __launch_bounds__(192, 1) gemm_fp8_blockscaled_kernel(const __gr
           umma_commit(empty_bar(stage));     // shared-memory stage free once these MMAs have read it
           umma_commit(tfull_bar(acc));       // partial sum of this k-block complete
           if (++stage == FSTAGES) { stage = 0; phase ^= 1u; }
-          if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+          if (++acc == NACC) { acc = 0; acc_phase ^= 1u; }
         }
       }
     }
   } else {
-    // ===================== promotion + epilogue (warps 2..5) =====================
+    // ===================== promotion + epilogue (warps 2..9) =====================
+    // warp w owns TMEM lanes 32*(w&3).. and the column half (w-2)>>2 of the tile: 64 fp32 accumulators per thread
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int HC = FBN / 2;
     int acc = 0; uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
       int m_blk, n_blk;
@@ -156,18 +161,28 @@ __global__ void __launch_bounds__(192, 1) gemm_fp8_blockscaled_kernel(const __gr
       const int row = m_blk * FBM + q * 32 + lane;
       const bool row_ok = row < p.M;
       const int ncol0 = g * p.N + n_blk * FBN;          // column index into the stacked B rows (for row-wise sB)
-      float accum[FBN];
+      const int cbase = half * HC;
+      float accum[HC];
 #pragma unroll
-      for (int c = 0; c < FBN; ++c) accum[c] = 0.f;
+      for (int c = 0; c < HC; ++c) accum[c] = 0.f;
+      const float* sb_blk = p.sB + (long long)(ncol0 / FBN) * num_kb;
+      // scales of the next k-block are fetched while the current one is folded in (a global load per k-block would
+      // otherwise sit on the critical path of every promotion)
+      float sa_next = row_ok ? __ldg(p.sA + row) : 0.f;
+      float sbs_next = p.b_scale_rowwise ? 1.f : __ldg(sb_blk);
       for (int kb = 0; kb < num_kb; ++kb) {
+        const float sa = sa_next, sbs = sbs_next;
+        if (kb + 1 < num_kb) {
+          sa_next = row_ok ? __ldg(p.sA + (long long)(kb + 1) * p.M + row) : 0.f;
+          if (!p.b_scale_rowwise) sbs_next = __ldg(sb_blk + kb + 1);
+        }
         if (!mbar_wait(tfull_bar(acc), acc_phase, p.status, 0x430u)) { alive = false; break; }
         tc_fence_after();
-        const float sa = row_ok ? __ldg(p.sA + (long long)kb * p.M + row) : 0.f;
-        const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * FBN);
+        const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * FBN + cbase);
         if (!p.b_scale_rowwise) {
-          const float s = sa * __ldg(p.sB + (long long)(ncol0 / FBN) * num_kb + kb);
+          const float s = sa * sbs;
 #pragma unroll
-          for (int c2 = 0; c2 < FBN; c2 += 32) {
+          for (int c2 = 0; c2 < HC; c2 += 32) {
             uint32_t r0[16], r1[16];                       // two 16-column loads in flight per wait
             tmem_ld_32x16(t_row + (uint32_t)c2, r0);
             tmem_ld_32x16(t_row + (uint32_t)(c2 + 16), r1);
@@ -179,9 +194,9 @@ __global__ void __launch_bounds__(192, 1) gemm_fp8_blockscaled_kernel(const __gr
             }
           }
         } else {
-          const float* sbrow = p.sB + (long long)kb * ((long long)p.G * p.N) + ncol0;
+          const float* sbrow = p.sB + (long long)kb * ((long long)p.G * p.N) + ncol0 + cbase;
 #pragma unroll
-          for (int c2 = 0; c2 < FBN; c2 += 32) {
+          for (int c2 = 0; c2 < HC; c2 += 32) {
             uint32_t r0[16], r1[16];
             tmem_ld_32x16(t_row + (uint32_t)c2, r0);
             tmem_ld_32x16(t_row + (uint32_t)(c2 + 16), r1);
@@ -189,8 +204,8 @@ __global__ void __launch_bounds__(192, 1) gemm_fp8_blockscaled_kernel(const __gr
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int ca = c2 + j, cb = c2 + 16 + j;
-              const float sb0 = (n_blk * FBN + ca < p.N) ? __ldg(sbrow + ca) : 0.f;
-              const float sb1 = (n_blk * FBN + cb < p.N) ? __ldg(sbrow + cb) : 0.f;
+              const float sb0 = (n_blk * FBN + cbase + ca < p.N) ? __ldg(sbrow + ca) : 0.f;
+              const float sb1 = (n_blk * FBN + cbase + cb < p.N) ? __ldg(sbrow + cb) : 0.f;
               accum[ca] = fmaf(sa * sb0, __uint_as_float(r0[j]), accum[ca]);
               accum[cb] = fmaf(sa * sb1, __uint_as_float(r1[j]), accum[cb]);
             }
@@ -198,16 +213,16 @@ __global__ void __launch_bounds__(192, 1) gemm_fp8_blockscaled_kernel(const __gr
         }
         tc_fence_before();
         mbar_arrive(tempty_bar(acc));
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        if (++acc == NACC) { acc = 0; acc_phase ^= 1u; }
       }
       if (!alive) break;
       if (row_ok) {
-        const int col_base = n_blk * FBN;
+        const int col_base = n_blk * FBN + cbase;
         if (EPI == FEPI_BF16) {
           __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + col_base;
-          if (col_base + FBN <= p.N && ((reinterpret_cast<uintptr_t>(drow) & 15) == 0)) {
+          if (col_base + HC <= p.N && ((reinterpret_cast<uintptr_t>(drow) & 15) == 0)) {
 #pragma unroll
-            for (int v = 0; v < FBN / 8; ++v) {
+            for (int v = 0; v < HC / 8; ++v) {
               uint32_t pk[4];
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
@@ -218,13 +233,13 @@ __global__ void __launch_bounds__(192, 1) gemm_fp8_blockscaled_kernel(const __gr
             }
           } else {
 #pragma unroll
-            for (int c = 0; c < FBN; ++c) if (col_base + c < p.N) drow[c] = __float2bfloat16_rn(accum[c]);
+            for (int c = 0; c < HC; ++c) if (col_base + c < p.N) drow[c] = __float2bfloat16_rn(accum[c]);
           }
         } else {
           float* drow = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + col_base;
-          if (col_base + FBN <= p.N && ((reinterpret_cast<uintptr_t>(drow) & 15) == 0)) {
+          if (col_base + HC <= p.N && ((reinterpret_cast<uintptr_t>(drow) & 15) == 0)) {
 #pragma unroll
-            for (int v = 0; v < FBN / 4; ++v) {
+            for (int v = 0; v < HC / 4; ++v) {
               float4 o = make_float4(accum[4 * v], accum[4 * v + 1], accum[4 * v + 2], accum[4 * v + 3]);
               if (EPI == FEPI_F32_ACC) {
                 const float4 old = *reinterpret_cast<float4*>(drow + 4 * v);
@@ -234,7 +249,7 @@ __global__ void __launch_bounds__(192, 1) gemm_fp8_blockscaled_kernel(const __gr
             }
           } else {
 #pragma unroll
-            for (int c = 0; c < FBN; ++c)
+            for (int c = 0; c < HC; ++c)
               if (col_base + c < p.N) drow[c] = (EPI == FEPI_F32_ACC) ? drow[c] + accum[c] : accum[c];
           }
         }
@@ -259,7 +274,7 @@ int launch_fp8(const Fp8Params& p, int grid, cudaStream_t s) {
     if (e != cudaSuccess) { msb_set_error("gemm_fp8: cannot set %d bytes of dynamic shared memory: %s", SMEM_TOTAL, cudaGetErrorString(e)); return 1; }
     attr_set = true;
   }
-  kern<<<grid, 192, SMEM_TOTAL, s>>>(p);
+  kern<<<grid, 320, SMEM_TOTAL, s>>>(p);
   MSB_CHECK_LAUNCH("gemm_fp8_blockscaled");
   return 0;
 }
