@@ -138,7 +138,45 @@ class FusedOps(Sm100Ops):
         return y, total
 
     @classmethod
-    def matmul_reduce_scatter(cls, x, w, group, nt=True):
+    def matmul_all_reduce(cls, x, w, group, nt=True):
+        """y = all_reduce(x @ W): the fused GEMM -> reduce-scatter kernel followed by an all-gather of the reduced row
+        shards (non-sequence-parallel tensor parallelism; reference: npu_mm_all_reduce_base / LCAL matmul_all_reduce)."""
+        ws = dist.get_world_size(group) if group is not None else 1
+        x2 = x.reshape(-1, x.shape[-1])
+        n = w.shape[0] if nt else w.shape[1]
+        if ws < 2 or not cls._eligible(x, w, group, x2.shape[0], n, x2.shape[1]):
+            return Sm100Ops.matmul_all_reduce(x, w, group, nt)
+        part = cls.matmul_reduce_scatter(x2, w, group, nt)
+        full = torch.empty(x2.shape[0], n, dtype=part.dtype, device=part.device)
+        dist.all_gather_into_tensor(full, part.contiguous(), group=group)
+        return full.view(*x.shape[:-1], n)
+
+    @classmethod
+    def matmul_all_reduce_add_rmsnorm(cls, x, w, residual, gamma, eps, group, nt=True):
+        """(h, y) with h = all_reduce(x @ W) + residual and y = rmsnorm(h) * gamma.  The residual is added inside the
+        owner-side reduction of the reduce-scatter, the norm runs on the row shard each rank owns (rows are
+        independent), and one all-gather returns both results (reference: aclnnMatmulAllReduceAddRmsNorm)."""
+        from .norm import rms_norm
+        ws = dist.get_world_size(group) if group is not None else 1
+        x2 = x.reshape(-1, x.shape[-1])
+        n = w.shape[0] if nt else w.shape[1]
+        res2 = residual.reshape(-1, n)
+        if ws < 2 or not cls._eligible(x, w, group, x2.shape[0], n, x2.shape[1]):
+            h = Sm100Ops.matmul_all_reduce(x, w, group, nt) + residual
+            return h, rms_norm(h, gamma, eps)
+        rows = x2.shape[0] // ws
+        r = dist.get_rank(group)
+        h_part = cls.matmul_reduce_scatter(x2, w, group, nt, residual=res2[r * rows:(r + 1) * rows].contiguous())
+        y_part = rms_norm(h_part, gamma, eps)
+        both = torch.stack([h_part, y_part]).contiguous()                      # [2, rows, n]
+        out = torch.empty(ws, 2, rows, n, dtype=both.dtype, device=both.device)
+        dist.all_gather_into_tensor(out, both, group=group)
+        h = out[:, 0].reshape(*x.shape[:-1], n)
+        y = out[:, 1].reshape(*x.shape[:-1], n)
+        return h, y
+
+    @classmethod
+    def matmul_reduce_scatter(cls, x, w, group, nt=True, residual=None):
         ws = dist.get_world_size(group) if group is not None else 1
         x2 = x.reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
@@ -146,7 +184,8 @@ class FusedOps(Sm100Ops):
         m, k = x2.shape
         n = w.shape[0] if nt else w.shape[1]
         if not cls._eligible(x, w, group, m, n, k) or x2.data_ptr() % 16 != 0:
-            return Sm100Ops.matmul_reduce_scatter(x, w, group, nt)
+            out = Sm100Ops.matmul_reduce_scatter(x, w, group, nt)
+            return out if residual is None else out + residual.view_as(out)
         L = loader.require_lib()
         c = _ctx(group)
         h = c.heap
@@ -165,7 +204,10 @@ class FusedOps(Sm100Ops):
         lead = (x.shape[0] // ws,) + tuple(x.shape[1:-1])
         out = torch.empty(*lead, n, dtype=torch.bfloat16, device=x.device)
         own = h.ptr(h.rank, off_partial + h.rank * rows * n * 2)
-        loader.check(L.msb_rs_reduce(ctypes.c_void_p(h.ptr(h.rank, off_stage)), ctypes.c_void_p(own), loader.p(out), None,
+        if residual is not None and (residual.dtype != torch.bfloat16 or not residual.is_contiguous() or residual.numel() != out.numel()):
+            raise ValueError("residual must be a contiguous bf16 tensor shaped like this rank's output shard")
+        loader.check(L.msb_rs_reduce(ctypes.c_void_p(h.ptr(h.rank, off_stage)), ctypes.c_void_p(own), loader.p(out),
+                                     loader.p(residual) if residual is not None else None,
                                      ctypes.c_longlong(rows), n, ws, h.rank, ctypes.c_void_p(h.ptr(h.rank, 0)),
                                      ctypes.c_uint(epoch), ctypes.c_void_p(G.status_word(x.device).data_ptr()), 0, st),
                      "rs_reduce")
