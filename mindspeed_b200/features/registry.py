@@ -564,6 +564,8 @@ class DistributedFeature(Feature):
         add_arg(g, "--hccl-ep-group-buffer-adaptive-factor", type=float, default=-1.0)
         add_arg(g, "--hccl-op-mode", type=str, default=None)
         add_arg(g, "--async-log-allreduce", action="store_true")
+        add_arg(g, "--no-fused-ulysses-a2a", action="store_true",
+                help="level 2 runs the Ulysses all-to-alls as peer-memory kernels with the layout transform fused in; this keeps NCCL")
         add_arg(g, "--use-fused-dist-opt", action="store_true",
                 help="distributed-optimizer step as one peer-memory kernel (reduce-scatter + AdamW + all-gather); "
                      "needs --use-distributed-optimizer, a data-parallel group of 2..8 GPUs in one NVSwitch domain and level 2")

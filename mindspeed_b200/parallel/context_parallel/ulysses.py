@@ -14,11 +14,30 @@ from ...ops import attention as A
 from .. import mappings as M
 
 
+_FUSED = {"on": False}
+
+
+def set_fused_all_to_all(flag: bool):
+    """Optimisation level 2: the exchanges run as peer-memory pull kernels with the layout transform folded in
+    (mindspeed_b200/ops/ulysses_comm.py) instead of permute + NCCL all-to-all."""
+    _FUSED["on"] = bool(flag)
+
+
+def _use_fused(x, group):
+    if not _FUSED["on"]:
+        return False
+    from ...ops import ulysses_comm as U
+    return U.eligible(x, group) and (x.shape[-1] * x.element_size() * (x.shape[2] if x.dim() == 4 else 1)) % 16 == 0
+
+
 def seq_to_heads(x, group):
     """[s/p, b, n, d] -> [s, b, n/p, d]"""
     p = dist.get_world_size(group)
     if p == 1:
         return x
+    if _use_fused(x, group) and (x.shape[2] // p) * x.shape[3] * x.element_size() % 16 == 0:
+        from ...ops.ulysses_comm import seq_to_heads_fused
+        return seq_to_heads_fused(x, group)
     sl, b, n, d = x.shape
     t = x.reshape(sl, b, p, n // p, d).permute(2, 0, 1, 3, 4).contiguous()  # [p, s/p, b, n/p, d]
     t = M.all_to_all(group, t.reshape(p * sl, b, n // p, d))
@@ -30,6 +49,9 @@ def heads_to_seq(x, group):
     p = dist.get_world_size(group)
     if p == 1:
         return x
+    if _use_fused(x, group):
+        from ...ops.ulysses_comm import heads_to_seq_fused
+        return heads_to_seq_fused(x, group)
     s, b, nl, d = x.shape
     t = M.all_to_all(group, x.contiguous())                                   # [p * s/p, b, n/p, d] by source = head group
     t = t.reshape(p, s // p, b, nl, d).permute(1, 2, 0, 3, 4).contiguous()    # [s/p, b, p, n/p, d]
