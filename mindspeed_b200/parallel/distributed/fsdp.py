@@ -293,6 +293,24 @@ class FullyShardedDataParallel(nn.Module):
     def forward(self, *a, **kw):
         return self.module(*a, **kw)
 
+    # ---- surface the training loop expects from a data-parallel wrapper ----
+    @property
+    def config(self):
+        return self.module.config
+
+    def zero_grad_buffer(self):
+        self.zero_grad()
+
+    def no_sync(self):
+        import contextlib
+        return contextlib.nullcontext()       # gradients of several micro-batches accumulate in the sharded .grad
+
+    def start_param_sync(self, *a, **kw):
+        return None                           # parameters are gathered on demand by the forward / backward hooks
+
+    def set_input_tensor(self, t):
+        return self.module.set_input_tensor(t)
+
     def optimizer_params(self) -> List[nn.Parameter]:
         return [u.opt_param for u in self.units]
 
@@ -338,3 +356,86 @@ def fully_shard(module: nn.Module, plan=None, **kw) -> FullyShardedDataParallel:
     elif isinstance(plan, dict):
         plan = FSDPPlan.from_dict(plan)
     return FullyShardedDataParallel(module, plan, **kw)
+
+
+class ShardedAdamW:
+    """AdamW over the flat shards of one or more ``FullyShardedDataParallel`` wrappers, with the optimizer surface of the
+    training loop (``step() -> (ok, grad_norm, num_zeros)``, ``zero_grad``, ``param_groups``).  Weight decay skips
+    one-dimensional parameters (norm weights, biases) through a per-element mask laid out like the flat shard; the
+    gradient norm for clipping is reduced over the ranks that hold different shards."""
+
+    def __init__(self, wrappers: Sequence[FullyShardedDataParallel], lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
+                 clip_grad: float = 0.0):
+        self.wrappers = list(wrappers)
+        self.param_groups = [dict(lr=lr, weight_decay=weight_decay, betas=betas, eps=eps, step=0)]
+        self.clip_grad = clip_grad
+        self.state = []
+        for w in self.wrappers:
+            for u in w.units:
+                mask = torch.zeros(u.padded, dtype=torch.float32, device=u.flat_shard.device)
+                off = 0
+                for n, shp in zip(u.numels, u.shapes):
+                    if len(shp) > 1:
+                        mask[off:off + n] = 1.0
+                    off += n
+                lo = u.s_rank * u.per
+                m = mask[lo:lo + u.per]
+                if u.plan.zero1_over_replicas and u.R > 1:
+                    m = m[u.r_rank * u.own:(u.r_rank + 1) * u.own]
+                self.state.append(dict(unit=u, wd_mask=m.clone(), m=torch.zeros_like(u.opt_param, dtype=torch.float32),
+                                       v=torch.zeros_like(u.opt_param, dtype=torch.float32)))
+
+    def zero_grad(self, set_to_none=True):
+        for w in self.wrappers:
+            w.zero_grad()
+
+    def get_loss_scale(self):
+        return torch.ones(1)
+
+    def reload_model_params(self):
+        return None
+
+    @torch.no_grad()
+    def step(self):
+        g = self.param_groups[0]
+        g["step"] += 1
+        t, lr, wd, (b1, b2), eps = g["step"], g["lr"], g["weight_decay"], g["betas"], g["eps"]
+        grad_norm = None
+        coef = 1.0
+        if self.clip_grad and self.clip_grad > 0:
+            sq = torch.zeros((), dtype=torch.float32, device=self.state[0]["m"].device)
+            for st in self.state:
+                gr = st["unit"].opt_param.grad
+                if gr is not None:
+                    sq += gr.float().pow(2).sum()
+            u0 = self.state[0]["unit"]
+            if u0.S > 1:
+                dist.all_reduce(sq, group=u0.shard_group)
+            if u0.plan.zero1_over_replicas and u0.R > 1:
+                dist.all_reduce(sq, group=u0.replica_group)
+            grad_norm = float(sq.sqrt())
+            coef = min(1.0, self.clip_grad / (grad_norm + 1e-6))
+        bc1, bc2 = 1.0 - b1 ** t, 1.0 - b2 ** t
+        for st in self.state:
+            p = st["unit"].opt_param
+            if p.grad is None:
+                continue
+            gr = p.grad.float() * coef
+            st["m"].mul_(b1).add_(gr, alpha=1 - b1)
+            st["v"].mul_(b2).addcmul_(gr, gr, value=1 - b2)
+            upd = (st["m"] / bc1) / ((st["v"] / bc2).sqrt() + eps)
+            p.data.mul_(1.0 - lr * wd * st["wd_mask"].to(p.dtype))
+            p.data.add_(upd.to(p.dtype), alpha=-lr)
+        for w in self.wrappers:
+            w.post_step()
+        return True, grad_norm, None
+
+    def state_dict(self):
+        return {"step": self.param_groups[0]["step"], "m": [s["m"] for s in self.state], "v": [s["v"] for s in self.state]}
+
+    def load_state_dict(self, sd):
+        self.param_groups[0]["step"] = sd["step"]
+        for s, m, v in zip(self.state, sd["m"], sd["v"]):
+            s["m"].copy_(m)
+            s["v"].copy_(v)
+

@@ -100,6 +100,15 @@ def get_model(model_provider_func, wrap_with_ddp=True):
     if not wrap_with_ddp:
         return models
     cfg = models[0].config
+    if getattr(args, "layerzero", False) or getattr(args, "fsdp2_config_path", None):
+        # fully sharded data parallel instead of bucketed DDP (+ optional ZeRO-1 of the optimizer state across replicas)
+        if ps.get_tensor_model_parallel_world_size() > 1 or pp > 1:
+            raise NotImplementedError("--layerzero / --fsdp2-config-path run with tensor and pipeline parallel size 1")
+        from ..parallel.distributed.fsdp import FSDPPlan, FullyShardedDataParallel
+        path = getattr(args, "fsdp2_config_path", None) or getattr(args, "layerzero_config", None)
+        plan = FSDPPlan.from_yaml(path) if path else FSDPPlan(zero1_over_replicas=bool(getattr(args, "layerzero", False)))
+        ranks = ps._ranks("dp")
+        return [FullyShardedDataParallel(m, plan, dp_group_ranks=ranks) for m in models]
     ddp_cfg = DistributedDataParallelConfig(
         grad_reduce_in_fp32=args.accumulate_allreduce_grads_in_fp32, overlap_grad_reduce=args.overlap_grad_reduce,
         overlap_param_gather=args.overlap_param_gather, use_distributed_optimizer=args.use_distributed_optimizer,
@@ -122,7 +131,13 @@ def setup_model_and_optimizer(model_provider_func, no_wd_decay_cond=None, scale_
                            optimizer_selection=args.optimizer_selection, use_ema=args.use_ema, ema_decay=args.ema_decay,
                            swap_optimizer=args.swap_optimizer, swap_optimizer_times=args.swap_optimizer_times,
                            quant_states=args.quant_states, reuse_fp32_param=args.reuse_fp32_param)
-    optimizer = get_megatron_optimizer(ocfg, model, no_wd_decay_cond, scale_lr_cond, lr_mult)
+    from ..parallel.distributed.fsdp import FullyShardedDataParallel as _FSDP
+    if isinstance(model[0], _FSDP):
+        from ..parallel.distributed.fsdp import ShardedAdamW
+        optimizer = ShardedAdamW(model, lr=args.lr, betas=(args.adam_beta1, args.adam_beta2), eps=args.adam_eps,
+                                 weight_decay=args.weight_decay, clip_grad=args.clip_grad)
+    else:
+        optimizer = get_megatron_optimizer(ocfg, model, no_wd_decay_cond, scale_lr_cond, lr_mult)
     sched = OptimizerParamScheduler(optimizer, args.lr, args.min_lr, args.lr_warmup_iters,
                                     args.lr_decay_iters or args.train_iters, args.lr_decay_style)
     cfg = model[0].module.config
