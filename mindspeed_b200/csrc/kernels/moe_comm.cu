@@ -203,6 +203,89 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeParams p) {
   }
 }
 
+// Builds every index table of a dispatch / combine pair in one launch (replaces ~25 small tensor operations whose host
+// launch cost dominated the layer): CTA e scans column e of the routing map and writes, for every routed token, its
+// position among this rank's tokens for expert e, the token id and its probability into the sorted lists (directly in
+// the staging slot the peers read); CTA 0 afterwards fills the chunk tables and the destination row bases from the
+// all-gathered count matrix ``counts`` [ep, ld] (ld >= E, row s = source rank s).
+template <typename PT>
+__global__ void __launch_bounds__(1024) moe_build_plan_kernel(const unsigned char* __restrict__ map, const PT* __restrict__ probs,
+                                                               const long long* __restrict__ counts, int ld, int T, int E, int E_loc, int ep,
+                                                               int me, int* __restrict__ rank_in_expert, int* __restrict__ sorted_tok,
+                                                               float* __restrict__ sorted_probs, long long* __restrict__ chunk_dst_start,
+                                                               long long* __restrict__ chunk_src_start, long long* __restrict__ dst_row_base,
+                                                               long long list_cap) {
+  __shared__ int warp_tot[32];
+  __shared__ long long s_src_off;
+  __shared__ int s_running;
+  const int e = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  if (tid == 0) {
+    long long off = 0;
+    for (int k = 0; k < e; ++k) off += counts[(long long)me * ld + k];
+    s_src_off = off;
+    s_running = 0;
+  }
+  __syncthreads();
+  const long long src_off = s_src_off;
+  for (int base = 0; base < T; base += blockDim.x) {
+    const int t = base + tid;
+    const int flag = (t < T && map[(long long)t * E + e] != 0) ? 1 : 0;
+    int incl = flag;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
+    if (lane == 31) warp_tot[wid] = incl;
+    __syncthreads();
+    if (wid == 0) {
+      int v = (lane < (int)(blockDim.x >> 5)) ? warp_tot[lane] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
+      warp_tot[lane] = v;                       // inclusive prefix of the warp totals
+    }
+    __syncthreads();
+    const int before = s_running + (wid ? warp_tot[wid - 1] : 0) + incl - flag;
+    if (t < T) {
+      rank_in_expert[(long long)t * E + e] = flag ? before : -1;
+      if (flag) {
+        const long long pos = src_off + before;
+        if (pos < list_cap) {
+          sorted_tok[pos] = t;
+          sorted_probs[pos] = (float)probs[(long long)t * E + e];
+        }
+      }
+    }
+    __syncthreads();
+    if (tid == 0) s_running += warp_tot[(blockDim.x >> 5) - 1];
+    __syncthreads();
+  }
+  if (e != 0) return;
+  // ---- tables from the count matrix ----
+  const int n_chunks = E_loc * ep;
+  const int lo = me * E_loc;
+  for (int c = tid; c < n_chunks; c += blockDim.x) {          // chunk c = (local expert el, source rank s)
+    const int el = c / ep, sr = c % ep;
+    long long off = 0;
+    for (int k = 0; k < lo + el; ++k) off += counts[(long long)sr * ld + k];
+    chunk_src_start[c] = off;
+  }
+  for (int ee = tid; ee < E; ee += blockDim.x) {
+    const int owner = ee / E_loc;
+    long long first = 0;
+    for (int k = owner * E_loc; k < ee; ++k)
+      for (int sr = 0; sr < ep; ++sr) first += counts[(long long)sr * ld + k];
+    for (int sr = 0; sr < me; ++sr) first += counts[(long long)sr * ld + ee];
+    dst_row_base[ee] = first;
+  }
+  if (tid == 0) {
+    long long acc = 0;
+    for (int c = 0; c < n_chunks; ++c) {
+      chunk_dst_start[c] = acc;
+      acc += counts[(long long)(c % ep) * ld + lo + c / ep];
+    }
+    chunk_dst_start[n_chunks] = acc;
+  }
+}
+
 }  // namespace
 
 // Host-visible argument block (mirrored by a ctypes.Structure in mindspeed_b200/ops/moe_comm.py).
@@ -278,3 +361,24 @@ MSB_API int msb_moe_combine(const MsbMoeCommArgs* a, cudaStream_t stream) {
   MSB_CHECK_LAUNCH("moe_combine");
   return 0;
 }
+
+// One launch that fills rank_in_expert [T, E], the sorted token / probability lists (at most ``list_cap`` entries) and the
+// chunk / row-base tables from the routing map and the all-gathered count matrix.  probs_dtype: MSB_F32 or MSB_BF16.
+MSB_API int msb_moe_build_plan(const unsigned char* map, const void* probs, int probs_dtype, const long long* counts, int ld, int T, int E,
+                               int E_loc, int ep, int me, int* rank_in_expert, int* sorted_tok, float* sorted_probs,
+                               long long* chunk_dst_start, long long* chunk_src_start, long long* dst_row_base, long long list_cap,
+                               cudaStream_t s) {
+  MSB_REQUIRE(map && probs && counts && rank_in_expert && sorted_tok && sorted_probs && chunk_dst_start && chunk_src_start && dst_row_base,
+              "moe_build_plan: null argument");
+  MSB_REQUIRE(T > 0 && E > 0 && E_loc > 0 && ep > 0 && E == E_loc * ep && me >= 0 && me < ep && ld >= E, "moe_build_plan: bad sizes");
+  if (probs_dtype == MSB_BF16)
+    moe_build_plan_kernel<__nv_bfloat16><<<E, 1024, 0, s>>>(map, (const __nv_bfloat16*)probs, counts, ld, T, E, E_loc, ep, me, rank_in_expert,
+                                                            sorted_tok, sorted_probs, chunk_dst_start, chunk_src_start, dst_row_base, list_cap);
+  else if (probs_dtype == MSB_F32)
+    moe_build_plan_kernel<float><<<E, 1024, 0, s>>>(map, (const float*)probs, counts, ld, T, E, E_loc, ep, me, rank_in_expert, sorted_tok,
+                                                    sorted_probs, chunk_dst_start, chunk_src_start, dst_row_base, list_cap);
+  else { msb_set_error("moe_build_plan: unsupported probability dtype %d", probs_dtype); return 2; }
+  MSB_CHECK_LAUNCH("moe_build_plan");
+  return 0;
+}
+

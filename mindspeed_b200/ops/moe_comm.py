@@ -84,12 +84,14 @@ class RoutingPlan:
     routes to global expert e (identical on every rank)."""
 
     def __init__(self, routing_map: torch.Tensor, counts: torch.Tensor, ep_rank: int, ep_size: int, n_routed: int,
-                 n_recv: int):
+                 n_recv: Optional[int] = None):
         T, E = routing_map.shape
         E_loc = E // ep_size
         dev = routing_map.device
         self.T, self.E, self.E_loc, self.ep, self.rank = T, E, E_loc, ep_size, ep_rank
-        self.n_routed, self.R = int(n_routed), int(n_recv)
+        # ``n_recv`` (rows this rank receives) may be filled in later: everything else is computed on the device from
+        # ``counts`` without a host read, so the tables and the staging copies can be queued before the one host sync
+        self.n_routed, self.R = int(n_routed), (None if n_recv is None else int(n_recv))
         self.map_u8 = routing_map.to(torch.uint8).contiguous()
         self.rank_in_expert = (torch.cumsum(self.map_u8.to(torch.int32), dim=0, dtype=torch.int32) - 1).contiguous()
         # (expert, token) pairs of this rank in ascending (expert, token) order
@@ -106,6 +108,41 @@ class RoutingPlan:
         per_e = counts.sum(0).view(ep_size, E_loc)
         first_row_of_expert = (torch.cumsum(per_e, dim=1) - per_e).view(-1)       # in the owner's layout
         self.dst_row_base = (first_row_of_expert + counts[:ep_rank].sum(0)).contiguous()
+
+
+def build_plan_fused(routing_map: torch.Tensor, probs: torch.Tensor, counts_ld: torch.Tensor, ep_rank: int, ep_size: int,
+                     n_routed: int) -> "RoutingPlan":
+    """Same tables as ``RoutingPlan(...)`` from ONE kernel launch (csrc/kernels/moe_comm.cu: msb_moe_build_plan).
+    ``counts_ld`` is the all-gathered [ep, ld] int64 matrix whose first E columns are the per-expert counts."""
+    from ._dtypes import code
+    L = loader.require_lib()
+    T, E = routing_map.shape
+    dev = routing_map.device
+    plan = RoutingPlan.__new__(RoutingPlan)
+    plan.T, plan.E, plan.E_loc, plan.ep, plan.rank = T, E, E // ep_size, ep_size, ep_rank
+    plan.n_routed, plan.R = int(n_routed), None
+    plan.map_u8 = routing_map.contiguous().view(torch.uint8) if routing_map.dtype == torch.bool else routing_map.to(torch.uint8).contiguous()
+    plan.rank_in_expert = torch.empty(T, E, dtype=torch.int32, device=dev)
+    cap = list_capacity(T, E)
+    plan.sorted_tok = torch.empty(max(1, plan.n_routed), dtype=torch.int32, device=dev)
+    plan.sorted_probs = torch.empty(max(1, plan.n_routed), dtype=torch.float32, device=dev)
+    n_chunks = plan.E_loc * ep_size
+    tables = torch.empty(2 * n_chunks + 1 + E, dtype=torch.int64, device=dev)
+    plan.chunk_dst_start = tables[:n_chunks + 1]
+    plan.chunk_src_start = tables[n_chunks + 1:2 * n_chunks + 1]
+    plan.dst_row_base = tables[2 * n_chunks + 1:]
+    plan.sorted_flat = None
+    pc = probs.contiguous()
+    if pc.dtype not in (torch.float32, torch.bfloat16):
+        pc = pc.float()
+    cl = counts_ld.contiguous()
+    loader.check(L.msb_moe_build_plan(loader.p(plan.map_u8), loader.p(pc), code(pc.dtype), loader.p(cl), int(cl.shape[1]), T, E, plan.E_loc,
+                                      ep_size, ep_rank, loader.p(plan.rank_in_expert), loader.p(plan.sorted_tok), loader.p(plan.sorted_probs),
+                                      loader.p(plan.chunk_dst_start), loader.p(plan.chunk_src_start), loader.p(plan.dst_row_base),
+                                      ctypes.c_longlong(min(cap, max(1, plan.n_routed))), ctypes.c_void_p(loader.stream_ptr())),
+                 "moe_build_plan")
+    plan._keep = (pc, cl)
+    return plan
 
 
 def _launch(fn_name: str, ctx: MoeCommContext, plan: RoutingPlan, out, out_probs, rows_off: int, tok_off: Optional[int],
@@ -177,15 +214,28 @@ def _stage_combine(ctx: MoeCommContext, plan: RoutingPlan, y: torch.Tensor, row_
     return off, (vals_off if row_vals is not None else None)
 
 
+def prestage_dispatch(comm: MoeCommContext, plan: RoutingPlan, x: torch.Tensor, probs: torch.Tensor):
+    """Queue the staging copies of a dispatch (hidden states, sorted token list, sorted probabilities) ahead of the
+    host synchronisation that determines the output size; returns the slot offsets for ``dispatch(..., staged=...)``."""
+    with torch.no_grad():
+        sorted_probs = plan.sorted_probs if getattr(plan, "sorted_probs", None) is not None \
+            else probs.reshape(-1)[plan.sorted_flat].float()
+        return _stage_dispatch(comm, plan, x.detach().contiguous(), sorted_probs)
+
+
 class _Dispatch(torch.autograd.Function):
     """(x [T,H], probs [T,E]) -> (rows [R,H] in expert order, row probabilities [R])."""
 
     @staticmethod
-    def forward(ctx, x, probs, comm: MoeCommContext, plan: RoutingPlan, cap_rows: int):
+    def forward(ctx, x, probs, comm: MoeCommContext, plan: RoutingPlan, cap_rows: int, staged=None):
         ctx.comm, ctx.plan, ctx.cap_rows = comm, plan, cap_rows
         ctx.x_dtype, ctx.p_dtype, ctx.H = x.dtype, probs.dtype, x.shape[1]
-        sorted_probs = probs.reshape(-1)[plan.sorted_flat].float()
-        off, tok_off, probs_off = _stage_dispatch(comm, plan, x.contiguous(), sorted_probs)
+        if staged is not None:
+            off, tok_off, probs_off = staged
+        else:
+            sorted_probs = plan.sorted_probs if getattr(plan, "sorted_probs", None) is not None \
+                else probs.reshape(-1)[plan.sorted_flat].float()
+            off, tok_off, probs_off = _stage_dispatch(comm, plan, x.contiguous(), sorted_probs)
         out = torch.empty(plan.R, x.shape[1], dtype=x.dtype, device=x.device)
         out_probs = torch.empty(plan.R, dtype=torch.float32, device=x.device)
         _launch("msb_moe_dispatch", comm, plan, out, out_probs, off, tok_off, probs_off, x.shape[1] * x.element_size())
@@ -201,7 +251,7 @@ class _Dispatch(torch.autograd.Function):
         dprobs = torch.zeros(plan.T, plan.E, dtype=torch.float32, device=d_rows.device) if vals is not None else None
         _launch("msb_moe_combine", comm, plan, dx, dprobs, off, None, vals_off, ctx.H * d_rows.element_size(),
                 ctx.cap_rows)
-        return dx, (dprobs.to(ctx.p_dtype) if dprobs is not None else None), None, None, None
+        return dx, (dprobs.to(ctx.p_dtype) if dprobs is not None else None), None, None, None, None
 
 
 class _Combine(torch.autograd.Function):
@@ -226,8 +276,8 @@ class _Combine(torch.autograd.Function):
         return dy, None, None, None
 
 
-def dispatch(x, probs, comm, plan, cap_rows):
-    return _Dispatch.apply(x, probs, comm, plan, cap_rows)
+def dispatch(x, probs, comm, plan, cap_rows, staged=None):
+    return _Dispatch.apply(x, probs, comm, plan, cap_rows, staged)
 
 
 def combine(y, comm, plan, cap_rows):

@@ -39,7 +39,8 @@ class FusedAlltoAllTokenDispatcher(MoEAlltoAllTokenDispatcher):
 
     def _eligible(self, h: torch.Tensor) -> bool:
         return (h.is_cuda and h.dtype == torch.bfloat16 and 2 <= self.ep_size <= MC.MAX_RANKS
-                and (h.shape[1] * h.element_size()) % 16 == 0 and self.num_experts == self.num_local_experts * self.ep_size)
+                and (h.shape[1] * h.element_size()) % 16 == 0 and self.num_experts == self.num_local_experts * self.ep_size
+                and getattr(self.config, "moe_expert_capacity_factor", None) is None)   # token dropping: library path
 
     def _counts(self, routing_map, T):
         """[ep, E + 1] on the device: per-expert counts of every source rank, last column = its token count."""
@@ -59,27 +60,32 @@ class FusedAlltoAllTokenDispatcher(MoEAlltoAllTokenDispatcher):
         T, H = h.shape
         E, E_loc, ep = self.num_experts, self.num_local_experts, self.ep_size
         allc = self._counts(routing_map, T)
+        topk = int(getattr(self.config, "moe_router_topk", 1) or 1)
+        cap_rows = self._capacity_rows(T)
+        if self._comm is None:
+            self._comm = MC.context(self.ep_group, MC.slot_bytes_needed(T, H, E, cap_rows, h.element_size()))
+        # index tables and staging copies are queued BEFORE the host read of the counts, so the GPU works through them
+        # while the host waits; only the output allocation and the kernel launch depend on host-side numbers
+        plan = MC.build_plan_fused(routing_map, probs.reshape(T, E), allc, self.ep_rank, ep, T * topk)
+        staged = MC.prestage_dispatch(self._comm, plan, h, probs.reshape(T, E))
         host = allc.cpu()                                              # the one host synchronisation of the layer
         if not bool((host[:, E] == T).all()):
             raise NotImplementedError("the fused MoE dispatcher needs the same number of tokens on every expert-parallel rank")
         counts_h = host[:, :E]
+        if int(counts_h[self.ep_rank].sum()) != T * topk:
+            raise NotImplementedError("the fused MoE dispatcher needs exactly top-k routed experts per token")
         recv_per_rank = counts_h.reshape(ep, ep, E_loc).sum(dim=(0, 2))   # rows every owner receives
-        cap_rows = self._capacity_rows(T)
         lo = self.ep_rank * E_loc
-        per_src_expert = counts_h[:, lo:lo + E_loc]
-        tokens_per_expert = per_src_expert.sum(0)
+        tokens_per_expert = counts_h[:, lo:lo + E_loc].sum(0)
         if int(recv_per_rank.max()) > cap_rows:
-            # same decision on every rank; reuse the counts for the library path's split sizes
+            # same decision on every rank (all see the same count matrix); the staged slot is simply not used
             self._fused_now = False
             self.fallback_calls += 1
             return super().token_permutation(hidden, probs, routing_map)
-        if self._comm is None:
-            self._comm = MC.context(self.ep_group, MC.slot_bytes_needed(T, H, E, cap_rows, h.element_size()))
-        plan = MC.RoutingPlan(routing_map, allc[:, :E], self.ep_rank, ep, int(counts_h[self.ep_rank].sum()),
-                              int(recv_per_rank[self.ep_rank]))
+        plan.R = int(recv_per_rank[self.ep_rank])
         self._plan, self._cap_rows, self._fused_now = plan, cap_rows, True
         self.fused_calls += 1
-        rows, row_probs = MC.dispatch(h, probs.reshape(T, E), self._comm, plan, cap_rows)
+        rows, row_probs = MC.dispatch(h, probs.reshape(T, E), self._comm, plan, cap_rows, staged)
         return rows, tokens_per_expert, row_probs
 
     def token_unpermutation(self, expert_out, bias=None):
