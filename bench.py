@@ -256,6 +256,9 @@ def main():
         print(json.dumps(out))
     if world > 1:
         dist.barrier()
+    if dist.is_initialized():
+        from mindspeed_b200.parallel.symm_mem import destroy_heaps
+        destroy_heaps()
         dist.destroy_process_group()
     return 0
 
