@@ -1,6 +1,6 @@
 """Kernel micro-benchmarks with roofline fractions.
 
-  python -m mindspeed_b200.ops.microbench [gemm|elementwise|attention|all] [--json out.json]
+  python -m mindspeed_b200.ops.microbench [gemm|fp8|elementwise|attention|all] [--json out.json]
 
 Timing: CUDA events on the launching stream, >= 3 warm-up launches, L2 flushed (a 256 MB buffer is rewritten)
 between timed launches, median of the timed launches.  Fractions are relative to the measured copy bandwidth
@@ -106,6 +106,22 @@ def bench_elementwise(out):
     rec("adam_flat", time_fn(lambda: adam_flat(p, gg, m, v, p16, 1e-4, 0.9, 0.95, 1e-8, 0.1, 1), iters=5), n * (4 * 4 + 3 * 4 + 2))
 
 
+def bench_fp8(out):
+    """Block-scaled fp8 GEMM (1x128 activation scales, 128x128 weight scales) on the layer shapes; fractions are of the
+    measured *bf16* cuBLAS peak (no fp8 library figure is recorded), so 1.0 means parity with bf16 at half the bytes."""
+    from . import gemm_fp8 as F
+    from .quant import quant_128x128, quant_1x128
+    pk = measured_peaks()
+    for name, M, N, K in (("fc1_fwd_tp1", 8192, 28672, 4096), ("fc2_fwd_tp1", 8192, 4096, 14336), ("fc1_fwd_tp8", 8192, 3584, 4096),
+                          ("expert_fc1", 16384, 3072, 4096), ("square_8k", 8192, 8192, 8192)):
+        xq, xs = quant_1x128(torch.randn(M, K, device="cuda"))
+        wq, ws = quant_128x128(torch.randn(N, K, device="cuda") * 0.05)
+        ms = time_fn(lambda: F.fp8_gemm(xq, xs, wq, ws))
+        tf = 2.0 * M * N * K / ms / 1e9
+        out.append({"kernel": "gemm_fp8_blockscaled", "case": name, "ms": ms, "tflops": tf, "frac_of_bf16_peak": tf / pk["bf16_tflops"]})
+        print(f"{name:14s} fp8_blockscaled  {ms:8.3f} ms  {tf:8.1f} TFLOP/s  {tf / pk['bf16_tflops']:.2f} of measured bf16 peak", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", nargs="?", default="all")
@@ -114,6 +130,8 @@ def main():
     out = []
     if a.what in ("gemm", "all"):
         bench_gemm(out)
+    if a.what in ("fp8", "all"):
+        bench_fp8(out)
     if a.what in ("elementwise", "all"):
         bench_elementwise(out)
     if a.what in ("attention", "all"):
