@@ -1,6 +1,6 @@
 """Kernel micro-benchmarks with roofline fractions.
 
-  python -m mindspeed_b200.ops.microbench [gemm|fp8|elementwise|attention|all] [--json out.json]
+  python -m mindspeed_b200.benchmarks.microbench [gemm|fp8|elementwise|attention|all] [--json out.json]
 
 Timing: CUDA events on the launching stream, >= 3 warm-up launches, L2 flushed (a 256 MB buffer is rewritten)
 between timed launches, median of the timed launches.  Fractions are relative to the measured copy bandwidth
@@ -16,7 +16,7 @@ import sys
 
 import torch
 
-from . import loader
+from ..ops import loader
 from ..training.flops import measured_peaks
 
 
@@ -45,8 +45,8 @@ def time_fn(fn, iters=10, warmup=3, flush=True):
     return statistics.median(ts)
 
 
-def bench_gemm(out):
-    from . import gemm as G
+def bench_gemm(out, variants=False):
+    from ..ops import gemm as G
     pk = measured_peaks()
     shapes = [("qkv_fwd_tp1", 8192, 6144, 4096), ("fc1_fwd_tp1", 8192, 28672, 4096), ("fc2_fwd_tp1", 8192, 4096, 14336),
               ("proj_fwd_tp1", 8192, 4096, 4096), ("qkv_fwd_tp8", 8192, 768, 4096), ("fc1_fwd_tp8", 8192, 3584, 4096),
@@ -58,6 +58,12 @@ def bench_gemm(out):
         acc = torch.zeros(N, K, device="cuda", dtype=torch.float32)
         fl = 2.0 * M * N * K
         rows = {}
+        if variants:      # every kernel variant side by side (1 = one-CTA, 2 / 3 = CTA pair 256x256 / 256x128)
+            for v in (1, 2, 3):
+                with G.variant(v):
+                    rows[f"fwd_v{v}"] = time_fn(lambda: G.linear_fwd(x, w))
+                    rows[f"dgrad_v{v}"] = time_fn(lambda: G.linear_dgrad(dy, w))
+                    rows[f"wgrad_v{v}"] = time_fn(lambda: G.linear_wgrad(dy, x, acc))
         rows["fwd_ours"] = time_fn(lambda: G.linear_fwd(x, w))
         rows["fwd_cublas"] = time_fn(lambda: torch.matmul(x, w.t()))
         rows["dgrad_ours"] = time_fn(lambda: G.linear_dgrad(dy, w))
@@ -73,10 +79,10 @@ def bench_gemm(out):
 
 
 def bench_elementwise(out):
-    from .activation import swiglu
-    from .norm import rms_norm
-    from .rope import rope_packed_qkv_
-    from .adam import adam_flat
+    from ..ops.activation import swiglu
+    from ..ops.norm import rms_norm
+    from ..ops.rope import rope_packed_qkv_
+    from ..ops.adam import adam_flat
     pk = measured_peaks()
     rows, h = 8192, 4096
 
@@ -109,8 +115,8 @@ def bench_elementwise(out):
 def bench_fp8(out):
     """Block-scaled fp8 GEMM (1x128 activation scales, 128x128 weight scales) on the layer shapes; fractions are of the
     measured *bf16* cuBLAS peak (no fp8 library figure is recorded), so 1.0 means parity with bf16 at half the bytes."""
-    from . import gemm_fp8 as F
-    from .quant import quant_128x128, quant_1x128
+    from ..ops import gemm_fp8 as F
+    from ..ops.quant import quant_128x128, quant_1x128
     pk = measured_peaks()
     for name, M, N, K in (("fc1_fwd_tp1", 8192, 28672, 4096), ("fc2_fwd_tp1", 8192, 4096, 14336), ("fc1_fwd_tp8", 8192, 3584, 4096),
                           ("expert_fc1", 16384, 3072, 4096), ("square_8k", 8192, 8192, 8192)):
@@ -128,8 +134,8 @@ def main():
     ap.add_argument("--json", default=None)
     a = ap.parse_args()
     out = []
-    if a.what in ("gemm", "all"):
-        bench_gemm(out)
+    if a.what in ("gemm", "gemm_variants", "all"):
+        bench_gemm(out, variants=(a.what == "gemm_variants"))
     if a.what in ("fp8", "all"):
         bench_fp8(out)
     if a.what in ("elementwise", "all"):

@@ -1,4 +1,4 @@
-"""Attention micro-benchmark: tcgen05 forward vs the framework library (part of ``ops.microbench``)."""
+"""Attention micro-benchmark: tcgen05 forward vs the framework library (part of ``benchmarks.microbench``)."""
 import torch
 
 from ..training.flops import measured_peaks
@@ -6,7 +6,7 @@ from .microbench import time_fn
 
 
 def bench_attention(out):
-    from .flash_sm100_impl import flash_fwd
+    from ..ops.flash_sm100_impl import flash_fwd
     pk = measured_peaks()
     for (s, nq, nkv) in [(8192, 32, 8), (8192, 4, 1), (4096, 32, 8), (16384, 8, 2)]:
         q = torch.randn(s, 1, nq, 128, device="cuda", dtype=torch.bfloat16)

@@ -1,7 +1,7 @@
 """Multi-GPU micro-benchmark of the fused GEMM + collective kernels against the library path.
 
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
-      -m mindspeed_b200.ops.microbench_comm [--json out.json] [--seq 8192]
+      -m mindspeed_b200.benchmarks.microbench_comm [--json out.json] [--seq 8192]
 
 For each tensor-parallel linear of a Llama-3-8B-shape layer at TP = N it times, on every rank,
 
@@ -66,8 +66,8 @@ def main():
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     group = dist.group.WORLD
-    from . import loader
-    from .fused_comm import FusedOps
+    from ..ops import loader
+    from ..ops.fused_comm import FusedOps
     from ..parallel.comm_ops import DefaultOps
     from ..training.flops import measured_peaks
     L = loader.require_lib()

@@ -1,7 +1,7 @@
 """Multi-GPU micro-benchmark of MoE token dispatch + combine: peer-memory kernels against NCCL all-to-all-v.
 
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
-      -m mindspeed_b200.ops.microbench_moe [--tokens 4096] [--hidden 4096] [--experts 8] [--topk 2] [--json out.json]
+      -m mindspeed_b200.benchmarks.microbench_moe [--tokens 4096] [--hidden 4096] [--experts 8] [--topk 2] [--json out.json]
 
 Every rank routes ``tokens`` rows of width ``hidden`` (bf16) to ``topk`` of ``experts`` experts spread over the N ranks
 (uniform random routing, fixed seed).  Timed per rank with CUDA events (3 warm-up rounds, L2 flushed and a barrier
@@ -43,8 +43,8 @@ def main():
     from ..parallel import parallel_state as ps
     from ..parallel.moe.fused_dispatcher import FusedAlltoAllTokenDispatcher
     from ..parallel.moe.token_dispatcher import MoEAlltoAllTokenDispatcher
-    from . import gemm as G
-    from . import loader
+    from ..ops import gemm as G
+    from ..ops import loader
     ps.initialize_model_parallel(expert_model_parallel_size=world)
     L = loader.require_lib()
     cfg = TransformerConfig(num_layers=1, hidden_size=a.hidden, num_attention_heads=8, ffn_hidden_size=a.hidden, num_moe_experts=a.experts,

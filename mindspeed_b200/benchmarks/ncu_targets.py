@@ -1,9 +1,9 @@
 """Small, self-terminating workloads for Nsight Compute captures of single kernels.
 
-  python -m mindspeed_b200.ops.ncu_targets gemm        # 3 launches each of fwd / dgrad / wgrad, 8192^3 bf16
-  python -m mindspeed_b200.ops.ncu_targets elementwise # rmsnorm / swiglu / rope / adam / cross-entropy once each
-  python -m mindspeed_b200.ops.ncu_targets fp8         # 3 launches of the block-scaled fp8 GEMM, 8192 x 8192 x 8192
-  python -m mindspeed_b200.ops.ncu_targets gemm_tp8    # the four forward GEMM shapes of a Llama-3-8B layer at TP8
+  python -m mindspeed_b200.benchmarks.ncu_targets gemm        # 3 launches each of fwd / dgrad / wgrad, 8192^3 bf16
+  python -m mindspeed_b200.benchmarks.ncu_targets elementwise # rmsnorm / swiglu / rope / adam / cross-entropy once each
+  python -m mindspeed_b200.benchmarks.ncu_targets fp8         # 3 launches of the block-scaled fp8 GEMM, 8192 x 8192 x 8192
+  python -m mindspeed_b200.benchmarks.ncu_targets gemm_tp8    # the four forward GEMM shapes of a Llama-3-8B layer at TP8
 
 Inputs exceed the 126 MB L2 but stay well under 2 GB on the device; there are only a handful of launches, so a
 ``--set full`` capture ends by itself within a minute or two.
@@ -14,7 +14,7 @@ import torch
 
 
 def gemm():
-    from . import gemm as G
+    from ..ops import gemm as G
     M = N = K = 8192
     x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
     w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
@@ -29,11 +29,11 @@ def gemm():
 
 
 def elementwise():
-    from .activation import swiglu
-    from .adam import adam_flat
-    from .cross_entropy import fused_vocab_parallel_cross_entropy
-    from .norm import rms_norm
-    from .rope import rope_packed_qkv_
+    from ..ops.activation import swiglu
+    from ..ops.adam import adam_flat
+    from ..ops.cross_entropy import fused_vocab_parallel_cross_entropy
+    from ..ops.norm import rms_norm
+    from ..ops.rope import rope_packed_qkv_
     rows, h = 16384, 4096
     x = torch.randn(rows, h, device="cuda", dtype=torch.bfloat16, requires_grad=True)
     w = torch.ones(h, device="cuda", dtype=torch.bfloat16, requires_grad=True)
@@ -56,9 +56,9 @@ def elementwise():
 
 
 def fp8():
-    from . import gemm as G
-    from . import gemm_fp8 as F
-    from .quant import quant_128x128, quant_1x128
+    from ..ops import gemm as G
+    from ..ops import gemm_fp8 as F
+    from ..ops.quant import quant_128x128, quant_1x128
     M = N = K = 8192
     x = torch.randn(M, K, device="cuda")
     w = torch.randn(N, K, device="cuda") * 0.05
@@ -81,7 +81,7 @@ def fp8():
 
 
 def gemm_tp8():
-    from . import gemm as G
+    from ..ops import gemm as G
     for (M, N, K) in ((8192, 768, 4096), (8192, 3584, 4096), (8192, 4096, 1792), (8192, 4096, 512)):
         x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
         w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)

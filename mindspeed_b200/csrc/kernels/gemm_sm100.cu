@@ -762,6 +762,32 @@ struct MsbGemmArgs {
   int wait_peers_before, signal_peers_after;
 };
 
+namespace msb {
+bool gemm2_eligible(const void* D, long long ldd, int epilogue);
+int gemm2_launch(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, long long lda, long long ldb,
+                 long long ldd, int a_mn, int b_mn, int epilogue, int bn, int max_ctas, int stream_k, unsigned int* status,
+                 cudaStream_t s);
+}
+
+// Kernel choice for the plain GEMM: 0 = by the time model below, 1 = one-CTA kernel (this file), 2 / 3 = CTA-pair kernel
+// (gemm2_sm100.cu) with 256 x 256 / 256 x 128 tiles.  Micro-benchmarks force a variant; training leaves it at 0.
+static int g_variant = 0;
+MSB_API void msb_gemm_set_variant(int v) { g_variant = (v >= 0 && v <= 3) ? v : 0; }
+MSB_API int msb_gemm_get_variant() { return g_variant; }
+
+// The CTA-pair kernel with 256 x 256 tiles wins on every measured layer shape; outputs at most 128 columns wide stay on
+// the one-CTA kernel's 128 x 128 tiles (half-empty 256-wide tiles would waste the tensor pipe).
+static int choose_variant(int M, int N, int sms) {
+  (void)M; (void)sms;
+  return N > 128 ? 2 : 1;
+}
+
+// Weight-gradient accumulation may balance k-blocks over the SMs (partial tiles summed by reduce-adds in an order that
+// varies run to run).  1 = allowed (default), 0 = whole tiles only: bit-reproducible accumulation.
+static int g_stream_k = 1;
+MSB_API void msb_gemm_set_stream_k(int v) { g_stream_k = v ? 1 : 0; }
+MSB_API int msb_gemm_get_stream_k() { return g_stream_k; }
+
 // Process-wide cap on the number of CTAs the persistent GEMM-class kernels launch (0 = no cap).  Two such kernels
 // on different streams share the GPU by SM count when each is capped (one CTA occupies a whole SM here).
 static int g_cta_limit = 0;
@@ -775,6 +801,15 @@ MSB_API int msb_gemm_bf16_ex(const MsbGemmArgs* a, cudaStream_t s) {
   MSB_REQUIRE(a->a_rows_per_src % BM == 0 || a->nsrc == 1, "gemm: rows per A source must be a multiple of %d", BM);
   MSB_REQUIRE(a->d_rows_per_dst % 32 == 0 || a->ndst == 1, "gemm: rows per destination must be a multiple of 32");
   const int sms = msb::num_sms();
+  if (a->nsrc == 1 && a->ndst == 1 && a->world <= 1 && a->m_tile_rot == 0 && a->d_row_offset == 0 && g_variant != 1 &&
+      msb::gemm2_eligible(a->D[0], a->ldd, a->epilogue)) {
+    int cap = a->max_ctas;
+    if (g_cta_limit > 0 && (cap == 0 || cap > g_cta_limit)) cap = g_cta_limit;
+    const int v = g_variant ? g_variant : choose_variant(a->M, a->N, cap > 0 && cap < sms ? cap : sms);
+    if (v != 1)
+      return msb::gemm2_launch(a->A[0], a->B, a->D[0], a->bias, a->M, a->N, a->K, a->lda, a->ldb, a->ldd, a->a_mn_major,
+                               a->b_mn_major, a->epilogue, v == 2 ? 256 : 128, cap, g_stream_k, a->status, s);
+  }
   const int bn = pick_bn(a->M, a->N, sms);
   GemmParams p;
   memset(&p, 0, sizeof(p));

@@ -55,6 +55,30 @@ class cta_limit:
         return False
 
 
+class variant:
+    """``with variant(v):`` force the plain GEMM onto one kernel: 1 = one-CTA kernel, 2 / 3 = CTA-pair kernel with
+    256 x 256 / 256 x 128 tiles, 0 = chosen per shape by the library's time model (the default).  For benchmarks and tests."""
+
+    def __init__(self, v: int):
+        self.v = int(v)
+
+    def __enter__(self):
+        L = loader.require_lib()
+        self.prev = L.msb_gemm_get_variant()
+        L.msb_gemm_set_variant(self.v)
+        return self
+
+    def __exit__(self, *exc):
+        loader.require_lib().msb_gemm_set_variant(self.prev)
+        return False
+
+
+def set_stream_k(on: bool) -> None:
+    """Allow (default) or forbid k-block balancing in the accumulate-into-fp32 weight-gradient GEMM.  Forbidding it
+    makes the accumulation order, hence the result bits, the same on every run."""
+    loader.require_lib().msb_gemm_set_stream_k(1 if on else 0)
+
+
 def supported(*tensors) -> bool:
     if loader.lib() is None:
         return False

@@ -77,6 +77,34 @@ def _default_wd_mult(name, p):
     return 0.0 if no_wd else 1.0
 
 
+def build_segments(bucket, names, lo, hi, cond) -> List[_Segment]:
+    """Hyper-parameter segments of the slice [lo, hi) of a bucket (offsets relative to ``lo``).  Parameters are walked in
+    buffer order (``bucket.params`` is reverse layer order, ascending offset); neighbours with equal
+    (weight-decay multiplier, lr multiplier, counted-in-norm) closer than the 64-element alignment padding merge.
+    Segment ends are rounded up to a multiple of 4 inside that padding (never past ``hi``) because the vectorised
+    kernels work on groups of four; the padding holds zeros with zero gradients, which AdamW leaves at zero.
+    ``cond(name, param) -> (wd_mult, lr_mult, in_norm)``."""
+    out: List[_Segment] = []
+    cur = None
+    for p in bucket.params:
+        ps_, pe_ = bucket.param_ranges[id(p)]
+        s, e = max(ps_, lo), min(pe_, hi)
+        if s >= e:
+            continue
+        e = min(hi, (e + 3) // 4 * 4)
+        wdm, lrm, in_norm = cond(names.get(id(p), ""), p)
+        seg = _Segment(s - lo, e - lo, wdm, lrm, in_norm)
+        if cur is not None and (cur.wd_mult, cur.lr_mult, cur.in_norm) == (wdm, lrm, in_norm) and seg.start - cur.end < 64:
+            cur.end = max(cur.end, seg.end)
+        else:
+            if cur is not None and seg.start < cur.end:     # rounding of the previous end reached into this parameter's padding
+                seg.start = cur.end
+            if seg.start < seg.end:
+                out.append(seg)
+                cur = seg
+    return out
+
+
 class DistributedOptimizer:
     """Works for both sharded (ZeRO-1) and replicated state; exposes the Megatron optimizer surface
     (``step``, ``zero_grad``, ``state_dict``, ``get_loss_scale``, ``param_groups``)."""
@@ -101,27 +129,22 @@ class DistributedOptimizer:
                     for b in buf.buckets:
                         st = _BucketState(buf, b, self.sharded and buf.dp_size > 1, use_master, config.use_ema,
                                           reuse=config.reuse_fp32_param)
-                        # segments: walk params in buffer order (bucket.params is reverse layer order, ascending offset)
-                        cur = None
-                        for p in b.params:
-                            ps_, pe_ = b.param_ranges[id(p)]
-                            lo, hi = max(ps_, st.lo), min(pe_, st.hi)
-                            if lo >= hi:
-                                continue
-                            name = names.get(id(p), "")
+                        def cond(name, p):
                             if no_weight_decay_cond is not None:
                                 wdm = 0.0 if no_weight_decay_cond(name, p) else 1.0
                             else:
                                 wdm = _default_wd_mult(name, p)
                             lrm = lr_mult if (scale_lr_cond is not None and scale_lr_cond(name, p)) else 1.0
                             in_norm = param_is_not_tensor_parallel_duplicate(p) and not getattr(p, "shared", False)
-                            seg = _Segment(lo - st.lo, hi - st.lo, wdm, lrm, in_norm)
-                            if cur is not None and (cur.wd_mult, cur.lr_mult, cur.in_norm) == (wdm, lrm, in_norm) and \
-                                    seg.start - cur.end < 64:
-                                cur.end = seg.end
-                            else:
-                                st.segments.append(seg)
-                                cur = seg
+                            return wdm, lrm, in_norm
+                        st.segments = build_segments(b, names, st.lo, st.hi, cond)
+                        # launches of the fused peer-memory step handshake with every peer, so each rank must issue the
+                        # same number per bucket: the layout is deterministic, every rank can count every rank's segments
+                        st.max_segments = len(st.segments)
+                        if self.sharded and buf.dp_size > 1:
+                            per = b.numel // buf.dp_size
+                            st.max_segments = max(len(build_segments(b, names, b.start + r * per, b.start + (r + 1) * per, cond))
+                                                  for r in range(buf.dp_size))
                         out.append(st)
         dev = self._dev or torch.device("cpu")
         self._norm_sq = torch.zeros(1, dtype=torch.float32, device=dev)
@@ -175,6 +198,8 @@ class DistributedOptimizer:
         on_gpu = self._dev is not None and self._dev.type == "cuda"
         grad_norm = None
         coef_dev, coef_host = None, 1.0
+        if any(getattr(st.buf, "fused", False) for st in self._all_states()):
+            return self._step_fused(lr, wd)      # computes the norm itself, on the reduced gradients
         if cfg.clip_grad > 0.0 or cfg.log_num_zeros_in_grad:
             nsq = self._grad_norm_sq()
             if on_gpu:
@@ -187,8 +212,6 @@ class DistributedOptimizer:
                 if not math.isfinite(nrm):
                     return False, grad_norm, None
                 coef_host = min(1.0, cfg.clip_grad / (nrm + 1e-6)) if cfg.clip_grad > 0 else 1.0
-        if any(getattr(st.buf, "fused", False) for st in self._all_states()):
-            return self._step_fused(lr, wd)
         for st in self._all_states():
             for sg in st.segments:
                 sl = slice(sg.start, sg.end)
@@ -250,6 +273,12 @@ class DistributedOptimizer:
             loader.check(L.msb_dist_opt_fused(ctypes.byref(a), ctypes.c_void_p(loader.stream_ptr())), "dist_opt_fused")
             st.last_epoch = a.epoch
 
+        def padded(st):
+            """This rank's segments followed by empty ones up to the group-wide maximum for the bucket: an empty launch
+            still performs the entry handshake and the exit flag, so every rank's epoch sequence is the same."""
+            empty = _Segment(0, 0, 0.0, 1.0, False)
+            return list(st.segments) + [empty] * (getattr(st, "max_segments", len(st.segments)) - len(st.segments))
+
         states = [st for st in self._all_states()]
         for st in states:
             if not getattr(st.buf, "fused", False) or st.residual is not None or st.master is None:
@@ -261,7 +290,7 @@ class DistributedOptimizer:
         if clip:
             self._norm_sq.zero_()
             for st in states:
-                for sg in st.segments:
+                for sg in padded(st):
                     launch(st, sg, True, False, False, False)
             dist.all_reduce(self._norm_sq, group=ps.get_data_parallel_group(with_context_parallel=True))
             mp = ps.get_model_parallel_group()
@@ -270,11 +299,11 @@ class DistributedOptimizer:
             adam_ops.clip_coef(self._norm_sq, cfg.clip_grad, self._coef, self._found_inf, self._norm)
             grad_norm = self._norm
             for st in states:
-                for sg in st.segments:
+                for sg in padded(st):
                     launch(st, sg, False, True, True, True)
         else:
             for st in states:
-                for sg in st.segments:
+                for sg in padded(st):
                     launch(st, sg, True, True, True, False)
         for st in states:                    # the next forward reads the parameter buffer: wait (bounded) for every peer's pushes
             h = st.buf.heap

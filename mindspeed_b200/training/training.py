@@ -253,6 +253,15 @@ def training_log(loss_dict, iteration, elapsed, grad_norm, skipped, lr):
     print_rank_last(msg)
 
 
+def check_kernel_status():
+    """Raise if a device-side bounded wait expired since the last check (GEMM mbarriers, all-gather / reduce-scatter
+    flags, MoE, Ulysses, fused optimizer step): such a kernel returns early with its outputs not computed, so the step
+    that contained it is invalid.  The RuntimeError names the wait's code and reaches the TTP exception handler.
+    Call after the step's synchronize; costs one 4-byte read per device that has launched such kernels."""
+    from ..ops import gemm as G
+    G.check_status()
+
+
 def train(forward_step_func, model, optimizer, opt_param_scheduler, train_data_iterator, process_non_loss_data_func=None):
     args = get_args()
     for m in model:
@@ -271,6 +280,7 @@ def train(forward_step_func, model, optimizer, opt_param_scheduler, train_data_i
         iteration += 1
         if torch.cuda.is_available() and next(model[0].parameters()).is_cuda:
             torch.cuda.synchronize()
+        check_kernel_status()
         elapsed = time.time() - t0
         if prof is not None:
             prof.step()

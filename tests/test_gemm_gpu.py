@@ -67,3 +67,72 @@ def test_bias_epilogue_and_determinism():
     G.check_status()
     assert torch.equal(y1, y2)
     assert _rel(y1, x.float() @ w.float().t() + b.float()) < 1e-2
+
+
+EDGE = [(130, 264, 72), (1000, 776, 520), (300, 136, 200), (256, 256, 64), (8192, 768, 512)]
+
+
+@pytest.mark.parametrize("v", [1, 2, 3])
+@pytest.mark.parametrize("M,N,K", EDGE)
+def test_every_kernel_variant_elementwise(v, M, N, K):
+    """Each kernel (one-CTA, CTA pair 256x256, CTA pair 256x128) against the fp32 product rounded to bf16, element by
+    element, on shapes with ragged M / N / K tiles; weight-gradient accumulation into fp32 twice."""
+    from mindspeed_b200.ops import gemm as G
+    torch.manual_seed(10 + v)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    dy = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    acc = torch.full((N, K), 0.5, device="cuda", dtype=torch.float32)
+    f32 = torch.empty(M, N, device="cuda", dtype=torch.float32)
+    with G.variant(v):
+        y = G.linear_fwd(x, w)
+        dx = G.linear_dgrad(dy, w)
+        dw = G.linear_wgrad(dy, x)
+        G.linear_wgrad(dy, x, acc)
+        G.linear_wgrad(dy, x, acc)
+        G._gemm(x, w, f32, M, N, K, K, K, N, 0, 0, G.EPI_F32)
+    torch.cuda.synchronize()
+    G.check_status()
+    # fp32 accumulation order differs from the reference's: allow one bf16 ulp of the result (2^-8 relative) plus a
+    # small absolute term for cancellation
+    for got, ref in ((y, x.float() @ w.float().t()), (dx, dy.float() @ w.float()), (dw, dy.float().t() @ x.float())):
+        torch.testing.assert_close(got.float(), ref, rtol=8e-3, atol=2e-2 * ref.abs().mean().item())
+    torch.testing.assert_close(f32, x.float() @ w.float().t(), rtol=1e-4, atol=1e-3 * (K ** 0.5))
+    torch.testing.assert_close(acc, 0.5 + 2 * (dy.float().t() @ x.float()), rtol=1e-4, atol=2e-3 * (M ** 0.5))
+
+
+def test_pair_kernel_bias_and_strided_output():
+    from mindspeed_b200.ops import gemm as G
+    torch.manual_seed(5)
+    x = torch.randn(640, 320, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(200, 320, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(200, device="cuda", dtype=torch.bfloat16)
+    with G.variant(2):
+        y = G.linear_fwd(x, w, bias=b)
+    torch.cuda.synchronize()
+    G.check_status()
+    torch.testing.assert_close(y.float(), x.float() @ w.float().t() + b.float(), rtol=8e-3, atol=0.3)
+
+
+def test_weight_gradient_accumulation_reproducible_without_stream_k():
+    from mindspeed_b200.ops import gemm as G
+    torch.manual_seed(6)
+    dy = torch.randn(4096, 1536, device="cuda", dtype=torch.bfloat16)
+    x = torch.randn(4096, 1024, device="cuda", dtype=torch.bfloat16)
+    ref = dy.float().t() @ x.float()
+    outs = []
+    G.set_stream_k(False)
+    try:
+        for _ in range(2):
+            acc = torch.zeros(1536, 1024, device="cuda", dtype=torch.float32)
+            G.linear_wgrad(dy, x, acc)
+            outs.append(acc)
+    finally:
+        G.set_stream_k(True)
+    acc = torch.zeros(1536, 1024, device="cuda", dtype=torch.float32)
+    G.linear_wgrad(dy, x, acc)                      # k-block balanced: same value up to fp32 summation order
+    torch.cuda.synchronize()
+    G.check_status()
+    assert torch.equal(outs[0], outs[1])
+    torch.testing.assert_close(outs[0], ref, rtol=1e-4, atol=0.05)
+    torch.testing.assert_close(acc, ref, rtol=1e-4, atol=0.05)
