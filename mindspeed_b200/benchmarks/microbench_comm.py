@@ -8,10 +8,9 @@ For each tensor-parallel linear of a Llama-3-8B-shape layer at TP = N it times, 
   fused   : one launch of the all-gather->GEMM kernel, or the GEMM->reduce-scatter kernel plus its owner-side sum
   library : NCCL all_gather_into_tensor + cuBLAS GEMM, or cuBLAS GEMM + NCCL reduce_scatter_tensor
 
-with CUDA events on the launching stream (3 warm-up launches, a 256 MB buffer rewritten between timed launches so
-that operands start outside L2, a barrier before each timed launch, and a short device-side delay in front of the
-first event so that the measured interval is device execution, not host launch latency) and reports the maximum
-over ranks of the per-rank median.  The roofline for a fused kernel is the slower of
+with CUDA events on the launching stream: 3 warm-up launches, then 10 x (256 MB buffer rewritten so that operands start
+outside L2, one call) back to back after a barrier and a device-side delay that lets the host queue the loop, minus the
+same loop with the rewrite alone; median of 3 such measurements, maximum over ranks.  The roofline for a fused kernel is the slower of
 
   FLOPs / measured cuBLAS bf16 peak           and           bytes that must cross NVLink per GPU / 770 GB/s
 
@@ -32,24 +31,32 @@ import torch.distributed as dist
 NVLINK_GBS = 770.0
 
 
-def _timed(fn, group, flush_buf, L, loader, iters=8, warmup=3):
+def _timed(fn, group, flush_buf, L, loader, iters=10, warmup=3):
+    """Steady-state time of one call: ``iters`` x (L2 flush + call) back to back between two events, minus the same loop
+    with the flush alone.  A device-side delay in front of the first event lets the host queue the whole loop first, so
+    the interval is device execution; ranks start together after a barrier and stay together through the collective
+    itself, so start-up skew is paid once per loop, not once per call."""
     for _ in range(warmup):
         fn()
-    ts = []
-    for _ in range(iters):
-        L.msb_l2_flush(ctypes.c_void_p(flush_buf.data_ptr()), ctypes.c_size_t(flush_buf.numel()),
-                       ctypes.c_void_p(loader.stream_ptr()))
+
+    def loop(with_fn):
         torch.cuda.synchronize()
         dist.barrier(group)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda._sleep(1_000_000)   # ~0.5 ms of device idle so the host has queued everything before e0 is reached
+        torch.cuda._sleep(12_000_000)
         e0.record()
-        fn()
+        for _ in range(iters):
+            L.msb_l2_flush(ctypes.c_void_p(flush_buf.data_ptr()), ctypes.c_size_t(flush_buf.numel()),
+                           ctypes.c_void_p(loader.stream_ptr()))
+            if with_fn:
+                fn()
         e1.record()
         torch.cuda.synchronize()
-        ts.append(e0.elapsed_time(e1))
-    t = torch.tensor([statistics.median(ts)], device="cuda")
+        return e0.elapsed_time(e1) / iters
+
+    ts = sorted(loop(True) - loop(False) for _ in range(3))
+    t = torch.tensor([ts[1]], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     return float(t.item())
 

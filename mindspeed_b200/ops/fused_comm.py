@@ -42,12 +42,42 @@ def _buf_bytes(request):
     return max(request, int(os.environ.get("MSB200_SYMM_BUF_MIB", 128)) * 1024 * 1024)
 
 
+class _Comm2Args(ctypes.Structure):
+    """Arguments of the CTA-pair fused kernels (csrc/kernels/gemm2_comm_sm100.cu, struct MsbComm2Args)."""
+    _fields_ = [("A", ctypes.c_void_p), ("B", ctypes.c_void_p), ("D", ctypes.c_void_p),
+                ("peer_buf", ctypes.c_void_p * MAX_SRC), ("residual", ctypes.c_void_p), ("ar_out", ctypes.c_void_p * MAX_SRC),
+                ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("b_mn_major", ctypes.c_int),
+                ("world", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_uint),
+                ("flag_local", ctypes.c_void_p), ("flag_peer", ctypes.c_void_p * MAX_SRC), ("status", ctypes.c_void_p),
+                ("wait_limit_ms", ctypes.c_int), ("max_ctas", ctypes.c_int)]
+
+
+MODE_AG, MODE_RS = 1, 2
+# 0: CTA-pair kernels wherever they cover the shape (default); 1: always the one-CTA fused kernels (comparisons)
+_FORCE_ONE_CTA = os.environ.get("MSB200_FUSED_ONE_CTA", "0") != "0"
+WAIT_LIMIT_MS = int(os.environ.get("MSB200_COMM_WAIT_MS", "10000"))
+
+
+def _pair_ok(L, m, n, k, ws, mode) -> bool:
+    return (not _FORCE_ONE_CTA) and bool(L.msb_gemm2_comm_supported(m, n, k, ws, mode))
+
+
 class _Ctx:
     """Per-process-group state: heap, buffer offsets, call parity."""
 
     def __init__(self, group):
         self.heap: SymmetricHeap = get_heap(group, _heap_bytes())
         self.ag_calls = 0
+
+    def fill_pair(self, a: _Comm2Args, epoch: int, dev):
+        h = self.heap
+        a.world, a.rank, a.epoch = h.world, h.rank, epoch
+        a.flag_local = h.ptr(h.rank, 0)
+        for r in range(h.world):
+            a.flag_peer[r] = h.ptr(r, 0)
+        a.status = G.status_word(dev).data_ptr()
+        a.wait_limit_ms = WAIT_LIMIT_MS
+        a.max_ctas = 0
 
     def fill_common(self, a: _CommArgs, epoch: int, dev):
         h = self.heap
@@ -127,13 +157,18 @@ class FusedOps(Sm100Ops):
         gathered[h.rank * rows:(h.rank + 1) * rows].copy_(x2)
         lead = (x.shape[0] * ws,) + tuple(x.shape[1:-1])
         y = torch.empty(*lead, n, dtype=torch.bfloat16, device=x.device)   # final shape: custom Functions must not return views
-        a = _CommArgs()
+        pair = _pair_ok(L, m, n, k, ws, MODE_AG)
+        a = _Comm2Args() if pair else _CommArgs()
         a.A, a.B, a.D = h.ptr(h.rank, off), w.data_ptr(), y.data_ptr()
         for r in range(ws):
             a.peer_buf[r] = h.ptr(r, off)
         a.M, a.N, a.K, a.b_mn_major = m, n, k, 0 if nt else 1
-        c.fill_common(a, h.next_epoch(), x.device)
-        loader.check(L.msb_gemm_allgather(ctypes.byref(a), ctypes.c_void_p(loader.stream_ptr())), "gemm_allgather")
+        if pair:
+            c.fill_pair(a, h.next_epoch(), x.device)
+            loader.check(L.msb_gemm2_allgather(ctypes.byref(a), ctypes.c_void_p(loader.stream_ptr())), "gemm2_allgather")
+        else:
+            c.fill_common(a, h.next_epoch(), x.device)
+            loader.check(L.msb_gemm_allgather(ctypes.byref(a), ctypes.c_void_p(loader.stream_ptr())), "gemm_allgather")
         total = gathered.view(*lead, k) if need_gathered else None
         return y, total
 
@@ -146,6 +181,10 @@ class FusedOps(Sm100Ops):
         n = w.shape[0] if nt else w.shape[1]
         if ws < 2 or not cls._eligible(x, w, group, x2.shape[0], n, x2.shape[1]):
             return Sm100Ops.matmul_all_reduce(x, w, group, nt)
+        if _pair_ok(loader.require_lib(), x2.shape[0], n, x2.shape[1], ws, MODE_RS) and x2.is_contiguous() and x2.data_ptr() % 16 == 0:
+            # one kernel: tiles -> owners' staging -> fp32 sum -> reduced rows written into every rank's output
+            full = cls._pair_reduce_scatter(_ctx(group), x, x2, w, x2.shape[0], n, x2.shape[1], nt, None, all_reduce=True)
+            return full.view(*x.shape[:-1], n)
         part = cls.matmul_reduce_scatter(x2, w, group, nt)
         full = torch.empty(x2.shape[0], n, dtype=part.dtype, device=part.device)
         dist.all_gather_into_tensor(full, part.contiguous(), group=group)
@@ -176,6 +215,37 @@ class FusedOps(Sm100Ops):
         return h, y
 
     @classmethod
+    def _pair_reduce_scatter(cls, c, x, x2, w, m, n, k, nt, residual, all_reduce):
+        """GEMM -> reduce-scatter (-> all-gather) on the CTA-pair kernel: tiles go from the epilogue straight into the
+        owners' staging slabs, the tail of the same kernel sums the slabs (+ residual).  With ``all_reduce`` the reduced
+        rows are also written into every rank's copy of a symmetric [m, n] buffer, which is returned as a fresh tensor."""
+        L = loader.require_lib()
+        h = c.heap
+        ws, rows = h.world, m // h.world
+        off_stage = h.alloc("rs_stage", _buf_bytes(m * n * 2))
+        a = _Comm2Args()
+        a.A, a.B = x2.data_ptr(), w.data_ptr()
+        for r in range(ws):
+            a.peer_buf[r] = h.ptr(r, off_stage)
+        a.M, a.N, a.K, a.b_mn_major = m, n, k, 0 if nt else 1
+        a.residual = residual.data_ptr() if residual is not None else None
+        out = None
+        if all_reduce:
+            off_ar = h.alloc("ar_out", _buf_bytes(m * n * 2))
+            for r in range(ws):
+                a.ar_out[r] = h.ptr(r, off_ar)
+            a.D = None
+        else:
+            lead = (x.shape[0] // ws,) + tuple(x.shape[1:-1])
+            out = torch.empty(*lead, n, dtype=torch.bfloat16, device=x.device)
+            a.D = out.data_ptr()
+        c.fill_pair(a, h.next_epoch(), x.device)
+        loader.check(L.msb_gemm2_reduce_scatter(ctypes.byref(a), ctypes.c_void_p(loader.stream_ptr())), "gemm2_reduce_scatter")
+        if all_reduce:
+            return h.tensor(off_ar, (m, n), torch.bfloat16).clone()     # the symmetric buffer is recycled by the next call
+        return out
+
+    @classmethod
     def matmul_reduce_scatter(cls, x, w, group, nt=True, residual=None):
         ws = dist.get_world_size(group) if group is not None else 1
         x2 = x.reshape(-1, x.shape[-1])
@@ -190,6 +260,10 @@ class FusedOps(Sm100Ops):
         c = _ctx(group)
         h = c.heap
         rows = m // ws
+        if residual is not None and (residual.dtype != torch.bfloat16 or not residual.is_contiguous() or residual.numel() != rows * n):
+            raise ValueError("residual must be a contiguous bf16 tensor shaped like this rank's output shard")
+        if _pair_ok(L, m, n, k, ws, MODE_RS):
+            return cls._pair_reduce_scatter(c, x, x2, w, m, n, k, nt, residual, all_reduce=False)
         off_partial = h.alloc("rs_partial", _buf_bytes(m * n * 2))
         off_stage = h.alloc("rs_stage", _buf_bytes(m * n * 2))
         a = _CommArgs()
@@ -204,8 +278,6 @@ class FusedOps(Sm100Ops):
         lead = (x.shape[0] // ws,) + tuple(x.shape[1:-1])
         out = torch.empty(*lead, n, dtype=torch.bfloat16, device=x.device)
         own = h.ptr(h.rank, off_partial + h.rank * rows * n * 2)
-        if residual is not None and (residual.dtype != torch.bfloat16 or not residual.is_contiguous() or residual.numel() != out.numel()):
-            raise ValueError("residual must be a contiguous bf16 tensor shaped like this rank's output shard")
         loader.check(L.msb_rs_reduce(ctypes.c_void_p(h.ptr(h.rank, off_stage)), ctypes.c_void_p(own), loader.p(out),
                                      loader.p(residual) if residual is not None else None,
                                      ctypes.c_longlong(rows), n, ws, h.rank, ctypes.c_void_p(h.ptr(h.rank, 0)),

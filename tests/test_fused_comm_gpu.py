@@ -36,6 +36,39 @@ def test_bounded_wait_returns_status_instead_of_hanging():
     assert (torch.ones(4, device=dev) * 2).sum().item() == 8
 
 
+def test_pair_kernel_entry_wait_runs_out_and_reports():
+    """CTA-pair GEMM -> reduce-scatter kernel with a peer that never enters the call: the entry handshake gives up after
+    its limit, every role skips its work, the status word names the missing peer and the context stays usable."""
+    from mindspeed_b200.ops import gemm as G, loader
+    from mindspeed_b200.ops.fused_comm import _Comm2Args
+    L = loader.require_lib()
+    dev = torch.device("cuda", 0)
+    m, n, k = 512, 256, 128
+    x = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=dev, dtype=torch.bfloat16)
+    out = torch.zeros(m // 2, n, device=dev, dtype=torch.bfloat16)
+    flags = [torch.zeros(2048, dtype=torch.int32, device=dev) for _ in range(2)]      # [1] stands in for the absent peer's heap
+    stage = [torch.zeros(2, m // 2, n, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+    st = G.status_word(dev)
+    st.zero_()
+    a = _Comm2Args()
+    a.A, a.B, a.D = x.data_ptr(), w.data_ptr(), out.data_ptr()
+    for r in range(2):
+        a.peer_buf[r] = stage[r].data_ptr()
+        a.flag_peer[r] = flags[r].data_ptr()
+    a.M, a.N, a.K, a.b_mn_major, a.world, a.rank, a.epoch = m, n, k, 0, 2, 0, 1
+    a.flag_local, a.status, a.wait_limit_ms, a.max_ctas = flags[0].data_ptr(), st.data_ptr(), 300, 0
+    rc = L.msb_gemm2_reduce_scatter(ctypes.byref(a), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0, loader.lib().msb_last_error()
+    torch.cuda.synchronize()
+    assert int(st[0].item()) == 0x101          # the wait for peer 1's entry flag ran out
+    with pytest.raises(RuntimeError, match="time-out"):
+        G.check_status(dev)
+    assert torch.equal(out, torch.zeros_like(out))
+    assert int(flags[1][0].item()) == 1        # this rank did announce itself to the peer
+    assert (torch.ones(4, device=dev) * 2).sum().item() == 8
+
+
 def _worker(rank, world, port, shapes, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank))
@@ -107,7 +140,7 @@ def test_fused_ag_gemm_and_gemm_rs_match_reference():
     from dist_utils import _free_port
     world = min(torch.cuda.device_count(), 8)
     world = 1 << (world.bit_length() - 1)
-    shapes = [(256, 512, 384), (1024, 1024, 768)]
+    shapes = [(256, 512, 384), (1024, 1024, 768), (128, 512, 256)]     # the last one is too small for the CTA-pair kernels
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
