@@ -1,12 +1,22 @@
-"""Checkpoint save / load in the ``torch_dist`` layout (and the legacy single-file ``torch`` layout).
+"""Checkpoint save / load in the ``torch_dist`` format (and resume / reshard on load).
 
-Directory layout (Megatron compatible):
+Directory layout (the one Megatron's ``torch_dist`` strategy writes):
     <save>/latest_checkpointed_iteration.txt
-    <save>/iter_0000010/.metadata, __<rank>_<n>.distcp      sharded tensors (model + optimizer)
+    <save>/iter_0000010/.metadata, __<rank>_<n>.distcp      torch.distributed.checkpoint files: sharded tensors
     <save>/iter_0000010/common.pt                            everything that is not a sharded tensor
-EMA weights are stored as extra ``ema.*`` optimizer-state keys (reference: mindspeed/checkpointing.py:43-153,322-410).
+    <save>/iter_0000010/rng_<rank>.pt                        per-rank RNG state
+The ``.distcp`` / ``.metadata`` files are written and read through ``torch.distributed.checkpoint`` (FileSystemWriter /
+FileSystemReader) with planners that take this package's chunk descriptions (key, global shape, offset of the local
+chunk) directly, so any tool that reads DCP checkpoints can open them, and loading re-reads whichever saved chunks overlap
+the new local shards under a different tensor / pipeline / data-parallel layout.  Model keys follow Megatron-core's
+convention: no chunk prefix, and the per-layer tensors of ``decoder.layers`` stacked along a leading layer axis
+(``decoder.layers.self_attention.linear_qkv.weight`` of shape [num_layers, ...]).  Optimizer state is keyed
+``optimizer.state.{exp_avg,exp_avg_sq,fp32_param,...}.<param key>`` with this package's own chunking (one row per
+tensor-parallel rank over the flattened local parameter), which Megatron's optimizer does not read.
+EMA weights are stored as extra ``ema`` optimizer-state keys (reference: mindspeed/checkpointing.py:43-153,322-410).
 Device-to-host staging is synchronous (the reference forces the same: core/megatron_basic/megatron_basic.py:135-156);
-``--async-save`` hands the file writing to a background thread after staging.
+``--async-save`` then hands planning and file writing to a background thread that talks over its own gloo group, and the
+training loop calls ``finalize_async_save`` before the next save and at exit.
 """
 from __future__ import annotations
 
@@ -16,104 +26,147 @@ from typing import Dict, List, Optional
 
 import torch
 import torch.distributed as dist
+import torch.distributed.checkpoint as dcp
+from torch.distributed.checkpoint import FileSystemReader, FileSystemWriter
+from torch.distributed.checkpoint.default_planner import DefaultLoadPlanner, DefaultSavePlanner
+from torch.distributed.checkpoint.metadata import ChunkStorageMetadata, MetadataIndex, TensorProperties
+from torch.distributed.checkpoint.planner import LoadPlan, SavePlan, TensorWriteData, WriteItem, WriteItemType
+from torch.distributed.checkpoint.planner_helpers import create_read_items_for_chunk_list
 
 from ..parallel import parallel_state as ps
 from .sharded import ShardedTensor, model_sharded_state_dict, optimizer_sharded_state_dict
 
 _ASYNC: List[threading.Thread] = []
+_ASYNC_ERR: List[BaseException] = []
+_CKPT_GROUP = {"group": None}
 
 
 def get_checkpoint_name(root, iteration):
     return os.path.join(root, f"iter_{iteration:07d}")
 
 
-def _save_sharded(sts: Dict[str, ShardedTensor], path: str):
-    """Write the chunks this rank owns (replica 0) and a merged ``.metadata``.
+class _ChunkSavePlanner(DefaultSavePlanner):
+    """Plans one SHARD write item per local chunk whose ``replica_id`` is 0; the default global planning then merges all
+    ranks' items into the checkpoint metadata (one tensor entry per key with the list of its chunks)."""
 
-    File format: one ``__<rank>_0.distcp`` per rank holding {key: [(offset, tensor), ...]} and a ``.metadata`` index
-    {key: {"shape", "dtype", "chunks": [(rank, offset, sizes)]}} merged on rank 0."""
-    rank = dist.get_rank() if dist.is_initialized() else 0
-    world = dist.get_world_size() if dist.is_initialized() else 1
-    mine, index = {}, {}
+    def __init__(self, shards: Dict[str, ShardedTensor]):
+        super().__init__(flatten_state_dict=False, flatten_sharded_tensors=False)
+        # several local chunks may share a key (the layers of a stacked tensor): index by (key, offset)
+        self.shards = {(st.key, tuple(st.global_offset)): st for st in shards.values() if st.replica_id == 0}
+
+    def set_up_planner(self, state_dict, storage_meta=None, is_coordinator=False):
+        super().set_up_planner({}, storage_meta, is_coordinator)
+
+    def create_local_plan(self) -> SavePlan:
+        items = []
+        for (key, _), st in self.shards.items():
+            t = st.data
+            items.append(WriteItem(index=MetadataIndex(key, torch.Size(st.global_offset)), type=WriteItemType.SHARD,
+                                   tensor_data=TensorWriteData(
+                                       chunk=ChunkStorageMetadata(offsets=torch.Size(st.global_offset), sizes=t.size()),
+                                       properties=TensorProperties.create_from_tensor(t), size=torch.Size(st.global_shape))))
+        self.plan = SavePlan(items)
+        return self.plan
+
+    def lookup_object(self, index: MetadataIndex):
+        return self.shards[(index.fqn, tuple(index.offset))].data
+
+
+class _ChunkLoadPlanner(DefaultLoadPlanner):
+    """Reads, for every local chunk, whichever saved chunks overlap it (any saved layout)."""
+
+    def __init__(self, shards: Dict[str, ShardedTensor], strict: bool):
+        super().__init__(flatten_state_dict=False, flatten_sharded_tensors=False, allow_partial_load=not strict)
+        self.shards = {(st.key, tuple(st.global_offset)): st for st in shards.values()}
+        self.strict, self.missing = strict, []
+
+    def set_up_planner(self, state_dict, metadata=None, is_coordinator=False):
+        super().set_up_planner({}, metadata, is_coordinator)
+
+    def create_local_plan(self) -> LoadPlan:
+        reqs = []
+        for (key, _), st in self.shards.items():
+            md = self.metadata.state_dict_metadata.get(key)
+            if md is None:
+                self.missing.append(key)
+                continue
+            if tuple(md.size) != tuple(st.global_shape):
+                raise RuntimeError(f"{key}: checkpoint global shape {tuple(md.size)} != expected {tuple(st.global_shape)}")
+            chunk = ChunkStorageMetadata(offsets=torch.Size(st.global_offset), sizes=st.data.size())
+            items = create_read_items_for_chunk_list(key, md, [chunk])
+            covered = 0
+            for it in items:
+                n = 1
+                for l in it.lengths:
+                    n *= int(l)
+                covered += n
+            if covered < st.data.numel() and self.strict:
+                raise RuntimeError(f"{key}: checkpoint covers {covered} of {st.data.numel()} elements of the local shard")
+            reqs += items
+        if self.missing and self.strict:
+            raise KeyError(f"keys missing from checkpoint: {self.missing[:5]} ...")
+        return LoadPlan(reqs)
+
+    def lookup_tensor(self, index: MetadataIndex) -> torch.Tensor:
+        return self.shards[(index.fqn, tuple(index.offset))].data
+
+    def commit_tensor(self, read_item, tensor) -> None:
+        pass
+
+
+def _use_dist() -> bool:
+    return dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+
+
+def _ckpt_group():
+    """A gloo group of all ranks used only by checkpoint threads, so their collectives never interleave with training's."""
+    if _CKPT_GROUP["group"] is None:
+        _CKPT_GROUP["group"] = dist.new_group(backend="gloo")
+    return _CKPT_GROUP["group"]
+
+
+def _stage(sts: Dict[str, ShardedTensor]) -> Dict[str, ShardedTensor]:
+    """Host copies of the chunks this rank writes (replica 0): after this the training step may overwrite the originals."""
+    out = {}
     for k, st in sts.items():
         if st.replica_id != 0:
             continue
-        t = st.data.detach().cpu().contiguous()
-        mine.setdefault(k, []).append((tuple(st.global_offset), t))
-        index.setdefault(k, {"shape": tuple(st.global_shape), "dtype": str(t.dtype), "chunks": []})["chunks"].append(
-            (rank, tuple(st.global_offset), tuple(t.shape)))
+        t = st.data.detach()
+        t = t.cpu().clone() if not t.is_cuda else t.to("cpu", copy=True)
+        out[k] = ShardedTensor(st.key, t.contiguous(), st.global_shape, st.global_offset, 0)
+    return out
+
+
+def _save_sharded(sts: Dict[str, ShardedTensor], path: str, group=None):
     os.makedirs(path, exist_ok=True)
-    torch.save(mine, os.path.join(path, f"__{rank}_0.distcp"))
-    gathered = [None] * world
-    if world > 1:
-        dist.all_gather_object(gathered, index)
-    else:
-        gathered = [index]
-    if rank == 0:
-        merged = {}
-        for idx in gathered:
-            for k, v in idx.items():
-                m = merged.setdefault(k, {"shape": v["shape"], "dtype": v["dtype"], "chunks": []})
-                if tuple(m["shape"]) != tuple(v["shape"]):
-                    raise RuntimeError(f"checkpoint key {k} has inconsistent global shapes {m['shape']} vs {v['shape']}")
-                m["chunks"].extend(v["chunks"])
-        with open(os.path.join(path, ".metadata"), "wb") as f:
-            torch.save(merged, f)
+    use = _use_dist()
+    dcp.save({}, storage_writer=FileSystemWriter(path, single_file_per_rank=True), planner=_ChunkSavePlanner(sts),
+             process_group=group if use else None, no_dist=not use)
 
 
 def _load_sharded(sts: Dict[str, ShardedTensor], path: str, strict: bool = True):
-    """Fill every local shard from whichever saved chunks overlap it (works across layouts)."""
-    with open(os.path.join(path, ".metadata"), "rb") as f:
-        meta = torch.load(f, weights_only=False)
-    cache = {}
+    """Fill every local shard from whichever saved chunks overlap it (works across layouts).  Every rank reads on its own:
+    no collective is involved, so ranks may ask for different keys."""
+    planner = _ChunkLoadPlanner(sts, strict)
+    dcp.load({}, storage_reader=FileSystemReader(path), planner=planner, no_dist=True)
+    return planner.missing
 
-    def rank_file(r):
-        if r not in cache:
-            cache[r] = torch.load(os.path.join(path, f"__{r}_0.distcp"), weights_only=False)
-        return cache[r]
 
-    missing = []
-    for k, st in sts.items():
-        if k not in meta:
-            missing.append(k)
-            continue
-        m = meta[k]
-        if tuple(m["shape"]) != tuple(st.global_shape):
-            raise RuntimeError(f"{k}: checkpoint global shape {m['shape']} != expected {st.global_shape}")
-        dst = st.data
-        lo = st.global_offset
-        hi = tuple(o + s for o, s in zip(lo, dst.shape))
-        covered = 0
-        for (r, off, sizes) in m["chunks"]:
-            c_hi = tuple(o + s for o, s in zip(off, sizes))
-            i_lo = tuple(max(a, b) for a, b in zip(lo, off))
-            i_hi = tuple(min(a, b) for a, b in zip(hi, c_hi))
-            if any(a >= b for a, b in zip(i_lo, i_hi)):
-                continue
-            src = None
-            for (o2, t) in rank_file(r)[k]:
-                if tuple(o2) == tuple(off):
-                    src = t
-            d_sl = tuple(slice(a - o, b - o) for a, b, o in zip(i_lo, i_hi, lo))
-            s_sl = tuple(slice(a - o, b - o) for a, b, o in zip(i_lo, i_hi, off))
-            with torch.no_grad():
-                dst[d_sl].copy_(src[s_sl].to(dst.dtype))
-            n = 1
-            for a, b in zip(i_lo, i_hi):
-                n *= (b - a)
-            covered += n
-        if covered < dst.numel() and strict:
-            raise RuntimeError(f"{k}: checkpoint covers {covered} of {dst.numel()} elements of the local shard")
-    if missing and strict:
-        raise KeyError(f"keys missing from checkpoint: {missing[:5]} ...")
-    return missing
+def finalize_async_save(blocking: bool = True):
+    """Wait for background checkpoint writes (all of them when ``blocking``, else only finished ones are reaped) and
+    re-raise an error that happened in one."""
+    for t in list(_ASYNC):
+        if blocking or not t.is_alive():
+            t.join()
+            _ASYNC.remove(t)
+    if _ASYNC_ERR:
+        raise RuntimeError("asynchronous checkpoint save failed") from _ASYNC_ERR.pop(0)
 
 
 def generate_state_dict(model, optimizer, opt_param_scheduler, iteration, args=None, rng=True):
     sharded: Dict[str, ShardedTensor] = {}
-    for i, chunk in enumerate(model):
-        pfx = "model." if len(model) == 1 else f"model{i}."
-        sharded.update(model_sharded_state_dict(chunk, pfx))
+    for chunk in model:      # keys carry global layer numbers, so chunks of one model never collide
+        sharded.update(model_sharded_state_dict(chunk, ""))
     common = {"iteration": iteration, "checkpoint_version": 3.0}
     if args is not None:
         common["args"] = {k: v for k, v in vars(args).items() if isinstance(v, (int, float, str, bool, list, tuple, type(None)))}
@@ -138,23 +191,43 @@ def save_checkpoint(iteration, model, optimizer, opt_param_scheduler, args=None,
             args = None
     save_dir = save_dir or args.save
     async_save = bool(getattr(args, "async_save", False)) if async_save is None else async_save
+    finalize_async_save(blocking=True)                 # at most one checkpoint in flight
     path = get_checkpoint_name(save_dir, iteration)
     sharded, common = generate_state_dict(model, optimizer if not getattr(args, "no_save_optim", False) else None,
                                           opt_param_scheduler, iteration, args, rng=not getattr(args, "no_save_rng", False))
     rank = dist.get_rank() if dist.is_initialized() else 0
     os.makedirs(path, exist_ok=True)
-    _save_sharded(sharded, path)                       # staging + write of this rank's file
-    # rng state differs per rank: every rank keeps its own copy next to the shared common file
-    torch.save({"rng_state": common.pop("rng_state", None)}, os.path.join(path, f"rng_{rank}.pt"))
-    if rank == 0:
-        torch.save(common, os.path.join(path, "common.pt"))
-    if dist.is_initialized():
-        dist.barrier()
-    if rank == 0:
-        with open(os.path.join(save_dir, "latest_checkpointed_iteration.txt"), "w") as f:
-            f.write(str(iteration))
-    if dist.is_initialized():
-        dist.barrier()
+    rng_state = {"rng_state": common.pop("rng_state", None)}
+
+    def write(shards, group):
+        _save_sharded(shards, path, group)
+        # rng state differs per rank: every rank keeps its own copy next to the shared common file
+        torch.save(rng_state, os.path.join(path, f"rng_{rank}.pt"))
+        if rank == 0:
+            torch.save(common, os.path.join(path, "common.pt"))
+        if _use_dist():
+            dist.barrier(group=group)
+        if rank == 0:
+            with open(os.path.join(save_dir, "latest_checkpointed_iteration.txt"), "w") as f:
+                f.write(str(iteration))
+        if _use_dist():
+            dist.barrier(group=group)
+
+    if not async_save:
+        write(sharded, None)
+        return path
+    staged = _stage(sharded)                           # synchronous device-to-host copy; the step may now go on
+    group = _ckpt_group() if _use_dist() else None
+
+    def run():
+        try:
+            write(staged, group)
+        except BaseException as e:   # surfaced by finalize_async_save
+            _ASYNC_ERR.append(e)
+
+    t = threading.Thread(target=run, name=f"ckpt-save-{iteration}", daemon=True)
+    t.start()
+    _ASYNC.append(t)
     return path
 
 

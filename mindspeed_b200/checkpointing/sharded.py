@@ -2,9 +2,10 @@
 
 A ``ShardedTensor`` names a global tensor (``key``, ``global_shape``) and says which rectangular chunk of it the
 local data is (``global_offset``); ``replica_id`` 0 marks the copy that gets written when several ranks hold the
-same chunk.  Saving converts these to ``torch.distributed._shard`` sharded tensors and hands them to
-``torch.distributed.checkpoint``, which writes ``.metadata`` + ``__{rank}_{n}.distcp``; loading under a different
-tensor / pipeline / data-parallel layout re-reads whichever chunks overlap the new local shards.
+same chunk.  Saving turns each into one shard write item of ``torch.distributed.checkpoint``, which writes ``.metadata`` +
+``__{rank}_{n}.distcp``; loading under a different tensor / pipeline / data-parallel layout re-reads whichever chunks
+overlap the new local shards.  Per-layer tensors are stacked along a leading layer axis under a key without the layer
+number, as Megatron-core does.
 (Megatron-core ``dist_checkpointing`` surface; reference usage mindspeed/checkpointing.py:78-106.)
 """
 from __future__ import annotations
@@ -51,12 +52,32 @@ def make_tp_sharded_tensors(state_dict: Dict[str, torch.Tensor], prefix: str, tp
     return out
 
 
-def _global_layer_name(name: str, layer_numbers: Dict[int, int]) -> str:
+def _stacked_layer_key(name: str, layer_numbers: Dict[int, int]):
+    """``decoder.layers.3.mlp.linear_fc1.weight`` -> (``decoder.layers.mlp.linear_fc1.weight``, global layer index).
+    Names outside ``decoder.layers`` come back unchanged with index None."""
     parts = name.split(".")
     if "layers" in parts:
         i = parts.index("layers")
-        parts[i + 1] = str(layer_numbers[int(parts[i + 1])] - 1)
-    return ".".join(parts)
+        if i + 1 < len(parts) and parts[i + 1].isdigit() and int(parts[i + 1]) in layer_numbers:
+            g = layer_numbers[int(parts[i + 1])] - 1
+            return ".".join(parts[:i + 1] + parts[i + 2:]), g
+    return name, None
+
+
+def _stack(st: ShardedTensor, layer: Optional[int], num_layers: int) -> ShardedTensor:
+    """Prepend the layer axis: the chunk becomes row ``layer`` of a [num_layers, ...] global tensor."""
+    if layer is None:
+        return st
+    return ShardedTensor(st.key, st.data.unsqueeze(0), (num_layers,) + tuple(st.global_shape), (layer,) + tuple(st.global_offset),
+                         st.replica_id)
+
+
+def _num_layers(inner) -> int:
+    cfg = getattr(inner, "config", None)
+    n = getattr(cfg, "num_layers", None)
+    if n:
+        return int(n)
+    return max([l.layer_number for l in inner.decoder.layers] + [0]) if hasattr(inner, "decoder") else 0
 
 
 def model_sharded_state_dict(model, prefix: str = "") -> Dict[str, ShardedTensor]:
@@ -79,22 +100,25 @@ def model_sharded_state_dict(model, prefix: str = "") -> Dict[str, ShardedTensor
     edp_rank = ps.get_expert_data_parallel_rank() if init else 0
     out: Dict[str, ShardedTensor] = {}
     items = list(inner.named_parameters()) + [(n, b) for n, b in inner.named_buffers() if b is not None and b.numel() > 0]
+    total_layers = _num_layers(inner)
     for name, p in items:
-        key = prefix + _global_layer_name(name, layer_numbers)
+        base, layer = _stacked_layer_key(name, layer_numbers)
+        key = prefix + base
         t = p.data if isinstance(p, torch.nn.Parameter) else p
         is_expert = not getattr(p, "allreduce", True)
         if is_expert and t.dim() == 3:
             gshape = (t.shape[0] * ep,) + tuple(t.shape[1:])
             goff = (ep_rank * t.shape[0],) + (0,) * (t.dim() - 1)
-            out[key] = ShardedTensor(key, t, gshape, goff, replica_id=edp_rank)
+            st = ShardedTensor(key, t, gshape, goff, replica_id=edp_rank)
         elif getattr(p, "tensor_model_parallel", False) and tp > 1:
             ax = p.partition_dim
             gshape, goff = list(t.shape), [0] * t.dim()
             gshape[ax] = t.shape[ax] * tp
             goff[ax] = tp_rank * t.shape[ax]
-            out[key] = ShardedTensor(key, t, tuple(gshape), tuple(goff), replica_id=dp_rank)
+            st = ShardedTensor(key, t, tuple(gshape), tuple(goff), replica_id=dp_rank)
         else:
-            out[key] = ShardedTensor(key, t, tuple(t.shape), (0,) * t.dim(), replica_id=dp_rank + 1000 * tp_rank)
+            st = ShardedTensor(key, t, tuple(t.shape), (0,) * t.dim(), replica_id=dp_rank + 1000 * tp_rank)
+        out[key if layer is None else f"{key}@{layer}"] = _stack(st, layer, total_layers)   # dict id; the checkpoint key is st.key
     return out
 
 
@@ -108,7 +132,8 @@ def optimizer_sharded_state_dict(optimizer, sharding_type: str = "fully_sharded_
     for chunk_i, chunk in enumerate(optimizer.model_chunks):
         inner = chunk.module
         layer_numbers = {i: l.layer_number for i, l in enumerate(inner.decoder.layers)} if hasattr(inner, "decoder") else {}
-        names = {id(p): _global_layer_name(n, layer_numbers) for n, p in inner.named_parameters()}
+        names = {id(p): _stacked_layer_key(n, layer_numbers) for n, p in inner.named_parameters()}
+        total_layers = _num_layers(inner)
         for st in optimizer._all_states():
             if st.buf not in chunk.buffers + chunk.expert_buffers:
                 continue
@@ -117,17 +142,18 @@ def optimizer_sharded_state_dict(optimizer, sharding_type: str = "fully_sharded_
                 lo, hi = max(ps_, st.lo), min(pe_, st.hi)
                 if lo >= hi:
                     continue
-                n = names[id(p)]
+                n, layer = names[id(p)]
                 split = getattr(p, "tensor_model_parallel", False)
                 rows, row = (tp, tp_rank) if split else (1, 0)
                 sl = slice(lo - st.lo, hi - st.lo)
                 replica = 0 if (split or tp_rank == 0) else tp_rank
                 replica += 0 if optimizer.sharded else st.buf.dp_rank
-                for kind, src in (("exp_avg", st.m), ("exp_avg_sq", st.v), ("master", st.master if (st.param16 is not None and st.master is not None) else None),
+                for kind, src in (("exp_avg", st.m), ("exp_avg_sq", st.v), ("fp32_param", st.master if (st.param16 is not None and st.master is not None) else None),
                                   ("residual", getattr(st, "residual", None)),
                                   ("ema", st.ema)):
                     if src is None:
                         continue
                     key = f"optimizer.state.{kind}.{n}"
-                    out[key] = ShardedTensor(key, src[sl].view(1, -1), (rows, pe_ - ps_), (row, lo - ps_), replica_id=replica)
+                    out[key if layer is None else f"{key}@{layer}"] = _stack(ShardedTensor(key, src[sl].view(1, -1), (rows, pe_ - ps_), (row, lo - ps_), replica_id=replica),
+                                      layer, total_layers)
     return out

@@ -1,8 +1,8 @@
 """Autograd wrapper of the tcgen05 flash-attention forward (csrc/kernels/flash_attn_sm100.cu).
 
-Forward: hand-written kernel producing O and the per-row log-sum-exp.  Backward: until the sm_100a backward kernel
-lands, the flash backward of the framework library is driven with this kernel's O and LSE (they use the same
-convention: natural-log LSE of the scaled scores), so the two halves are interchangeable.
+Forward and backward are the hand-written kernels of csrc/kernels/flash2_sm100.cu; the LSE convention (natural log of
+the softmax denominator of the scaled scores) is the one ring attention and the reference implementation use, so blocks
+computed here can be merged with or differentiated against a global LSE.
 """
 from __future__ import annotations
 
@@ -14,23 +14,11 @@ import torch
 from . import gemm as G
 from . import loader
 
-_RNG = {}
-
-
-def _rng_template(dev):
-    """Placeholder rng-state tensors of the right type for the library backward (dropout is 0, so they are unused)."""
-    t = _RNG.get(dev)
-    if t is None:
-        q = torch.zeros(1, 1, 16, 64, device=dev, dtype=torch.bfloat16)
-        res = torch.ops.aten._scaled_dot_product_flash_attention(q, q, q, 0.0, False, False)
-        t = (res[6], res[7])
-        _RNG[dev] = t
-    return t
-
-
-def flash_fwd(q, k, v, causal, scale, q_offset=None):
-    """q [sq,b,nq,128], k/v [sk,b,nkv,128] bf16 (strided views allowed) -> (o [sq,b,nq,128], lse [b,nq,sq] fp32)."""
+def flash_fwd(q, k, v, causal, scale, q_offset=None, kernel=2):
+    """q [sq,b,nq,128], k/v [sk,b,nkv,128] bf16 (strided views allowed) -> (o [sq,b,nq,128], lse [b,nq,sq] fp32).
+    ``kernel`` 2 = two query tiles per CTA with P in tensor memory (default), 1 = the single-tile kernel."""
     L = loader.require_lib()
+    fn = L.msb_flash_fwd2 if kernel == 2 else L.msb_flash_fwd
     sq, b, nq, d = q.shape
     sk, nkv = k.shape[0], k.shape[2]
     for t in (q, k, v):
@@ -42,11 +30,43 @@ def flash_fwd(q, k, v, causal, scale, q_offset=None):
         q_offset = sk - sq if causal else 0
     ll = ctypes.c_longlong
     st = G.status_word(q.device)
-    loader.check(L.msb_flash_fwd(loader.p(q), loader.p(k), loader.p(v), loader.p(o), loader.p(lse), sq, sk, b, nq, nkv,
+    loader.check(fn(loader.p(q), loader.p(k), loader.p(v), loader.p(o), loader.p(lse), sq, sk, b, nq, nkv,
                                  ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)), ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)),
                                  ll(v.stride(0)), ll(v.stride(1)), ll(v.stride(2)), int(causal), int(q_offset),
                                  ctypes.c_float(scale), loader.p(st), ctypes.c_void_p(loader.stream_ptr())), "flash_fwd")
     return o, lse
+
+
+def flash_bwd(dout, q, k, v, o, lse, causal, scale, q_offset=None):
+    """Gradients (dq, dk, dv) on the tcgen05 backward kernel.  Shapes as ``flash_fwd``; ``o`` contiguous, ``lse`` the
+    forward's (or, for ring attention, the global) log-sum-exp.  dQ is accumulated in fp32 by the key tiles (TMA
+    reduce-adds, so its low bits can differ between runs) and rounded to bf16 once at the end."""
+    L = loader.require_lib()
+    sq, b, nq, d = q.shape
+    sk, nkv = k.shape[0], k.shape[2]
+    if q_offset is None:
+        q_offset = sk - sq if causal else 0
+    if dout.stride(-1) != 1 or any((st * 2) % 16 for st in dout.stride()[:-1]) or dout.data_ptr() % 16:
+        dout = dout.contiguous()
+    o = o if o.is_contiguous() else o.contiguous()
+    lse = lse if lse.is_contiguous() else lse.contiguous()
+    dev = q.device
+    sq_pad = (sq + 127) // 128 * 128
+    dq32 = torch.zeros(sq, b, nq, d, dtype=torch.float32, device=dev)
+    never_seen = causal and (sq + q_offset < sk)       # trailing key tiles that no query row reaches keep zero gradients
+    alloc = torch.zeros if never_seen else torch.empty
+    dk = alloc(sk, b, nkv, d, dtype=torch.bfloat16, device=dev)
+    dv = alloc(sk, b, nkv, d, dtype=torch.bfloat16, device=dev)
+    stats = torch.empty(2, b, nq, sq_pad, dtype=torch.float32, device=dev)
+    ll = ctypes.c_longlong
+    st = G.status_word(dev)
+    loader.check(L.msb_flash_bwd(loader.p(q), loader.p(k), loader.p(v), loader.p(o), loader.p(dout), loader.p(lse), loader.p(dq32),
+                                 loader.p(dk), loader.p(dv), loader.p(stats[0]), loader.p(stats[1]), sq, sk, b, nq, nkv,
+                                 ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)), ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)),
+                                 ll(v.stride(0)), ll(v.stride(1)), ll(v.stride(2)), ll(dout.stride(0)), ll(dout.stride(1)),
+                                 ll(dout.stride(2)), int(causal), int(q_offset), ctypes.c_float(scale), loader.p(st),
+                                 ctypes.c_void_p(loader.stream_ptr())), "flash_bwd")
+    return dq32.to(torch.bfloat16), dk, dv
 
 
 class _FlashFn(torch.autograd.Function):
@@ -62,19 +82,8 @@ class _FlashFn(torch.autograd.Function):
     def backward(ctx, do, _dlse):
         q, k, v, o, lse = ctx.saved_tensors
         causal, scale = ctx.meta
-        sq, b, nq, d = q.shape
-        sk, nkv = k.shape[0], k.shape[2]
-        rep = nq // nkv
-        qb, kb, vb = q.permute(1, 2, 0, 3), k.permute(1, 2, 0, 3), v.permute(1, 2, 0, 3)
-        if rep > 1:
-            kb, vb = kb.repeat_interleave(rep, 1), vb.repeat_interleave(rep, 1)
-        seed, off = _rng_template(q.device)
-        dq, dk, dv = torch.ops.aten._scaled_dot_product_flash_attention_backward(
-            do.permute(1, 2, 0, 3), qb, kb, vb, o.permute(1, 2, 0, 3), lse, None, None, sq, sk, 0.0, causal, seed, off, scale=scale)
-        if rep > 1:
-            dk = dk.reshape(b, nkv, rep, sk, d).sum(2)
-            dv = dv.reshape(b, nkv, rep, sk, d).sum(2)
-        return dq.permute(2, 0, 1, 3), dk.permute(2, 0, 1, 3), dv.permute(2, 0, 1, 3), None, None
+        dq, dk, dv = flash_bwd(do, q, k, v, o, lse, causal, scale)
+        return dq, dk, dv, None, None
 
 
 def flash_attention(q, k, v, causal, softmax_scale, return_lse):

@@ -312,6 +312,7 @@ def pretrain(train_valid_test_dataset_provider, model_provider, model_type=None,
     train_iter = train_valid_test_dataset_provider(args)
     history = train(forward_step_func, model, optimizer, sched, train_iter, process_non_loss_data_func)
     if args.save:
-        from ..checkpointing import save_checkpoint
+        from ..checkpointing import finalize_async_save, save_checkpoint
         save_checkpoint(args.iteration, model, optimizer, sched)
+        finalize_async_save(blocking=True)       # --async-save: the last checkpoint is on disk before pretrain returns
     return history
