@@ -68,6 +68,7 @@ def main():
     p.add_argument("--hidden", type=int, default=4096)
     p.add_argument("--ffn", type=int, default=14336)
     p.add_argument("--qkv", type=int, default=6144)
+    p.add_argument("--timeline", action="store_true", help="print CTA 0's in-kernel time stamps of one fused launch per case")
     a = p.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -123,6 +124,16 @@ def main():
         yl = yl[0] if isinstance(yl, tuple) else yl
         err = (yf.float() - yl.float()).abs().max().item()
         ref = yl.float().abs().max().item()
+        if a.timeline:
+            from ..ops import fused_comm as FC
+            FC.TIMELINE = torch.zeros(8, dtype=torch.int64, device="cuda")
+            torch.cuda.synchronize(); dist.barrier(group); fused(); torch.cuda.synchronize()
+            ts = FC.TIMELINE.tolist()
+            FC.TIMELINE = None
+            if rank == 0:
+                rel = [(t - ts[0]) / 1e3 if t else None for t in ts]
+                print(f"    timeline us (CTA 0): handshake {rel[1]}, copy done {rel[2]}, loads issued {rel[3]}, epilogue done {rel[4]}, "
+                      f"rs flags in {rel[5]}, end {rel[6]}", flush=True)
         t_f = _timed(fused, group, flush, L, loader)
         t_l = _timed(lib, group, flush, L, loader)
         t_roof = max(flops / peak, link_bytes / (NVLINK_GBS * 1e9)) * 1e3

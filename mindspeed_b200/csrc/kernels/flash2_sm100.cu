@@ -206,20 +206,19 @@ __global__ void __launch_bounds__(320, 1) flash_fwd2_sm100_kernel(const __grid_c
       const int limit = p.causal ? (q_idx + p.q_offset - key0) : FB;    // keys [0, limit] of this tile are visible to this row
       const int vis = min(limit, p.sk - 1 - key0);
       const bool need_mask = vis < FB - 1;
-      // pass 1: row maximum (raw scores)
-      float m_tile = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < FB; c += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tS + (uint32_t)c, r);
-        tmem_ld_wait();
+      // the whole score row into registers (four loads in flight, one wait), masked where needed
+      uint32_t sv[FB];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(r[i]);
-          if (need_mask && c + i > vis) v = -INFINITY;
-          m_tile = fmaxf(m_tile, v);
-        }
+      for (int c = 0; c < FB; c += 32) tmem_ld_32x32(tS + (uint32_t)c, sv + c);
+      tmem_ld_wait();
+      if (__any_sync(0xffffffffu, need_mask)) {
+#pragma unroll
+        for (int i = 0; i < FB; ++i)
+          if (i > vis) sv[i] = 0xff800000u;              // -inf
       }
+      float m_tile = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < FB; ++i) m_tile = fmaxf(m_tile, __uint_as_float(sv[i]));
       const float m_tile2 = m_tile * p.scale_log2;
       // rescale O only when the maximum has grown a lot (decision per warp: the TMEM accesses are warp-wide)
       const bool grow = m_tile2 > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && m_tile2 > -INFINITY);
@@ -244,24 +243,21 @@ __global__ void __launch_bounds__(320, 1) flash_fwd2_sm100_kernel(const __grid_c
         m_used = m_new;
       }
       const float m_ref = (m_used == -INFINITY) ? 0.f : m_used;
-      // pass 2: probabilities -> packed bf16 over the first 64 columns of S, row sum
+      // probabilities -> packed bf16 over the first 64 columns of S, row sum (masked scores are -inf -> 0)
       float l_tile = 0.f;
-#pragma unroll 1
+      const float neg_ref = -m_ref;
+#pragma unroll
       for (int c = 0; c < FB; c += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tS + (uint32_t)c, r);
-        tmem_ld_wait();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float a = __uint_as_float(r[2 * i]), b = __uint_as_float(r[2 * i + 1]);
-          const float pa = (need_mask && c + 2 * i > vis) ? 0.f : exp2f(a * p.scale_log2 - m_ref);
-          const float pb = (need_mask && c + 2 * i + 1 > vis) ? 0.f : exp2f(b * p.scale_log2 - m_ref);
+          const float pa = exp2f(fmaf(__uint_as_float(sv[c + 2 * i]), p.scale_log2, neg_ref));
+          const float pb = exp2f(fmaf(__uint_as_float(sv[c + 2 * i + 1]), p.scale_log2, neg_ref));
           l_tile += pa + pb;
           __nv_bfloat162 h = __floats2bfloat162_rn(pa, pb);
           pk[i] = *reinterpret_cast<uint32_t*>(&h);
         }
-        tmem_st_32x16(tS + (uint32_t)(c >> 1), pk);      // columns [c/2, c/2 + 16): already consumed part of S
+        tmem_st_32x16(tS + (uint32_t)(c >> 1), pk);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -577,6 +573,13 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
       const size_t stat = ((size_t)batch * p.nq + head) * p.sq_pad + (size_t)i * FB + ch * 64;
       const float4* lse2_v = reinterpret_cast<const float4*>(p.lse2 + stat);
       const float4* dlt_v = reinterpret_cast<const float4*>(p.delta + stat);
+      if (it + 1 < n_it && lane < 4) {
+        // pull the next iteration's statistics (2 x 256 bytes per warp) into L1 now, so its loads do not wait on L2
+        const int it2 = it + 1;
+        const size_t stat2 = ((size_t)batch * p.nq + (g * rep + it2 / n_i)) * p.sq_pad + (size_t)(i_start + it2 % n_i) * FB + ch * 64;
+        const float* a2 = (lane < 2 ? p.lse2 : p.delta) + stat2 + (lane & 1) * 32;
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(a2));
+      }
       // keys of this tile visible to query row r: key <= r + q_offset (causal), key < sk
       const bool full_tile = (!p.causal || key0 + FB - 1 <= i * FB + p.q_offset) && key0 + FB <= p.sk;
       float pv[64];

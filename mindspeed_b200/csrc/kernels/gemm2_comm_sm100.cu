@@ -79,6 +79,8 @@ struct Comm2Params {
   uint4* out;                    // [R, N]
   const uint4* residual;         // optional [R, N]
   uint4* ar_out[MAX_R];          // optional: every rank's all-reduce output [M, N]
+  unsigned long long* timeline;  // optional [8]: %globaltimer stamps written by CTA 0 (entry, handshake done, copy / producer /
+                                 // epilogue loops done, RS flags in, RS sum done); for the micro-benchmark's breakdown
 };
 
 struct Smem {
@@ -176,6 +178,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(224, 1) gemm2_comm_k
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
+  auto stamp = [&](int i) { if (p.timeline && blockIdx.x == 0) p.timeline[i] = globaltimer_ns(); };
+  if (threadIdx.x == 0) stamp(0);
   // ---- entry handshake: every peer has entered this call ----
   bool alive = true;
   {
@@ -187,6 +191,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(224, 1) gemm2_comm_k
       alive = wait_flag_ge(p.flag_local + F_ENTRY + threadIdx.x, p.epoch, p.status, 0x100u + threadIdx.x, p.wait_ns);
     alive = __syncthreads_and(alive);
   }
+  if (threadIdx.x == 0) stamp(1);
 
   if (alive) {
     if (warp == 0) {
@@ -219,6 +224,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(224, 1) gemm2_comm_k
             if (++stage == NSTAGE) { stage = 0; phase ^= 1u; }
           }
         }
+        stamp(3);
         for (int i = 0; i < NSTAGE && alive; ++i) {      // tail: all commits aimed at this CTA have landed
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, 0x11u)) { alive = false; break; }
           if (++stage == NSTAGE) { stage = 0; phase ^= 1u; }
@@ -329,6 +335,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(224, 1) gemm2_comm_k
       }
       if (alive) finish_owner();
       if (lane == 0) tma_store_wait<0>();
+      if (warp == 2 && lane == 0) stamp(4);
     } else if (MODE == MODE_AG) {
       // ===================== copy warp (warp 6): push this rank's slab to the peers =====================
       if (lane == 0) {
@@ -398,6 +405,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(224, 1) gemm2_comm_k
           if (!store_item(k)) alive = false;
         tma_store_wait<0>();
         if (alive) signal_upto(stored);
+        stamp(2);
       }
     }
   }
@@ -410,6 +418,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(224, 1) gemm2_comm_k
     }
     if (threadIdx.x == 0 && *((volatile unsigned int*)p.status) != 0u) s_ok = 0;
     __syncthreads();
+    if (threadIdx.x == 0) stamp(5);
     if (s_ok) {
       const long long n_v4 = (long long)p.rows_per_rank * p.N / 8;
       const long long ar_off = (long long)p.rank * n_v4;
@@ -464,6 +473,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(224, 1) gemm2_comm_k
   tc_fence_before();
   __syncwarp();
   cluster_sync_all();
+  if (threadIdx.x == 0) stamp(6);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, TMEM_COLS);
@@ -503,6 +513,7 @@ struct MsbComm2Args {
   unsigned int* status;
   int wait_limit_ms;             // 0: default (10 s)
   int max_ctas;                  // 0: all SMs
+  unsigned long long* timeline;  // optional [8] device words for CTA 0's time stamps
 };
 
 static int fill_comm2(Comm2Params& p, const MsbComm2Args* a, int mode) {
@@ -518,6 +529,7 @@ static int fill_comm2(Comm2Params& p, const MsbComm2Args* a, int mode) {
   p.flag_local = a->flag_local;
   for (int i = 0; i < MAX_R; ++i) p.flag_peer[i] = a->flag_peer[i];
   p.status = a->status;
+  p.timeline = a->timeline;
   p.wait_ns = (a->wait_limit_ms > 0 ? (unsigned long long)a->wait_limit_ms : 10000ull) * 1000000ull;
   const int tiles_per_rank = p.rows_per_rank / (2 * BM);
   p.group_m = 8;

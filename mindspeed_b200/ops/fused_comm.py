@@ -49,13 +49,16 @@ class _Comm2Args(ctypes.Structure):
                 ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("b_mn_major", ctypes.c_int),
                 ("world", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_uint),
                 ("flag_local", ctypes.c_void_p), ("flag_peer", ctypes.c_void_p * MAX_SRC), ("status", ctypes.c_void_p),
-                ("wait_limit_ms", ctypes.c_int), ("max_ctas", ctypes.c_int)]
+                ("wait_limit_ms", ctypes.c_int), ("max_ctas", ctypes.c_int), ("timeline", ctypes.c_void_p)]
 
 
 MODE_AG, MODE_RS = 1, 2
 # 0: CTA-pair kernels wherever they cover the shape (default); 1: always the one-CTA fused kernels (comparisons)
 _FORCE_ONE_CTA = os.environ.get("MSB200_FUSED_ONE_CTA", "0") != "0"
 WAIT_LIMIT_MS = int(os.environ.get("MSB200_COMM_WAIT_MS", "10000"))
+
+
+TIMELINE = None      # set to a uint64 [8] device tensor to collect CTA 0's time stamps of the next pair-kernel launch
 
 
 def _pair_ok(L, m, n, k, ws, mode) -> bool:
@@ -78,6 +81,7 @@ class _Ctx:
         a.status = G.status_word(dev).data_ptr()
         a.wait_limit_ms = WAIT_LIMIT_MS
         a.max_ctas = 0
+        a.timeline = TIMELINE.data_ptr() if TIMELINE is not None else None
 
     def fill_common(self, a: _CommArgs, epoch: int, dev):
         h = self.heap

@@ -136,3 +136,45 @@ def test_weight_gradient_accumulation_reproducible_without_stream_k():
     assert torch.equal(outs[0], outs[1])
     torch.testing.assert_close(outs[0], ref, rtol=1e-4, atol=0.05)
     torch.testing.assert_close(acc, ref, rtol=1e-4, atol=0.05)
+
+
+@pytest.mark.parametrize("sizes,K,N", [([300, 0, 37, 512, 64, 129], 256, 384), ([1000, 2000, 17, 983], 512, 1024), ([5, 3], 64, 128),
+                                       ([256] * 8, 1024, 512)])
+def test_grouped_gemm_forward_and_gradients(sizes, K, N):
+    """One launch per direction over all experts, row ranges taken from a device tensor; ragged expert boundaries, empty
+    and tiny experts; weight gradient both as a returned tensor and accumulated into an fp32 main_grad."""
+    from mindspeed_b200.ops import gemm as G
+    from mindspeed_b200.ops.grouped_gemm import grouped_gemm
+    torch.manual_seed(7)
+    E, R = len(sizes), sum(sizes)
+    x = (torch.randn(R + 40, K, device="cuda") * 0.5).bfloat16().requires_grad_(True)     # 40 spare rows past the last expert
+    w = (torch.randn(E, K, N, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    counts = torch.tensor(sizes, device="cuda", dtype=torch.int64)
+    y = grouped_gemm(x, w, counts)
+    dy = torch.randn(R + 40, N, device="cuda").bfloat16()
+    dy[R:] = 0
+    (y[:R].float() * dy[:R].float()).sum().backward()
+    torch.cuda.synchronize()
+    G.check_status()
+    xf, wf = x.detach().float(), w.detach().float()
+    ry = torch.zeros(R, N, device="cuda")
+    rdx = torch.zeros(R, K, device="cuda")
+    rdw = torch.zeros(E, K, N, device="cuda")
+    s = 0
+    for e, n in enumerate(sizes):
+        ry[s:s + n] = xf[s:s + n] @ wf[e]
+        rdx[s:s + n] = dy[s:s + n].float() @ wf[e].t()
+        rdw[e] = xf[s:s + n].t() @ dy[s:s + n].float()
+        s += n
+    torch.testing.assert_close(y[:R].float(), ry, rtol=1e-2, atol=2e-2 * ry.abs().mean().item() + 1e-3)
+    torch.testing.assert_close(x.grad[:R].float(), rdx, rtol=1e-2, atol=2e-2 * rdx.abs().mean().item() + 1e-3)
+    torch.testing.assert_close(w.grad.float(), rdw, rtol=1e-2, atol=2e-2 * rdw.abs().mean().item() + 1e-3)
+    # accumulate into main_grad twice
+    w2 = w.detach().clone().requires_grad_(True)
+    w2.main_grad = torch.full((E, K, N), 0.25, device="cuda", dtype=torch.float32)
+    for _ in range(2):
+        y2 = grouped_gemm(x.detach(), w2, counts)
+        (y2[:R].float() * dy[:R].float()).sum().backward()
+    torch.cuda.synchronize()
+    G.check_status()
+    torch.testing.assert_close(w2.main_grad, 0.25 + 2 * rdw, rtol=1e-3, atol=2e-3 * rdw.abs().mean().item() + 1e-3)
