@@ -385,6 +385,7 @@ struct BwdParams {
   int causal, q_offset;
   float scale, scale_log2;
   unsigned int* status;
+  int debug;
 };
 
 struct BwdSmem {
@@ -600,7 +601,7 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
           for (int e = 0; e < 4; ++e) {
             const int c = 4 * c4 + e;
             const float sc = __uint_as_float(c < 32 ? r0[c] : r1[c - 32]);
-            float pr = exp2f(sc * p.scale_log2 - ls[e]);
+            float pr = (p.debug & 2) ? sc : exp2f(sc * p.scale_log2 - ls[e]);
             if (!full_tile && (key >= p.sk || (p.causal && key > qrow0 + c + p.q_offset))) pr = 0.f;
             pv[c] = pr;
           }
@@ -679,7 +680,7 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
           }
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0 && qr < p.sq) {
+          if (lane == 0 && qr < p.sq && !(p.debug & 1)) {
             tma_reduce_add_4d(&p.tmdQ, my4k, ch * 64 + rnd * 32, head, batch, qr);
             tma_store_commit();
           }
@@ -770,6 +771,7 @@ MSB_API int msb_flash_bwd(const void* q, const void* k, const void* v, const voi
   p.lse2 = lse2; p.delta = delta;
   p.sq = sq; p.sk = sk; p.b = b; p.nq = nq; p.nkv = nkv; p.sq_pad = sq_pad; p.causal = causal; p.q_offset = q_offset;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+  { const char* d = getenv("MSB200_FLASH_DEBUG"); p.debug = d ? atoi(d) : 0; }
   static bool attr = false;
   if (!attr) {
     cudaError_t e = cudaFuncSetAttribute(flash_bwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL);

@@ -128,9 +128,28 @@ __device__ __forceinline__ uint4 ld_cg_v4(const uint4* p) {
   return v;
 }
 
-// tile order: m-tiles (256 rows) grouped so that a group never straddles two ranks' rows, groups visited starting at
-// rank `first`'s rows; inside a group n-major so CTA pairs running together share A and B panels in L2
-__device__ __forceinline__ void tile_mn(int t, int num_m, int num_n, int group_m, int rot, int& m, int& n) {
+// Tile order.
+// MODE_AG: m-tiles (256 rows) grouped so that a group never straddles two ranks' rows, groups visited starting at this
+//   rank's rows (the order in which slabs arrive); inside a group n-major so CTA pairs running together share A and B panels.
+// MODE_RS: consecutive tiles belong to consecutive owners (rank+1, rank+2, ..., own rows last in every round of W tiles), so at
+//   any moment the pairs of this GPU store to all peers at once and NVLink is busy for the whole kernel instead of idling
+//   while the own rows are computed.  Tiles are grouped (about 8 m-tiles, the same number from every owner) and swept n-major
+//   inside a group, so the group's A panels stay in L2 while the B panels stream.
+template <int MODE>
+__device__ __forceinline__ void tile_mn(int t, int num_m, int num_n, int group_m, int rot, int world, int rank, int tiles_per_rank,
+                                        int& m, int& n) {
+  if (MODE == MODE_RS) {
+    // group = `group_m` m-tiles of EVERY owner; inside a group n is the slow index and owners alternate fastest
+    const int gw = group_m * world;
+    const int per_group = gw * num_n;
+    const int g = t / per_group;
+    const int r = t - g * per_group;
+    n = r / gw;
+    const int mm = r - n * gw;
+    const int owner = (rank + 1 + mm % world) % world;
+    m = owner * tiles_per_rank + g * group_m + mm / world;
+    return;
+  }
   const int per_group = group_m * num_n;
   const int g = t / per_group;
   const int r = t - g * per_group;
@@ -200,7 +219,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(224, 1) gemm2_comm_k
         int stage = 0; uint32_t phase = 0;
         for (int t = pair; t < num_tiles && alive; t += npairs) {
           int m_blk, n_blk;
-          tile_mn(t, num_m, num_n, p.group_m, rot, m_blk, n_blk);
+          tile_mn<MODE>(t, num_m, num_n, p.group_m, rot, p.world, p.rank, tiles_per_rank, m_blk, n_blk);
           if (MODE == MODE_AG && (m_blk / tiles_per_rank) != p.rank) {
             if (!wait_flag_ge(p.flag_local + F_READY + m_blk, p.ready_target, p.status, 0x40u, p.wait_ns)) { alive = false; break; }
             asm volatile("fence.proxy.async.global;" ::: "memory");   // peers' writes -> this thread's TMA (async proxy) reads
@@ -268,29 +287,38 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(224, 1) gemm2_comm_k
       const unsigned int owner_target = (unsigned int)(tiles_per_rank * num_n * 8);   // epilogue warps per owner
       int acc = 0; uint32_t acc_phase = 0;
       uint32_t chunk = 0;
-      int cur_owner = -1; unsigned int cur_count = 0;      // RS: tiles of `cur_owner` this warp has stored so far
-      // RS: this warp's tiles for an owner are in that owner's staging once its stores have completed; count them on
-      // this GPU's per-owner counter and, when the owner's last warp-tile is in, raise this rank's flag at the owner.
-      // One full-completion wait per owner, not per tile: stores of consecutive tiles stay in flight.
-      auto finish_owner = [&]() {
-        if (MODE != MODE_RS || cur_owner < 0 || lane != 0) return;
+      unsigned int owner_count[MAX_R];                     // RS: tiles of each owner this warp has stored
+#pragma unroll
+      for (int o = 0; o < MAX_R; ++o) owner_count[o] = 0;
+      // RS: this warp's tiles are in the owners' staging once its stores have completed; it then adds its counts to this
+      // GPU's per-owner counters and, for every owner whose last warp-tile is in, raises this rank's flag at that owner.
+      // One full-completion wait per warp, not per tile: stores of consecutive tiles stay in flight.
+      auto finish_owners = [&]() {
+        if (MODE != MODE_RS || lane != 0) return;
         tma_store_wait<0>();
         __threadfence_system();
-        const unsigned int prev = atomicAdd(p.flag_local + F_PHASE + cur_owner, cur_count);
-        if (prev + cur_count == owner_target) {
-          p.flag_local[F_PHASE + cur_owner] = 0u;                     // ready for the next call
-          __threadfence_system();
-          st_release_sys(p.flag_peer[cur_owner] + F_DONE + p.rank, p.epoch);
+#pragma unroll
+        for (int o = 0; o < MAX_R; ++o) {
+          if (o >= p.world) break;
+          // every warp reports to every owner's counter (possibly with 0) so the last reporter can be recognised
+          const unsigned int prev = atomicAdd(p.flag_local + F_PHASE + o, owner_count[o] + 0x10000u);
+          if ((prev >> 16) + 1u == (unsigned int)(gridDim.x * 4) && (prev & 0xffffu) + owner_count[o] == owner_target) {
+            p.flag_local[F_PHASE + o] = 0u;                             // ready for the next call
+            __threadfence_system();
+            st_release_sys(p.flag_peer[o] + F_DONE + p.rank, p.epoch);
+          }
         }
       };
       for (int t = pair; t < num_tiles && alive; t += npairs) {
         int m_blk, n_blk;
-        tile_mn(t, num_m, num_n, p.group_m, rot, m_blk, n_blk);
+        tile_mn<MODE>(t, num_m, num_n, p.group_m, rot, p.world, p.rank, tiles_per_rank, m_blk, n_blk);
         if (!mbar_wait(tfull_bar(acc), acc_phase, p.status, 0x30u, p.wait_ns)) { alive = false; break; }
         tc_fence_after();
         const int owner = m_blk / tiles_per_rank;
-        if (owner != cur_owner) { finish_owner(); cur_owner = owner; cur_count = 0; }
-        ++cur_count;
+        if (MODE == MODE_RS) {
+#pragma unroll
+          for (int o = 0; o < MAX_R; ++o) if (o == owner) ++owner_count[o];
+        }
         const int row0 = m_blk * (2 * BM) + (int)cta * BM + q * 32;
         const int drow = (MODE == MODE_RS) ? row0 - owner * p.rows_per_rank : row0;
         const CUtensorMap* tmD = (MODE == MODE_RS) ? &p.tmD[owner] : &p.tmD[0];
@@ -333,7 +361,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(224, 1) gemm2_comm_k
         if (lane == 0) mbar_arrive_cluster(lead_tempty[acc]);
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
-      if (alive) finish_owner();
+      if (alive) finish_owners();
       if (lane == 0) tma_store_wait<0>();
       if (warp == 2 && lane == 0) stamp(4);
     } else if (MODE == MODE_AG) {
@@ -533,6 +561,7 @@ static int fill_comm2(Comm2Params& p, const MsbComm2Args* a, int mode) {
   p.wait_ns = (a->wait_limit_ms > 0 ? (unsigned long long)a->wait_limit_ms : 10000ull) * 1000000ull;
   const int tiles_per_rank = p.rows_per_rank / (2 * BM);
   p.group_m = 8;
+  if (mode == MODE_RS) p.group_m = 8 / a->world > 0 ? 8 / a->world : 1;   // per owner; a group holds group_m * world m-tiles
   while (tiles_per_rank % p.group_m != 0) p.group_m >>= 1;
   if (mode == MODE_AG) {
     rc = make_tmap_2d(&p.tmD[0], a->D, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->M, a->N, a->N, 32, 64);
