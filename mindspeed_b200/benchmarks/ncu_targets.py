@@ -4,6 +4,7 @@
   python -m mindspeed_b200.benchmarks.ncu_targets elementwise # rmsnorm / swiglu / rope / adam / cross-entropy once each
   python -m mindspeed_b200.benchmarks.ncu_targets fp8         # 3 launches of the block-scaled fp8 GEMM, 8192 x 8192 x 8192
   python -m mindspeed_b200.benchmarks.ncu_targets gemm_tp8    # the four forward GEMM shapes of a Llama-3-8B layer at TP8
+  python -m mindspeed_b200.benchmarks.ncu_targets flash       # 2 launches each of flash-attention forward and backward
 
 Inputs exceed the 126 MB L2 but stay well under 2 GB on the device; there are only a handful of launches, so a
 ``--set full`` capture ends by itself within a minute or two.
@@ -91,5 +92,21 @@ def gemm_tp8():
     G.check_status()
 
 
+def flash():
+    """Two launches each of the flash-attention forward and backward kernels: seq 4096, 8 query / 2 KV heads, causal."""
+    from ..ops import gemm as G
+    from ..ops.flash_sm100_impl import flash_bwd, flash_fwd
+    s, nq, nkv = 4096, 8, 2
+    q = torch.randn(s, 1, nq, 128, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(s, 1, nkv, 128, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(s, 1, nkv, 128, device="cuda", dtype=torch.bfloat16)
+    do = torch.randn(s, 1, nq, 128, device="cuda", dtype=torch.bfloat16)
+    for _ in range(2):
+        o, lse = flash_fwd(q, k, v, True, 128 ** -0.5)
+        flash_bwd(do, q, k, v, o, lse, True, 128 ** -0.5)
+    torch.cuda.synchronize()
+    G.check_status()
+
+
 if __name__ == "__main__":
-    {"gemm": gemm, "elementwise": elementwise, "fp8": fp8, "gemm_tp8": gemm_tp8}[sys.argv[1] if len(sys.argv) > 1 else "gemm"]()
+    {"gemm": gemm, "elementwise": elementwise, "fp8": fp8, "gemm_tp8": gemm_tp8, "flash": flash}[sys.argv[1] if len(sys.argv) > 1 else "gemm"]()

@@ -47,20 +47,37 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s: far beyond any healthy intra-kernel wait
 
 // Bounded wait. Returns true when the phase completed, false on time-out (status word set to `code`).
+// The fast path is a tight try_wait loop (the instruction itself suspends the thread for a short, hardware-chosen time when
+// the phase is not complete); the wall clock and the shared status word are looked at only once per 1024 polls, because a
+// global-memory read in the polling loop would add its latency to every hand-over between the roles of a kernel.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int* status, unsigned int code,
                                           uint64_t limit_ns = WAIT_LIMIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (globaltimer_ns() - t0 > limit_ns) {
-      if (status) atomicCAS(status, 0u, code);
-      return false;
+  uint64_t t0 = 0;
+  for (uint32_t spins = 1;; ++spins) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 1023u) == 0u) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > limit_ns) {
+        if (status) atomicCAS(status, 0u, code);
+        return false;
+      }
+      if (status && *((volatile unsigned int*)status) != 0u) return false;  // someone else already gave up
     }
-    if (status && *((volatile unsigned int*)status) != 0u) return false;  // someone else already gave up
   }
+}
+
+// The same wait for a whole warp (all 32 lanes must call it): lane 0 polls, the others sleep at the warp barrier instead of
+// hammering the barrier word (hundreds of polling threads slow the MMA and TMA traffic of the same SM down), then every lane
+// looks at the completed phase once so that it has observed the completion itself.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, unsigned int* status, unsigned int code,
+                                               uint64_t limit_ns = WAIT_LIMIT_NS) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, status, code, limit_ns) ? 1 : 0;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  if (ok) (void)mbar_try_wait(bar, parity);
+  return ok != 0;
 }
 
 // ---------------- TMA ----------------

@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(320, 1) flash_fwd2_sm100_kernel(const __grid_c
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(s_full(t), 1); mbar_init(p_full(t), 128); mbar_init(pv_done(t), 1); }
+    for (int t = 0; t < 2; ++t) { mbar_init(s_full(t), 1); mbar_init(p_full(t), 4); mbar_init(pv_done(t), 1); }
     mbar_fence_init();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
@@ -261,7 +261,8 @@ __global__ void __launch_bounds__(320, 1) flash_fwd2_sm100_kernel(const __grid_c
       }
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(p_full(t));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full(t));       // one arrival per warp: 128 arrivals on one barrier would serialise
       l_run += l_tile;
     }
     // ---- epilogue of this tile ----
@@ -385,7 +386,6 @@ struct BwdParams {
   int causal, q_offset;
   float scale, scale_log2;
   unsigned int* status;
-  int debug;
 };
 
 struct BwdSmem {
@@ -471,8 +471,8 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(qdo_full(s), 1); mbar_init(qdo_empty(s), 1); }
-    mbar_init(st_full, 1); mbar_init(dpt_full, 1); mbar_init(pt_ready, 256); mbar_init(ds_ready, 256);
-    mbar_init(dq_full, 1); mbar_init(dq_drained, 256); mbar_init(acc_done, 1);
+    mbar_init(st_full, 1); mbar_init(dpt_full, 1); mbar_init(pt_ready, 8); mbar_init(ds_ready, 8);
+    mbar_init(dq_full, 1); mbar_init(dq_drained, 8); mbar_init(acc_done, 1);
     mbar_fence_init();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
@@ -570,17 +570,11 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
       const uint32_t ip = (uint32_t)(it & 1);
       const int head = g * rep + it / n_i, i = i_start + it % n_i;
       const int qrow0 = i * FB + ch * 64;              // first query row of this thread's 64 columns
-      // row statistics of this thread's 64 query columns: the same addresses for the whole warp (broadcast loads, L1 hits)
+      // row statistics of this warp's 64 query columns: lane l fetches columns 2l and 2l+1 now (the latency hides behind the
+      // wait for S^T) and the loops below broadcast them with shuffles
       const size_t stat = ((size_t)batch * p.nq + head) * p.sq_pad + (size_t)i * FB + ch * 64;
-      const float4* lse2_v = reinterpret_cast<const float4*>(p.lse2 + stat);
-      const float4* dlt_v = reinterpret_cast<const float4*>(p.delta + stat);
-      if (it + 1 < n_it && lane < 4) {
-        // pull the next iteration's statistics (2 x 256 bytes per warp) into L1 now, so its loads do not wait on L2
-        const int it2 = it + 1;
-        const size_t stat2 = ((size_t)batch * p.nq + (g * rep + it2 / n_i)) * p.sq_pad + (size_t)(i_start + it2 % n_i) * FB + ch * 64;
-        const float* a2 = (lane < 2 ? p.lse2 : p.delta) + stat2 + (lane & 1) * 32;
-        asm volatile("prefetch.global.L1 [%0];" ::"l"(a2));
-      }
+      const float2 my_lse = __ldg(reinterpret_cast<const float2*>(p.lse2 + stat) + lane);
+      const float2 my_dlt = __ldg(reinterpret_cast<const float2*>(p.delta + stat) + lane);
       // keys of this tile visible to query row r: key <= r + q_offset (causal), key < sk
       const bool full_tile = (!p.causal || key0 + FB - 1 <= i * FB + p.q_offset) && key0 + FB <= p.sk;
       float pv[64];
@@ -594,17 +588,12 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
         tmem_ld_wait();
         named_bar(3 + q, 64);                           // the partner warp (other column half, same lanes) has read its scores too
 #pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) {
-          const float4 l4 = __ldg(lse2_v + c4);
-          const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int c = 4 * c4 + e;
-            const float sc = __uint_as_float(c < 32 ? r0[c] : r1[c - 32]);
-            float pr = (p.debug & 2) ? sc : exp2f(sc * p.scale_log2 - ls[e]);
-            if (!full_tile && (key >= p.sk || (p.causal && key > qrow0 + c + p.q_offset))) pr = 0.f;
-            pv[c] = pr;
-          }
+        for (int c = 0; c < 64; ++c) {
+          const float ls = __shfl_sync(0xffffffffu, (c & 1) ? my_lse.y : my_lse.x, c >> 1);
+          const float sc = __uint_as_float(c < 32 ? r0[c] : r1[c - 32]);
+          float pr = exp2f(fmaf(sc, p.scale_log2, -ls));
+          if (!full_tile && (key >= p.sk || (p.causal && key > qrow0 + c + p.q_offset))) pr = 0.f;
+          pv[c] = pr;
         }
         uint32_t pk[32];
 #pragma unroll
@@ -616,7 +605,8 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
         tmem_st_32x16(tST + lane_addr + (uint32_t)(ch * 32 + 16), pk + 16);
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(pt_ready);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pt_ready);
       }
       // ---- dS^T ----
       if (!mbar_wait(dpt_full, ip, p.status, 0x431u)) { ok = false; break; }
@@ -632,16 +622,12 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
         __syncwarp();
         uint32_t pk[32];
 #pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) {
-          const float4 d4 = __ldg(dlt_v + c4);
-          const int c = 4 * c4;
-          const float d0 = pv[c] * (__uint_as_float(c < 32 ? r0[c] : r1[c - 32]) - d4.x);
-          const float d1 = pv[c + 1] * (__uint_as_float(c + 1 < 32 ? r0[c + 1] : r1[c + 1 - 32]) - d4.y);
-          const float d2 = pv[c + 2] * (__uint_as_float(c + 2 < 32 ? r0[c + 2] : r1[c + 2 - 32]) - d4.z);
-          const float d3 = pv[c + 3] * (__uint_as_float(c + 3 < 32 ? r0[c + 3] : r1[c + 3 - 32]) - d4.w);
-          __nv_bfloat162 h0 = __floats2bfloat162_rn(d0, d1), h1 = __floats2bfloat162_rn(d2, d3);
-          pk[2 * c4] = *reinterpret_cast<uint32_t*>(&h0);
-          pk[2 * c4 + 1] = *reinterpret_cast<uint32_t*>(&h1);
+        for (int c = 0; c < 32; ++c) {
+          const float dl0 = __shfl_sync(0xffffffffu, my_dlt.x, c), dl1 = __shfl_sync(0xffffffffu, my_dlt.y, c);
+          const float d0 = pv[2 * c] * (__uint_as_float(2 * c < 32 ? r0[2 * c] : r1[2 * c - 32]) - dl0);
+          const float d1 = pv[2 * c + 1] * (__uint_as_float(2 * c + 1 < 32 ? r0[2 * c + 1] : r1[2 * c + 1 - 32]) - dl1);
+          __nv_bfloat162 hh = __floats2bfloat162_rn(d0, d1);
+          pk[c] = *reinterpret_cast<uint32_t*>(&hh);
         }
         tmem_st_32x16(tDPT + lane_addr + (uint32_t)(ch * 32), pk);
         tmem_st_32x16(tDPT + lane_addr + (uint32_t)(ch * 32 + 16), pk + 16);
@@ -653,7 +639,8 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
         tmem_st_wait();
         fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive(ds_ready);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ds_ready);
       }
       // ---- dQ: lanes are query rows now; this warp drains rows 32q.. of d columns 64ch.. in two rounds of 32 columns ----
       if (!mbar_wait(dq_full, ip, p.status, 0x432u)) { ok = false; break; }
@@ -665,7 +652,8 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
         tmem_ld_32x32(tD + 32u, r1);
         tmem_ld_wait();
         tc_fence_before();
-        mbar_arrive(dq_drained);                         // the MMA thread may overwrite S^T / dP^T
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dq_drained);          // the MMA thread may overwrite S^T / dP^T
         const int qr = i * FB + q * 32;                  // first query row of this warp's block
 #pragma unroll
         for (int rnd = 0; rnd < 2; ++rnd) {
@@ -680,7 +668,7 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
           }
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0 && qr < p.sq && !(p.debug & 1)) {
+          if (lane == 0 && qr < p.sq) {
             tma_reduce_add_4d(&p.tmdQ, my4k, ch * 64 + rnd * 32, head, batch, qr);
             tma_store_commit();
           }
@@ -771,7 +759,6 @@ MSB_API int msb_flash_bwd(const void* q, const void* k, const void* v, const voi
   p.lse2 = lse2; p.delta = delta;
   p.sq = sq; p.sk = sk; p.b = b; p.nq = nq; p.nkv = nkv; p.sq_pad = sq_pad; p.causal = causal; p.q_offset = q_offset;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-  { const char* d = getenv("MSB200_FLASH_DEBUG"); p.debug = d ? atoi(d) : 0; }
   static bool attr = false;
   if (!attr) {
     cudaError_t e = cudaFuncSetAttribute(flash_bwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL);

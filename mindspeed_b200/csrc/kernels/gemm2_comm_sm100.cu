@@ -312,7 +312,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(224, 1) gemm2_comm_k
       for (int t = pair; t < num_tiles && alive; t += npairs) {
         int m_blk, n_blk;
         tile_mn<MODE>(t, num_m, num_n, p.group_m, rot, p.world, p.rank, tiles_per_rank, m_blk, n_blk);
-        if (!mbar_wait(tfull_bar(acc), acc_phase, p.status, 0x30u, p.wait_ns)) { alive = false; break; }
+        if (!mbar_wait_warp(tfull_bar(acc), acc_phase, p.status, 0x30u, p.wait_ns)) { alive = false; break; }
         tc_fence_after();
         const int owner = m_blk / tiles_per_rank;
         if (MODE == MODE_RS) {

@@ -228,7 +228,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1) gemm2_groupe
     TileCursor<MODE> cur(p, pair, npairs);
     int m_blk, n_blk;
     while (alive && cur.next(m_blk, n_blk)) {
-      if (!mbar_wait(tfull_bar(acc), acc_phase, p.status, 0x30u)) { alive = false; break; }
+      if (!mbar_wait_warp(tfull_bar(acc), acc_phase, p.status, 0x30u)) { alive = false; break; }
       tc_fence_after();
       // first output row of this warp; GG_ROWS: absolute row of Y, rows at or beyond `limit` belong to the next expert
       const int row0 = (MODE == GG_ROWS ? cur.start : 0) + m_blk * (2 * BM) + (int)cta * BM + q * 32;

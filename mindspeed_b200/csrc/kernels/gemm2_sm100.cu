@@ -223,7 +223,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1) gemm2_sm100_
     while (alive && it.next()) {
       int m_blk, n_blk;
       tile_coords2(it.tile, num_m, num_n, p.group_m, m_blk, n_blk);
-      if (!mbar_wait(tfull_bar(acc), acc_phase, p.status, 0x30u)) { alive = false; break; }
+      if (!mbar_wait_warp(tfull_bar(acc), acc_phase, p.status, 0x30u)) { alive = false; break; }
       tc_fence_after();
       const int row0 = m_blk * (2 * BM) + (int)cta * BM + q * 32;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
