@@ -367,9 +367,11 @@ MSB_API int msb_flash_fwd2(const void* q, const void* k, const void* v, void* o,
 // buffer with TMA reduce-adds (other key tiles add into the same rows).
 //   warp 0      TMA producer: K, V once; Q_i, dO_i, LSE_i, delta_i into a 2-stage ring
 //   warp 1      MMA issuer (one thread)
-//   warps 2-9   compute: warp w owns key rows 32 (w mod 4) .. +31 and query columns 64 ((w-2)/4) .. +63 of the tile:
-//               P^T = exp2(S^T scale log2e - LSE log2e), dS^T = P^T (dP^T - delta); the softmax scale is applied when dQ
-//               and dK leave the SM
+//   warps 2-5   softmax: warp w owns key rows 32 (w mod 4) .. +31 and all 128 query columns of the tile:
+//               P^T = exp2(S^T scale log2e - LSE log2e), dS^T = P^T (dP^T - delta)
+//   warps 6-9   dQ: read the finished dQ tile out of tensor memory (which frees S^T / dP^T for the next iteration at
+//               once), apply the softmax scale and add it into global memory, off the critical path of the next tile
+//               (all eight warps share the final write-out of dK and dV, where the scale of dK is applied)
 // delta = rowsum(dO * O) and the LSE in log2 units are prepared by flash_bwd_prep_kernel into buffers padded to whole tiles
 // (padding rows get LSE = +inf so their probabilities are zero).
 // reference semantics: the attention grad op of the reference, mindspeed/ops/csrc/cann/fusion_attention_v2.cpp:431-439.
@@ -379,12 +381,13 @@ namespace {
 struct BwdParams {
   CUtensorMap tmQ, tmK, tmV, tmdO;  // bf16, dims {d, head, batch, seq}
   CUtensorMap tmdQ;                 // fp32 [sq, b, nq, d], dims {d, head, batch, seq}, box {32, 1, 1, 32}
-  CUtensorMap tmdK, tmdV;           // bf16 [sk, b, nkv, d] outputs
+  CUtensorMap tmdK, tmdV;           // [sk, b, nkv, d] outputs: bf16 stores, or fp32 reduce-add targets (box {32,1,1,32}) when split_heads
   const float* lse2;                // [b, nq, sq_pad] LSE * log2(e) (+inf where no key is visible / padding)
   const float* delta;               // [b, nq, sq_pad]
   int sq, sk, b, nq, nkv, sq_pad;
   int causal, q_offset;
   float scale, scale_log2;
+  int split_heads;                  // 1: one CTA per (key tile, QUERY head); dK / dV partial sums are added into fp32 buffers
   unsigned int* status;
 };
 
@@ -456,8 +459,11 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // key tiles that many query tiles see (early ones, when causal) first
   const int j = (int)blockIdx.x;
-  const int g = blockIdx.y, batch = blockIdx.z;
-  const int rep = p.nq / p.nkv;
+  // without the split a CTA walks all query heads of its KV head; with it (few KV heads: too few CTAs otherwise) one each
+  const int rep_all = p.nq / p.nkv;
+  const int g = p.split_heads ? (int)blockIdx.y / rep_all : (int)blockIdx.y, batch = blockIdx.z;
+  const int head0 = p.split_heads ? (int)blockIdx.y : g * rep_all;
+  const int rep = p.split_heads ? 1 : rep_all;
   const int key0 = j * FB;
   const int n_q = (p.sq + FB - 1) / FB;
   int i_start = 0;
@@ -471,8 +477,8 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(qdo_full(s), 1); mbar_init(qdo_empty(s), 1); }
-    mbar_init(st_full, 1); mbar_init(dpt_full, 1); mbar_init(pt_ready, 8); mbar_init(ds_ready, 8);
-    mbar_init(dq_full, 1); mbar_init(dq_drained, 8); mbar_init(acc_done, 1);
+    mbar_init(st_full, 1); mbar_init(dpt_full, 1); mbar_init(pt_ready, 4); mbar_init(ds_ready, 4);
+    mbar_init(dq_full, 1); mbar_init(dq_drained, 4); mbar_init(acc_done, 1);
     mbar_fence_init();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
@@ -494,7 +500,7 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
       for (int it = 0; it < n_it && ok; ++it) {
         const int s = it & 1;
         const uint32_t ph = (uint32_t)((it >> 1) & 1);
-        const int head = g * rep + it / n_i, i = i_start + it % n_i;
+        const int head = head0 + it / n_i, i = i_start + it % n_i;
         if (!mbar_wait(qdo_empty(s), ph ^ 1u, p.status, 0x410u)) { ok = false; break; }
         mbar_arrive_expect_tx(qdo_full(s), 2 * TILE_BYTES);
         const uint32_t qs = base + BwdSmem::Q_OFF + s * TILE_BYTES, ds = base + BwdSmem::DO_OFF + s * TILE_BYTES;
@@ -557,99 +563,120 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
       if (ok) umma_commit(acc_done);
     }
   } else {
-    // ===================== compute warps 2..9 =====================
-    const int q = warp & 3, ch = (warp - 2) >> 2;
+    // ===================== warps 2..5: P^T and dS^T;  warps 6..9: dQ out of the SM =====================
+    const int q = warp & 3;
+    const bool drainer = warp >= 6;
+    const int ch = (warp - 2) >> 2;                    // column half this warp drains from dK / dV at the very end
     const int row = q * 32 + lane;                     // key row inside the tile == TMEM lane (query row when draining dQ)
     const int key = key0 + row;
     const uint32_t lane_addr = ((uint32_t)(q * 32) << 16);
-    const uint32_t my4k = base + BwdSmem::DS_OFF + (uint32_t)(ch * HALF_BYTES + q * 4096);   // this warp's private 4 KB
-    uint8_t* my4k_ptr = base_ptr + BwdSmem::DS_OFF + ch * HALF_BYTES + q * 4096;
+    // rows 32q .. 32q+31 of the two 64-column halves of the dS^T buffer: 2 x 4 KB shared by softmax warp q (dS^T rows) and
+    // drain warp q (dQ staging); the pair hands them back and forth over named barrier 3 + q
+    uint8_t* piece_ptr[2] = {base_ptr + BwdSmem::DS_OFF + q * 4096, base_ptr + BwdSmem::DS_OFF + HALF_BYTES + q * 4096};
+    const uint32_t piece[2] = {base + BwdSmem::DS_OFF + (uint32_t)(q * 4096), base + BwdSmem::DS_OFF + (uint32_t)(HALF_BYTES + q * 4096)};
     bool ok = true;
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int s = it & 1;
-      const uint32_t ip = (uint32_t)(it & 1);
-      const int head = g * rep + it / n_i, i = i_start + it % n_i;
-      const int qrow0 = i * FB + ch * 64;              // first query row of this thread's 64 columns
-      // row statistics of this warp's 64 query columns: lane l fetches columns 2l and 2l+1 now (the latency hides behind the
-      // wait for S^T) and the loops below broadcast them with shuffles
-      const size_t stat = ((size_t)batch * p.nq + head) * p.sq_pad + (size_t)i * FB + ch * 64;
-      const float2 my_lse = __ldg(reinterpret_cast<const float2*>(p.lse2 + stat) + lane);
-      const float2 my_dlt = __ldg(reinterpret_cast<const float2*>(p.delta + stat) + lane);
-      // keys of this tile visible to query row r: key <= r + q_offset (causal), key < sk
-      const bool full_tile = (!p.causal || key0 + FB - 1 <= i * FB + p.q_offset) && key0 + FB <= p.sk;
-      float pv[64];
-      // ---- P^T ----
-      if (!mbar_wait(st_full, ip, p.status, 0x430u)) { ok = false; break; }
-      tc_fence_after();
-      {
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32(tST + lane_addr + (uint32_t)(ch * 64), r0);
-        tmem_ld_32x32(tST + lane_addr + (uint32_t)(ch * 64 + 32), r1);
-        tmem_ld_wait();
-        named_bar(3 + q, 64);                           // the partner warp (other column half, same lanes) has read its scores too
+    if (!drainer) {
+      // ---------------- softmax warps: one thread per key row, all 128 query columns ----------------
+      auto load_stats = [&](int it2, float4& l, float4& d) {
+        const size_t stat = ((size_t)batch * p.nq + (head0 + it2 / n_i)) * p.sq_pad + (size_t)(i_start + it2 % n_i) * FB;
+        l = __ldg(reinterpret_cast<const float4*>(p.lse2 + stat) + lane);
+        d = __ldg(reinterpret_cast<const float4*>(p.delta + stat) + lane);
+      };
+      // row statistics of the tile's 128 query columns: lane l holds columns 4l .. 4l+3, fetched one iteration ahead (an
+      // L2 / HBM round trip is longer than a phase); the loops broadcast them with shuffles
+      float4 nxt_lse = make_float4(0.f, 0.f, 0.f, 0.f), nxt_dlt = nxt_lse;
+      if (n_it > 0) load_stats(0, nxt_lse, nxt_dlt);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const uint32_t ip = (uint32_t)(it & 1);
+        const int i = i_start + it % n_i;
+        const float4 my_lse = nxt_lse, my_dlt = nxt_dlt;
+        if (it + 1 < n_it) load_stats(it + 1, nxt_lse, nxt_dlt);
+        const float ls4[4] = {my_lse.x, my_lse.y, my_lse.z, my_lse.w};
+        const float dl4[4] = {my_dlt.x, my_dlt.y, my_dlt.z, my_dlt.w};
+        // keys of this tile visible to query row r: key <= r + q_offset (causal), key < sk
+        // <=> query column c of the tile is visible to this thread's key iff c >= first_c
+        const int first_c = (key >= p.sk) ? FB : (p.causal ? key - p.q_offset - i * FB : 0);
+        uint32_t ppk[64];                              // P^T of this row, packed bf16 pairs (kept for dS^T)
+        // ---- P^T = exp2(S^T scale log2e - LSE log2e), 64 columns at a time ----
+        if (!mbar_wait(st_full, ip, p.status, 0x430u)) { ok = false; break; }
+        tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          const float ls = __shfl_sync(0xffffffffu, (c & 1) ? my_lse.y : my_lse.x, c >> 1);
-          const float sc = __uint_as_float(c < 32 ? r0[c] : r1[c - 32]);
-          float pr = exp2f(fmaf(sc, p.scale_log2, -ls));
-          if (!full_tile && (key >= p.sk || (p.causal && key > qrow0 + c + p.q_offset))) pr = 0.f;
-          pv[c] = pr;
-        }
-        uint32_t pk[32];
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(tST + lane_addr + (uint32_t)(h * 64), r0);
+          tmem_ld_32x32(tST + lane_addr + (uint32_t)(h * 64 + 32), r1);
+          tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          __nv_bfloat162 hh = __floats2bfloat162_rn(pv[2 * c], pv[2 * c + 1]);
-          pk[c] = *reinterpret_cast<uint32_t*>(&hh);
+          for (int c = 0; c < 32; ++c) {
+            float pr[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int cc = 2 * c + e;
+              const float ls = __shfl_sync(0xffffffffu, ls4[cc & 3], h * 16 + (cc >> 2));
+              const float sc = __uint_as_float(cc < 32 ? r0[cc] : r1[cc - 32]);
+              const float v = exp2f(fmaf(sc, p.scale_log2, -ls));
+              pr[e] = (h * 64 + cc < first_c) ? 0.f : v;   // a select, never a branch (a short-circuit test per element costs one)
+            }
+            __nv_bfloat162 hh = __floats2bfloat162_rn(pr[0], pr[1]);
+            ppk[h * 32 + c] = *reinterpret_cast<uint32_t*>(&hh);
+          }
+          // P^T columns [32h, 32h+32) overwrite S^T columns this warp has already read (nobody else touches these lanes)
+          tmem_st_32x16(tST + lane_addr + (uint32_t)(h * 32), ppk + h * 32);
+          tmem_st_32x16(tST + lane_addr + (uint32_t)(h * 32 + 16), ppk + h * 32 + 16);
         }
-        tmem_st_32x16(tST + lane_addr + (uint32_t)(ch * 32), pk);
-        tmem_st_32x16(tST + lane_addr + (uint32_t)(ch * 32 + 16), pk + 16);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(pt_ready);
-      }
-      // ---- dS^T ----
-      if (!mbar_wait(dpt_full, ip, p.status, 0x431u)) { ok = false; break; }
-      tc_fence_after();
-      {
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32(tDPT + lane_addr + (uint32_t)(ch * 64), r0);
-        tmem_ld_32x32(tDPT + lane_addr + (uint32_t)(ch * 64 + 32), r1);
-        tmem_ld_wait();
-        named_bar(3 + q, 64);
-        // the reduce-adds of the previous iteration's dQ read this warp's 4 KB: they must be done before it is rewritten
-        if (lane == 0) tma_store_wait_read<0>();
-        __syncwarp();
-        uint32_t pk[32];
+        // ---- dS^T = P^T (dP^T - delta) ----
+        if (!mbar_wait(dpt_full, ip, p.status, 0x431u)) { ok = false; break; }
+        tc_fence_after();
+        named_bar(3 + q, 64);                           // drain warp q has handed the two staging pieces back
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float dl0 = __shfl_sync(0xffffffffu, my_dlt.x, c), dl1 = __shfl_sync(0xffffffffu, my_dlt.y, c);
-          const float d0 = pv[2 * c] * (__uint_as_float(2 * c < 32 ? r0[2 * c] : r1[2 * c - 32]) - dl0);
-          const float d1 = pv[2 * c + 1] * (__uint_as_float(2 * c + 1 < 32 ? r0[2 * c + 1] : r1[2 * c + 1 - 32]) - dl1);
-          __nv_bfloat162 hh = __floats2bfloat162_rn(d0, d1);
-          pk[c] = *reinterpret_cast<uint32_t*>(&hh);
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(tDPT + lane_addr + (uint32_t)(h * 64), r0);
+          tmem_ld_32x32(tDPT + lane_addr + (uint32_t)(h * 64 + 32), r1);
+          tmem_ld_wait();
+          uint32_t pk[32];
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const float dl0 = __shfl_sync(0xffffffffu, dl4[(2 * c) & 3], h * 16 + ((2 * c) >> 2));
+            const float dl1 = __shfl_sync(0xffffffffu, dl4[(2 * c + 1) & 3], h * 16 + ((2 * c + 1) >> 2));
+            const uint32_t pp = ppk[h * 32 + c];
+            const float p0 = __uint_as_float(pp << 16), p1 = __uint_as_float(pp & 0xffff0000u);
+            const float d0 = p0 * (__uint_as_float(2 * c < 32 ? r0[2 * c] : r1[2 * c - 32]) - dl0);
+            const float d1 = p1 * (__uint_as_float(2 * c + 1 < 32 ? r0[2 * c + 1] : r1[2 * c + 1 - 32]) - dl1);
+            __nv_bfloat162 hh = __floats2bfloat162_rn(d0, d1);
+            pk[c] = *reinterpret_cast<uint32_t*>(&hh);
+          }
+          tmem_st_32x16(tDPT + lane_addr + (uint32_t)(h * 32), pk);
+          tmem_st_32x16(tDPT + lane_addr + (uint32_t)(h * 32 + 16), pk + 16);
+          // shared-memory copy for the dQ MMA: row = key, 64 query columns = 8 chunks of 16 bytes, 128-byte swizzle
+          uint8_t* srow = piece_ptr[h] + lane * 128;
+#pragma unroll
+          for (int cchunk = 0; cchunk < 8; ++cchunk)
+            *reinterpret_cast<uint4*>(srow + ((cchunk ^ (row & 7)) << 4)) = make_uint4(pk[4 * cchunk], pk[4 * cchunk + 1], pk[4 * cchunk + 2], pk[4 * cchunk + 3]);
         }
-        tmem_st_32x16(tDPT + lane_addr + (uint32_t)(ch * 32), pk);
-        tmem_st_32x16(tDPT + lane_addr + (uint32_t)(ch * 32 + 16), pk + 16);
-        // shared-memory copy for the dQ MMA: row = key, 64 query columns = 8 chunks of 16 bytes, 128-byte swizzle
-        uint8_t* srow = my4k_ptr + lane * 128;
-#pragma unroll
-        for (int cchunk = 0; cchunk < 8; ++cchunk)
-          *reinterpret_cast<uint4*>(srow + ((cchunk ^ (row & 7)) << 4)) = make_uint4(pk[4 * cchunk], pk[4 * cchunk + 1], pk[4 * cchunk + 2], pk[4 * cchunk + 3]);
         tmem_st_wait();
         fence_proxy_async_smem();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(ds_ready);
       }
-      // ---- dQ: lanes are query rows now; this warp drains rows 32q.. of d columns 64ch.. in two rounds of 32 columns ----
-      if (!mbar_wait(dq_full, ip, p.status, 0x432u)) { ok = false; break; }
-      tc_fence_after();
-      {
-        const uint32_t tD = (ch == 0 ? tST : tDPT) + 64u + lane_addr;
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32(tD, r0);
-        tmem_ld_32x32(tD + 32u, r1);
+    } else {
+      // ---------------- drain warps: dQ (lanes = query rows) -> scale -> staging -> TMA reduce-add into the fp32 dQ ----------------
+      asm volatile("bar.arrive %0, 64;" ::"r"(3 + q) : "memory");      // the staging pieces start out free
+      for (int it = 0; it < n_it && ok; ++it) {
+        const uint32_t ip = (uint32_t)(it & 1);
+        const int head = head0 + it / n_i, i = i_start + it % n_i;
+        if (!mbar_wait(dq_full, ip, p.status, 0x432u)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t r[4][32];                               // d columns 32k .. 32k+31 of this lane's query row
+        tmem_ld_32x32(tST + 64u + lane_addr, r[0]);
+        tmem_ld_32x32(tST + 96u + lane_addr, r[1]);
+        tmem_ld_32x32(tDPT + 64u + lane_addr, r[2]);
+        tmem_ld_32x32(tDPT + 96u + lane_addr, r[3]);
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
@@ -658,20 +685,29 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
 #pragma unroll
         for (int rnd = 0; rnd < 2; ++rnd) {
           if (rnd == 1) { if (lane == 0) tma_store_wait_read<0>(); __syncwarp(); }
-          const uint32_t* rr = rnd == 0 ? r0 : r1;
-          uint8_t* srow = my4k_ptr + lane * 128;
 #pragma unroll
-          for (int cchunk = 0; cchunk < 8; ++cchunk) {
-            float4 o4 = make_float4(__uint_as_float(rr[4 * cchunk]) * p.scale, __uint_as_float(rr[4 * cchunk + 1]) * p.scale,
-                                    __uint_as_float(rr[4 * cchunk + 2]) * p.scale, __uint_as_float(rr[4 * cchunk + 3]) * p.scale);
-            *reinterpret_cast<float4*>(srow + ((cchunk ^ (lane & 7)) << 4)) = o4;
+          for (int b2 = 0; b2 < 2; ++b2) {
+            const uint32_t* rr = r[rnd * 2 + b2];
+            uint8_t* srow = piece_ptr[b2] + lane * 128;
+#pragma unroll
+            for (int cchunk = 0; cchunk < 8; ++cchunk) {
+              float4 o4 = make_float4(__uint_as_float(rr[4 * cchunk]) * p.scale, __uint_as_float(rr[4 * cchunk + 1]) * p.scale,
+                                      __uint_as_float(rr[4 * cchunk + 2]) * p.scale, __uint_as_float(rr[4 * cchunk + 3]) * p.scale);
+              *reinterpret_cast<float4*>(srow + ((cchunk ^ (lane & 7)) << 4)) = o4;
+            }
           }
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0 && qr < p.sq) {
-            tma_reduce_add_4d(&p.tmdQ, my4k, ch * 64 + rnd * 32, head, batch, qr);
+            tma_reduce_add_4d(&p.tmdQ, piece[0], rnd * 64, head, batch, qr);
+            tma_reduce_add_4d(&p.tmdQ, piece[1], rnd * 64 + 32, head, batch, qr);
             tma_store_commit();
           }
+        }
+        if (it + 1 < n_it) {
+          if (lane == 0) tma_store_wait_read<0>();       // the reduce-adds have read the staging: hand it back
+          __syncwarp();
+          asm volatile("bar.arrive %0, 64;" ::"r"(3 + q) : "memory");
         }
       }
     }
@@ -681,6 +717,38 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
       tc_fence_after();
       if (lane == 0) tma_store_wait_read<0>();
       __syncwarp();
+      if (p.split_heads) {
+        // partial sums of one query head: fp32 through this warp's own 8 KB of staging, two [32 x 32] boxes per tensor
+        const uint32_t st_addr = base + BwdSmem::Q_OFF + (uint32_t)((warp - 2) * 8192);
+        uint8_t* st_ptr = base_ptr + BwdSmem::Q_OFF + (warp - 2) * 8192;
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {
+          const uint32_t tA = (which == 0 ? tDV : tDK) + lane_addr + (uint32_t)(ch * 64);
+          const float mul = which == 0 ? 1.f : p.scale;
+          if (which == 1) { if (lane == 0) tma_store_wait_read<0>(); __syncwarp(); }
+#pragma unroll
+          for (int b2 = 0; b2 < 2; ++b2) {
+            uint32_t r[32];
+            tmem_ld_32x32(tA + (uint32_t)(b2 * 32), r);
+            tmem_ld_wait();
+            uint8_t* srow = st_ptr + b2 * 4096 + lane * 128;
+#pragma unroll
+            for (int cchunk = 0; cchunk < 8; ++cchunk)
+              *reinterpret_cast<float4*>(srow + ((cchunk ^ (lane & 7)) << 4)) =
+                  make_float4(__uint_as_float(r[4 * cchunk]) * mul, __uint_as_float(r[4 * cchunk + 1]) * mul,
+                              __uint_as_float(r[4 * cchunk + 2]) * mul, __uint_as_float(r[4 * cchunk + 3]) * mul);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (ok && lane == 0 && key0 + q * 32 < p.sk) {
+            const CUtensorMap* tm = which == 0 ? &p.tmdV : &p.tmdK;
+            tma_reduce_add_4d(tm, st_addr, ch * 64, g, batch, key0 + q * 32);
+            tma_reduce_add_4d(tm, st_addr + 4096u, ch * 64 + 32, g, batch, key0 + q * 32);
+            tma_store_commit();
+          }
+        }
+        if (lane == 0) tma_store_wait<0>();
+      } else {
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {          // 0: dV (no scale), 1: dK (softmax scale)
         const uint32_t tA = (which == 0 ? tDV : tDK) + lane_addr + (uint32_t)(ch * 64);
@@ -713,6 +781,7 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
         tma_store_commit();
       }
       if (lane == 0) tma_store_wait<0>();
+      }
     }
   }
   tc_fence_before();
@@ -725,8 +794,10 @@ __global__ void __launch_bounds__(320, 1) flash_bwd_sm100_kernel(const __grid_co
 // lse [b, nq, sq]; dq32 [sq, b, nq, 128] fp32 ZERO-INITIALISED by the caller (key tiles add into it), dk / dv
 // [sk, b, nkv, 128] bf16 contiguous, zero-initialised when some key tile is visible to no query; lse2 / delta: scratch
 // fp32 [b, nq, ceil(sq / 128) * 128] each.
+// split_heads = 1: dk / dv are fp32 [sk, b, nkv, 128] ZERO-INITIALISED buffers that every query head adds into (use when
+// ceil(sk / 128) * nkv * b is well below the SM count); 0: bf16 outputs written once.
 MSB_API int msb_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
-                          float* dq32, void* dk, void* dv, float* lse2, float* delta, int sq, int sk, int b, int nq, int nkv,
+                          float* dq32, void* dk, void* dv, float* lse2, float* delta, int split_heads, int sq, int sk, int b, int nq, int nkv,
                           long long q_ss, long long q_sb, long long q_sh, long long k_ss, long long k_sb, long long k_sh,
                           long long v_ss, long long v_sb, long long v_sh, long long do_ss, long long do_sb, long long do_sh,
                           int causal, int q_offset, float scale, unsigned int* status, cudaStream_t s) {
@@ -747,8 +818,17 @@ MSB_API int msb_flash_bwd(const void* q, const void* k, const void* v, const voi
   rc = make_map4(&p.tmK, k, sk, nkv, b, k_ss, k_sb, k_sh); if (rc) return rc;
   rc = make_map4(&p.tmV, v, sk, nkv, b, v_ss, v_sb, v_sh); if (rc) return rc;
   rc = make_map4(&p.tmdO, dout, sq, nq, b, do_ss, do_sb, do_sh); if (rc) return rc;
-  rc = make_map4(&p.tmdK, dk, sk, nkv, b, (long long)b * nkv * FD, (long long)nkv * FD, FD); if (rc) return rc;
-  rc = make_map4(&p.tmdV, dv, sk, nkv, b, (long long)b * nkv * FD, (long long)nkv * FD, FD); if (rc) return rc;
+  if (!split_heads) {
+    rc = make_map4(&p.tmdK, dk, sk, nkv, b, (long long)b * nkv * FD, (long long)nkv * FD, FD); if (rc) return rc;
+    rc = make_map4(&p.tmdV, dv, sk, nkv, b, (long long)b * nkv * FD, (long long)nkv * FD, FD); if (rc) return rc;
+  } else {
+    uint64_t dims[4] = {(uint64_t)FD, (uint64_t)nkv, (uint64_t)b, (uint64_t)sk};
+    uint64_t str[3] = {(uint64_t)FD * 4, (uint64_t)nkv * FD * 4, (uint64_t)b * nkv * FD * 4};
+    uint32_t box[4] = {32, 1, 1, 32};
+    rc = make_tmap_nd(&p.tmdK, dk, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, 4, dims, str, box); if (rc) return rc;
+    rc = make_tmap_nd(&p.tmdV, dv, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, 4, dims, str, box); if (rc) return rc;
+  }
+  p.split_heads = split_heads ? 1 : 0;
   {
     uint64_t dims[4] = {(uint64_t)FD, (uint64_t)nq, (uint64_t)b, (uint64_t)sq};
     uint64_t str[3] = {(uint64_t)FD * 4, (uint64_t)nq * FD * 4, (uint64_t)b * nq * FD * 4};
@@ -765,7 +845,7 @@ MSB_API int msb_flash_bwd(const void* q, const void* k, const void* v, const voi
     if (e != cudaSuccess) { msb_set_error("flash_bwd: cannot set dynamic shared memory: %s", cudaGetErrorString(e)); return 1; }
     attr = true;
   }
-  dim3 grid((sk + FB - 1) / FB, nkv, b);
+  dim3 grid((sk + FB - 1) / FB, split_heads ? nq : nkv, b);
   flash_bwd_sm100_kernel<<<grid, 320, BwdSmem::TOTAL, s>>>(p);
   MSB_CHECK_LAUNCH("flash_bwd_sm100");
   return 0;

@@ -25,6 +25,7 @@ HOST_LIB = os.path.join(CSRC, "libmsb200_host.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
               "-I" + os.path.join(CSRC, "include")]
+NVCC_FLAGS += os.environ.get("MSB200_NVCC_EXTRA", "").split()     # extra flags for experiments (part of the object hash)
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-fstack-protector-strong", "-D_FORTIFY_SOURCE=2",
              "-I" + os.path.join(CSRC, "include"), "-pthread"]
 

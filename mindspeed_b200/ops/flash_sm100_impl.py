@@ -54,18 +54,28 @@ def flash_bwd(dout, q, k, v, o, lse, causal, scale, q_offset=None):
     sq_pad = (sq + 127) // 128 * 128
     dq32 = torch.zeros(sq, b, nq, d, dtype=torch.float32, device=dev)
     never_seen = causal and (sq + q_offset < sk)       # trailing key tiles that no query row reaches keep zero gradients
-    alloc = torch.zeros if never_seen else torch.empty
-    dk = alloc(sk, b, nkv, d, dtype=torch.bfloat16, device=dev)
-    dv = alloc(sk, b, nkv, d, dtype=torch.bfloat16, device=dev)
+    # few (key tile, KV head) pairs would leave most SMs idle: then one CTA per QUERY head, partial dK / dV summed in fp32
+    n_ctas = ((sk + 127) // 128) * nkv * b
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    split = nq > nkv and n_ctas < 2 * sms
+    if split:
+        dk = torch.zeros(sk, b, nkv, d, dtype=torch.float32, device=dev)
+        dv = torch.zeros(sk, b, nkv, d, dtype=torch.float32, device=dev)
+    else:
+        alloc = torch.zeros if never_seen else torch.empty
+        dk = alloc(sk, b, nkv, d, dtype=torch.bfloat16, device=dev)
+        dv = alloc(sk, b, nkv, d, dtype=torch.bfloat16, device=dev)
     stats = torch.empty(2, b, nq, sq_pad, dtype=torch.float32, device=dev)
     ll = ctypes.c_longlong
     st = G.status_word(dev)
     loader.check(L.msb_flash_bwd(loader.p(q), loader.p(k), loader.p(v), loader.p(o), loader.p(dout), loader.p(lse), loader.p(dq32),
-                                 loader.p(dk), loader.p(dv), loader.p(stats[0]), loader.p(stats[1]), sq, sk, b, nq, nkv,
+                                 loader.p(dk), loader.p(dv), loader.p(stats[0]), loader.p(stats[1]), int(split), sq, sk, b, nq, nkv,
                                  ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)), ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)),
                                  ll(v.stride(0)), ll(v.stride(1)), ll(v.stride(2)), ll(dout.stride(0)), ll(dout.stride(1)),
                                  ll(dout.stride(2)), int(causal), int(q_offset), ctypes.c_float(scale), loader.p(st),
                                  ctypes.c_void_p(loader.stream_ptr())), "flash_bwd")
+    if split:
+        dk, dv = dk.to(torch.bfloat16), dv.to(torch.bfloat16)
     return dq32.to(torch.bfloat16), dk, dv
 
 
