@@ -66,9 +66,14 @@ class CoreAttention(nn.Module):
         elif attention_mask is not None and not self.causal:
             out = attn_ops.attention_ref(q, k, v, causal=False, softmax_scale=self.softmax_scale, mask=attention_mask)
         else:
-            # "auto" keeps the library kernel while it is the faster one on this shape; "sm100" forces the hand-written one
+            # "auto": the hand-written tcgen05 forward / backward at optimisation level >= 1 (shapes it does not cover fall
+            # back inside flash_attention), the library kernel at level 0; "library" / "sm100" force one
             want = getattr(self.config, "attention_backend", "auto")
-            backend = "sm100" if (want == "sm100" and self.config.optimization_level >= 1) else None
+            backend = None
+            if want == "library":
+                backend = "library"
+            elif self.config.optimization_level >= 1 and want in ("auto", "sm100"):
+                backend = "sm100"
             out = attn_ops.flash_attention(q, k, v, causal=self.causal, softmax_scale=self.softmax_scale, backend=backend)
         if self.dropout_p > 0 and self.training:
             with get_cuda_rng_tracker().fork():

@@ -129,6 +129,13 @@ def attn_bwd_ref(dout, q, k, v, out, lse, causal, softmax_scale=None, q_offset=0
 
 def attn_fwd_block(q, k, v, causal, softmax_scale=None):
     """(out [sq,b,nq,dv], lse [b,nq,sq] fp32, ctx) for one (Q block, KV block) pair; causal = top-left aligned."""
+    if q.is_cuda and get_backend(q) == "sm100":
+        from . import flash_sm100
+        if flash_sm100.supports(q, k, v, causal):
+            from .flash_sm100_impl import flash_fwd
+            scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(q.shape[-1])
+            out, lse = flash_fwd(q, k, v, causal, scale, q_offset=0)
+            return out, lse, "sm100"
     if q.is_cuda and get_backend(q) != "ref":
         sq, b, nq, d = q.shape
         nkv = k.shape[2]
@@ -147,6 +154,10 @@ def attn_fwd_block(q, k, v, causal, softmax_scale=None):
 
 
 def attn_bwd_block(dout, q, k, v, out, lse, causal, softmax_scale=None, ctx=None):
+    if isinstance(ctx, str) and ctx == "sm100":
+        from .flash_sm100_impl import flash_bwd
+        scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(q.shape[-1])
+        return flash_bwd(dout, q, k, v, out, lse, causal, scale, q_offset=0)
     if q.is_cuda and get_backend(q) != "ref" and ctx is not None:
         sq, b, nq, d = q.shape
         sk, nkv = k.shape[0], k.shape[2]

@@ -14,8 +14,17 @@ def supports(q, k, v, causal) -> bool:
     L = loader.lib()
     if L is None or not hasattr(L, "msb_flash_fwd"):
         return False
+    if not hasattr(L, "msb_flash_fwd2") or not hasattr(L, "msb_flash_bwd"):
+        return False
     d = q.shape[-1]
-    return q.dtype == torch.bfloat16 and d == 128 and v.shape[-1] == 128 and q.shape[0] % 128 == 0 and k.shape[0] % 128 == 0
+    if not (q.is_cuda and q.dtype == k.dtype == v.dtype == torch.bfloat16 and d == 128 and k.shape[-1] == 128 and v.shape[-1] == 128):
+        return False
+    if causal and k.shape[0] < q.shape[0]:
+        return False
+    for t in (q, k, v):           # TMA needs a contiguous head dim, 16-byte aligned strides and base
+        if t.stride(-1) != 1 or any((st * 2) % 16 for st in t.stride()[:-1]) or t.data_ptr() % 16:
+            return False
+    return True
 
 
 def flash_attention(q, k, v, causal, softmax_scale, return_lse):

@@ -68,7 +68,8 @@ def ulysses_attention(q, k, v, config, group, causal=True, softmax_scale=None, l
     if inner is not None:
         o = inner(qh, kh, vh)
     else:
-        backend = "sm100" if (config is not None and config.optimization_level >= 1 and
-                              getattr(config, "attention_backend", "auto") == "sm100") else None
+        want = getattr(config, "attention_backend", "auto") if config is not None else "library"
+        backend = "library" if want == "library" else (
+            "sm100" if (config is not None and config.optimization_level >= 1 and q.is_cuda) else None)
         o = A.flash_attention(qh, kh, vh, causal=causal, softmax_scale=softmax_scale, backend=backend)
     return heads_to_seq(o, group)

@@ -77,6 +77,9 @@ def initialize_megatron(extra_args_provider=None, args_defaults=None, ignore_unk
                parallel_num=max(2, getattr(args, "coc_parallel_num", 2)))
     from ..parallel.pipeline.schedules import set_schedule
     set_schedule(fm.resolve("schedule", None))
+    from ..ops.attention import set_backend as set_attention_backend
+    want = getattr(args, "attention_backend", "auto")
+    set_attention_backend("sm100" if (args.optimization_level >= 1 and want != "library" and torch.cuda.is_available()) else None)
     from ..parallel.context_parallel.ulysses import set_fused_all_to_all
     set_fused_all_to_all(args.optimization_level >= 2 and torch.cuda.is_available()
                          and not getattr(args, "no_fused_ulysses_a2a", False))
