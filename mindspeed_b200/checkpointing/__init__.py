@@ -279,3 +279,55 @@ def load_checkpoint(model, optimizer, opt_param_scheduler, load_dir=None, args=N
             if rs.get("cuda") is not None and torch.cuda.is_available():
                 torch.cuda.set_rng_state(rs["cuda"])
     return common.get("iteration", it)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Fault dumps (TTP): collective-free, because some ranks are gone when a dump is requested.
+# reference: mindspeed/core/training.py dump hooks of the TTP feature (mindspeed/features_manager/high_availability/*).
+# ---------------------------------------------------------------------------------------------------------------------
+def save_fault_dump(iteration, model, optimizer, dump_dir, save_optimizer=True, save_rng=True, keep=1):
+    """Every calling rank writes ALL its local shards (replicas included) to ``<dump_dir>/iter_<n>/rank_<r>/`` as a
+    self-contained torch.distributed.checkpoint directory planned without collectives, then prunes older dumps so that at
+    most ``keep`` remain.  The ranks of one complete replica together hold the whole state."""
+    import shutil
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    sharded, common = generate_state_dict(model, optimizer if save_optimizer else None, None, iteration, None, rng=save_rng)
+    everything = {k: ShardedTensor(st.key, st.data, st.global_shape, st.global_offset, 0) for k, st in sharded.items()}
+    path = os.path.join(get_checkpoint_name(dump_dir, iteration), f"rank_{rank}")
+    os.makedirs(path, exist_ok=True)
+    dcp.save({}, storage_writer=FileSystemWriter(path, single_file_per_rank=True), planner=_ChunkSavePlanner(everything), no_dist=True)
+    torch.save(common, os.path.join(path, "common.pt"))
+    with open(os.path.join(path, "complete"), "w") as f:
+        f.write(str(iteration))
+    dumps = sorted(d for d in os.listdir(dump_dir) if d.startswith("iter_"))
+    for old in dumps[:-max(1, int(keep))]:
+        if old != os.path.basename(get_checkpoint_name(dump_dir, iteration)):
+            shutil.rmtree(os.path.join(dump_dir, old, f"rank_{rank}"), ignore_errors=True)
+    return path
+
+
+def wait_for_fault_dump(dump_dir, ranks, timeout_s=60.0, poll_s=0.5):
+    """Block until the newest dump under ``dump_dir`` holds a ``complete`` marker of every rank in ``ranks`` (they write
+    independently); returns its iteration directory, or None when the time runs out."""
+    import time as _time
+    t0 = _time.time()
+    while _time.time() - t0 <= timeout_s:
+        dumps = sorted(d for d in os.listdir(dump_dir) if d.startswith("iter_")) if os.path.isdir(dump_dir) else []
+        if dumps:
+            p = os.path.join(dump_dir, dumps[-1])
+            if all(os.path.exists(os.path.join(p, f"rank_{r}", "complete")) for r in ranks):
+                return p
+        _time.sleep(poll_s)
+    return None
+
+
+def load_fault_dump(model, optimizer, dump_path, rank=None, strict=True):
+    """Reload this rank's own shards from a dump written by ``save_fault_dump`` under the same parallel layout."""
+    rank = (dist.get_rank() if dist.is_initialized() else 0) if rank is None else rank
+    path = os.path.join(dump_path, f"rank_{rank}")
+    sharded, _ = generate_state_dict(model, optimizer, None, 0, None, rng=False)
+    _load_sharded(sharded, path, strict=strict)
+    common = torch.load(os.path.join(path, "common.pt"), weights_only=False)
+    if optimizer is not None and "optimizer" in common:
+        optimizer.step_count = common["optimizer"]["step"]
+    return common.get("iteration", 0)

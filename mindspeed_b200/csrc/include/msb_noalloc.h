@@ -21,7 +21,9 @@
  *   - The function calls no cudaMalloc, cudaFree or other allocating routine, on any call.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
  *     current) and remembers it. Make that first call during normal set-up, before any stream capture begins
- *     on that device.
+ *     on that device. The remembered address is kept in a plain per-device table without a lock: two host threads
+ *     that make their first call on the same device at the same time both look the address up and store the same
+ *     value, which is harmless.
  *   - All calls on a device share the one array, and it keeps whatever the previous call left in it. This
  *     function needs no clearing (it overwrites every slot it later reads), but two calls whose kernels can
  *     overlap on the GPU, for instance on two streams without an ordering between them, would race on the

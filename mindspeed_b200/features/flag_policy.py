@@ -1,0 +1,120 @@
+"""What happens to a registered flag that no code path reads.
+
+Every command-line flag of the reference is accepted by the parser so that existing launch scripts keep working
+(reference flag surface: mindspeed/arguments.py:27-929 and the ``register_args`` of mindspeed/features_manager/*).
+A flag must then do one of three things, and ``tests/test_flag_policy_cpu.py`` fails when a flag does none:
+
+  * be read by the framework (the normal case);
+  * appear in ``NO_EFFECT`` with the reason why it changes nothing here (a knob of the reference's hardware or software
+    stack without a counterpart on this one, a launcher-only value, or a behaviour this framework always has);
+    setting it prints one notice at start-up instead of silently doing nothing;
+  * appear in ``UNSUPPORTED`` with a message; setting it to a non-default value stops the run in ``validate_args``.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+NO_EFFECT: Dict[str, str] = {
+    # --- knobs of the reference's device / communication stack ---
+    "aiqos": "per-communicator QoS classes exist only on the reference's interconnect",
+    "aiqos-enable-roce": "per-communicator QoS classes exist only on the reference's interconnect",
+    "aiqos-mode": "per-communicator QoS classes exist only on the reference's interconnect",
+    "aiqos-schedule": "per-communicator QoS classes exist only on the reference's interconnect",
+    "hccl-ep-group-buffer-adaptive-factor": "communicator buffer sizing of the reference's collective library; NCCL sizes are set with --nccl-group-buffer",
+    "hccl-op-mode": "execution mode of the reference's collective library",
+    "jit-compile": "operator JIT switch of the reference's device runtime; kernels here are built ahead of time",
+    "use-fusion-attn-v2": "selects between two vendor attention ops; there is one attention kernel family here",
+    "megatron-cp-in-bnsd": "layout hint for the vendor attention op; the tcgen05 kernels read strided [s, b, n, d] directly",
+    "attention-mask-on-cpu": "the causal mask is generated inside the attention kernels, no mask tensor is built",
+    "pre-tockens": "sliding-window bounds of the vendor attention op; attention here is full or causal",
+    "next-tockens": "sliding-window bounds of the vendor attention op; attention here is full or causal",
+    "fill-neg-inf": "mask fill value of the unfused softmax path; masked scores are -inf in every kernel here",
+    "te-comparison-with-bf16": "debug comparison hook of the reference's TE shim",
+    "te-comparison-with-cpu": "debug comparison hook of the reference's TE shim",
+    "te-gmm-mode": "grouped-GEMM backend choice of the reference's TE shim; one grouped kernel here",
+    "no-use-gmm-fp8": "grouped-GEMM backend choice of the reference's TE shim; fp8 experts follow --fp8-format",
+    "fp8-reuse-quantized-weight": "quantised weights are always cached across micro-batches (models/te_compat.py)",
+    "transformer-impl": "one implementation (this package's modules with the TE-compatible surface)",
+    "use-mcore-models": "the core model classes are the only ones",
+    # --- always-on behaviours ---
+    "gemm-gradient-accumulation-fusion": "weight gradients always accumulate into main_grad inside the GEMM epilogue",
+    "no-bias-swiglu-fusion": "SwiGLU is fused whenever the optimisation level allows; level 0 gives the unfused path",
+    "coc-mode": "sub-mode of the chunk-pipelining path; --use-ascend-coc / --coc-fused-kernel select the back end",
+    "enable-overlap-ag-with-matmul": "the fused all-gather -> GEMM kernel always overlaps",
+    "enable-overlap-matmul-with-rs": "the fused GEMM -> reduce-scatter kernel always overlaps",
+    "enable-backward-overlap-ag-with-matmul": "backward uses the same fused kernels as forward",
+    "moe-permutation-async-comm": "the dispatcher's collectives are already asynchronous with respect to the permute kernels",
+    "moe-dynamic-padding": "the grouped GEMM takes ragged expert row ranges, no padding is needed",
+    "ckpt-fully-parallel-save": "every rank always writes its own shard file",
+    "dist-ckpt-optim-sharding-type": "one optimizer-state chunking is implemented (see checkpointing/sharded.py)",
+    "mock-data": "synthetic data is used whenever no --data-path is given",
+    # --- launcher-only values (consumed by auto_settings / torchrun, not by a rank) ---
+    "master-addr": "launcher value", "node-rank": "launcher value", "nproc-per-node": "launcher value",
+    "target-nnodes": "search target of --auto-settings only",
+    "auto-settings-log-level": "verbosity of --auto-settings only",
+    "num-workers": "the synthetic and indexed datasets are read in-process",
+    "tokenizer-not-use-fast": "passed to the HF tokenizer only by the data tools",
+}
+
+UNSUPPORTED: Dict[str, str] = {
+    "ampipe-degree": "attention-MoE micro-pipelining (ampipe) is not implemented; use --moe-fb-overlap",
+    "use-pipe-experts": "pipelined experts are part of the legacy DeepSpeed-style MoE only (mindspeed_b200.legacy_moe)",
+    "pipe-experts-multi-data": "pipelined experts are part of the legacy DeepSpeed-style MoE only (mindspeed_b200.legacy_moe)",
+    "pipe-experts-multi-stream": "pipelined experts are part of the legacy DeepSpeed-style MoE only (mindspeed_b200.legacy_moe)",
+    "moe-model-type": "the DeepSpeed-style MoE is selected through mindspeed_b200.legacy_moe, not through this flag",
+    "moe-bmm-mc2": "use --moe-alltoall-mc2 (peer-memory dispatch / combine) with --moe-grouped-gemm",
+    "moe-unperm2-mem-optim-swap": "host swap of the unpermute buffer is not implemented; use --moe-zero-memory",
+    "use-multiparameter-pipeline-model-parallel": "pipeline stages exchange one tensor; multi-tensor stage interfaces are not implemented",
+    "quant-grads": "quantised gradient buffers are not implemented (quantised optimizer states: --quant-states)",
+    "compress-activation": "activation compression is available as a codec (ops/compress.py) but not wired into recompute / swap",
+    "compress-optimizer": "optimizer-state compression is available as a codec (ops/compress.py) but not wired into the step",
+    "compress-dense": "activation compression is available as a codec (ops/compress.py) but not wired into recompute / swap",
+    "automated-pipeline": "the pipeline-balancing solver exists (memory/auto_pipeline.py) but is not run from the training loop",
+    "automated-pipeline-perf": "the pipeline-balancing solver exists (memory/auto_pipeline.py) but is not run from the training loop",
+    "adaptive-recompute-device-swap": "adaptive recompute decides recompute only; combine it with --swap-attention for host swap",
+    "adaptive-cp-dynamic-attn-mask": "adaptive CP takes one mask per run",
+    "adaptive-cp-manually-set-mask-list": "adaptive CP derives its mask list itself",
+    "adaptive-cp-only-reschedule": "adaptive CP always remaps and reschedules",
+    "adaptive-cp-without-coarse": "adaptive CP always uses the coarsened search",
+    "alibi-fusion-attn-type": "ALiBi runs on the reference (eager) attention path only; the fused kernels have no bias input",
+    "alibi-diagonal-opposite": "ALiBi runs on the reference (eager) attention path only; the fused kernels have no bias input",
+    "square-alibi-mask": "ALiBi runs on the reference (eager) attention path only; the fused kernels have no bias input",
+    "use-dsa-absorb": "DeepSeek sparse attention is not implemented (lightning indexer only, ops/lightning_indexer.py)",
+    "use-fused-lightning-indexer": "the lightning indexer is a PyTorch op (ops/lightning_indexer.py); no fused kernel yet",
+    "use-fused-lightning-indexer-kl-loss": "the lightning indexer is a PyTorch op (ops/lightning_indexer.py); no fused kernel yet",
+    "use-fused-sparse-flash-attention": "sparse flash attention is not implemented",
+    "kl-loss-reduction": "only used by the lightning-indexer KL loss, which is not wired into training",
+    "fix-sub-seq-length": "fixed-length sub-sequence packing for EOD-reset CP is not implemented",
+    "moe-allgather-overlap-comm": "overlap is implemented for the alltoall dispatcher (--moe-alltoall-overlap-comm)",
+    "balanced-moe-experts": "hot-expert replication helpers exist (parallel/moe/expert_placement.py) but are not driven by the training loop",
+    "balanced-moe-hot-expert-num": "hot-expert replication helpers exist (parallel/moe/expert_placement.py) but are not driven by the training loop",
+    "trans-hot-expert-group-num": "hot-expert replication helpers exist (parallel/moe/expert_placement.py) but are not driven by the training loop",
+    "enable-fine-grained-expert-placement": "only whole-expert placement is implemented (--enable-expert-placement)",
+    "fine-grained-expert-placement-thre": "only whole-expert placement is implemented (--enable-expert-placement)",
+    "data-path": "indexed datasets are built with mindspeed_b200.data_tools and passed to a custom provider; pretrain_gpt.py reads synthetic data",
+    "no-qad-enable": "distillation is driven through mindspeed_b200.qat.distill, not through this switch",
+    "recompute-module-list": "module-level recompute is selected with --recompute-granularity / --recompute-activation-function / --recompute-norm",
+}
+
+
+def check_flags(args, parser) -> None:
+    """Called at the end of ``validate_args``: stop on unsupported flags, print one notice per no-effect flag that was set."""
+    from ..utils.logging import print_rank_0
+    dests = {}
+    for a in parser._actions:
+        for o in a.option_strings:
+            if o.startswith("--"):
+                dests[o[2:]] = (a.dest, a.default)
+    bad = []
+    for flag, why in UNSUPPORTED.items():
+        if flag in dests:
+            dest, default = dests[flag]
+            if getattr(args, dest, default) != default:
+                bad.append(f"--{flag}: {why}")
+    if bad:
+        raise NotImplementedError("flags without an implementation were set:\n  " + "\n  ".join(bad))
+    for flag, why in NO_EFFECT.items():
+        if flag in dests:
+            dest, default = dests[flag]
+            if getattr(args, dest, default) != default:
+                print_rank_0(f"note: --{flag} has no effect here ({why})")

@@ -97,6 +97,14 @@ class SelfAttention(nn.Module):
         self.linear_qkv = Col(config.hidden_size, qkv_out, config=config, init_method=config.init_method,
                                                bias=config.add_bias_linear or config.add_qkv_bias, gather_output=False,
                                                skip_bias_add=False)
+        # row ranges of the q / k / v blocks inside the fused weight (per local KV group: qpg query heads, one key, one value):
+        # optimizers that treat the three projections separately (Muon) read this
+        blocks, row = [], 0
+        for _ in range(self.ng):
+            blocks.append((row, row + self.qpg * self.d)); row += self.qpg * self.d
+            blocks.append((row, row + self.d)); row += self.d
+            blocks.append((row, row + self.d)); row += self.d
+        self.linear_qkv.weight.qkv_row_blocks = blocks
         self.core_attention = CoreAttention(config, layer_number, attn_mask_type)
         self.linear_proj = Row(self.nq_total * self.d, config.hidden_size, config=config,
                                              init_method=config.output_layer_init_method, bias=config.add_bias_linear,

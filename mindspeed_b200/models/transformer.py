@@ -116,6 +116,13 @@ class TransformerLayer(nn.Module):
         else:
             self.mlp = MLP(config)
         self.recompute_norm = bool(getattr(config, "recompute_norm", False))
+        # --recompute-norm-num-layers / --recompute-activation-function-num-layers: only the first N layers of a stage
+        n_norm = getattr(config, "recompute_norm_num_layers", None)
+        if n_norm is not None and layer_number > n_norm:
+            self.recompute_norm = False
+        n_act = getattr(config, "recompute_activation_function_num_layers", None)
+        if n_act is not None and layer_number > n_act and hasattr(self.mlp, "recompute_activation"):
+            self.mlp.recompute_activation = False
 
     def _norm(self, norm, x):
         return norm(x)

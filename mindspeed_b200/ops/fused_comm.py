@@ -97,10 +97,11 @@ _CTX = {}
 
 
 def _ctx(group) -> _Ctx:
-    c = _CTX.get(id(group))
+    key = tuple(dist.get_process_group_ranks(group))      # global ranks: survives re-creation of the group object
+    c = _CTX.get(key)
     if c is None:
         c = _Ctx(group)
-        _CTX[id(group)] = c
+        _CTX[key] = c
     return c
 
 

@@ -61,10 +61,10 @@ _CTX = {}
 
 
 def context(group, slot_bytes: int) -> MoeCommContext:
-    c = _CTX.get(id(group))
+    c = _CTX.get(tuple(dist.get_process_group_ranks(group)))
     if c is None:
         c = MoeCommContext(group, slot_bytes)
-        _CTX[id(group)] = c
+        _CTX[tuple(dist.get_process_group_ranks(group))] = c
     elif c.slot_bytes < slot_bytes:
         raise RuntimeError(f"MoE staging slot of {c.slot_bytes} bytes is too small for {slot_bytes}; raise "
                            "MSB200_MOE_STAGE_FACTOR before the first MoE layer runs")

@@ -1,4 +1,5 @@
-"""Quantisation to fp8 with block scales (eager forms and oracles of csrc/kernels/quant.cu).
+"""Quantisation to fp8 with block scales: eager PyTorch forms, which are also the oracles of the CUDA quantiser
+(``msb_quant_1x128`` in csrc/kernels/misc_ops.cu).
 
   quantize_blockwise(x, block, pow2)          1-D blocks of ``block`` elements, one scale each (optimizer states)
   quant_1x128 / quant_128x128                 activation (per row, 128 along K) and weight (128x128 tiles) scaling of the

@@ -41,11 +41,11 @@ _CTX = {}
 
 
 def _ctx(group, nbytes) -> _Ctx:
-    c = _CTX.get(id(group))
+    c = _CTX.get(tuple(dist.get_process_group_ranks(group)))
     if c is None:
         floor = int(os.environ.get("MSB200_ULYSSES_SLOT_MIB", "64")) << 20
         c = _Ctx(group, max(nbytes, floor))
-        _CTX[id(group)] = c
+        _CTX[tuple(dist.get_process_group_ranks(group))] = c
     if c.slot_bytes < nbytes:
         raise RuntimeError(f"Ulysses staging slot of {c.slot_bytes} bytes is too small for {nbytes}; raise MSB200_ULYSSES_SLOT_MIB")
     return c

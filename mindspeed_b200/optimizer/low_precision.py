@@ -38,7 +38,8 @@ class QuantStateDistributedOptimizer(DistributedOptimizer):
 
     @torch.no_grad()
     def step(self):
-        # materialise fp32 moments bucket by bucket, run the standard step on them, requantise
+        # materialise the fp32 moments of every bucket, run the standard step on them, requantise: the resident state
+        # between steps is the quantised one; during the step the fp32 moments of all buckets exist at once
         for st in self._all_states():
             st.m = st.qm.load(slice(None)).contiguous()
             st.v = st.qv.load(slice(None)).contiguous()

@@ -229,10 +229,21 @@ def build_muon_optimizer(config, model_chunks):
             else:
                 adam_p.append(p)
     tp_group = ps.get_tensor_model_parallel_group(check_initialized=False)
+    # --muon-fp32-matmul-prec: precision of the fp32 matmuls of the Newton-Schulz iteration (low = tf32 allowed)
+    prec = g("muon_fp32_matmul_prec", "medium")
+    torch.set_float32_matmul_precision({"low": "medium", "medium": "high", "high": "highest"}.get(prec, "high"))
+    if g("muon_scalar_optimizer", "adam") not in ("adam", "adamw"):
+        raise NotImplementedError("--muon-scalar-optimizer: only adam is available for the non-matrix parameters")
+    split = None
+    if g("muon_split_qkv", True):
+        def split(p):
+            """Row ranges of the q / k / v blocks of a fused QKV weight (None for other parameters)."""
+            blocks = getattr(p, "qkv_row_blocks", None)
+            return blocks
     muon = Muon(muon_p, lr=config.lr, momentum=g("muon_momentum", 0.95), nesterov=g("muon_nesterov", False),
                 weight_decay=config.weight_decay, ns_steps=g("muon_num_ns_steps", 5), coefficient_type=g("muon_coefficient_type", "quintic"),
                 scale_mode=g("muon_scale_mode", "spectral"), extra_scale_factor=g("muon_extra_scale_factor", 1.0),
-                tp_mode=g("muon_tp_mode", "blockwise"), tp_group=tp_group)
+                tp_mode=g("muon_tp_mode", "blockwise"), tp_group=tp_group, split_qkv=split)
     adam = AdamW(adam_p, lr=config.lr, betas=(config.adam_beta1, config.adam_beta2), eps=config.adam_eps, weight_decay=0.0)
 
     class _MainGradBridge(ChainedOptimizer):

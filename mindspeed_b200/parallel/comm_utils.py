@@ -203,12 +203,23 @@ def group_options(args) -> Dict[str, NcclOptions]:
 
 
 # ---- gloo-free host-object movement --------------------------------------------------------------------------
-def gather_to_rank0_sliced(local: torch.Tensor, group, slice_bytes: int = 10 * 1024 * 1024,
+def default_slice_bytes() -> int:
+    """--nccl-slice-size / --hccl-slice-size (bytes, one flag with two spellings) when arguments are set, else 10 MB."""
+    try:
+        from ..training.global_vars import get_args
+        nbytes = getattr(get_args(), "hccl_slice_size", None)
+        return int(nbytes) if nbytes else 10 * 1024 * 1024
+    except RuntimeError:
+        return 10 * 1024 * 1024
+
+
+def gather_to_rank0_sliced(local: torch.Tensor, group, slice_bytes: Optional[int] = None,
                            device: Optional[torch.device] = None) -> Optional[List[torch.Tensor]]:
     """Gather equally shaped host tensors to group rank 0 through the device, ``slice_bytes`` at a time, so that no
     gloo group and no device buffer larger than ``world * slice_bytes`` is needed.  Returns the list on rank 0."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     flat = local.reshape(-1)
+    slice_bytes = slice_bytes or default_slice_bytes()
     per = max(1, slice_bytes // max(1, flat.element_size()))
     dev = device or (torch.device("cuda", torch.cuda.current_device()) if dist.get_backend(group) == "nccl" else torch.device("cpu"))
     outs = [torch.empty_like(flat, device="cpu") for _ in range(world)] if rank == 0 else None
@@ -226,10 +237,11 @@ def gather_to_rank0_sliced(local: torch.Tensor, group, slice_bytes: int = 10 * 1
 
 
 def scatter_from_rank0_sliced(parts: Optional[List[torch.Tensor]], like: torch.Tensor, group,
-                              slice_bytes: int = 10 * 1024 * 1024, device: Optional[torch.device] = None) -> torch.Tensor:
+                              slice_bytes: Optional[int] = None, device: Optional[torch.device] = None) -> torch.Tensor:
     """Inverse of ``gather_to_rank0_sliced``: rank 0 holds one host tensor per rank, every rank receives its own."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     out = torch.empty_like(like, device="cpu").reshape(-1)
+    slice_bytes = slice_bytes or default_slice_bytes()
     per = max(1, slice_bytes // max(1, out.element_size()))
     dev = device or (torch.device("cuda", torch.cuda.current_device()) if dist.get_backend(group) == "nccl" else torch.device("cpu"))
     src = dist.get_global_rank(group, 0)

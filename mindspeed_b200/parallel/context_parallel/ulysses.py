@@ -61,10 +61,22 @@ def heads_to_seq(x, group):
 def ulysses_attention(q, k, v, config, group, causal=True, softmax_scale=None, layer_number=1, inner=None):
     p = dist.get_world_size(group)
     nkv = k.shape[2]
-    if nkv < p:
-        rep = p // nkv
-        k, v = k.repeat_interleave(rep, dim=2), v.repeat_interleave(rep, dim=2)
-    qh, kh, vh = seq_to_heads(q, group), seq_to_heads(k, group), seq_to_heads(v, group)
+    if nkv < p and bool(getattr(config, "use_ulysses_allgather_kv", False)) and p % nkv == 0:
+        # --use-ulysses-allgather-kv: fewer KV heads than ranks.  Instead of repeating the KV heads up to the group size
+        # and sending the copies through the all-to-all, gather K and V along the sequence (gradient: reduce-scatter) and
+        # keep only the KV head this rank's query heads use (reference: ulysses_context_parallel.py:456-557,589-595)
+        qh = seq_to_heads(q, group)
+        r = dist.get_rank(group)
+        kv_idx = r * nkv // p
+        # gather every KV head (each rank must contribute the same heads), then keep the one this rank's queries use;
+        # the other heads get zero gradient here and their real gradient from the ranks that use them
+        kh = M.gather_from_sequence_parallel_region(k.contiguous(), True, group)[:, :, kv_idx:kv_idx + 1]
+        vh = M.gather_from_sequence_parallel_region(v.contiguous(), True, group)[:, :, kv_idx:kv_idx + 1]
+    else:
+        if nkv < p:
+            rep = p // nkv
+            k, v = k.repeat_interleave(rep, dim=2), v.repeat_interleave(rep, dim=2)
+        qh, kh, vh = seq_to_heads(q, group), seq_to_heads(k, group), seq_to_heads(v, group)
     if inner is not None:
         o = inner(qh, kh, vh)
     else:

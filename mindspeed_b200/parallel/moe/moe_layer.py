@@ -45,6 +45,9 @@ class MoELayer(nn.Module):
         self.shared_overlap = bool(config.moe_shared_expert_overlap or overlap)
         self._side = None
         self.zero_memory = getattr(config, "moe_zero_memory", "disable")
+        n_zm = getattr(config, "moe_zero_memory_num_layers", None)
+        if n_zm is not None and layer_number > n_zm:
+            self.zero_memory = "disable"       # --moe-zero-memory-num-layers: only the first N MoE layers of a stage trade recompute for memory
 
     def _forward(self, hidden_states):
         probs, routing_map = self.router(hidden_states)

@@ -32,6 +32,25 @@ class TopKRouter(nn.Module):
         else:
             self.expert_bias = None
         self.fix_router = bool(getattr(config, "fix_router", False))
+        self.track_load = bool(getattr(config, "print_expert_load", False) or getattr(config, "enable_expert_placement", False))
+        self.register_buffer("expert_load", torch.zeros(self.num_experts, dtype=torch.float32), persistent=False)
+
+    @torch.no_grad()
+    def permute_experts(self, old, new):
+        """After expert weights moved between slots (``old`` / ``new``: slot -> expert id), reorder the router's rows so
+        that output column s again scores the expert stored in slot s.  Replicated state: every rank does the same."""
+        old_slot = {e: s for s, e in enumerate(old)}
+        idx = torch.tensor([old_slot[e] for e in new], device=self.weight.device)
+        self.weight.copy_(self.weight.index_select(0, idx))
+        if self.expert_bias is not None:
+            self.expert_bias.copy_(self.expert_bias.index_select(0, idx))
+            self.local_tokens_per_expert.copy_(self.local_tokens_per_expert.index_select(0, idx))
+
+    def pop_expert_load(self):
+        """Tokens per expert accumulated since the last call (device tensor), and reset."""
+        out = self.expert_load.clone()
+        self.expert_load.zero_()
+        return out
 
     def gating(self, x):
         return torch.nn.functional.linear(x.float(), self.weight.float())
@@ -71,6 +90,10 @@ class TopKRouter(nn.Module):
         if self.expert_bias is not None and self.training:
             with torch.no_grad():
                 self.local_tokens_per_expert += rmap.sum(0).float()
+        if self.track_load and self.training:
+            # tokens routed to each expert since the last report (--print-expert-load / --enable-expert-placement)
+            with torch.no_grad():
+                self.expert_load += rmap.sum(0).float()
         if self.score_function == "softmax":
             scores_for_loss = torch.softmax(logits.float(), dim=-1)
         else:

@@ -12,6 +12,12 @@ def forward_backward_pipelining_with_cutinhalf(*, forward_step_func, data_iterat
                                                micro_batch_size, forward_only=False, collect_non_loss_data=False,
                                                dw_detach=True, order="greedy", **_):
     pp = ps.get_pipeline_model_parallel_world_size()
+    try:
+        from ...training.global_vars import get_args
+        # --dualpipev-dw-detach: split every backward into input-gradient and weight-gradient work so that W fills bubbles
+        dw_detach = bool(getattr(get_args(), "dualpipev_dw_detach", dw_detach))
+    except RuntimeError:
+        pass
     if len(model) != 2:
         raise RuntimeError("DualPipeV needs exactly two model chunks per rank")
     name = "dualpipev_greedy" if order == "greedy" else "dualpipev"

@@ -111,7 +111,8 @@ _HEAPS: Dict[int, SymmetricHeap] = {}
 
 def get_heap(group, nbytes: int, tag: str = "tp") -> SymmetricHeap:
     """One heap per (group, tag): kernel families with their own flag words and buffers keep separate heaps."""
-    key = (id(group), tag)
+    # keyed by the group's global ranks, not by object identity: a destroyed and re-created group must not pick up a stale heap
+    key = (tuple(dist.get_process_group_ranks(group)) if group is not None else ("world",), tag)
     h = _HEAPS.get(key)
     if h is None:
         h = SymmetricHeap(group, nbytes)

@@ -199,6 +199,7 @@ def parse_args(extra_args_provider=None, ignore_unknown_args=False, args_list=No
     if args.yaml_cfg:
         from .yaml_arguments import load_yaml
         args = load_yaml(args.yaml_cfg, args)
+    args._parser = p                       # validate_args compares values with the parser's defaults (features/flag_policy.py)
     args.rank = int(os.getenv("RANK", "0"))
     args.world_size = int(os.getenv("WORLD_SIZE", "1"))
     if args.local_rank is None:
@@ -259,6 +260,18 @@ def _core_validate(args):
             raise AssertionError("num_experts must be divisible by expert parallel size")
     if args.ckpt_format == "torch_dist":
         args.use_dist_ckpt = True
+    if getattr(args, "moe_use_sinkhorn", False):
+        args.moe_router_load_balancing_type = "sinkhorn"
+    n_shared = getattr(args, "n_shared_experts", None)
+    if n_shared and not args.moe_shared_expert_intermediate_size:
+        # DeepSeek-style count of always-on experts -> one shared MLP of n x the routed experts' width
+        args.moe_shared_expert_intermediate_size = n_shared * (args.moe_ffn_hidden_size or args.ffn_hidden_size)
+    cf = getattr(args, "moe_train_capacity_factor", None)
+    if args.num_experts and cf is not None and cf != 1.0 and not getattr(args, "moe_no_drop", False):
+        if getattr(args, "moe_expert_capacity_factor", None) is None:
+            args.moe_expert_capacity_factor = cf                                    # legacy spelling of the capacity factor
+    if getattr(args, "moe_no_drop", False):
+        args.moe_expert_capacity_factor = None                                      # never drop tokens
     return args
 
 
@@ -268,6 +281,10 @@ def validate_args(args):
     _core_validate(args)
     fm.post_validate_features_args(args)
     fm.validate_features_args(args)
+    parser = getattr(args, "_parser", None)
+    if parser is not None:
+        from ..features.flag_policy import check_flags
+        check_flags(args, parser)
     return args
 
 

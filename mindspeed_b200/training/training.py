@@ -6,7 +6,9 @@ mindspeed/functional/tflops_calculate/adaptor.py:196-231.
 """
 from __future__ import annotations
 
+import json
 import math
+import os
 import time
 from typing import Callable, List, Optional
 
@@ -124,6 +126,12 @@ def get_model(model_provider_func, wrap_with_ddp=True):
 def setup_model_and_optimizer(model_provider_func, no_wd_decay_cond=None, scale_lr_cond=None, lr_mult=1.0):
     args = get_args()
     model = get_model(model_provider_func)
+    if no_wd_decay_cond is None and getattr(args, "apply_wd_to_qk_layernorm", False):
+        # default rule (no decay on biases and 1-D tensors) except that the q / k layer-norm gains do decay
+        def no_wd_decay_cond(name, p):
+            if "q_layernorm" in name or "k_layernorm" in name:
+                return False
+            return name.endswith(".bias") or p.dim() == 1
     ocfg = OptimizerConfig(optimizer=args.optimizer, lr=args.lr, min_lr=args.min_lr, weight_decay=args.weight_decay,
                            bf16=args.bf16, fp16=args.fp16, params_dtype=args.params_dtype, adam_beta1=args.adam_beta1,
                            adam_beta2=args.adam_beta2, adam_eps=args.adam_eps, clip_grad=args.clip_grad,
@@ -138,8 +146,11 @@ def setup_model_and_optimizer(model_provider_func, no_wd_decay_cond=None, scale_
                                  weight_decay=args.weight_decay, clip_grad=args.clip_grad)
     else:
         optimizer = get_megatron_optimizer(ocfg, model, no_wd_decay_cond, scale_lr_cond, lr_mult)
-    sched = OptimizerParamScheduler(optimizer, args.lr, args.min_lr, args.lr_warmup_iters,
-                                    args.lr_decay_iters or args.train_iters, args.lr_decay_style)
+    decay_iters = args.lr_decay_iters or args.train_iters
+    warmup = args.lr_warmup_iters
+    if getattr(args, "lr_warmup_fraction", None) is not None:
+        warmup = int(args.lr_warmup_fraction * decay_iters)          # --lr-warmup-fraction overrides --lr-warmup-iters
+    sched = OptimizerParamScheduler(optimizer, args.lr, args.min_lr, warmup, decay_iters, args.lr_decay_style)
     cfg = model[0].module.config
     cfg.finalize_model_grads_func = finalize_model_grads
     if args.swap_attention:
@@ -253,6 +264,60 @@ def training_log(loss_dict, iteration, elapsed, grad_norm, skipped, lr):
     print_rank_last(msg)
 
 
+class ScalarWriter:
+    """--tensorboard-dir: scalars go to a TensorBoard event file when the tensorboard package is importable, and always to
+    ``scalars.jsonl`` in the same directory (one {"step", "tag", "value"} object per line)."""
+
+    def __init__(self, log_dir):
+        os.makedirs(log_dir, exist_ok=True)
+        self.f = open(os.path.join(log_dir, "scalars.jsonl"), "a")
+        try:
+            from torch.utils.tensorboard import SummaryWriter
+            self.tb = SummaryWriter(log_dir=log_dir)
+        except Exception:
+            self.tb = None
+
+    def add_scalar(self, tag, value, step):
+        self.f.write(json.dumps({"step": int(step), "tag": tag, "value": float(value)}) + "\n")
+        self.f.flush()
+        if self.tb is not None:
+            self.tb.add_scalar(tag, float(value), int(step))
+
+    def close(self):
+        self.f.close()
+        if self.tb is not None:
+            self.tb.close()
+
+
+def evaluate(forward_step_func, data_iterator, model, eval_iters):
+    """Mean loss over ``eval_iters`` forward-only steps (reference: Megatron ``evaluate``; --eval-interval / --eval-iters)."""
+    args = get_args()
+    for m in model:
+        m.eval()
+    fb = get_forward_backward_func()
+    totals = {}
+    with torch.no_grad():
+        for _ in range(eval_iters):
+            losses = fb(forward_step_func=forward_step_func, data_iterator=data_iterator, model=model,
+                        num_microbatches=get_num_microbatches(), seq_length=args.seq_length,
+                        micro_batch_size=args.micro_batch_size, decoder_seq_length=None, forward_only=True)
+            for d in losses or []:
+                for k, v in d.items():
+                    t = v.detach().float() if torch.is_tensor(v) else torch.tensor(float(v))
+                    totals[k] = totals.get(k, 0) + t
+    for m in model:
+        m.train()
+    out = {}
+    for k, t in totals.items():
+        out[k] = float(t[0] / t[1]) if (torch.is_tensor(t) and t.numel() == 2) else float(t) / max(1, eval_iters * get_num_microbatches())
+    return out
+
+
+def _moe_routers(model):
+    from ..parallel.moe.router import TopKRouter
+    return [m for chunk in model for m in chunk.modules() if isinstance(m, TopKRouter)]
+
+
 def check_kernel_status():
     """Raise if a device-side bounded wait expired since the last check (GEMM mbarriers, all-gather / reduce-scatter
     flags, MoE, Ulysses, fused optimizer step): such a kernel returns early with its outputs not computed, so the step
@@ -273,6 +338,9 @@ def train(forward_step_func, model, optimizer, opt_param_scheduler, train_data_i
         prof = build_profiler(args)
         prof.__enter__()
     history = []
+    writer = ScalarWriter(args.tensorboard_dir) if (args.tensorboard_dir and args.rank == args.world_size - 1) else None
+    routers = _moe_routers(model) if (getattr(args, "print_expert_load", False) or getattr(args, "enable_expert_placement", False)) else []
+    planners = {}
     while iteration < args.train_iters:
         t0 = time.time()
         loss_dict, skipped, grad_norm, _ = train_step(forward_step_func, train_data_iterator, model, optimizer,
@@ -286,6 +354,22 @@ def train(forward_step_func, model, optimizer, opt_param_scheduler, train_data_i
             prof.step()
         if iteration % args.log_interval == 0:
             training_log(loss_dict, iteration, elapsed, grad_norm, skipped, optimizer.param_groups[0]["lr"])
+            if writer is not None:
+                for k, v in loss_dict.items():
+                    writer.add_scalar(k, float(v), iteration)
+                writer.add_scalar("learning-rate", optimizer.param_groups[0]["lr"], iteration)
+                writer.add_scalar("iteration-time", elapsed, iteration)
+                if grad_norm is not None:
+                    writer.add_scalar("grad-norm", float(grad_norm), iteration)
+        if routers and (iteration % args.log_interval == 0 or
+                        (getattr(args, "enable_expert_placement", False) and iteration % args.expert_placement_freq == 0)):
+            _expert_load_step(args, model, optimizer, routers, planners, iteration)
+        if args.eval_interval and args.eval_iters and iteration % args.eval_interval == 0:
+            ev = evaluate(forward_step_func, train_data_iterator, model, args.eval_iters)
+            print_rank_last(f" validation at iteration {iteration:8d} | " + " | ".join(f"{k}: {v:.6E}" for k, v in ev.items()))
+            if writer is not None:
+                for k, v in ev.items():
+                    writer.add_scalar(f"{k} validation", v, iteration)
         history.append({k: float(v) for k, v in loss_dict.items()})
         if args.save and args.save_interval and iteration % args.save_interval == 0:
             from ..checkpointing import save_checkpoint
@@ -294,8 +378,46 @@ def train(forward_step_func, model, optimizer, opt_param_scheduler, train_data_i
             break
     if prof is not None:
         prof.__exit__(None, None, None)
+    if writer is not None:
+        writer.close()
     args.iteration = iteration
     return history
+
+
+def _expert_load_step(args, model, optimizer, routers, planners, iteration):
+    """--print-expert-load: log the tokens each expert received since the last report.  --enable-expert-placement: every
+    --expert-placement-freq iterations feed the loads to a planner per MoE layer and move expert weights between the
+    expert-parallel ranks when that lowers the heaviest rank's load (reference: mindspeed/core/transformer/moe/
+    expert_placement/executor.py:44-586 and its hook in mindspeed/training.py:78-160)."""
+    from ..parallel.moe.expert_placement import ExpertPlacementExecutor, ExpertPlacementPlanner
+    ep = ps.get_expert_model_parallel_world_size()
+    for li, r in enumerate(routers):
+        load = r.pop_expert_load()
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(load, group=ps.get_data_parallel_group(with_context_parallel=True))
+        if getattr(args, "print_expert_load", False):
+            print_rank_0(f" iteration {iteration:8d} | moe layer {li} tokens per expert: {[int(x) for x in load.tolist()]}")
+        if getattr(args, "enable_expert_placement", False) and ep > 1 and iteration % args.expert_placement_freq == 0:
+            pl = planners.setdefault(li, ExpertPlacementPlanner(r.num_experts, ep))
+            pl.record(load)
+            new = pl.plan()
+            if new != pl.placement:
+                layer = _moe_layer_of(model, r)
+                tensors = [p.data for p in layer.experts.parameters()]
+                ExpertPlacementExecutor(ps.get_expert_model_parallel_group()).apply(tensors, pl.placement, new)
+                r.permute_experts(pl.placement, new)
+                pl.commit(new)
+                if hasattr(optimizer, "reload_model_params"):
+                    optimizer.reload_model_params()
+
+
+def _moe_layer_of(model, router):
+    from ..parallel.moe.moe_layer import MoELayer
+    for chunk in model:
+        for m in chunk.modules():
+            if isinstance(m, MoELayer) and m.router is router:
+                return m
+    raise RuntimeError("router does not belong to a MoE layer of this model")
 
 
 def pretrain(train_valid_test_dataset_provider, model_provider, model_type=None, forward_step_func=None,
@@ -305,10 +427,22 @@ def pretrain(train_valid_test_dataset_provider, model_provider, model_type=None,
     if args.auto_settings:
         from ..auto_settings import AutoSettings
         return AutoSettings().auto_setting_fun(args)
-    if args.ttp_enabled:
-        from ..ttp import install_ttp
-        install_ttp(args)
     model, optimizer, sched = setup_model_and_optimizer(model_provider)
+    if args.ttp_enabled:
+        from ..checkpointing import load_fault_dump, save_fault_dump, wait_for_fault_dump
+        from ..ttp import install_ttp
+
+        def dump(ranks):
+            # the controller names the ranks of one complete replica; each of them writes its shards without collectives
+            if args.rank in ranks:
+                save_fault_dump(args.iteration, model, optimizer, args.ttp_dump_dir, save_optimizer=args.ttp_save_optimizer,
+                                save_rng=args.ttp_save_rng, keep=args.ttp_max_dump_ckpt_to_keep)
+        install_ttp(args, dump_fn=dump)
+        if not args.load and os.path.isdir(args.ttp_dump_dir) and os.listdir(args.ttp_dump_dir):
+            # restart after a fault: wait for the dump of this rank to be complete, then resume from it
+            found = wait_for_fault_dump(args.ttp_dump_dir, [args.rank], timeout_s=args.ttp_wait_dump_file_timeout)
+            if found is not None:
+                args.iteration = load_fault_dump(model, optimizer if args.ttp_save_optimizer else None, found)
     train_iter = train_valid_test_dataset_provider(args)
     history = train(forward_step_func, model, optimizer, sched, train_iter, process_non_loss_data_func)
     if args.save:

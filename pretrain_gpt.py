@@ -20,7 +20,8 @@ def model_provider(pre_process=True, post_process=True):
                     pre_process=pre_process, post_process=post_process, parallel_output=True,
                     share_embeddings_and_output_weights=not args.untie_embeddings_and_output_weights,
                     position_embedding_type=args.position_embedding_type, rotary_percent=args.rotary_percent,
-                    rotary_base=args.rotary_base, rope_scaling=args.use_rope_scaling)
+                    rotary_base=args.rotary_base, rope_scaling=args.use_rope_scaling,
+                    seq_len_interpolation_factor=args.rotary_seq_len_interpolation_factor)
 
 
 def loss_func(loss_mask, output_tensor):

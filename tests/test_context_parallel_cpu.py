@@ -35,6 +35,7 @@ def _run(rank, world, algo, nq, nkv, causal, extra):
     cfg.context_parallel_algo = algo
     cfg.context_parallel_kv_cache_policy = extra.get("cache")
     cfg.context_parallel_cache_interval = 0
+    cfg.use_ulysses_allgather_kv = bool(extra.get("allgather_kv", False))
     s, b, d = 32 * world, 2, 16
     q, k, v, w = _full(3, s, b, nq, nkv, d)
     qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
@@ -59,6 +60,8 @@ def _run(rank, world, algo, nq, nkv, causal, extra):
     ("megatron_cp_algo", 4, 4, 4, True, {"overlap": True, "cache": "full"}),
     ("ulysses_cp_algo", 2, 4, 2, True, {}),
     ("ulysses_cp_algo", 4, 4, 2, True, {}),
+    ("ulysses_cp_algo", 4, 4, 2, True, {"allgather_kv": True}),       # fewer KV heads than ranks: K/V gathered along the sequence
+    ("ulysses_cp_algo", 2, 4, 1, True, {"allgather_kv": True}),
     ("kvallgather_cp_algo", 2, 4, 2, True, {}),
     ("hybrid_cp_algo", 4, 4, 4, True, {}),
 ])

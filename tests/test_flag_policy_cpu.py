@@ -1,0 +1,65 @@
+"""No silent flags: every registered command-line flag is read by some code path, or is listed with a reason as having no
+effect on this hardware, or is refused when set."""
+import os
+import re
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG = os.path.join(ROOT, "mindspeed_b200")
+
+
+def _strip_definitions(txt):
+    out, skip = [], False
+    for ln in txt.splitlines():
+        if "add_argument(" in ln or "add_arg(" in ln:
+            skip = ln.count("(") - ln.count(")") > 0
+            continue
+        if skip:
+            if ln.count("(") - ln.count(")") < 0:
+                skip = False
+            continue
+        out.append(ln)
+    return "\n".join(out)
+
+
+def _registered_flags():
+    sys.path.insert(0, ROOT)
+    from mindspeed_b200.training.arguments import build_parser
+    flags = {}
+    for a in build_parser()._actions:
+        for o in a.option_strings:
+            if o.startswith("--") and o != "--help":
+                flags[o[2:]] = a.dest
+    return flags
+
+
+def test_every_flag_is_read_or_has_a_stated_policy():
+    from mindspeed_b200.features.flag_policy import NO_EFFECT, UNSUPPORTED
+    flags = _registered_flags()
+    src = ""
+    for dp, _, fn in os.walk(PKG):
+        for f in fn:
+            if f.endswith(".py") and f != "flag_policy.py":
+                txt = open(os.path.join(dp, f)).read()
+                if f in ("registry.py", "arguments.py"):
+                    txt = _strip_definitions(txt)
+                src += txt + "\n"
+    for f in ("pretrain_gpt.py", "bench.py"):
+        src += open(os.path.join(ROOT, f)).read()
+    silent = [f for f, d in sorted(flags.items())
+              if not re.search(r"\b" + re.escape(d) + r"\b", src) and f not in NO_EFFECT and f not in UNSUPPORTED]
+    assert not silent, f"flags that parse but nothing reads and no policy covers: {silent}"
+    unknown = [f for f in list(NO_EFFECT) + list(UNSUPPORTED) if f not in flags]
+    assert not unknown, f"policy entries for flags that are not registered: {unknown}"
+
+
+def test_unsupported_flag_stops_and_no_effect_flag_is_announced(capsys):
+    from mindspeed_b200.training.arguments import parse_args, validate_args
+    base = ["--num-layers", "2", "--hidden-size", "64", "--num-attention-heads", "4", "--seq-length", "32",
+            "--micro-batch-size", "1", "--vocab-size", "128"]
+    with pytest.raises(NotImplementedError, match="quant-grads"):
+        validate_args(parse_args(args_list=base + ["--quant-grads"]))
+    validate_args(parse_args(args_list=base + ["--jit-compile"]))
+    assert "--jit-compile has no effect here" in capsys.readouterr().out
