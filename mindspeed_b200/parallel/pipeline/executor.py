@@ -1,9 +1,19 @@
-"""Executes a pipeline ``Plan`` (plan.py) on this rank: lockstep slots, one batched send/receive group per slot.
+"""Executes a pipeline ``Plan`` (plan.py) on this rank: lockstep slots of compute with point-to-point exchange between them.
 
-Every tensor is sent in the slot after it was produced and received in that same slot, so both ends always put
-the matching operations into the same ``batch_isend_irecv`` group and the order inside a group is canonical
-(sorted by direction, chunk and micro-batch) on both sides.  Communication stays on NCCL point-to-point
-(gloo on CPU); the next slot's receives are not posted early, which keeps memory bounded by the plan itself.
+Every tensor is sent in the slot after it was produced and received in that same slot; the order of the messages of a
+slot is canonical (sorted by direction, chunk and micro-batch) on both ends.  Communication stays on NCCL point-to-point
+(gloo on CPU).  Two modes:
+
+  lock-step (default)   one ``batch_isend_irecv`` group per slot, waited for before the slot's compute.
+  overlapped            (``--overlap-p2p-communication``) the receives of slot t+1 are posted BEFORE slot t's compute and the
+                        sends of slot t+1 right after it, as individual isend / irecv calls; a receive is waited for only
+                        when its slot starts, a send when its buffer is recycled.  So a slot's transfers fly while the slot
+                        before it computes on the neighbour.  Messages that move up the ranks use the pipeline group, messages
+                        that move down use the second pipeline group: inside one communicator the dependency between a
+                        blocked receive and the send that feeds it then always points the same way along the ranks, so no
+                        cycle of mutually waiting ranks can form (reference: the even / odd ordered async exchange and the
+                        second group of mindspeed/core/pipeline_parallel/p2p_communication.py:460-542,
+                        optimize_send_recv_comm/parallel_state.py:15-66).
 
 B / W split: when the plan contains W operations for a chunk, its B runs with the weight-gradient store enabled
 (linear layers queue their weight-gradient GEMMs, reference: mindspeed/core/weight_grad_store.py:63-240) and the W
@@ -99,28 +109,61 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
         for m in model:
             _set_linear_deferral(m, True)
     key = lambda m: (m.kind, m.src, m.dst, m.src_chunk, m.mb)
+    group_down = ps._group("pp_new_stream", check=False)
+    overlap = bool(getattr(config, "overlap_p2p_comm", False)) and group_down is not None
+
+    def msgs(table, t):
+        out = sorted(table.get((rank, t), []), key=key)
+        return [m for m in out if m.kind == "act"] if forward_only else out
+
+    def comm_of(m):
+        return pp_group if m.dst > m.src else group_down
+
+    pending_recv: Dict[int, list] = {}
+    pending_send: List[tuple] = []
+    grad_pool: List[torch.Tensor] = []
+
+    def post_recvs(t):
+        lst = []
+        for m in msgs(plan.recvs, t):
+            buf = grad_pool.pop() if (m.kind == "grad" and grad_pool) else torch.empty(shape, dtype=dtype, device=dev)
+            lst.append((m, buf, dist.irecv(buf, pp_ranks[m.src], group=comm_of(m))))
+        pending_recv[t] = lst
+
+    def post_sends(t):
+        for m in msgs(plan.sends, t):
+            ten = outbox.pop((m.kind, m.src_chunk, m.mb)).contiguous()
+            pending_send.append((dist.isend(ten, pp_ranks[m.dst], group=comm_of(m)), ten))   # keep the tensor alive
+
     try:
+        if overlap:
+            post_recvs(0)
         for t in range(plan.num_slots):
-            sends = sorted(plan.sends.get((rank, t), []), key=key)
-            recvs = sorted(plan.recvs.get((rank, t), []), key=key)
-            if forward_only:
-                sends = [m for m in sends if m.kind == "act"]
-                recvs = [m for m in recvs if m.kind == "act"]
-            ops, bufs = [], []
-            allm = sorted(sends + recvs, key=key)
-            for m in allm:
-                if m.src == rank and m in sends:
-                    ten = outbox.pop((m.kind, m.src_chunk, m.mb))
-                    ops.append(dist.P2POp(dist.isend, ten.contiguous(), pp_ranks[m.dst], pp_group))
-                else:
-                    buf = torch.empty(shape, dtype=dtype, device=dev)
-                    bufs.append((m, buf))
-                    ops.append(dist.P2POp(dist.irecv, buf, pp_ranks[m.src], pp_group))
-            if ops:
-                for r in dist.batch_isend_irecv(ops):
-                    r.wait()
-            for m, buf in bufs:
-                inbox[(m.kind, m.dst_chunk, m.mb)] = buf
+            if overlap:
+                for m, buf, req in pending_recv.pop(t):
+                    req.wait()
+                    inbox[(m.kind, m.dst_chunk, m.mb)] = buf
+                if t + 1 < plan.num_slots:
+                    post_recvs(t + 1)            # flies while this slot computes here and the slot before it on the peer
+                while pending_send and pending_send[0][0].is_completed():
+                    pending_send.pop(0)
+            else:
+                sends, recvs = msgs(plan.sends, t), msgs(plan.recvs, t)
+                ops, bufs = [], []
+                allm = sorted(sends + recvs, key=key)
+                for m in allm:
+                    if m.src == rank and m in sends:
+                        ten = outbox.pop((m.kind, m.src_chunk, m.mb))
+                        ops.append(dist.P2POp(dist.isend, ten.contiguous(), pp_ranks[m.dst], pp_group))
+                    else:
+                        buf = torch.empty(shape, dtype=dtype, device=dev)
+                        bufs.append((m, buf))
+                        ops.append(dist.P2POp(dist.irecv, buf, pp_ranks[m.src], pp_group))
+                if ops:
+                    for r in dist.batch_isend_irecv(ops):
+                        r.wait()
+                for m, buf in bufs:
+                    inbox[(m.kind, m.dst_chunk, m.mb)] = buf
             for op in plan.table[rank][t]:
                 if forward_only and op.kind != "F":
                     continue
@@ -172,6 +215,8 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
                     if has_w:
                         WeightGradStore.enable(True)
                     g = S.backward_step(inp, out, og, None, config)
+                    if overlap and og is not None and og.is_leaf and not og.requires_grad:
+                        grad_pool.append(og)     # the received output gradient has been consumed: reuse its storage
                     if has_w:
                         WeightGradStore.flush()
                         WeightGradStore.enable(False)
@@ -183,6 +228,10 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
                             outbox[("grad", op.chunk, op.mb)] = g
                 else:  # W
                     WeightGradStore.pop()
+            if overlap and t + 1 < plan.num_slots:
+                post_sends(t + 1)                # what this slot produced leaves now; nobody waits for it here
+        for req, _ in pending_send:
+            req.wait()
     finally:
         ps.set_stage_override(None, None)
         ps.set_virtual_pipeline_model_parallel_rank(saved_vpp[0])

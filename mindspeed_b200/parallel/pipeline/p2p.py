@@ -73,14 +73,16 @@ def _communicate(*, tensor_send_next, tensor_send_prev, recv_prev, recv_next, te
         if ops:
             reqs = dist.batch_isend_irecv(ops)
     else:
-        # even ranks send first, odd ranks receive first; with a second group, receives use it
-        rg = group2 if group2 is not None else group
+        # even ranks send first, odd ranks receive first.  With a second group, traffic that moves up the ranks (send to
+        # next / receive from previous) stays on the pipeline group and traffic that moves down uses the second one: a send
+        # and its matching receive are always on the same communicator, and the two directions never queue behind each other
+        down = group2 if group2 is not None else group
         even = ps.get_pipeline_model_parallel_rank() % 2 == 0
         seq = []
         s_next = (dist.isend, tensor_send_next, next_r, group)
-        r_prev = (dist.irecv, t_prev, prev_r, rg)
-        s_prev = (dist.isend, tensor_send_prev, prev_r, group)
-        r_next = (dist.irecv, t_next, next_r, rg)
+        r_prev = (dist.irecv, t_prev, prev_r, group)
+        s_prev = (dist.isend, tensor_send_prev, prev_r, down)
+        r_next = (dist.irecv, t_next, next_r, down)
         seq = [s_next, r_prev, s_prev, r_next] if even else [r_prev, s_next, r_next, s_prev]
         for fn, t, peer, g in seq:
             if t is not None:

@@ -68,7 +68,8 @@ def initialize_megatron(extra_args_provider=None, args_defaults=None, ignore_unk
             ulysses_degree_in_cp=args.ulysses_degree_in_cp if args.context_parallel_algo.startswith("hybrid") else None,
             cp_window_size=args.cp_window_size,
             tp_2d=args.tp_2d, tp_x=args.tp_x, tp_y=args.tp_y,
-            optimize_send_recv_comm=args.optimize_send_recv_comm,
+            # the overlapped pipeline exchange needs one communicator per direction (executor.py)
+            optimize_send_recv_comm=args.optimize_send_recv_comm or getattr(args, "overlap_p2p_comm", False),
         )
     set_random_seed(args.seed)
     fm.apply_features(args)

@@ -152,6 +152,12 @@ def _train(rank, world, extra, bidirectional):
     (2, ["--pipeline-model-parallel-size", "2", "--num-layers-per-virtual-pipeline-stage", "1", "--recompute-in-advance"], False),
     (2, ["--pipeline-model-parallel-size", "2", "--schedules-method", "chimera"], True),
     (2, ["--pipeline-model-parallel-size", "2", "--schedules-method", "dualpipe"], True),
+    # receives of the next slot posted before this slot's compute, sends right after it, one communicator per direction
+    (2, ["--pipeline-model-parallel-size", "2", "--overlap-p2p-communication"], False),
+    (2, ["--pipeline-model-parallel-size", "2", "--num-layers-per-virtual-pipeline-stage", "1", "--overlap-p2p-communication"], False),
+    (2, ["--pipeline-model-parallel-size", "2", "--schedules-method", "dualpipev", "--overlap-p2p-communication"], False),
+    (2, ["--pipeline-model-parallel-size", "2", "--schedules-method", "dualpipe", "--overlap-p2p-communication"], True),
+    (4, ["--pipeline-model-parallel-size", "4", "--overlap-p2p-communication"], False),
 ])
 def test_pipeline_matches_no_pipeline(world, extra, bidir):
     ref = run_distributed(_train, 1, [], False)[0]
