@@ -419,7 +419,8 @@ def main(argv=None):
                "clocks": clocks, "e2e": e2e, "baseline_arm": base, "fused_comm_check": comm_check,
                "truncated": bool(truncated), "requested_steps": a.steps, "budget_s": a.max_seconds,
                "projected_s": round((time.time() - _T_START), 1), "warmup_step_ms": step_ms,
-               "gpu_launches": int(launches), "impl": "ours"}
+               "gpu_launches": int(launches), "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 2),
+               "impl": "ours"}
         print(json.dumps(out))
         sys.stdout.flush()
     if world > 1:

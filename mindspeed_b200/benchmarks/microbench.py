@@ -32,11 +32,15 @@ def time_fn(fn, iters=10, warmup=3, flush=True):
         fn()
     ts = []
     for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        # a device-side delay first: the host enqueues the flush, the start event and fn's launches while the GPU spins, so
+        # the interval between the events holds device time only, not the host's launch latency (which would otherwise add
+        # 50-100 us to every kernel shorter than that)
+        torch.cuda._sleep(400000)
         if flush:
             b = _flush_buf()
             L.msb_l2_flush(ctypes.c_void_p(b.data_ptr()), ctypes.c_size_t(b.numel()), ctypes.c_void_p(loader.stream_ptr()))
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
         e0.record()
         fn()
         e1.record()
@@ -97,6 +101,13 @@ def bench_elementwise(out):
     y = rms_norm(x, w)
     g = torch.randn_like(y)
     rec("rmsnorm_bwd", time_fn(lambda: torch.autograd.grad(y, (x, w), g, retain_graph=True)), 3 * x.numel() * 2)
+    from ..ops.norm import add_rms_norm
+    r = torch.randn_like(x, requires_grad=True)
+    rec("add_rmsnorm_fwd", time_fn(lambda: add_rms_norm(x, r, w)), 4 * x.numel() * 2)
+    hh, yy = add_rms_norm(x, r, w)
+    g2 = torch.randn_like(hh)
+    rec("add_rmsnorm_bwd", time_fn(lambda: torch.autograd.grad((hh, yy), (x, r, w), (g2, g), retain_graph=True)), 4 * x.numel() * 2)
+    del r, hh, yy, g2
     f = 14336
     z = torch.randn(rows, 2 * f, device="cuda", dtype=torch.bfloat16, requires_grad=True)
     rec("swiglu_fwd", time_fn(lambda: swiglu(z)), 3 * rows * f * 2)

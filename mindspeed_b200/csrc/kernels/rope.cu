@@ -88,6 +88,69 @@ __global__ void __launch_bounds__(256) rope_bf16_vec_kernel(const __nv_bfloat16*
     *reinterpret_cast<uint4*>(yo + j + half) = ob;
   }
 }
+
+// Token-major vector path (head_dim / 16 a power of two): a block walks tokens, a thread owns one (head, 8-element slot)
+// of the token, so the per-element index arithmetic is a shift and a mask, the position row is found once per token,
+// and TOK tokens are loaded before any of them is rotated (2 * TOK 16-byte loads in flight per thread).
+template <int TOK>
+__global__ void __launch_bounds__(512, 2) rope_bf16_token_kernel(const __nv_bfloat16* x, __nv_bfloat16* y, const float* __restrict__ cosv,
+                                                               const float* __restrict__ sinv, long long tokens, int heads, int head_dim,
+                                                               long long token_stride_in, long long head_stride_in,
+                                                               long long token_stride_out, long long head_stride_out, int tokens_per_pos,
+                                                               int group_heads, int rope_heads, float sin_sign, int vec_shift) {
+  const int half = head_dim >> 1;
+  const int per_token = heads << vec_shift;
+  const bool in_place = (x == y) && token_stride_in == token_stride_out && head_stride_in == head_stride_out;
+  for (long long t0 = (long long)blockIdx.x * TOK; t0 < tokens; t0 += (long long)gridDim.x * TOK) {
+    for (int i = threadIdx.x; i < per_token; i += blockDim.x) {
+      const int h = i >> vec_shift;
+      const int j = (i & ((1 << vec_shift) - 1)) << 3;
+      const bool rotate = (h % group_heads) < rope_heads;
+      if (!rotate && in_place) continue;
+      uint4 va[TOK], vb[TOK];
+#pragma unroll
+      for (int u = 0; u < TOK; ++u) {
+        if (t0 + u < tokens) {
+          const __nv_bfloat16* xi = x + (t0 + u) * token_stride_in + (long long)h * head_stride_in;
+          va[u] = *reinterpret_cast<const uint4*>(xi + j);
+          vb[u] = *reinterpret_cast<const uint4*>(xi + j + half);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < TOK; ++u) {
+        if (t0 + u >= tokens) break;
+        __nv_bfloat16* yo = y + (t0 + u) * token_stride_out + (long long)h * head_stride_out;
+        if (!rotate) {
+          *reinterpret_cast<uint4*>(yo + j) = va[u];
+          *reinterpret_cast<uint4*>(yo + j + half) = vb[u];
+          continue;
+        }
+        const long long pos = (t0 + u) / tokens_per_pos;
+        const float4* c0 = reinterpret_cast<const float4*>(cosv + pos * head_dim + j);
+        const float4* s0 = reinterpret_cast<const float4*>(sinv + pos * head_dim + j);
+        const float4* c1 = reinterpret_cast<const float4*>(cosv + pos * head_dim + j + half);
+        const float4* s1 = reinterpret_cast<const float4*>(sinv + pos * head_dim + j + half);
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&va[u]);
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&vb[u]);
+        uint4 oa, ob;
+        __nv_bfloat162* qa = reinterpret_cast<__nv_bfloat162*>(&oa);
+        __nv_bfloat162* qb = reinterpret_cast<__nv_bfloat162*>(&ob);
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {       // four elements of each half per pass: keeps the live cos / sin values at 16
+          const float4 ca = __ldg(c0 + q), sa = __ldg(s0 + q), cb = __ldg(c1 + q), sb = __ldg(s1 + q);
+          const float2 a0 = __bfloat1622float2(pa[2 * q]), a1 = __bfloat1622float2(pa[2 * q + 1]);
+          const float2 b0 = __bfloat1622float2(pb[2 * q]), b1 = __bfloat1622float2(pb[2 * q + 1]);
+          qa[2 * q] = __floats2bfloat162_rn(a0.x * ca.x - b0.x * sa.x * sin_sign, a0.y * ca.y - b0.y * sa.y * sin_sign);
+          qa[2 * q + 1] = __floats2bfloat162_rn(a1.x * ca.z - b1.x * sa.z * sin_sign, a1.y * ca.w - b1.y * sa.w * sin_sign);
+          qb[2 * q] = __floats2bfloat162_rn(b0.x * cb.x + a0.x * sb.x * sin_sign, b0.y * cb.y + a0.y * sb.y * sin_sign);
+          qb[2 * q + 1] = __floats2bfloat162_rn(b1.x * cb.z + a1.x * sb.z * sin_sign, b1.y * cb.w + a1.y * sb.w * sin_sign);
+        }
+        *reinterpret_cast<uint4*>(yo + j) = oa;
+        *reinterpret_cast<uint4*>(yo + j + half) = ob;
+      }
+    }
+  }
+}
 }  // namespace
 
 MSB_API int msb_rope(const void* x, void* y, const float* cosv, const float* sinv, long long tokens, int heads,
@@ -100,6 +163,24 @@ MSB_API int msb_rope(const void* x, void* y, const float* cosv, const float* sin
                       head_stride_in % 8 == 0 && token_stride_out % 8 == 0 && head_stride_out % 8 == 0 &&
                       (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0 &&
                       (reinterpret_cast<uintptr_t>(cosv) & 7) == 0 && (reinterpret_cast<uintptr_t>(sinv) & 7) == 0;
+  const int vph = head_dim / 16;
+  const bool cs16 = (reinterpret_cast<uintptr_t>(cosv) & 15) == 0 && (reinterpret_cast<uintptr_t>(sinv) & 15) == 0;
+  if (vec_ok && cs16 && vph > 0 && (vph & (vph - 1)) == 0 && (long long)heads * vph <= (1 << 20)) {
+    int shift = 0;
+    while ((1 << shift) < vph) ++shift;
+    constexpr int TOK = 2;
+    const int per_token = heads * vph;
+    int th = ((per_token + 31) / 32) * 32;
+    if (th > 512) th = 512;
+    long long gv = (tokens + TOK - 1) / TOK;
+    const long long cap = (long long)msb::num_sms() * (th > 256 ? 2 : 4);   // resident blocks at <= 64 registers
+    if (gv > cap) gv = cap;
+    rope_bf16_token_kernel<TOK><<<(int)gv, th, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, cosv, sinv, tokens, heads, head_dim,
+                                                       token_stride_in, head_stride_in, token_stride_out, head_stride_out,
+                                                       tokens_per_pos, group_heads, rope_heads, backward ? -1.f : 1.f, shift);
+    MSB_CHECK_LAUNCH("rope_bf16_token");
+    return 0;
+  }
   if (vec_ok) {
     const long long total = tokens * heads * (head_dim / 16);
     long long gv = (total + 255) / 256;

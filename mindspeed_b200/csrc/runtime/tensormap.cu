@@ -19,10 +19,22 @@ PFN_encodeTiled get_encode_tiled() {
   return fn;
 }
 
+// The encode call is a driver entry point: it needs a context current on the calling thread, but a thread whose first
+// CUDA work is this call (an autograd worker thread running a GEMM as its first backward node on device 0) has none yet,
+// because only runtime calls bind the primary context lazily.  One runtime call per thread does that.
+static inline void ensure_context() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows, uint64_t cols,
                  uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
   PFN_encodeTiled enc = get_encode_tiled();
   if (!enc) { msb_set_error("cuTensorMapEncodeTiled is not available from this driver"); return 1; }
+  ensure_context();
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) { msb_set_error("tensor map base %p is not 16-byte aligned", base); return 2; }
   if ((ld * elem_bytes) % 16 != 0) { msb_set_error("tensor map row pitch %llu bytes is not a multiple of 16", (unsigned long long)(ld * elem_bytes)); return 2; }
   cuuint64_t gdim[2] = {cols, rows};
@@ -46,6 +58,7 @@ int make_tmap_nd(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int
                  const uint64_t* strides_bytes, const uint32_t* box) {
   PFN_encodeTiled enc = get_encode_tiled();
   if (!enc) { msb_set_error("cuTensorMapEncodeTiled is not available from this driver"); return 1; }
+  ensure_context();
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) { msb_set_error("tensor map base %p is not 16-byte aligned", base); return 2; }
   cuuint64_t gdim[5]; cuuint64_t gstr[4]; cuuint32_t bx[5]; cuuint32_t es[5];
   for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }

@@ -7,7 +7,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops.norm import rms_norm
+from ..ops.norm import add_rms_norm, rms_norm
 
 
 class RMSNorm(nn.Module):
@@ -25,6 +25,10 @@ class RMSNorm(nn.Module):
 
     def forward(self, x):
         return rms_norm(x, self.weight, self.eps, self.zero_centered, fused=self.fused)
+
+    def forward_add(self, x, residual):
+        """(x + residual, norm(x + residual)): the residual add rides in the norm's pass over the row."""
+        return add_rms_norm(x, residual, self.weight, self.eps, self.zero_centered, fused=self.fused)
 
 
 class LayerNorm(nn.Module):

@@ -142,9 +142,17 @@ class TransformerLayer(nn.Module):
                                                       packed_seq_params=packed_seq_params)
         if self.config.apply_residual_connection_post_layernorm:
             residual = ln
-        hidden_states = _bda(attn_out, attn_bias, residual, self.hidden_dropout, self.training)
+        ln2 = None
+        if (attn_bias is None and not (self.hidden_dropout > 0.0 and self.training) and not self.recompute_norm
+                and not self.config.apply_residual_connection_post_layernorm and hasattr(self.pre_mlp_layernorm, "forward_add")):
+            # residual add and the MLP's norm in one pass over the row (and one kernel in backward)
+            hidden_states, ln2 = self.pre_mlp_layernorm.forward_add(attn_out, residual)
+        else:
+            hidden_states = _bda(attn_out, attn_bias, residual, self.hidden_dropout, self.training)
         residual = hidden_states
-        if self.recompute_norm and self.training and hidden_states.requires_grad and not self.is_moe:
+        if ln2 is not None:
+            mlp_out, mlp_bias = self.mlp(ln2)
+        elif self.recompute_norm and self.training and hidden_states.requires_grad and not self.is_moe:
             ck2 = CheckpointWithoutOutput()
             ln2 = ck2.checkpoint(self.pre_mlp_layernorm, False, hidden_states)
             mlp_out, mlp_bias = self.mlp(ln2)

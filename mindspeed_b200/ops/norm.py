@@ -64,6 +64,55 @@ class _RMSNormFn(torch.autograd.Function):
         return dx, dw, None, None
 
 
+class _AddRMSNormFn(torch.autograd.Function):
+    """(h, y) = (x + residual, rmsnorm(x + residual) * weight) in one pass over the row; the backward adds the
+    gradient that reaches h directly to the one that comes back through the norm inside the same kernel
+    (reference: the residual-add + norm fusion of mindspeed/ops/csrc/cann/npu_dropout_add_layer_norm.cpp, RMSNorm form)."""
+
+    @staticmethod
+    def forward(ctx, x, residual, weight, eps, zero_centered):
+        L = loader.require_lib()
+        xc, rc = x.contiguous(), residual.contiguous()
+        cols = xc.shape[-1]
+        rows = xc.numel() // cols
+        h, y = torch.empty_like(xc), torch.empty_like(xc)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        loader.check(L.msb_add_rmsnorm_fwd(loader.p(xc), loader.p(rc), loader.p(weight), loader.p(h), loader.p(y), loader.p(rstd),
+                                           rows, cols, ctypes.c_float(eps), int(zero_centered), code(x.dtype),
+                                           ctypes.c_void_p(loader.stream_ptr())), "add_rmsnorm_fwd")
+        ctx.save_for_backward(h, weight, rstd)
+        ctx.zero_centered = zero_centered
+        ctx.mark_non_differentiable(rstd)
+        return h, y
+
+    @staticmethod
+    def backward(ctx, dh, dy):
+        L = loader.require_lib()
+        h, weight, rstd = ctx.saved_tensors
+        cols = h.shape[-1]
+        rows = h.numel() // cols
+        dw = torch.empty_like(weight)
+        if dy is None:
+            return dh, dh, torch.zeros_like(weight), None, None
+        dx = torch.empty_like(h)
+        L.msb_rmsnorm_bwd_scratch_elems.restype = ctypes.c_size_t
+        scratch = _get_scratch(h.device, L.msb_rmsnorm_bwd_scratch_elems(rows, cols))
+        loader.check(L.msb_rmsnorm_bwd_add(loader.p(dy.contiguous()), loader.p(h), loader.p(weight), loader.p(rstd), loader.p(dx),
+                                           loader.p(dw), loader.p(scratch), rows, cols, int(ctx.zero_centered), 0, code(h.dtype),
+                                           loader.p(dh.contiguous()) if dh is not None else None,
+                                           ctypes.c_void_p(loader.stream_ptr())), "rmsnorm_bwd_add")
+        return dx, dx, dw, None, None
+
+
+def add_rms_norm(x, residual, weight, eps=1e-5, zero_centered=False, fused=True):
+    """Returns (h, y) with h = x + residual and y = rmsnorm(h) * weight."""
+    if (fused and x.is_cuda and loader.use_kernels(x) and weight.dtype == x.dtype and residual.dtype == x.dtype
+            and x.shape == residual.shape and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384):
+        return _AddRMSNormFn.apply(x, residual, weight, eps, zero_centered)
+    h = x + residual
+    return h, rms_norm(h, weight, eps, zero_centered, fused)
+
+
 def rms_norm(x, weight, eps=1e-5, zero_centered=False, fused=True):
     if fused and x.is_cuda and loader.use_kernels(x) and weight.dtype == x.dtype:
         return _RMSNormFn.apply(x, weight, eps, zero_centered)

@@ -178,14 +178,14 @@ def _new_group(ranks, backend=None, timeout=None, pg_options=None):
     return dist.new_group(ranks, **kwargs)
 
 
-def _register(name: str, all_ranks: List[List[int]], backend=None, timeout=None, make_group=True):
+def _register(name: str, all_ranks: List[List[int]], backend=None, timeout=None, make_group=True, pg_options=None):
     """Create one process group per rank list; remember the one this rank is in."""
     if _S.rank_offset:
         all_ranks = [[r + _S.rank_offset for r in ranks] for ranks in all_ranks]
     _S.all_groups[name] = all_ranks
     mine = None
     for ranks in all_ranks:
-        g = _new_group(ranks, backend=backend, timeout=timeout) if make_group else None
+        g = _new_group(ranks, backend=backend, timeout=timeout, pg_options=pg_options) if make_group else None
         if _S.rank in ranks:
             mine = _Group(list(ranks), g)
     if mine is not None:
@@ -288,8 +288,19 @@ def initialize_model_parallel(
         raise RuntimeError("dense and expert rank grids disagree on pipeline groups")
     _S.sizes = dict(tp=tp, pp=pp, cp=cp, dp=dp, ep=ep, etp=etp, edp=edp)
 
+    # Per-group NCCL settings: a YAML file ({group name: {max_ctas, min_ctas, cga_cluster_size}}) over these defaults.
+    # The pipeline groups carry point-to-point transfers that are posted ahead of time and then wait for the peer while
+    # this GPU computes; a waiting NCCL kernel holds its thread blocks, so those groups get few of them.
+    nccl_cfgs = {"pp": {"max_ctas": 8, "cga_cluster_size": 2}, "pp_new_stream": {"max_ctas": 8, "cga_cluster_size": 2}}
+    if nccl_communicator_config_path:
+        import yaml
+        with open(nccl_communicator_config_path) as f:
+            nccl_cfgs.update(yaml.safe_load(f) or {})
+    on_nccl = make and torch.cuda.is_available() and dist.get_backend() == "nccl"
+
     def reg(name, ranks, backend=None):
-        return _register(name, ranks, backend=backend, timeout=timeout, make_group=make)
+        opts = get_nccl_options(name, nccl_cfgs) if (on_nccl and backend is None) else None
+        return _register(name, ranks, backend=backend, timeout=timeout, make_group=make, pg_options=opts)
 
     # data parallel (+ gloo twin, + with context parallel)
     reg("dp", dense.get_ranks("dp"))

@@ -22,6 +22,37 @@ def _dev():
         dist.get_backend(ps.get_pipeline_model_parallel_group()) != "gloo" else torch.device("cpu")
 
 
+def warm_up_p2p(groups=None):
+    """Create the point-to-point channels of every neighbour pair, in one fixed order on all ranks.
+
+    NCCL builds the communicator of a rank pair inside the first send / receive between them, and that call blocks
+    until the other side makes its matching call.  When ranks first touch two communicators in different orders (one
+    posts a receive on the downward group while its neighbour posts one on the upward group), each blocks inside the
+    creation of a different communicator and neither returns.  Walking the pairs (r, r+1) - and the wrap-around pair
+    used by interleaved schedules - in rank order, group by group, rules that out; afterwards any posting order works.
+    """
+    pp = ps.get_pipeline_model_parallel_world_size()
+    if pp <= 1:
+        return
+    if groups is None:
+        groups = [ps.get_pipeline_model_parallel_group(), ps._group("pp_new_stream", check=False)]
+    ranks = ps._ranks("pp")
+    me = ps.get_pipeline_model_parallel_rank()
+    dev = _dev()
+    pairs = [(r, r + 1) for r in range(pp - 1)] + ([(pp - 1, 0)] if pp > 2 else [])
+    for g in groups:
+        if g is None:
+            continue
+        for a, b in pairs:
+            for src, dst in ((a, b), (b, a)):
+                if me == src:
+                    dist.send(torch.zeros(1, device=dev), ranks[dst], group=g)
+                elif me == dst:
+                    dist.recv(torch.empty(1, device=dev), ranks[src], group=g)
+    if dev.type == "cuda":
+        torch.cuda.synchronize()
+
+
 def _communicate_shapes(send_next, send_prev, recv_prev, recv_next, config):
     """Exchange 3-d shapes with the neighbours when sequence lengths vary."""
     group = ps.get_pipeline_model_parallel_group()

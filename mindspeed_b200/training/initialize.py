@@ -71,6 +71,9 @@ def initialize_megatron(extra_args_provider=None, args_defaults=None, ignore_unk
             # the overlapped pipeline exchange needs one communicator per direction (executor.py)
             optimize_send_recv_comm=args.optimize_send_recv_comm or getattr(args, "overlap_p2p_comm", False),
         )
+    if getattr(args, "overlap_p2p_comm", False) and args.pipeline_model_parallel_size > 1:
+        from ..parallel.pipeline.p2p import warm_up_p2p
+        warm_up_p2p()                    # pair communicators are created here, in one order on every rank
     set_random_seed(args.seed)
     fm.apply_features(args)
     kind = fm.resolve("tp_comm_ops", "default")

@@ -15,7 +15,8 @@ def _close(a, b, dtype, scale=1.0):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("rows,cols", [(64, 4096), (33, 512), (7, 520), (4, 12288)])
+@pytest.mark.parametrize("rows,cols", [(64, 4096), (33, 512), (7, 520), (4, 12288), (1000, 1024), (2500, 4096), (700, 8192),
+                                       (300, 16384), (5, 20000), (9, 1028)])
 def test_rmsnorm(dtype, rows, cols):
     from mindspeed_b200.ops.norm import rms_norm, rms_norm_ref
     torch.manual_seed(0)
@@ -30,6 +31,37 @@ def test_rmsnorm(dtype, rows, cols):
     yr.backward(g.float())
     _close(x.grad, xr.grad, dtype, 2)
     _close(w.grad, wr.grad, dtype, 4)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,cols,zc", [(2500, 4096, False), (333, 1024, True), (64, 8192, False), (5, 20000, False)])
+def test_add_rmsnorm(dtype, rows, cols, zc):
+    """Residual add fused with the norm: both outputs and all three gradients, with a gradient on each output."""
+    from mindspeed_b200.ops.norm import add_rms_norm, rms_norm_ref
+    torch.manual_seed(3)
+    x = torch.randn(rows, cols, device="cuda", dtype=dtype, requires_grad=True)
+    r = torch.randn(rows, cols, device="cuda", dtype=dtype, requires_grad=True)
+    w = (0.1 * torch.randn(cols, device="cuda") + (0.0 if zc else 1.0)).to(dtype).requires_grad_(True)
+    h, y = add_rms_norm(x, r, w, 1e-5, zc)
+    xr, rr, wr = (t.detach().float().requires_grad_(True) for t in (x, r, w))
+    # the kernel normalises the sum rounded to the tensor type (straight-through for the gradient)
+    hr = (xr + rr) + ((xr + rr).to(dtype).float() - (xr + rr)).detach()
+    yr = rms_norm_ref(hr, wr, 1e-5, zc)
+    _close(h, hr, dtype)
+    _close(y, yr, dtype)
+    gh, gy = torch.randn_like(h), torch.randn_like(y)
+    torch.autograd.backward([h, y], [gh, gy])
+    torch.autograd.backward([hr, yr], [gh.float(), gy.float()])
+    _close(x.grad, xr.grad, dtype, 2)
+    _close(r.grad, rr.grad, dtype, 2)
+    _close(w.grad, wr.grad, dtype, 6)
+    # only the norm output is used downstream
+    x.grad = r.grad = w.grad = None
+    h2, y2 = add_rms_norm(x, r, w, 1e-5, zc)
+    y2.backward(gy)
+    xr.grad = None
+    rms_norm_ref((xr + rr) + ((xr + rr).to(dtype).float() - (xr + rr)).detach(), wr, 1e-5, zc).backward(gy.float())
+    _close(x.grad, xr.grad, dtype, 2)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
@@ -64,10 +96,11 @@ def test_swiglu_weighted():
 
 
 @pytest.mark.parametrize("interleaved", [False, True])
-def test_rope(interleaved):
+@pytest.mark.parametrize("s,b,d", [(96, 2, 128), (97, 1, 128), (33, 3, 64), (20, 1, 96), (1031, 1, 256)])
+def test_rope(interleaved, s, b, d):
     from mindspeed_b200.ops.rope import apply_rope, apply_rope_ref, rope_packed_qkv_
     torch.manual_seed(3)
-    s, b, n, d = 96, 2, 6, 128
+    n = 6
     ang = torch.outer(torch.arange(s, device="cuda").float(), 1.0 / (10000 ** (torch.arange(0, d, 2, device="cuda").float() / d)))
     emb = torch.stack((ang, ang), -1).reshape(s, d) if interleaved else torch.cat((ang, ang), -1)
     cos, sin = emb.cos().contiguous(), emb.sin().contiguous()
