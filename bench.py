@@ -61,6 +61,7 @@ def parse(argv=None):
                    help="wall-clock budget of the whole run, counted from process start")
     p.add_argument("--e2e-steps", type=int, default=-1, help="-1: chosen from the step time")
     p.add_argument("--baseline-steps", type=int, default=-1, help="-1: chosen from the step time; 0 disables the arm")
+    p.add_argument("--extra", type=str, default="", help="further training flags, space separated (reported in config)")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-comm-check", action="store_true")
     p.add_argument("--profile-dir", type=str, default=None,
@@ -283,7 +284,7 @@ def main(argv=None):
         kw["gbs"] = a.global_batch
     args_list = PRESETS[a.model](**kw)
     lay, par, rl = layout_args(a, n)
-    args_list += lay + ["--train-iters", "1000000", "--log-interval", "1000000"]
+    args_list += lay + ["--train-iters", "1000000", "--log-interval", "1000000"] + a.extra.split()
     if a.num_layers is not None:
         i = args_list.index("--num-layers")
         args_list[i + 1] = str(a.num_layers)
@@ -411,7 +412,7 @@ def main(argv=None):
                "mfu_of_sustained_bf16_peak": f_model / (step_s * n * peaks["bf16_tflops_sustained"] * 1e12),
                "config": {"model": a.model, "global_batch": args.global_batch_size, "seq_len": args.seq_length,
                           "micro_batch": args.micro_batch_size, "num_layers": args.num_layers, "parallelism": par,
-                          "optimization_level": a.level, "recompute_layers": rl,
+                          "optimization_level": a.level, "recompute_layers": rl, "extra_flags": a.extra,
                           "reuse_fp32_param": bool(getattr(args, "reuse_fp32_param", False)),
                           "same_config_for_all_n": "no: one GPU recomputes 8 layers and packs the fp32 masters to fit 180 GB; "
                                                    "hfu_of_measured_bf16_peak counts the recomputed FLOPs",

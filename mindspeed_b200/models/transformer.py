@@ -194,6 +194,7 @@ class TransformerBlock(nn.Module):
                 layers.append(TransformerLayer(config, layer_number=i + 1))
         self.layers = nn.ModuleList(layers)
         self.num_layers_per_pipeline_rank = n
+        self.fb_overlap = None           # set by the schedule for the duration of one step (parallel/moe/fb_overlap.BlockOverlap)
         self.final_layernorm = build_norm(config, config.hidden_size) if (post_process and post_layer_norm) else None
 
     def set_input_tensor(self, t):
@@ -244,7 +245,12 @@ class TransformerBlock(nn.Module):
     def forward(self, hidden_states, attention_mask=None, rotary_pos_emb=None, packed_seq_params=None, **kwargs):
         if not self.pre_process:
             hidden_states = self.input_tensor
-        if self.config.recompute_granularity == "full" and self.training:
+        if self.fb_overlap is not None and self.training and torch.is_grad_enabled():
+            # forward of this micro-batch interleaved with the layer backward of the previous one (--moe-fb-overlap);
+            # returns a detached leaf: the schedule's loss backward stops there and seeds the next interleaved backward
+            hidden_states = self.fb_overlap.forward(hidden_states, attention_mask=attention_mask, rotary_pos_emb=rotary_pos_emb,
+                                                    packed_seq_params=packed_seq_params)
+        elif self.config.recompute_granularity == "full" and self.training:
             hidden_states = self._checkpointed_forward(hidden_states, attention_mask, rotary_pos_emb, packed_seq_params)
         else:
             for layer in self.layers:

@@ -139,30 +139,65 @@ def _restore_dispatcher(d, snap):
         setattr(d, k, v)
 
 
+def _tensors(xs):
+    return [t for t in xs if isinstance(t, torch.Tensor)]
+
+
 class _Streams:
+    """The compute stream is the caller's current stream; communication stages run on a second one.
+
+    A tensor produced on one stream and consumed on the other is recorded on the consumer's stream, so that the caching
+    allocator does not hand its memory to a later allocation on the producer's stream while the consumer still reads it.
+    """
+
     def __init__(self, device):
         self.cuda = isinstance(device, torch.device) and device.type == "cuda"
         self.comm = torch.cuda.Stream(device=device) if self.cuda else None
 
-    def on_comm(self, fn):
-        """Run ``fn`` on the communication stream, ordered after what the compute stream has queued so far."""
+    def mark(self):
+        """An event on the compute stream: work queued on it afterwards does not hold back ``on_comm(..., after=event)``."""
+        return torch.cuda.current_stream().record_event() if self.cuda else None
+
+    def on_comm(self, fn, inputs=(), after=None):
+        """Run ``fn`` on the communication stream, ordered after ``after`` (an event from ``mark``) or, without one,
+        after everything the compute stream has queued so far."""
         if not self.cuda:
             return fn()
-        self.comm.wait_stream(torch.cuda.current_stream())
+        main = torch.cuda.current_stream()
+        if after is not None:
+            self.comm.wait_event(after)
+        else:
+            self.comm.wait_stream(main)
+        for t in _tensors(inputs):
+            t.record_stream(self.comm)
         with torch.cuda.stream(self.comm):
-            return fn()
+            out = fn()
+        for t in _tensors(out if isinstance(out, (tuple, list)) else (out,)):
+            t.record_stream(main)
+        return out
 
     def join(self):
         if self.cuda:
             torch.cuda.current_stream().wait_stream(self.comm)
 
 
-def forward_layer_staged(staged: StagedMoELayer, hidden: torch.Tensor, **attn_kw) -> Tuple[torch.Tensor, LayerGraph]:
-    """Plain (non-overlapped) staged forward; returns the detached output and the graph for a later backward."""
+COMM_STAGES = (1, 3)        # dispatch and combine
+
+
+def forward_layer_staged(staged: StagedMoELayer, hidden: torch.Tensor, streams: Optional[_Streams] = None,
+                         **attn_kw) -> Tuple[torch.Tensor, LayerGraph]:
+    """Plain (non-overlapped) staged forward; returns the detached output and the graph for a later backward.
+
+    With ``streams`` the dispatch and combine stages run on the communication stream: autograd executes a node's backward
+    on the stream of its forward, so this is what later lets their backward overlap another micro-batch's compute."""
     g = LayerGraph()
     cur: Tuple = (hidden,)
-    for fn in staged.functions(**attn_kw):
-        cur = g.run_stage(fn, cur)
+    for k, fn in enumerate(staged.functions(**attn_kw)):
+        if streams is not None and k in COMM_STAGES:
+            cur = streams.on_comm(lambda fn=fn, cur=cur: g.run_stage(fn, cur), cur)
+            streams.join()
+        else:
+            cur = g.run_stage(fn, cur)
     return cur[0], g
 
 
@@ -182,21 +217,26 @@ def forward_backward_overlapped(fwd: StagedMoELayer, hidden: torch.Tensor, bwd_g
     st = streams or _Streams(hidden.device)
     f_attn, f_disp, f_exp, f_comb = fwd.functions(**attn_kw)
     g = LayerGraph()
+    # In every slot the piece that never blocks the host is queued first.  F.dispatch reads the split sizes back to the
+    # host; queued after B.experts, that wait is spent while the GPU runs B.experts.
     # slot 1: F.attention on compute | B.combine on comm
-    gb = st.on_comm(lambda: bwd_graph.backward_stage((grad_out,)))
+    gb = st.on_comm(lambda: bwd_graph.backward_stage((grad_out,)), (grad_out,))
     cur = g.run_stage(f_attn, (hidden,))
     st.join()
     # slot 2: B.experts on compute | F.dispatch on comm
-    cur2 = st.on_comm(lambda: g.run_stage(f_disp, cur))
-    gb = bwd_graph.backward_stage(gb)
+    ev = st.mark()                       # everything both pieces need is complete here; B.experts must not delay F.dispatch
+    gb_e = bwd_graph.backward_stage(gb)
+    cur2 = st.on_comm(lambda: g.run_stage(f_disp, cur), cur, after=ev)
     st.join()
     # slot 3: F.experts on compute | B.dispatch on comm
-    gb2 = st.on_comm(lambda: bwd_graph.backward_stage(gb))
+    ev = st.mark()
     cur3 = g.run_stage(f_exp, cur2)
+    gb2 = st.on_comm(lambda: bwd_graph.backward_stage(gb_e), gb_e, after=ev)
     st.join()
     # slot 4: B.attention on compute | F.combine on comm
-    out = st.on_comm(lambda: g.run_stage(f_comb, cur3))
+    ev = st.mark()
     gin = bwd_graph.backward_stage(gb2)
+    out = st.on_comm(lambda: g.run_stage(f_comb, cur3), cur3, after=ev)
     st.join()
     return out[0], g, gin[0]
 
@@ -233,3 +273,61 @@ def run_microbatches_overlapped(layers: Sequence, inputs: List[torch.Tensor], gr
         grad = backward_layer_staged(g, grad)
     gins[n - 1] = grad
     return outs, gins
+
+
+class BlockOverlap:
+    """Forward of micro-batch i through a stack of layers interleaved with the backward of micro-batch i-1, driven from
+    inside ``TransformerBlock.forward`` so that the ordinary ``forward_step`` / loss function stay unchanged.
+
+    Per micro-batch the block keeps the staged graphs of its layers, the (attached) block input and a detached leaf as
+    block output.  The loss backward of the schedule stops at that leaf; its ``.grad`` is the seed of the layer backward
+    that runs interleaved with the next micro-batch's forward (or alone in ``finish``).
+    reference: the 1F1B-overlap entry of mindspeed/core/transformer/moe/moe_feature/fb_overlap/overlap_funcs/fwdbwd.py:37-380
+    and its scheduling in vpp_schedules.py:300-990.
+    """
+
+    def __init__(self, layers: Sequence):
+        self.staged = [StagedMoELayer(l) for l in layers]
+        self.streams: Optional[_Streams] = None
+        self.prev = None          # (graphs, block input, output leaf) of the micro-batch whose backward is pending
+
+    def forward(self, hidden: torch.Tensor, **attn_kw) -> torch.Tensor:
+        if self.streams is None:
+            self.streams = _Streams(hidden.device)
+        graphs: List[LayerGraph] = []
+        h = hidden.detach()
+        if self.prev is None:
+            for s in self.staged:
+                h, g = forward_layer_staged(s, h, self.streams, **attn_kw)
+                graphs.append(g)
+        else:
+            p_graphs, p_in, p_leaf = self.prev
+            grad = p_leaf.grad
+            if grad is None:
+                raise RuntimeError("forward/backward overlap: the previous micro-batch's loss backward has not run")
+            n = len(self.staged)
+            for k, s in enumerate(self.staged):
+                h, g, grad = forward_backward_overlapped(s, h, p_graphs[n - 1 - k], grad, self.streams, **attn_kw)
+                graphs.append(g)
+            self._finish_input(p_in, grad)
+        leaf = h.detach().requires_grad_(True)
+        self.prev = (graphs, hidden, leaf)
+        return leaf
+
+    @staticmethod
+    def _finish_input(block_input, grad):
+        if isinstance(block_input, torch.Tensor) and block_input.requires_grad and grad is not None:
+            block_input.backward(grad)
+
+    def finish(self):
+        """Backward of the last micro-batch (nothing left to overlap with)."""
+        if self.prev is None:
+            return
+        graphs, p_in, p_leaf = self.prev
+        self.prev = None
+        grad = p_leaf.grad
+        if grad is None:
+            return
+        for g in reversed(graphs):
+            grad = backward_layer_staged(g, grad)
+        self._finish_input(p_in, grad)

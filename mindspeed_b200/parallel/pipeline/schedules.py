@@ -159,6 +159,9 @@ def forward_backward_no_pipelining(*, forward_step_func, data_iterator, model, n
     no_sync = _no_sync(model, config)
     store: List = []
     total_tokens = torch.zeros([], dtype=torch.int)
+    if getattr(config, "moe_fb_overlap", False) and not forward_only and num_microbatches > 1:
+        return _no_pipelining_fb_overlap(forward_step_func, data_iterator, model, num_microbatches, config, no_sync, store,
+                                         total_tokens, collect_non_loss_data)
     with no_sync():
         for i in range(num_microbatches - 1):
             out, nt = forward_step(forward_step_func, data_iterator, model, num_microbatches, None, store, config,
@@ -175,6 +178,36 @@ def forward_backward_no_pipelining(*, forward_step_func, data_iterator, model, n
         fin = getattr(config, "finalize_model_grads_func", None)
         if fin is not None:
             fin([model], total_tokens.to(out.device) if config.calculate_per_token_loss else None)
+    return store
+
+
+def _no_pipelining_fb_overlap(forward_step_func, data_iterator, model, num_microbatches, config, no_sync, store, total_tokens,
+                              collect_non_loss_data):
+    """``--moe-fb-overlap`` without pipeline parallelism: the layer stack runs micro-batch i's forward interleaved, stage
+    by stage, with micro-batch i-1's backward, so each all-to-all of one hides under the attention / expert compute of the
+    other (reference: mindspeed/core/transformer/moe/moe_feature/fb_overlap/overlap_funcs/fwdbwd.py:37-380).
+
+    The loss backward of a micro-batch only reaches the detached output of the layer stack; the stack's own backward is
+    run by the next forward (or by ``finish``).  Every backward except the last micro-batch's runs under ``no_sync``."""
+    from ...models.transformer import TransformerBlock
+    from ..moe.fb_overlap import BlockOverlap
+    block = next(m for m in model.modules() if isinstance(m, TransformerBlock))
+    block.fb_overlap = BlockOverlap(block.layers)
+    try:
+        with no_sync():
+            for i in range(num_microbatches):
+                out, nt = forward_step(forward_step_func, data_iterator, model, num_microbatches, None, store, config,
+                                       collect_non_loss_data, is_first_microbatch=(i == 0), current_microbatch=i)
+                total_tokens += nt.cpu() if torch.is_tensor(nt) else nt
+                if i < num_microbatches - 1:
+                    backward_step(None, out, None, None, config)
+        backward_step(None, out, None, None, config)
+        block.fb_overlap.finish()
+    finally:
+        block.fb_overlap = None
+    fin = getattr(config, "finalize_model_grads_func", None)
+    if fin is not None:
+        fin([model], total_tokens.to(out.device) if config.calculate_per_token_loss else None)
     return store
 
 

@@ -80,3 +80,29 @@ def test_layer_graph_stage_bookkeeping():
     (gx,) = g.backward_stage((ga, gb))
     assert g.stages_left == 0
     assert torch.allclose(gx, 2 * (x.detach() + 1) + 2 * x.detach())
+
+
+def _train_losses(rank, world, extra):
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import io
+    from contextlib import redirect_stdout
+    import pretrain_gpt as pg
+    from test_pipeline_cpu import BASE
+    from mindspeed_b200.training import pretrain
+    moe = ["--num-experts", "4", "--moe-router-topk", "2", "--moe-token-dispatcher-type", "alltoall", "--moe-grouped-gemm",
+           "--moe-aux-loss-coeff", "0.01", "--expert-model-parallel-size", str(world), "--use-distributed-optimizer"]
+    with redirect_stdout(io.StringIO()):
+        hist = pretrain(pg.train_valid_test_datasets_provider, pg.model_provider, forward_step_func=pg.forward_step,
+                        args_list=BASE + moe + list(extra))
+    return [h["lm loss"] for h in hist]
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_training_with_fb_overlap_matches_plain_schedule(world):
+    """``--moe-fb-overlap`` (micro-batch i's forward interleaved with micro-batch i-1's backward inside the layer stack)
+    gives the same losses as the plain schedule, with expert parallelism and the distributed optimizer."""
+    ref = run_distributed(_train_losses, world, [])[0]
+    got = run_distributed(_train_losses, world, ["--moe-fb-overlap"])[0]
+    assert len(ref) == 3
+    for a, b in zip(ref, got):
+        assert abs(a - b) < 1e-5 * max(1.0, abs(a)), (ref, got)

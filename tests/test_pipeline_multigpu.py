@@ -103,10 +103,11 @@ def _reference(extra=()):
     return _REF[key]
 
 
-def _close(a, b, tol):
+def _close(a, b, tol, decreasing=True):
     for x, y in zip(a, b):
         assert abs(x - y) < tol * max(1.0, abs(x)), (a, b)
-    assert b[-1] < b[0]
+    if decreasing:
+        assert b[-1] < b[0]
 
 
 @pytest.mark.parametrize("extra", [
@@ -134,4 +135,17 @@ def _ngpu():
 ])
 def test_pipeline_with_expert_parallel_follows_one_gpu(extra):
     n = 8 if _ngpu() >= 8 else 4
-    _close(_reference(MOE), _run(n, MOE + ["--expert-model-parallel-size", str(n // 2)] + extra, 29740), 0.03)
+    _close(_reference(MOE), _run(n, MOE + ["--expert-model-parallel-size", str(n // 2)] + extra, 29740), 0.01, decreasing=False)
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_moe_forward_backward_overlap_follows_one_gpu(overlap):
+    """Expert parallelism 2 with the fused dispatcher on two GPUs, plain and with ``--moe-fb-overlap`` (forward of one
+    micro-batch interleaved with the backward of the previous one on two streams): the loss follows the one-GPU run."""
+    extra = MOE + ["--expert-model-parallel-size", "2", "--moe-alltoall-mc2"] + (["--moe-fb-overlap"] if overlap else [])
+    ref, got = _reference(MOE), _run(2, extra, 29750 + int(overlap))
+    log_dir = os.environ.get("MSB200_TEST_LOG_DIR")
+    if log_dir:
+        with open(os.path.join(log_dir, f"moe_fb_overlap_{int(overlap)}.json"), "w") as f:
+            json.dump({"ref": ref, "got": got}, f)
+    _close(ref, got, 0.01, decreasing=False)      # four steps of a freshly initialised router do not lower the loss yet
