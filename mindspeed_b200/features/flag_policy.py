@@ -64,7 +64,6 @@ UNSUPPORTED: Dict[str, str] = {
     "moe-model-type": "the DeepSpeed-style MoE is selected through mindspeed_b200.legacy_moe, not through this flag",
     "moe-bmm-mc2": "use --moe-alltoall-mc2 (peer-memory dispatch / combine) with --moe-grouped-gemm",
     "moe-unperm2-mem-optim-swap": "host swap of the unpermute buffer is not implemented; use --moe-zero-memory",
-    "use-multiparameter-pipeline-model-parallel": "pipeline stages exchange one tensor; multi-tensor stage interfaces are not implemented",
     "quant-grads": "quantised gradient buffers are not implemented (quantised optimizer states: --quant-states)",
     "compress-activation": "activation compression is available as a codec (ops/compress.py) but not wired into recompute / swap",
     "compress-optimizer": "optimizer-state compression is available as a codec (ops/compress.py) but not wired into the step",

@@ -231,7 +231,10 @@ class ContextParallelFeature(Feature):
         g = parser.add_argument_group(title=self.feature_name)
         add_arg(g, "--context-parallel-algo", type=str, default="megatron_cp_algo",
                 choices=["megatron_cp_algo", "ulysses_cp_algo", "hybrid_cp_algo", "hybrid_adaptive_cp_algo",
-                         "adaptive_cp_algo", "kvallgather_cp_algo"])
+                         "adaptive_cp_algo", "kvallgather_cp_algo", "hamilton_cp_algo"])
+        add_arg(g, "--hamilton-path-num", type=int, default=0,
+                help="hamilton_cp_algo: number of edge-disjoint cycles the KV block is split over (0: as many as the "
+                     "context-parallel size allows)")
         add_arg(g, "--cp-window-size", type=int, default=1)
         add_arg(g, "--attention-mask-type", type=str, default="causal", choices=["causal", "general"])
         add_arg(g, "--use-cp-send-recv-overlap", action="store_true")
@@ -279,6 +282,15 @@ class ContextParallelFeature(Feature):
                 raise AssertionError("hybrid context parallel needs seq_length divisible by 2 * cp")
         if algo == "kvallgather_cp_algo" and args.attention_mask_type != "causal":
             raise AssertionError("KV-allgather context parallel supports causal attention only")
+        if algo == "hamilton_cp_algo":
+            if args.attention_mask_type == "causal":
+                raise AssertionError("Hamilton context parallel supports full attention only (--attention-mask-type general)")
+            import math
+            paths = sum(1 for s_ in range(1, cp) if math.gcd(s_, cp) == 1)
+            if not (0 <= args.hamilton_path_num <= paths):
+                raise AssertionError(f"--hamilton-path-num must be within 0..{paths} for context parallel size {cp}")
+            if seq % cp != 0:
+                raise AssertionError("Hamilton context parallel needs seq_length divisible by cp")
 
 
 class FlashAttentionFeature(Feature):
@@ -378,6 +390,15 @@ class PipelineMiscFeature(Feature):
         add_arg(g, "--recompute-module-list", type=str, default=None)
 
     def validate_args(self, args):
+        if args.use_multiparameter_pipeline_model_parallel and not getattr(args, "pipeline_tensor_shapes", None):
+            # a model whose stages hand over several tensors sets args.pipeline_tensor_shapes itself; the default is the
+            # one hidden-state tensor (reference: mindspeed/features_manager/pipeline_parallel/multi_parameter.py:38-52)
+            import torch
+            s_ = args.seq_length // max(1, getattr(args, "context_parallel_size", 1))
+            if getattr(args, "sequence_parallel", False):
+                s_ //= args.tensor_model_parallel_size
+            dt = torch.bfloat16 if getattr(args, "bf16", False) else torch.float16 if getattr(args, "fp16", False) else torch.float32
+            args.pipeline_tensor_shapes = [{"shape": (s_, args.micro_batch_size, args.hidden_size), "dtype": dt}]
         if args.recompute_in_bubble and args.recompute_in_advance:
             raise AssertionError("--recompute-in-bubble and --recompute-in-advance are exclusive")
         if (args.recompute_in_bubble or args.recompute_in_advance):

@@ -1,4 +1,4 @@
-"""Context parallelism: ring (double ring), Ulysses, hybrid, KV-allgather, adaptive.
+"""Context parallelism: ring (double ring), Ulysses, hybrid, KV-allgather, adaptive, Hamilton (multi-cycle ring).
 
 ``dispatch_context_parallel_attention`` is the single entry used by the attention module
 (reference: mindspeed/core/context_parallel/dot_product_attention.py:134-322).
@@ -24,6 +24,9 @@ def dispatch_context_parallel_attention(q, k, v, config, causal=True, softmax_sc
     if algo == "kvallgather_cp_algo":
         from .kvallgather import kv_allgather_attention
         return kv_allgather_attention(q, k, v, config, softmax_scale=softmax_scale)
+    if algo == "hamilton_cp_algo":
+        from .hamilton import hamilton_attention
+        return hamilton_attention(q, k, v, config, causal=causal, softmax_scale=softmax_scale)
     if algo in ("adaptive_cp_algo", "hybrid_adaptive_cp_algo"):
         from .adaptive import adaptive_attention
         return adaptive_attention(q, k, v, config, attention_mask, softmax_scale=softmax_scale)

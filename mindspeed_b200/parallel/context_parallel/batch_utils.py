@@ -40,7 +40,7 @@ def slice_for_cp(val, seq_dim, algo, cp=None, r=None):
         ring, rr = ps.get_context_parallel_for_hybrid_ring_world_size(), ps.get_context_parallel_for_hybrid_ring_rank()
         v = _ring_slice(val, seq_dim, ring, rr)
         return _contig_slice(v, seq_dim, u, ur)
-    if algo in ("adaptive_cp_algo",):
+    if algo in ("adaptive_cp_algo", "hamilton_cp_algo"):       # full attention: no causal balancing, contiguous slices
         return _contig_slice(val, seq_dim, cp, r)
     return _ring_slice(val, seq_dim, cp, r)  # megatron_cp_algo, kvallgather (2-chunk, causal balanced)
 

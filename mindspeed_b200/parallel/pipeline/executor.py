@@ -85,9 +85,19 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
     rank = ps.get_pipeline_model_parallel_rank()
     pl = plan.placement
     Sn = pl.num_stages
-    shape = S.get_tensor_shapes(seq_length=seq_length, micro_batch_size=micro_batch_size, config=config)[0]
+    # what crosses a stage boundary: one [s, b, h] tensor, or the list given by ``config.pipeline_tensor_shapes``
+    # (--use-multiparameter-pipeline-model-parallel).  Internally a payload is always a list; gradients exist for its
+    # floating-point entries only.
+    specs = S.get_tensor_specs(seq_length=seq_length, micro_batch_size=micro_batch_size, config=config)
+    multi = S.is_multi_parameter(config)
+    gspecs = [sp for sp in specs if sp[1].is_floating_point]
     dev = next(model[0].parameters()).device
-    dtype = config.pipeline_dtype
+
+    def specs_of(m):
+        return specs if m.kind == "act" else gspecs
+
+    def unwrap(payload):
+        return payload if multi else payload[0]
     has_w = any(op.kind == "W" for ops in plan.table[rank] for op in ops)
     lazy = {(op.chunk, op.mb) for ops in plan.table[rank] for op in ops if op.kind == "R"}   # forwards that drop activations
     stash: Dict[Tuple[int, int], tuple] = {}
@@ -123,26 +133,33 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
     pending_send: List[tuple] = []
     grad_pool: List[torch.Tensor] = []
 
+    def new_bufs(m):
+        if m.kind == "grad" and grad_pool and not multi:
+            return [grad_pool.pop()]
+        return [torch.empty(sh, dtype=dt, device=dev) for sh, dt in specs_of(m)]
+
     def post_recvs(t):
         lst = []
         for m in msgs(plan.recvs, t):
-            buf = grad_pool.pop() if (m.kind == "grad" and grad_pool) else torch.empty(shape, dtype=dtype, device=dev)
-            lst.append((m, buf, dist.irecv(buf, pp_ranks[m.src], group=comm_of(m))))
+            bufs = new_bufs(m)
+            lst.append((m, bufs, [dist.irecv(b, pp_ranks[m.src], group=comm_of(m)) for b in bufs]))
         pending_recv[t] = lst
 
     def post_sends(t):
         for m in msgs(plan.sends, t):
-            ten = outbox.pop((m.kind, m.src_chunk, m.mb)).contiguous()
-            pending_send.append((dist.isend(ten, pp_ranks[m.dst], group=comm_of(m)), ten))   # keep the tensor alive
+            for ten in outbox.pop((m.kind, m.src_chunk, m.mb)):
+                ten = ten.contiguous()
+                pending_send.append((dist.isend(ten, pp_ranks[m.dst], group=comm_of(m)), ten))   # keep the tensor alive
 
     try:
         if overlap:
             post_recvs(0)
         for t in range(plan.num_slots):
             if overlap:
-                for m, buf, req in pending_recv.pop(t):
-                    req.wait()
-                    inbox[(m.kind, m.dst_chunk, m.mb)] = buf
+                for m, bufs, reqs in pending_recv.pop(t):
+                    for req in reqs:
+                        req.wait()
+                    inbox[(m.kind, m.dst_chunk, m.mb)] = bufs
                 if t + 1 < plan.num_slots:
                     post_recvs(t + 1)            # flies while this slot computes here and the slot before it on the peer
                 while pending_send and pending_send[0][0].is_completed():
@@ -153,12 +170,13 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
                 allm = sorted(sends + recvs, key=key)
                 for m in allm:
                     if m.src == rank and m in sends:
-                        ten = outbox.pop((m.kind, m.src_chunk, m.mb))
-                        ops.append(dist.P2POp(dist.isend, ten.contiguous(), pp_ranks[m.dst], pp_group))
+                        for ten in outbox.pop((m.kind, m.src_chunk, m.mb)):
+                            ops.append(dist.P2POp(dist.isend, ten.contiguous(), pp_ranks[m.dst], pp_group))
                     else:
-                        buf = torch.empty(shape, dtype=dtype, device=dev)
-                        bufs.append((m, buf))
-                        ops.append(dist.P2POp(dist.irecv, buf, pp_ranks[m.src], pp_group))
+                        got = [torch.empty(sh, dtype=dt, device=dev) for sh, dt in specs_of(m)]
+                        bufs.append((m, got))
+                        for buf in got:
+                            ops.append(dist.P2POp(dist.irecv, buf, pp_ranks[m.src], pp_group))
                 if ops:
                     for r in dist.batch_isend_irecv(ops):
                         r.wait()
@@ -176,7 +194,10 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
                     inp = None
                     if stage > 0:
                         inp = inbox.pop(("act", op.chunk, op.mb))
-                        inp.requires_grad_(not forward_only)
+                        for x in inp:
+                            if x.is_floating_point():
+                                x.requires_grad_(not forward_only)
+                        inp = unwrap(inp)
                     drop = (op.chunk, op.mb) in lazy and not forward_only
                     if drop:
                         # RiPipe: run without building a graph, remember (input, batch, RNG) for the R op
@@ -195,10 +216,11 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
                         outputs[(op.chunk, op.mb)] = out
                     if stage < Sn - 1:
                         dr, dc = pl.holder(pipe, stage + 1)
+                        outs = list(out) if isinstance(out, (list, tuple)) else [out]
                         if dr == rank:
-                            inbox[("act", dc, op.mb)] = out.detach().clone()
+                            inbox[("act", dc, op.mb)] = [o.detach().clone() for o in outs]
                         else:
-                            outbox[("act", op.chunk, op.mb)] = out.detach()
+                            outbox[("act", op.chunk, op.mb)] = [o.detach() for o in outs]
                 elif op.kind == "R":
                     inp, batches, rng = stash.pop((op.chunk, op.mb))
                     now = _rng_capture()
@@ -214,18 +236,19 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
                     og = None if stage == Sn - 1 else inbox.pop(("grad", op.chunk, op.mb))
                     if has_w:
                         WeightGradStore.enable(True)
-                    g = S.backward_step(inp, out, og, None, config)
-                    if overlap and og is not None and og.is_leaf and not og.requires_grad:
-                        grad_pool.append(og)     # the received output gradient has been consumed: reuse its storage
+                    g = S.backward_step(inp, out, None if og is None else unwrap(og), None, config)
+                    if overlap and not multi and og is not None and og[0].is_leaf and not og[0].requires_grad:
+                        grad_pool.append(og[0])  # the received output gradient has been consumed: reuse its storage
                     if has_w:
                         WeightGradStore.flush()
                         WeightGradStore.enable(False)
                     if stage > 0:
                         dr, dc = pl.holder(pipe, stage - 1)
+                        gl = list(g) if isinstance(g, (list, tuple)) else [g]
                         if dr == rank:
-                            inbox[("grad", dc, op.mb)] = g
+                            inbox[("grad", dc, op.mb)] = gl
                         else:
-                            outbox[("grad", op.chunk, op.mb)] = g
+                            outbox[("grad", op.chunk, op.mb)] = gl
                 else:  # W
                     WeightGradStore.pop()
             if overlap and t + 1 < plan.num_slots:

@@ -115,8 +115,46 @@ def forward_step(forward_step_func, data_iterator, model, num_microbatches, inpu
     return output_tensor, num_tokens
 
 
+def is_multi_parameter(config) -> bool:
+    return bool(getattr(config, "use_multiparameter_pipeline_model_parallel", False)) and \
+        bool(getattr(config, "pipeline_tensor_shapes", None))
+
+
+def get_tensor_specs(*, seq_length, micro_batch_size, config):
+    """[(shape, dtype)] of what one stage hands to the next: the [s, b, h] hidden state, or with
+    ``--use-multiparameter-pipeline-model-parallel`` the entries of ``config.pipeline_tensor_shapes``
+    ([{"shape": ..., "dtype": ...}], reference: mindspeed/features_manager/pipeline_parallel/multi_parameter.py:38-52)."""
+    if is_multi_parameter(config):
+        return [(tuple(d["shape"]), d["dtype"]) for d in config.pipeline_tensor_shapes]
+    shape = get_tensor_shapes(seq_length=seq_length, micro_batch_size=micro_batch_size, config=config)[0]
+    return [(shape, config.pipeline_dtype)]
+
+
+def _backward_step_multi(inputs, outputs, output_grads, config):
+    """Stage backward when the stage interface is a list of tensors: gradients flow through the floating-point entries
+    (reference: mindspeed/core/pipeline_parallel/multiparameter_schedules.py:46-108)."""
+    ins = [] if inputs is None else (list(inputs) if isinstance(inputs, (list, tuple)) else [inputs])
+    outs = list(outputs) if isinstance(outputs, (list, tuple)) else [outputs]
+    for x in ins:
+        if x.is_floating_point() and x.requires_grad:
+            x.retain_grad()
+    if output_grads is None:
+        loss = outs[0]
+        if getattr(config, "grad_scale_func", None) is not None:
+            loss = config.grad_scale_func(loss)
+        loss.backward()
+    else:
+        grads = list(output_grads) if isinstance(output_grads, (list, tuple)) else [output_grads]
+        fouts = [o for o in outs if o.is_floating_point()]
+        pairs = [(o, g) for o, g in zip(fouts, grads) if o.requires_grad]
+        torch.autograd.backward([p[0] for p in pairs], [p[1] for p in pairs])
+    return [x.grad if x.grad is not None else torch.zeros_like(x) for x in ins if x.is_floating_point()]
+
+
 def backward_step(input_tensor, output_tensor, output_tensor_grad, model_type, config):
     """Backward of one micro-batch; returns the gradient w.r.t. the stage input (None on the first stage)."""
+    if isinstance(input_tensor, (list, tuple)) or isinstance(output_tensor, (list, tuple)):
+        return _backward_step_multi(input_tensor, output_tensor, output_tensor_grad, config)
     if input_tensor is not None and input_tensor.requires_grad:
         input_tensor.retain_grad()
     if output_tensor_grad is None and getattr(config, "grad_scale_func", None) is not None:
@@ -222,6 +260,14 @@ def forward_backward_pipelining_without_interleaving(*, forward_step_func, data_
                                                      seq_length, micro_batch_size, decoder_seq_length=None,
                                                      forward_only=False, collect_non_loss_data=False, first_val_step=None):
     """Non-interleaved 1F1B: warm-up forwards, steady 1F1B, cool-down backwards."""
+    if is_multi_parameter(_cfg(model)):
+        # list-valued stage interfaces are handled by the plan executor (same 1F1B order, as data)
+        from .executor import run_plan
+        from .interleaved import _plan
+        plan = _plan("1f1b", ps.get_pipeline_model_parallel_world_size(), num_microbatches)
+        return run_plan(plan, forward_step_func=forward_step_func, data_iterator=data_iterator, model=model,
+                        num_microbatches=num_microbatches, seq_length=seq_length, micro_batch_size=micro_batch_size,
+                        forward_only=forward_only, collect_non_loss_data=collect_non_loss_data)
     if isinstance(model, list):
         model = model[0]
     if isinstance(data_iterator, list):

@@ -36,6 +36,7 @@ def _run(rank, world, algo, nq, nkv, causal, extra):
     cfg.context_parallel_kv_cache_policy = extra.get("cache")
     cfg.context_parallel_cache_interval = 0
     cfg.use_ulysses_allgather_kv = bool(extra.get("allgather_kv", False))
+    cfg.hamilton_path_num = extra.get("paths", 0)
     s, b, d = 32 * world, 2, 16
     q, k, v, w = _full(3, s, b, nq, nkv, d)
     qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
@@ -64,6 +65,10 @@ def _run(rank, world, algo, nq, nkv, causal, extra):
     ("ulysses_cp_algo", 2, 4, 1, True, {"allgather_kv": True}),
     ("kvallgather_cp_algo", 2, 4, 2, True, {}),
     ("hybrid_cp_algo", 4, 4, 4, True, {}),
+    # Hamilton: the KV block split over edge-disjoint cycles (strides coprime to the group size), full attention
+    ("hamilton_cp_algo", 4, 4, 2, False, {}),                  # 4 ranks: strides 1 and 3
+    ("hamilton_cp_algo", 5, 4, 4, False, {"paths": 4}),        # 5 ranks: strides 1, 2, 3, 4
+    ("hamilton_cp_algo", 3, 2, 1, False, {"paths": 1}),        # one path = a plain ring
 ])
 def test_cp_attention_matches_full(algo, world, nq, nkv, causal, extra):
     for r in run_distributed(_run, world, algo, nq, nkv, causal, extra):
@@ -125,3 +130,21 @@ def test_adaptive_cp_host_algorithms():
     order = search_kmeans(c2, 2)
     assert sorted(order) == list(range(8))
     assert len({int(fam[i]) for i in order[:4]}) == 1 and len({int(fam[i]) for i in order[4:]}) == 1
+
+
+def test_hamilton_cycles_are_hamiltonian_and_edge_disjoint():
+    from mindspeed_b200.parallel.context_parallel.hamilton import hamilton_strides, max_paths
+    for n in (2, 3, 4, 5, 8, 12):
+        strides = hamilton_strides(n, max_paths(n))
+        edges = set()
+        for s in strides:
+            seen, r = set(), 0
+            for _ in range(n):
+                seen.add(r)
+                e = (r, (r + s) % n)
+                assert e not in edges
+                edges.add(e)
+                r = (r + s) % n
+            assert len(seen) == n and r == 0        # visits every rank once and closes
+    with pytest.raises(ValueError):
+        hamilton_strides(8, 5)                      # 8 ranks have 4 such cycles

@@ -149,6 +149,8 @@ def _train(rank, world, extra, bidirectional):
     (2, ["--pipeline-model-parallel-size", "2", "--num-layers-per-virtual-pipeline-stage", "1"], False),
     (2, ["--pipeline-model-parallel-size", "2", "--schedules-method", "dualpipev"], False),
     (2, ["--pipeline-model-parallel-size", "2", "--recompute-in-bubble"], False),
+    # list-valued stage interface with its default content (the one hidden-state tensor), through the plan executor
+    (2, ["--pipeline-model-parallel-size", "2", "--use-multiparameter-pipeline-model-parallel"], False),
     (2, ["--pipeline-model-parallel-size", "2", "--num-layers-per-virtual-pipeline-stage", "1", "--recompute-in-advance"], False),
     (2, ["--pipeline-model-parallel-size", "2", "--schedules-method", "chimera"], True),
     (2, ["--pipeline-model-parallel-size", "2", "--schedules-method", "dualpipe"], True),
@@ -167,3 +169,78 @@ def test_pipeline_matches_no_pipeline(world, extra, bidir):
     got = [sum(v) / len(v) for v in zip(*have)] if bidir else have[0]
     for a, b in zip(ref, got):
         assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (ref, got)
+
+
+def _multi_param(rank, world, overlap):
+    """Two stages that hand over (hidden, side tensor, integer positions): gradients of both floating tensors return."""
+    import torch.distributed as dist
+    import torch.nn as nn
+    from mindspeed_b200.config import TransformerConfig
+    from mindspeed_b200.parallel import parallel_state as ps
+    from mindspeed_b200.parallel.pipeline.schedules import get_forward_backward_func
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ps.initialize_model_parallel(pipeline_model_parallel_size=world, optimize_send_recv_comm=overlap)
+    cfg = TransformerConfig(num_layers=2, hidden_size=8, num_attention_heads=2, use_cpu_initialization=True, optimization_level=0,
+                            pipeline_model_parallel_size=world)
+    cfg.pipeline_dtype = torch.float32
+    cfg.use_multiparameter_pipeline_model_parallel = True
+    cfg.overlap_p2p_comm = overlap
+    cfg.pipeline_tensor_shapes = [{"shape": (4, 3), "dtype": torch.float32}, {"shape": (4, 2), "dtype": torch.float32},
+                                  {"shape": (4,), "dtype": torch.int64}]
+    torch.manual_seed(0)
+    lin0, lin_a, lin1, emb = nn.Linear(5, 3), nn.Linear(5, 2), nn.Linear(3, 2), nn.Embedding(7, 2)
+
+    class Stage(nn.Module):
+        def __init__(self, first):
+            super().__init__()
+            self.config, self.first, self.inp = cfg, first, None
+            if first:
+                self.lin0, self.lin_a = lin0, lin_a
+            else:
+                self.lin1, self.emb = lin1, emb
+
+        def set_input_tensor(self, t):
+            self.inp = t
+
+        def forward(self, x, pos):
+            if self.first:
+                return self.lin0(x), torch.tanh(self.lin_a(x)), pos
+            h, side, p = self.inp
+            return ((self.lin1(h) + self.emb(p)) * side).sum()
+
+    data = [(torch.randn(4, 5, generator=torch.Generator().manual_seed(10 + i)), torch.arange(4) + i % 3) for i in range(4)]
+
+    def step(it, model):
+        x, pos = next(it)
+        out = model(x, pos)
+        return out, (lambda o: (o, {"l": o.detach()}))
+
+    # one-process oracle on the same parameters
+    ref = {}
+    for x, pos in data:
+        l = ((lin1(lin0(x)) + emb(pos)) * torch.tanh(lin_a(x))).sum() / len(data)
+        l.backward()
+    for n, m in (("lin0", lin0), ("lin_a", lin_a), ("lin1", lin1), ("emb", emb)):
+        ref[n] = m.weight.grad.clone()
+        m.zero_grad()
+    model = Stage(first=(rank == 0))
+    fb = get_forward_backward_func()
+    store = fb(forward_step_func=step, data_iterator=iter(data), model=[model], num_microbatches=len(data), seq_length=4,
+               micro_batch_size=1, forward_only=False)
+    errs = {}
+    for n in (("lin0", "lin_a") if rank == 0 else ("lin1", "emb")):
+        errs[n] = (getattr(model, n).weight.grad - ref[n]).abs().max().item()
+    ps.destroy_model_parallel()
+    dist.destroy_process_group()
+    return errs, len(store)
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_multi_parameter_stage_interface(overlap):
+    """``--use-multiparameter-pipeline-model-parallel``: stages exchange a list of tensors described by
+    ``pipeline_tensor_shapes``; integer entries travel forward only."""
+    res = run_distributed(_multi_param, 2, overlap)
+    for errs, _ in res:
+        for n, e in errs.items():
+            assert e < 1e-5, (n, e)
+    assert res[1][1] == 4 and res[0][1] == 0        # losses are collected on the last stage
