@@ -84,10 +84,6 @@ UNSUPPORTED: Dict[str, str] = {
     "use-fused-sparse-flash-attention": "sparse flash attention is not implemented",
     "kl-loss-reduction": "only used by the lightning-indexer KL loss, which is not wired into training",
     "fix-sub-seq-length": "fixed-length sub-sequence packing for EOD-reset CP is not implemented",
-    "moe-allgather-overlap-comm": "overlap is implemented for the alltoall dispatcher (--moe-alltoall-overlap-comm)",
-    "balanced-moe-experts": "hot-expert replication helpers exist (parallel/moe/expert_placement.py) but are not driven by the training loop",
-    "balanced-moe-hot-expert-num": "hot-expert replication helpers exist (parallel/moe/expert_placement.py) but are not driven by the training loop",
-    "trans-hot-expert-group-num": "hot-expert replication helpers exist (parallel/moe/expert_placement.py) but are not driven by the training loop",
     "enable-fine-grained-expert-placement": "only whole-expert placement is implemented (--enable-expert-placement)",
     "fine-grained-expert-placement-thre": "only whole-expert placement is implemented (--enable-expert-placement)",
     "data-path": "indexed datasets are built with mindspeed_b200.data_tools and passed to a custom provider; pretrain_gpt.py reads synthetic data",

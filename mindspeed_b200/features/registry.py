@@ -471,6 +471,16 @@ class MoEFeature(Feature):
                 raise AssertionError("the overlapped / fused alltoall dispatcher needs --moe-grouped-gemm")
             if getattr(args, "moe_token_dispatcher_type", "alltoall") not in ("alltoall", "alltoall_seq"):
                 raise AssertionError("alltoall overlap needs --moe-token-dispatcher-type alltoall")
+        if args.balanced_moe_experts:
+            if getattr(args, "expert_model_parallel_size", 1) <= 1 or not getattr(args, "moe_grouped_gemm", False):
+                raise AssertionError("--balanced-moe-experts needs expert parallel size > 1 and --moe-grouped-gemm")
+            if args.moe_alltoall_mc2:
+                raise AssertionError("--balanced-moe-experts leaves tokens with fewer than top-k remote experts; the fused "
+                                     "dispatcher (--moe-alltoall-mc2) needs exactly top-k per token")
+            if ne and not (0 < args.balanced_moe_hot_expert_num <= ne):
+                raise AssertionError("--balanced-moe-hot-expert-num must be within 1..num_experts")
+        if args.moe_allgather_overlap_comm and getattr(args, "moe_token_dispatcher_type", "alltoall") != "allgather":
+            raise AssertionError("--moe-allgather-overlap-comm needs --moe-token-dispatcher-type allgather")
         if args.moe_fb_overlap:
             if getattr(args, "moe_token_dispatcher_type", "") != "alltoall" or not getattr(args, "moe_grouped_gemm", False):
                 raise AssertionError("--moe-fb-overlap needs the alltoall dispatcher and grouped GEMM")

@@ -51,11 +51,16 @@ class GroupedMLP(nn.Module):
 
     def forward(self, permuted_tokens, tokens_per_expert, permuted_probs=None):
         """permuted_tokens [R, H] sorted by local expert; tokens_per_expert [E_local] (host list or tensor)."""
+        return self.run(permuted_tokens, tokens_per_expert, permuted_probs, self.weight1, self.weight2), None
+
+    def run(self, permuted_tokens, tokens_per_expert, permuted_probs, weight1, weight2):
+        """The expert MLP on explicit stacked weights [n, H, F1] / [n, F, H] (the module's own, or replicas of other
+        ranks' experts)."""
         if permuted_tokens.shape[0] == 0:
             # keep the parameters in the graph so data-parallel reduction sees zero gradients
-            z = (self.weight1.sum() + self.weight2.sum()) * 0
-            return permuted_tokens + z.to(permuted_tokens.dtype), None
-        h = grouped_gemm(permuted_tokens, self.weight1, tokens_per_expert, trans_b=False)
+            z = (weight1.sum() + weight2.sum()) * 0
+            return permuted_tokens + z.to(permuted_tokens.dtype)
+        h = grouped_gemm(permuted_tokens, weight1, tokens_per_expert, trans_b=False)
         if self.config.gated_linear_unit and self.config.activation_func is F.silu:
             a = swiglu(h, permuted_probs, fused=self.fused)
         else:
@@ -66,8 +71,7 @@ class GroupedMLP(nn.Module):
                 a = self.config.activation_func(h)
             if permuted_probs is not None:
                 a = a * permuted_probs.unsqueeze(-1).to(a.dtype)
-        out = grouped_gemm(a, self.weight2, tokens_per_expert, trans_b=False)
-        return out, None
+        return grouped_gemm(a, weight2, tokens_per_expert, trans_b=False)
 
 
 class SequentialMLP(nn.Module):

@@ -29,7 +29,9 @@ class MoELayer(nn.Module):
         overlap = bool(getattr(config, "moe_alltoall_overlap_comm", False))
         fused = bool(getattr(config, "moe_alltoall_mc2", False)) and config.optimization_level >= 2
         if kind == "allgather":
-            self.token_dispatcher = MoEAllGatherTokenDispatcher(self.num_local_experts, self.local_expert_indices, config)
+            self.token_dispatcher = MoEAllGatherTokenDispatcher(self.num_local_experts, self.local_expert_indices, config,
+                                                                overlap=bool(getattr(config, "moe_allgather_overlap_comm", False)))
+            overlap = overlap or self.token_dispatcher.overlap
         elif kind in ("alltoall", "alltoall_seq"):
             if fused and torch.cuda.is_available():
                 from .fused_dispatcher import FusedAlltoAllTokenDispatcher
@@ -44,12 +46,21 @@ class MoELayer(nn.Module):
             self.shared_experts = SharedExpertMLP(config)
         self.shared_overlap = bool(config.moe_shared_expert_overlap or overlap)
         self._side = None
+        # --balanced-moe-experts: the busiest experts are replicated on every expert-parallel rank for one step at a time;
+        # their tokens never leave the rank (reference: moe_feature/balanced_moe/modules/moe_layer.py, token_dispatcher.py)
+        self.balanced = bool(getattr(config, "balanced_moe_experts", False)) and ep > 1 and bool(config.moe_grouped_gemm)
+        self.hot_k = int(getattr(config, "balanced_moe_hot_expert_num", 3) or 0)
+        self.hot_groups = int(getattr(config, "trans_hot_expert_group_num", 1) or 1)
+        self.hot_experts = []
+        self._load = None
         self.zero_memory = getattr(config, "moe_zero_memory", "disable")
         n_zm = getattr(config, "moe_zero_memory_num_layers", None)
         if n_zm is not None and layer_number > n_zm:
             self.zero_memory = "disable"       # --moe-zero-memory-num-layers: only the first N MoE layers of a stage trade recompute for memory
 
     def _forward(self, hidden_states):
+        if hasattr(self.token_dispatcher, "pre_gather"):
+            self.token_dispatcher.pre_gather(hidden_states)      # in flight while the router computes
         probs, routing_map = self.router(hidden_states)
         shared = None
         if self.shared_experts is not None and self.shared_overlap and hidden_states.is_cuda:
@@ -58,9 +69,18 @@ class MoELayer(nn.Module):
             self._side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self._side):
                 shared = self.shared_experts(hidden_states)
+        hot_out = None
+        if self.balanced:
+            with torch.no_grad():
+                cnt = routing_map.sum(0).float()
+                self._load = cnt if self._load is None else self._load + cnt
+            if self.hot_experts:
+                probs, routing_map, hot_out = self._hot_path(hidden_states, probs, routing_map)
         dispatched, tokens_per_expert, pprobs = self.token_dispatcher.token_permutation(hidden_states, probs.to(hidden_states.dtype), routing_map)
         expert_out, _ = self.experts(dispatched, tokens_per_expert, pprobs)
         out, _ = self.token_dispatcher.token_unpermutation(expert_out)
+        if hot_out is not None:
+            out = out + hot_out
         if self.shared_experts is not None:
             if shared is None:
                 shared = self.shared_experts(hidden_states)
@@ -68,6 +88,36 @@ class MoELayer(nn.Module):
                 torch.cuda.current_stream().wait_stream(self._side)
             out = out + shared
         return out
+
+    def _hot_path(self, hidden_states, probs, routing_map):
+        """Tokens routed to a hot expert are computed here with a replica of its weights; returns the routing that is left
+        for the dispatcher and the hot experts' contribution to the output."""
+        from .expert_placement import replicate_hot_experts, split_hot_routing
+        from .moe_utils import permute, unpermute
+        hot = self.hot_experts
+        cold_map, cold_probs, hot_map, hot_probs = split_hot_routing(routing_map, probs, hot)
+        ep_group = ps.get_expert_model_parallel_group()
+        w1 = replicate_hot_experts(self.experts.weight1, self.local_expert_indices, hot, ep_group, self.hot_groups)
+        w2 = replicate_hot_experts(self.experts.weight2, self.local_expert_indices, hot, ep_group, self.hot_groups)
+        h = hidden_states.reshape(-1, hidden_states.shape[-1])
+        rows, order = permute(h, hot_map)
+        row_probs = hot_probs.t().contiguous().masked_select(hot_map.t().contiguous()).to(h.dtype)
+        y = self.experts.run(rows, hot_map.sum(0).cpu(), row_probs, w1, w2)
+        hot_out = unpermute(y, order, h.shape).view(hidden_states.shape)
+        return cold_probs, cold_map, hot_out
+
+    def refresh_hot_experts(self):
+        """Once per optimizer step: choose the ``balanced_moe_hot_expert_num`` busiest experts of the step that just ended
+        (token counts summed over the expert-parallel group, so every rank picks the same set)."""
+        if not self.balanced or self._load is None:
+            return self.hot_experts
+        import torch.distributed as dist
+        from .expert_placement import select_hot_experts
+        load = self._load.clone()
+        dist.all_reduce(load, group=ps.get_expert_model_parallel_group())
+        self.hot_experts = select_hot_experts(load, min(self.hot_k, load.numel())) if self.hot_k > 0 else []
+        self._load = None
+        return self.hot_experts
 
     def forward(self, hidden_states):
         if self.training and (self.config.moe_layer_recompute or self.zero_memory != "disable"):

@@ -35,21 +35,61 @@ class MoETokenDispatcher:
         self.shared_experts = se
 
 
+class _GatherRowsAsync(torch.autograd.Function):
+    """All-gather along dim 0 that returns before the collective has finished: the caller keeps the work handle and
+    waits on it right before the first use.  Backward is the matching reduce-scatter."""
+
+    @staticmethod
+    def forward(ctx, x, group, holder):
+        ctx.group = group
+        world = dist.get_world_size(group)
+        out = torch.empty((x.shape[0] * world,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        holder.append(dist.all_gather_into_tensor(out, x.contiguous(), group=group, async_op=True))
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        world = dist.get_world_size(ctx.group)
+        dx = torch.empty((dout.shape[0] // world,) + tuple(dout.shape[1:]), dtype=dout.dtype, device=dout.device)
+        dist.reduce_scatter_tensor(dx, dout.contiguous(), group=ctx.group)
+        return dx, None, None
+
+
 class MoEAllGatherTokenDispatcher(MoETokenDispatcher):
     """Every EP rank gathers all tokens, computes its local experts on the ones routed to them, and the results are
-    reduce-scattered back (reference: moe_layer_overlap_allgather.py; docs megatron-moe-allgather-dispatcher.md)."""
+    reduce-scattered back (reference: moe_layer_overlap_allgather.py; docs megatron-moe-allgather-dispatcher.md).
 
-    def __init__(self, num_local_experts, local_expert_indices, config):
+    ``overlap`` (``--moe-allgather-overlap-comm``): the layer calls ``pre_gather`` before the router, so the all-gather of
+    the hidden states - the large transfer, which does not depend on the routing - is in flight while the router (and the
+    shared expert) compute; only the small gathers of probabilities and routing map follow the router."""
+
+    def __init__(self, num_local_experts, local_expert_indices, config, overlap: bool = False):
         super().__init__(config)
         self.num_local_experts, self.local_expert_indices = num_local_experts, local_expert_indices
         self.group = ps.get_expert_tensor_and_model_parallel_group(check_initialized=False)
         self.gsize = ps.get_expert_tensor_and_model_parallel_world_size()
+        self.overlap = overlap
+        self._pre = None
+
+    def pre_gather(self, hidden):
+        """Start the all-gather of the hidden states; ``token_permutation`` picks the result up."""
+        if not self.overlap or self.gsize <= 1:
+            return
+        holder = []
+        h = hidden.reshape(-1, hidden.shape[-1])
+        self._pre = (_GatherRowsAsync.apply(h, self.group, holder), holder)
 
     def token_permutation(self, hidden, probs, routing_map):
         self.hidden_shape = hidden.shape
         h = hidden.reshape(-1, hidden.shape[-1])
+        pre, self._pre = self._pre, None
         if self.gsize > 1:
-            h = M.gather_from_sequence_parallel_region(h, group=self.group)
+            if pre is not None:
+                h, holder = pre
+                for w in holder:
+                    w.wait()
+            else:
+                h = M.gather_from_sequence_parallel_region(h, group=self.group)
             probs = M.gather_from_sequence_parallel_region(probs, group=self.group)
             with torch.no_grad():
                 routing_map = M.all_gather_first_dim(routing_map.to(torch.uint8), self.group).bool()

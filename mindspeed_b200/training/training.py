@@ -223,6 +223,13 @@ def _train_step_inner(forward_step_func, data_iterator, model, optimizer, opt_pa
                             num_microbatches=get_num_microbatches(), seq_length=args.seq_length,
                             micro_batch_size=args.micro_batch_size, decoder_seq_length=None, forward_only=False)
     ok, grad_norm, num_zeros = optimizer.step()
+    if getattr(args, "balanced_moe_experts", False):
+        # the experts that were busiest in this step are replicated on every expert-parallel rank for the next one
+        from ..parallel.moe.moe_layer import MoELayer
+        for chunk in model:
+            for mod in chunk.modules():
+                if isinstance(mod, MoELayer):
+                    mod.refresh_hot_experts()
     if fp8_recipe is not None:
         from ..models.te_compat import clear_fp8_weight_cache
         clear_fp8_weight_cache()       # weights moved: cached quantised copies are stale

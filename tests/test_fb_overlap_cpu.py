@@ -106,3 +106,13 @@ def test_training_with_fb_overlap_matches_plain_schedule(world):
     assert len(ref) == 3
     for a, b in zip(ref, got):
         assert abs(a - b) < 1e-5 * max(1.0, abs(a)), (ref, got)
+
+
+def test_training_with_hot_expert_replicas_matches_plain_dispatch():
+    """``--balanced-moe-experts``: after the first step the busiest experts are replicated on both expert-parallel ranks and
+    their tokens are computed locally; outputs and gradients (returned to the owner) are those of the plain dispatch."""
+    ref = run_distributed(_train_losses, 2, [])[0]
+    got = run_distributed(_train_losses, 2, ["--balanced-moe-experts", "--balanced-moe-hot-expert-num", "2",
+                                             "--trans-hot-expert-group-num", "2"])[0]
+    for a, b in zip(ref, got):
+        assert abs(a - b) < 1e-5 * max(1.0, abs(a)), (ref, got)

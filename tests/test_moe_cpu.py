@@ -12,12 +12,16 @@ from dist_utils import run_distributed  # noqa: E402
 def _make_config(ep, dispatcher, grouped=True, shared=False, score="softmax"):
     import torch.nn.functional as F
     from mindspeed_b200.config import TransformerConfig
-    return TransformerConfig(num_layers=2, hidden_size=64, num_attention_heads=4, ffn_hidden_size=128, num_moe_experts=4,
+    overlap_gather = dispatcher == "allgather_overlap"
+    dispatcher = "allgather" if overlap_gather else dispatcher
+    cfg = TransformerConfig(num_layers=2, hidden_size=64, num_attention_heads=4, ffn_hidden_size=128, num_moe_experts=4,
                              moe_router_topk=2, moe_ffn_hidden_size=96, moe_grouped_gemm=grouped, gated_linear_unit=True,
                              activation_func=F.silu, add_bias_linear=False, expert_model_parallel_size=ep,
                              moe_token_dispatcher_type=dispatcher, moe_aux_loss_coeff=0.01, use_cpu_initialization=True,
                              moe_shared_expert_intermediate_size=64 if shared else None, optimization_level=0,
                              moe_router_score_function=score, hidden_dropout=0.0, attention_dropout=0.0)
+    cfg.moe_allgather_overlap_comm = overlap_gather     # all-gather of the hidden states started before the router
+    return cfg
 
 
 def _set_weights(layer, local_experts):
@@ -73,7 +77,8 @@ def _run(rank, world, ep, dispatcher, grouped, shared, score):
 
 
 @pytest.mark.parametrize("dispatcher,grouped,shared,score", [("alltoall", True, False, "softmax"), ("alltoall", False, True, "sigmoid"),
-                                                            ("allgather", True, False, "softmax")])
+                                                            ("allgather", True, False, "softmax"),
+                                                            ("allgather_overlap", True, True, "softmax")])
 def test_expert_parallel_matches_single_rank(dispatcher, grouped, shared, score):
     ref_outs, ref_grads = run_distributed(_run, 1, 1, dispatcher, grouped, shared, score)[0]
     res = run_distributed(_run, 2, 2, dispatcher, grouped, shared, score)
