@@ -477,6 +477,9 @@ class MoEFeature(Feature):
             if args.moe_alltoall_mc2:
                 raise AssertionError("--balanced-moe-experts leaves tokens with fewer than top-k remote experts; the fused "
                                      "dispatcher (--moe-alltoall-mc2) needs exactly top-k per token")
+            if getattr(args, "use_fused_dist_opt", False) or getattr(args, "ddp_average_in_collective", False):
+                raise AssertionError("--balanced-moe-experts adds the replicas' gradients after the data-parallel reduction; "
+                                     "it is not combined with --use-fused-dist-opt or --ddp-average-in-collective")
             if ne and not (0 < args.balanced_moe_hot_expert_num <= ne):
                 raise AssertionError("--balanced-moe-hot-expert-num must be within 1..num_experts")
         if args.moe_allgather_overlap_comm and getattr(args, "moe_token_dispatcher_type", "alltoall") != "allgather":

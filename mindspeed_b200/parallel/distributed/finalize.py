@@ -62,11 +62,25 @@ def _update_router_expert_bias(model, config):
                 m.update_expert_bias()
 
 
+def _return_hot_expert_grads(model, config):
+    """--balanced-moe-experts: gradients of the hot experts' replicas go back to the owners (one collective per MoE layer,
+    in module order, on every rank)."""
+    if not getattr(config, "balanced_moe_experts", False):
+        return
+    group = ps.get_data_parallel_group(with_context_parallel=True)
+    for chunk in model:
+        for m in chunk.modules():
+            if hasattr(m, "return_hot_grads"):
+                buf = getattr(chunk, "_param_to_buffer", {}).get(id(m.experts.weight1)) if hasattr(m.experts, "weight1") else None
+                m.return_hot_grads(group, buf.gradient_scaling_factor if buf is not None else 1.0)
+
+
 def finalize_model_grads(model: List[torch.nn.Module], num_tokens: Optional[torch.Tensor] = None):
     config = (model[0].module if hasattr(model[0], "module") else model[0]).config
     for chunk in model:
         if hasattr(chunk, "finish_grad_sync"):
             chunk.finish_grad_sync()
+    _return_hot_expert_grads(model, config)
     _allreduce_sequence_parallel_grads(model, config)
     _allreduce_embedding_grads(model, config)
     _update_router_expert_bias(model, config)

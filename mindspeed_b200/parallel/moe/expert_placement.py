@@ -144,42 +144,16 @@ def broadcast_hot_experts(stacked: torch.Tensor, local_ids: Sequence[int], hot: 
     return out
 
 
-class _ReplicateHot(torch.autograd.Function):
-    """[k, ...] replicas of the hot experts' stacked weights on every rank of the group; the backward sums the replicas'
-    gradients over the group and hands each row to its owner, so the owner's parameter receives the gradient of all
-    tokens that any rank processed with a replica."""
-
-    @staticmethod
-    def forward(ctx, stacked, local_ids, hot, group, n_groups):
-        ctx.local_ids, ctx.hot, ctx.group, ctx.shape = list(local_ids), list(hot), group, stacked.shape
-        out = torch.zeros(len(hot), *stacked.shape[1:], dtype=stacked.dtype, device=stacked.device)
-        import os
-        if os.environ.get("MSB_DBG"):
-            print("DBG fwd", dist.get_rank(), tuple(out.shape), hot, file=__import__("sys").stderr, flush=True)
-        for i, e in enumerate(hot):
-            if e in ctx.local_ids:
-                out[i].copy_(stacked[ctx.local_ids.index(e)])
-        if group is not None and dist.get_world_size(group) > 1:
-            # several smaller collectives: the first replicas are usable while the others are still in flight
-            works = [dist.all_reduce(c, group=group, async_op=True) for c in out.chunk(max(1, min(n_groups, len(hot))), 0)]
-            for w in works:
-                w.wait()
-        return out
-
-    @staticmethod
-    def backward(ctx, dout):
-        dout = dout.contiguous()
-        import os
-        if os.environ.get("MSB_DBG"):
-            print("DBG bwd", dist.get_rank(), tuple(dout.shape), ctx.hot, file=__import__("sys").stderr, flush=True)
-        if ctx.group is not None and dist.get_world_size(ctx.group) > 1:
-            dist.all_reduce(dout, group=ctx.group)
-        d = torch.zeros(ctx.shape, dtype=dout.dtype, device=dout.device)
-        for i, e in enumerate(ctx.hot):
-            if e in ctx.local_ids:
-                d[ctx.local_ids.index(e)].copy_(dout[i])
-        return d, None, None, None, None
-
-
-def replicate_hot_experts(stacked, local_ids, hot, group, n_groups=1):
-    return _ReplicateHot.apply(stacked, local_ids, hot, group, n_groups)
+def replicate_hot_experts(stacked: torch.Tensor, local_ids: Sequence[int], hot: Sequence[int], group, n_groups: int = 1) -> torch.Tensor:
+    """[len(hot), ...] copies of the hot experts' rows of ``stacked`` on every rank of ``group`` (each row is contributed by
+    its one owner).  ``n_groups`` collectives instead of one, so the first replicas are usable while the rest is in flight."""
+    out = torch.zeros(len(hot), *stacked.shape[1:], dtype=stacked.dtype, device=stacked.device)
+    local_ids = list(local_ids)
+    for i, e in enumerate(hot):
+        if e in local_ids:
+            out[i].copy_(stacked[local_ids.index(e)])
+    if group is not None and dist.get_world_size(group) > 1:
+        works = [dist.all_reduce(c, group=group, async_op=True) for c in out.chunk(max(1, min(n_groups, len(hot))), 0)]
+        for w in works:
+            w.wait()
+    return out

@@ -57,8 +57,11 @@ class GroupedMLP(nn.Module):
         """The expert MLP on explicit stacked weights [n, H, F1] / [n, F, H] (the module's own, or replicas of other
         ranks' experts)."""
         if permuted_tokens.shape[0] == 0:
-            # keep the parameters in the graph so data-parallel reduction sees zero gradients
+            # keep the parameters in the graph so data-parallel reduction sees zero gradients, and the probabilities too:
+            # their all-to-all has a backward collective that the peers run, so this rank must run it as well
             z = (weight1.sum() + weight2.sum()) * 0
+            if permuted_probs is not None:
+                z = z + permuted_probs.sum().to(z.dtype) * 0
             return permuted_tokens + z.to(permuted_tokens.dtype)
         h = grouped_gemm(permuted_tokens, weight1, tokens_per_expert, trans_b=False)
         if self.config.gated_linear_unit and self.config.activation_func is F.silu:

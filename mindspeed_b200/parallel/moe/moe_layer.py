@@ -53,6 +53,7 @@ class MoELayer(nn.Module):
         self.hot_groups = int(getattr(config, "trans_hot_expert_group_num", 1) or 1)
         self.hot_experts = []
         self._load = None
+        self._hot_w1 = self._hot_w2 = None
         self.zero_memory = getattr(config, "moe_zero_memory", "disable")
         n_zm = getattr(config, "moe_zero_memory_num_layers", None)
         if n_zm is not None and layer_number > n_zm:
@@ -90,34 +91,59 @@ class MoELayer(nn.Module):
         return out
 
     def _hot_path(self, hidden_states, probs, routing_map):
-        """Tokens routed to a hot expert are computed here with a replica of its weights; returns the routing that is left
-        for the dispatcher and the hot experts' contribution to the output."""
-        from .expert_placement import replicate_hot_experts, split_hot_routing
+        """Tokens routed to a hot expert are computed here with the replica of its weights; returns the routing that is left
+        for the dispatcher and the hot experts' contribution to the output.  No collective: the replicas were fetched once,
+        after the last optimizer step, and their gradients go back to the owners once, after the last micro-batch."""
+        from .expert_placement import split_hot_routing
         from .moe_utils import permute, unpermute
-        hot = self.hot_experts
-        cold_map, cold_probs, hot_map, hot_probs = split_hot_routing(routing_map, probs, hot)
-        ep_group = ps.get_expert_model_parallel_group()
-        w1 = replicate_hot_experts(self.experts.weight1, self.local_expert_indices, hot, ep_group, self.hot_groups)
-        w2 = replicate_hot_experts(self.experts.weight2, self.local_expert_indices, hot, ep_group, self.hot_groups)
+        cold_map, cold_probs, hot_map, hot_probs = split_hot_routing(routing_map, probs, self.hot_experts)
         h = hidden_states.reshape(-1, hidden_states.shape[-1])
         rows, order = permute(h, hot_map)
         row_probs = hot_probs.t().contiguous().masked_select(hot_map.t().contiguous()).to(h.dtype)
-        y = self.experts.run(rows, hot_map.sum(0).cpu(), row_probs, w1, w2)
+        y = self.experts.run(rows, hot_map.sum(0).cpu(), row_probs, self._hot_w1, self._hot_w2)
         hot_out = unpermute(y, order, h.shape).view(hidden_states.shape)
         return cold_probs, cold_map, hot_out
 
     def refresh_hot_experts(self):
-        """Once per optimizer step: choose the ``balanced_moe_hot_expert_num`` busiest experts of the step that just ended
-        (token counts summed over the expert-parallel group, so every rank picks the same set)."""
+        """Once per optimizer step, after the update: choose the ``balanced_moe_hot_expert_num`` busiest experts of the step
+        that just ended (token counts summed over the expert-parallel group, so every rank picks the same set) and fetch
+        replicas of their new weights."""
         if not self.balanced or self._load is None:
             return self.hot_experts
         import torch.distributed as dist
-        from .expert_placement import select_hot_experts
+        from .expert_placement import replicate_hot_experts, select_hot_experts
+        group = ps.get_expert_model_parallel_group()
         load = self._load.clone()
-        dist.all_reduce(load, group=ps.get_expert_model_parallel_group())
-        self.hot_experts = select_hot_experts(load, min(self.hot_k, load.numel())) if self.hot_k > 0 else []
+        dist.all_reduce(load, group=group)
         self._load = None
+        self.hot_experts = select_hot_experts(load, min(self.hot_k, load.numel())) if self.hot_k > 0 else []
+        if self.hot_experts:
+            with torch.no_grad():
+                self._hot_w1 = replicate_hot_experts(self.experts.weight1.data, self.local_expert_indices, self.hot_experts,
+                                                     group, self.hot_groups).requires_grad_(True)
+                self._hot_w2 = replicate_hot_experts(self.experts.weight2.data, self.local_expert_indices, self.hot_experts,
+                                                     group, self.hot_groups).requires_grad_(True)
         return self.hot_experts
+
+    def return_hot_grads(self, group, scale: float):
+        """After the data-parallel gradient reduction: sum the replicas' gradients over ``group`` (every rank that holds
+        replicas, i.e. the whole data-parallel domain of this layer) and add each hot expert's rows, times ``scale`` (the
+        factor the reduction applied to ordinary expert gradients), to its owner's gradient."""
+        if not self.hot_experts or self._hot_w1 is None:
+            return
+        import torch.distributed as dist
+        grads = [w.grad if w.grad is not None else torch.zeros_like(w) for w in (self._hot_w1, self._hot_w2)]
+        flat = torch.cat([g.reshape(-1).float() for g in grads])
+        if group is not None and dist.get_world_size(group) > 1:
+            dist.all_reduce(flat, group=group)
+        n1 = grads[0].numel()
+        parts = (flat[:n1].view_as(grads[0]), flat[n1:].view_as(grads[1]))
+        for param, g in zip((self.experts.weight1, self.experts.weight2), parts):
+            dst = param.main_grad if hasattr(param, "main_grad") else param.grad
+            for i, e in enumerate(self.hot_experts):
+                if e in self.local_expert_indices and dst is not None:
+                    dst[self.local_expert_indices.index(e)].add_((g[i] * scale).to(dst.dtype))
+        self._hot_w1.grad = self._hot_w2.grad = None
 
     def forward(self, hidden_states):
         if self.training and (self.config.moe_layer_recompute or self.zero_memory != "disable"):
