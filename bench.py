@@ -96,12 +96,12 @@ class ClockSampler:
     Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
-    def __init__(self, index):
-        self.index, self.proc, self.lines = index, None, []
+    def __init__(self, index, period_ms=200):
+        self.index, self.proc, self.lines, self.period_ms = index, None, [], int(period_ms)
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", str(self.period_ms),
                                           "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -364,7 +364,9 @@ def main(argv=None):
     k, ke, kb, truncated = (int(x) for x in plan.tolist())
 
     # ---- the timed region: exactly k steps, device-resident inputs ----
-    sampler = ClockSampler(torch.cuda.current_device())
+    # 200 ms samples; 500 ms once a step takes seconds (still several samples per step, fewer driver queries beside a
+    # model that synchronises with the host in every layer)
+    sampler = ClockSampler(torch.cuda.current_device(), 200 if step_ms < 2000 else 500)
     barrier()
     if rank == 0:
         sampler.start()

@@ -529,7 +529,8 @@ class MemoryFeature(Feature):
         add_arg(g, "--smart-swap", action="store_true")
         add_arg(g, "--reuse-fp32-param", action="store_true")
         add_arg(g, "--compress-dense", type=str, default="disable", choices=["disable", "level0", "level1"])
-        add_arg(g, "--compress-activation", action="store_true")
+        add_arg(g, "--compress-activation", type=str, default="",
+                help='layers whose saved activations are stored compressed: "0" = all, or e.g. "1,3-5" (1-based)')
         add_arg(g, "--compress-optimizer", action="store_true")
         add_arg(g, "--adaptive-recompute-device-size", type=int, default=-1)
         add_arg(g, "--adaptive-recompute-profiling-step", type=int, default=10)
@@ -543,6 +544,13 @@ class MemoryFeature(Feature):
             raise AssertionError("--reuse-fp32-param is incompatible with fused_ema_adamw")
         if args.reuse_fp32_param and not getattr(args, "bf16", False):
             raise AssertionError("--reuse-fp32-param needs --bf16")
+        if args.compress_activation not in ("", None):
+            from ..memory.compress_activation import parse_layers
+            args.compress_activation = parse_layers(args.compress_activation, args.num_layers)
+            if getattr(args, "recompute_granularity", None) == "full":
+                raise AssertionError("--compress-activation stores what a layer saves for backward; full recompute saves nothing")
+        else:
+            args.compress_activation = []
         if args.smart_swap and (args.swap_attention or args.adaptive_memory_optimization):
             raise AssertionError("--smart-swap excludes --swap-attention / --adaptive-memory-optimization")
 
@@ -576,6 +584,10 @@ class OptimizerFeature(Feature):
         add_arg(g, "--apply-wd-to-qk-layernorm", action="store_true")
 
     def validate_args(self, args):
+        if getattr(args, "compress_optimizer", False) and (args.swap_optimizer or args.quant_states or
+                                                          getattr(args, "use_fused_dist_opt", False) or getattr(args, "virtual_optimizer", None)):
+            raise AssertionError("--compress-optimizer keeps the moments encoded between steps; it is not combined with "
+                                 "--swap-optimizer, --quant-states, --virtual-optimizer or --use-fused-dist-opt")
         if args.swap_optimizer and args.quant_states:
             raise AssertionError("--swap-optimizer is incompatible with the low-precision optimizer")
         if args.quant_states == "hif8":

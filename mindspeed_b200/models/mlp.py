@@ -41,6 +41,16 @@ class MLP(nn.Module):
         return self.activation_func(h)
 
     def forward(self, hidden_states):
+        level = getattr(self.config, "compress_dense", "disable")
+        if level in ("level0", "level1") and self.training and torch.is_grad_enabled() and not getattr(self, "is_expert", False):
+            # --compress-dense: level0 stores the MLP's input compressed, level1 everything the MLP saves for backward
+            from ..memory.compress_activation import CompressSavedActivations
+            only = {hidden_states.data_ptr()} if level == "level0" else None
+            with CompressSavedActivations(only=only):
+                return self._forward(hidden_states)
+        return self._forward(hidden_states)
+
+    def _forward(self, hidden_states):
         h, b1 = self.linear_fc1(hidden_states)
         if self.recompute_activation and self.training and h.requires_grad:
             ck = CheckpointWithoutOutput()

@@ -115,6 +115,8 @@ class TransformerLayer(nn.Module):
             self.mlp = MoELayer(config, layer_number=self.layer_number)
         else:
             self.mlp = MLP(config)
+        sel = getattr(config, "compress_activation", None) or []
+        self.compress_saved = isinstance(sel, (list, tuple)) and self.layer_number in sel
         self.recompute_norm = bool(getattr(config, "recompute_norm", False))
         # --recompute-norm-num-layers / --recompute-activation-function-num-layers: only the first N layers of a stage
         n_norm = getattr(config, "recompute_norm_num_layers", None)
@@ -128,6 +130,14 @@ class TransformerLayer(nn.Module):
         return norm(x)
 
     def forward(self, hidden_states, attention_mask=None, rotary_pos_emb=None, packed_seq_params=None, **kwargs):
+        if self.compress_saved and self.training and torch.is_grad_enabled():
+            # --compress-activation: what this layer saves for backward is stored losslessly compressed
+            from ..memory.compress_activation import CompressSavedActivations
+            with CompressSavedActivations():
+                return self._forward(hidden_states, attention_mask, rotary_pos_emb, packed_seq_params, **kwargs)
+        return self._forward(hidden_states, attention_mask, rotary_pos_emb, packed_seq_params, **kwargs)
+
+    def _forward(self, hidden_states, attention_mask=None, rotary_pos_emb=None, packed_seq_params=None, **kwargs):
         residual = hidden_states
         if self.recompute_norm and self.training and hidden_states.requires_grad:
             ck = CheckpointWithoutOutput()

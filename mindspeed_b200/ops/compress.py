@@ -30,7 +30,7 @@ class Compressed:
     dtype: torch.dtype
     numel: int
     header: torch.Tensor      # [n_blocks, 2] uint8
-    mant: torch.Tensor        # sign + mantissa, int16 / int32 container
+    mant: torch.Tensor        # sign + mantissa: uint8 (bf16), [n, 3] uint8 (fp32), int16 (fp16)
     packed: torch.Tensor      # uint8 bit stream of exponent offsets
     offsets: torch.Tensor     # [n_blocks + 1] int64 byte offsets into ``packed``
 
@@ -44,8 +44,8 @@ class Compressed:
 
     @property
     def nbytes_payload(self) -> int:
-        """Bytes that scale with the tensor: mantissa bits are counted at their true width (they are stored in a wider
-        container here for simplicity; a packed store keeps sign+mantissa in (1 + mantissa_bits) bits)."""
+        """Bytes that scale with the tensor, with the mantissa bits counted at their true width (equal to the stored size
+        for bf16 and fp32; fp16's 11 bits sit in an int16)."""
         _, ebits, mbits = _LAYOUT[self.dtype]
         return (self.numel * (1 + mbits) + 7) // 8 + self.packed.numel() + self.header.numel()
 
@@ -83,8 +83,24 @@ def compress(x: torch.Tensor) -> Compressed:
     weights = (1 << torch.arange(8, device=x.device)).to(torch.uint8)
     packed = (stream.view(-1, 8) * weights).sum(dim=1).to(torch.uint8)
     header = torch.stack([mn.to(torch.uint8), width.to(torch.uint8)], dim=1)
-    return Compressed(tuple(x.shape), x.dtype, n, header, mant.to(itype if mbits + 1 <= 15 or itype == torch.int32 else torch.int32),
-                      packed, offsets)
+    return Compressed(tuple(x.shape), x.dtype, n, header, _store_mantissa(mant, mbits), packed, offsets)
+
+
+def _store_mantissa(mant: torch.Tensor, mbits: int) -> torch.Tensor:
+    """sign + mantissa in whole bytes: 8 bits for bf16 (one uint8 per value), 24 for fp32 (three), 11 for fp16 (kept in an
+    int16: no byte-aligned packing)."""
+    if mbits + 1 <= 8:
+        return mant.to(torch.uint8)
+    if mbits + 1 == 24:
+        return torch.stack([(mant >> s) & 0xFF for s in (0, 8, 16)], dim=1).to(torch.uint8)
+    return mant.to(torch.int16)
+
+
+def _load_mantissa(m: torch.Tensor, mbits: int) -> torch.Tensor:
+    if m.dtype == torch.uint8 and m.dim() == 2:
+        m = m.to(torch.int64)
+        return m[:, 0] | (m[:, 1] << 8) | (m[:, 2] << 16)
+    return m.to(torch.int64) & ((1 << (mbits + 1)) - 1)
 
 
 def decompress(c: Compressed) -> torch.Tensor:
@@ -103,7 +119,7 @@ def decompress(c: Compressed) -> torch.Tensor:
     bits[keep] = stream[:int(keep.sum())]
     off = (bits << bit_idx).sum(-1)
     exp = (off + mn.unsqueeze(1)).reshape(-1)
-    mant = c.mant.to(torch.int64) & ((1 << (mbits + 1)) - 1)
+    mant = _load_mantissa(c.mant, mbits)
     sign = mant >> mbits
     frac = mant & ((1 << mbits) - 1)
     word = (sign << (ebits + mbits)) | (exp << mbits) | frac

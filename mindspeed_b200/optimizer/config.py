@@ -42,3 +42,4 @@ class OptimizerConfig:
     swap_optimizer_times: int = 16
     quant_states: Optional[str] = None
     reuse_fp32_param: bool = False
+    compress_optimizer: bool = False

@@ -382,6 +382,9 @@ def get_megatron_optimizer(config: OptimizerConfig, model_chunks, no_weight_deca
     if config.swap_optimizer:
         from .swap_optimizer import SwapDistributedOptimizer
         return SwapDistributedOptimizer(config, model_chunks, no_weight_decay_cond, scale_lr_cond, lr_mult)
+    if getattr(config, "compress_optimizer", False):
+        from .compressed_states import CompressedStateDistributedOptimizer
+        return CompressedStateDistributedOptimizer(config, model_chunks, no_weight_decay_cond, scale_lr_cond, lr_mult)
     if config.quant_states:
         from .low_precision import QuantStateDistributedOptimizer
         return QuantStateDistributedOptimizer(config, model_chunks, no_weight_decay_cond, scale_lr_cond, lr_mult)

@@ -138,7 +138,8 @@ def setup_model_and_optimizer(model_provider_func, no_wd_decay_cond=None, scale_
                            use_distributed_optimizer=args.use_distributed_optimizer,
                            optimizer_selection=args.optimizer_selection, use_ema=args.use_ema, ema_decay=args.ema_decay,
                            swap_optimizer=args.swap_optimizer, swap_optimizer_times=args.swap_optimizer_times,
-                           quant_states=args.quant_states, reuse_fp32_param=args.reuse_fp32_param)
+                           quant_states=args.quant_states, reuse_fp32_param=args.reuse_fp32_param,
+                           compress_optimizer=bool(getattr(args, "compress_optimizer", False)))
     from ..parallel.distributed.fsdp import FullyShardedDataParallel as _FSDP
     if isinstance(model[0], _FSDP):
         from ..parallel.distributed.fsdp import ShardedAdamW

@@ -1,6 +1,12 @@
 """Smart swap (profile -> policy -> execute), adaptive recompute (profile -> knapsack -> apply), auto pipeline split."""
+import os
+import sys
+
+import pytest
 import torch
 import torch.nn as nn
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 from mindspeed_b200.memory import adaptive_recompute as AR
 from mindspeed_b200.memory import auto_pipeline as AP
@@ -109,3 +115,46 @@ def test_auto_pipeline_balances_time_under_memory():
     mbs, plan = AP.search_micro_batch(lambda m: [LP(1.0 * m ** 0.9, 2.0 * m ** 0.9, 100 * m, 10 * m, 50) for _ in range(8)],
                                       [1, 2, 4], global_batch=32, dp=1, pp=4, budget_bytes=3000)
     assert mbs in (1, 2, 4) and plan.feasible
+
+
+def _train_compress(rank, world, extra):
+    import io
+    from contextlib import redirect_stdout
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import pretrain_gpt as pg
+    from test_pipeline_cpu import BASE
+    from mindspeed_b200.memory import compress_activation as CA
+    from mindspeed_b200.training import pretrain
+    CA.MIN_NUMEL = 256                       # the test model's activations are tiny
+    CA.reset_stats()
+    with redirect_stdout(io.StringIO()):
+        hist = pretrain(pg.train_valid_test_datasets_provider, pg.model_provider, forward_step_func=pg.forward_step,
+                        args_list=BASE + list(extra))
+    return [h["lm loss"] for h in hist], dict(CA.CompressSavedActivations.stats)
+
+
+def test_compress_activation_is_lossless_and_smaller():
+    """``--compress-activation`` / ``--compress-dense``: identical losses (the codec is bit-exact) and fewer stored bytes."""
+    from dist_utils import run_distributed
+    ref, st0 = run_distributed(_train_compress, 1, [])[0]
+    assert st0["tensors"] == 0
+    for extra in (["--compress-activation", "1,3-4"], ["--compress-activation", "0"], ["--compress-dense", "level1"],
+                  ["--compress-dense", "level0"]):
+        got, st = run_distributed(_train_compress, 1, extra)[0]
+        assert got == ref, (extra, ref, got)
+        assert st["tensors"] > 0 and st["stored"] < 0.95 * st["raw"], (extra, st)
+    # Adam moments held encoded between steps: same trajectory, with and without the distributed optimizer
+    got, _ = run_distributed(_train_compress, 1, ["--compress-optimizer"])[0]
+    assert got == ref, (ref, got)
+    ref2 = run_distributed(_train_compress, 2, ["--use-distributed-optimizer"])[0][0]
+    got2 = run_distributed(_train_compress, 2, ["--use-distributed-optimizer", "--compress-optimizer"])[0][0]
+    assert got2 == ref2, (ref2, got2)
+
+
+def test_compress_activation_layer_spec():
+    from mindspeed_b200.memory.compress_activation import parse_layers
+    assert parse_layers("0", 4) == [1, 2, 3, 4]
+    assert parse_layers("1,3-4", 6) == [1, 3, 4]
+    assert parse_layers("", 4) == []
+    with pytest.raises(ValueError):
+        parse_layers("5", 4)
