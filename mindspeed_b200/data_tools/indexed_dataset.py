@@ -67,14 +67,26 @@ class IndexedDatasetBuilder:
             f.write(np.asarray(self.doc_idx, dtype=np.int64).tobytes())
 
 
+# Megatron's index files ("MMIDIDX", version 1) have the same sections in the same order with their own dtype codes; corpora
+# tokenised for the reference (mindspeed/tools/preprocess_data.py writes this format) are read as they are.
+MEGATRON_MAGIC = b"MMIDIDX\x00\x00"
+MEGATRON_DTYPES = {1: np.uint8, 2: np.int8, 3: np.int16, 4: np.int32, 5: np.int64, 6: np.float64, 7: np.float32, 8: np.uint16}
+
+
 class MMapIndexedDataset:
     def __init__(self, prefix: str):
         with open(prefix + ".idx", "rb") as f:
-            if f.read(len(MAGIC)) != MAGIC:
-                raise ValueError(f"{prefix}.idx is not an indexed dataset of this format")
+            head = f.read(len(MAGIC))
+            if head == MAGIC:
+                table = DTYPES
+            elif head[:len(MEGATRON_MAGIC)] == MEGATRON_MAGIC:
+                table = MEGATRON_DTYPES
+                f.seek(len(MEGATRON_MAGIC))
+            else:
+                raise ValueError(f"{prefix}.idx is neither this package's nor Megatron's indexed-dataset format")
             _, code, n, nd = struct.unpack("<QBQQ", f.read(25))
             header = f.tell()
-        self.dtype = np.dtype(DTYPES[code])
+        self.dtype = np.dtype(table[code])
         idx = np.memmap(prefix + ".idx", mode="r", dtype=np.uint8)
         o = header
         self.lengths = np.frombuffer(idx, dtype=np.int32, count=n, offset=o); o += 4 * n

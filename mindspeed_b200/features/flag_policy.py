@@ -83,7 +83,6 @@ UNSUPPORTED: Dict[str, str] = {
     "fix-sub-seq-length": "fixed-length sub-sequence packing for EOD-reset CP is not implemented",
     "enable-fine-grained-expert-placement": "only whole-expert placement is implemented (--enable-expert-placement)",
     "fine-grained-expert-placement-thre": "only whole-expert placement is implemented (--enable-expert-placement)",
-    "data-path": "indexed datasets are built with mindspeed_b200.data_tools and passed to a custom provider; pretrain_gpt.py reads synthetic data",
     "no-qad-enable": "distillation is driven through mindspeed_b200.qat.distill, not through this switch",
     "recompute-module-list": "module-level recompute is selected with --recompute-granularity / --recompute-activation-function / --recompute-norm",
 }

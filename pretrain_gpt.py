@@ -45,6 +45,21 @@ def forward_step(data_iterator, model):
 
 
 def train_valid_test_datasets_provider(args):
+    if getattr(args, "data_path", None):
+        # indexed token datasets (this package's or Megatron's .bin / .idx); documents packed into seq_length + 1 windows
+        from mindspeed_b200.training.gpt_dataset import build_train_valid_test_datasets
+        n_train = args.train_iters * args.global_batch_size if args.train_iters else None
+        eod = None
+        if args.reset_position_ids or args.eod_mask_loss:
+            from mindspeed_b200.tokenizer.tokenizer import build_tokenizer
+            eod = build_tokenizer(args).eod        # the end-of-document id the corpus was tokenised with
+        train, _, _ = build_train_valid_test_datasets(args.data_path, args.split, args.seq_length, args.seed, (n_train, None, None),
+                                                      eod_token=eod, reset_position_ids=args.reset_position_ids,
+                                                      reset_attention_mask=False, eod_mask_loss=args.eod_mask_loss)
+        if train is None:
+            raise ValueError("--split leaves no documents for training")
+        return BatchIterator(train, args.micro_batch_size, ps.get_data_parallel_rank(), ps.get_data_parallel_world_size(),
+                             start=args.iteration * args.global_batch_size)
     ds = SyntheticGPTDataset(args.padded_vocab_size, args.seq_length, 1 << 20, seed=args.seed)
     return BatchIterator(ds, args.micro_batch_size, ps.get_data_parallel_rank(), ps.get_data_parallel_world_size(),
                          start=args.iteration * args.global_batch_size)
