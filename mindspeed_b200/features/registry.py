@@ -413,6 +413,28 @@ class PipelineMiscFeature(Feature):
         if isinstance(args.pipeline_num_transformer_layers, str):
             import ast
             args.pipeline_num_transformer_layers = ast.literal_eval(args.pipeline_num_transformer_layers)
+        if args.automated_pipeline or args.automated_pipeline_perf:
+            # layers per stage (and layers to recompute per stage) from the model shape, so that the stage that also holds
+            # the output layer gets fewer transformer layers (reference: mindspeed/core/memory/auto_pipeline/*,
+            # mindspeed/core/performance/auto_pipeline_perf/*); --automated-pipeline-perf also picks the micro-batch size
+            pp = getattr(args, "pipeline_model_parallel_size", 1)
+            if pp < 2:
+                raise AssertionError("--automated-pipeline needs pipeline parallelism")
+            if getattr(args, "num_layers_per_virtual_pipeline_stage", None) or getattr(args, "schedules_method", None) or \
+                    args.pipeline_num_transformer_layers or getattr(args, "pipeline_model_parallel_layout", None):
+                raise AssertionError("--automated-pipeline chooses the 1F1B layer split itself: no virtual stages, V / "
+                                     "bidirectional schedules or hand-written layer lists")
+            from ..memory.auto_pipeline import plan_from_args
+            mbs, plan = plan_from_args(args, search_micro_batch_size=bool(args.automated_pipeline_perf))
+            if not plan.feasible:
+                raise AssertionError("--automated-pipeline: no layer split fits the memory budget")
+            args.micro_batch_size = mbs
+            args.pipeline_num_transformer_layers = list(plan.layers_per_stage)
+            if any(plan.recompute_per_stage) and not getattr(args, "recompute_granularity", None):
+                args.recompute_granularity, args.recompute_method = "full", "block"
+                args.enable_recompute_layers_per_pp_rank = True
+                args.recompute_num_layers = list(plan.recompute_per_stage)
+            args.automated_pipeline_plan = plan
 
     def configure(self, manager, args):
         if args.recompute_in_bubble:

@@ -120,3 +120,65 @@ def search_micro_batch(profile_fn: Callable[[int], Sequence[LayerProfile]], cand
     if best is None:
         raise RuntimeError("no micro-batch size yields a feasible pipeline split within the memory budget")
     return best
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# From command-line arguments to a plan (--automated-pipeline / --automated-pipeline-perf)
+# ---------------------------------------------------------------------------------------------------------------------
+def analytic_layer_profiles(args, micro_batch_size: Optional[int] = None, peak_flops: float = 1.4e15) -> List[LayerProfile]:
+    """Per-layer profile from the model shape alone (no profiling run): GEMM and attention FLOPs at ``peak_flops``, saved
+    activations and parameters in bytes, per tensor- / context-parallel rank.  The embedding is charged to the first layer
+    and the output layer + loss to the last one, which is what makes an even split uneven in time."""
+    mbs = micro_batch_size or args.micro_batch_size
+    tp = max(1, getattr(args, "tensor_model_parallel_size", 1))
+    cp = max(1, getattr(args, "context_parallel_size", 1))
+    s, h = args.seq_length // cp, args.hidden_size
+    heads = args.num_attention_heads
+    groups = getattr(args, "num_query_groups", None) or heads
+    kv = getattr(args, "kv_channels", None) or h // heads
+    ffn = getattr(args, "ffn_hidden_size", None) or 4 * h
+    gated = 2 if getattr(args, "swiglu", False) else 1
+    ne = getattr(args, "num_experts", None)
+    topk = getattr(args, "moe_router_topk", 1) or 1
+    ep = max(1, getattr(args, "expert_model_parallel_size", 1))
+    tokens = mbs * s
+    qkv_out = heads * kv + 2 * groups * kv
+    attn_params = h * qkv_out + heads * kv * h
+    mlp_params = (gated + 1) * h * ffn
+    dense_flops = 2 * tokens * (attn_params + mlp_params * (topk if ne else 1)) / tp
+    attn_flops = 4 * mbs * s * (args.seq_length) * heads * kv / tp / 2          # causal: half of the square
+    fwd = (dense_flops + attn_flops) / peak_flops
+    params = (attn_params + (mlp_params * ne / ep if ne else mlp_params)) / tp
+    bpe = 2                                                                     # bf16 / fp16 activations
+    sp = tp if getattr(args, "sequence_parallel", False) else 1
+    act = tokens * bpe * (h * 4 / sp + qkv_out / tp + heads * kv / tp + (gated + 1) * ffn * (topk if ne else 1) / tp)
+    layer = LayerProfile(fwd, 2 * fwd, int(act), int(tokens * h * bpe / sp), int(params * bpe))
+    out = [dataclasses.replace(layer) for _ in range(args.num_layers)]
+    vocab = getattr(args, "padded_vocab_size", None) or getattr(args, "vocab_size", None) or 32000
+    head_fwd = 2 * tokens * h * vocab / tp / peak_flops
+    out[0] = dataclasses.replace(out[0], param_bytes=out[0].param_bytes + int(vocab * h * bpe / tp))
+    last = out[-1]
+    out[-1] = dataclasses.replace(last, fwd_time=last.fwd_time + head_fwd, bwd_time=last.bwd_time + 2 * head_fwd,
+                                  act_bytes=last.act_bytes + int(tokens * vocab * 4 / tp),
+                                  param_bytes=last.param_bytes + int(vocab * h * bpe / tp))
+    return out
+
+
+def plan_from_args(args, budget_bytes: Optional[int] = None, search_micro_batch_size: bool = False) -> Tuple[int, PipelinePlan]:
+    """(micro-batch size, plan) for the configured model: layers per pipeline stage and layers to recompute per stage.
+    The memory budget is ``--adaptive-recompute-device-size`` (MiB) when given, else 90 % of 180 GB."""
+    pp = args.pipeline_model_parallel_size
+    world = getattr(args, "world_size", None) or 1
+    dp = max(1, world // (pp * max(1, args.tensor_model_parallel_size) * max(1, getattr(args, "context_parallel_size", 1))))
+    if budget_bytes is None:
+        mib = getattr(args, "adaptive_recompute_device_size", -1) or -1
+        budget_bytes = int(mib) * (1 << 20) if mib and mib > 0 else int(0.9 * 180e9)
+    # bytes of training state per byte of 16-bit parameter: fp32 gradient (2x) + fp32 master and two moments (6x), the
+    # latter divided over the data-parallel ranks by the distributed optimizer
+    mult = 1.0 + 2.0 + 6.0 / (dp if getattr(args, "use_distributed_optimizer", False) else 1)
+    if search_micro_batch_size:
+        cands = [m for m in (1, 2, 4, 8) if args.global_batch_size % (m * dp) == 0]
+        return search_micro_batch(lambda m: analytic_layer_profiles(args, m), cands, args.global_batch_size, dp, pp, budget_bytes,
+                                  state_multiplier=mult)
+    n_mb = max(1, args.global_batch_size // (args.micro_batch_size * dp))
+    return args.micro_batch_size, solve_pipeline(analytic_layer_profiles(args), pp, n_mb, budget_bytes, state_multiplier=mult)

@@ -85,6 +85,14 @@ def get_transformer_layer_offset(config, vp_stage: Optional[int] = None) -> int:
         # chunk 0 holds layers [r*per, ...), chunk 1 holds the mirror slice counted from the end
         # (reference: mindspeed/core/pipeline_parallel/dualpipev/dualpipev_chunks.py:43-53)
         return r * per if chunk == 0 else config.num_layers - (r + 1) * per
+    per_stage = getattr(config, "pipeline_num_transformer_layers", None)
+    if per_stage:
+        # explicit (possibly uneven) layer counts: the offset is what the stages before this one hold
+        if isinstance(per_stage[0], (list, tuple)):
+            vp = vp_stage if vp_stage is not None else (ps.get_virtual_pipeline_model_parallel_rank() or 0)
+            before = sum(per_stage[rr][v] for v in range(vp) for rr in range(pp))
+            return before + sum(per_stage[rr][vp] for rr in range(r))
+        return sum(per_stage[:r])
     n = get_num_layers_to_build(config)
     vpp = ps.get_virtual_pipeline_model_parallel_world_size()
     if vpp is not None:

@@ -158,3 +158,21 @@ def test_compress_activation_layer_spec():
     assert parse_layers("", 4) == []
     with pytest.raises(ValueError):
         parse_layers("5", 4)
+
+
+def test_automated_pipeline_gives_the_output_stage_fewer_layers():
+    import types
+    from mindspeed_b200.memory.auto_pipeline import plan_from_args
+    a = types.SimpleNamespace(micro_batch_size=1, tensor_model_parallel_size=1, context_parallel_size=1, seq_length=8192,
+                              hidden_size=4096, num_attention_heads=32, num_query_groups=8, kv_channels=128, ffn_hidden_size=14336,
+                              swiglu=True, num_experts=None, moe_router_topk=1, expert_model_parallel_size=1, num_layers=32,
+                              padded_vocab_size=128256, sequence_parallel=False, pipeline_model_parallel_size=4, world_size=8,
+                              global_batch_size=64, use_distributed_optimizer=True, adaptive_recompute_device_size=-1)
+    mbs, plan = plan_from_args(a)
+    assert mbs == 1 and plan.feasible and sum(plan.layers_per_stage) == 32
+    assert plan.layers_per_stage[-1] < max(plan.layers_per_stage)           # the 128k-vocabulary head costs about two layers
+    assert max(plan.stage_times) / min(plan.stage_times) < 1.2
+    # a tight budget forces recompute on the early stages, which hold the most micro-batches in flight
+    a.adaptive_recompute_device_size = 40 * 1024
+    _, tight = plan_from_args(a)
+    assert tight.feasible and tight.recompute_per_stage[0] >= tight.recompute_per_stage[-1] and sum(tight.recompute_per_stage) > 0

@@ -149,6 +149,8 @@ def _train(rank, world, extra, bidirectional):
     (2, ["--pipeline-model-parallel-size", "2", "--num-layers-per-virtual-pipeline-stage", "1"], False),
     (2, ["--pipeline-model-parallel-size", "2", "--schedules-method", "dualpipev"], False),
     (2, ["--pipeline-model-parallel-size", "2", "--recompute-in-bubble"], False),
+    # layers per stage chosen from the model shape (the stage with the output layer gets fewer transformer layers)
+    (2, ["--pipeline-model-parallel-size", "2", "--automated-pipeline", "--vocab-size", "2048", "--num-layers", "5"], False),
     # list-valued stage interface with its default content (the one hidden-state tensor), through the plan executor
     (2, ["--pipeline-model-parallel-size", "2", "--use-multiparameter-pipeline-model-parallel"], False),
     (2, ["--pipeline-model-parallel-size", "2", "--num-layers-per-virtual-pipeline-stage", "1", "--recompute-in-advance"], False),
@@ -162,7 +164,9 @@ def _train(rank, world, extra, bidirectional):
     (4, ["--pipeline-model-parallel-size", "4", "--overlap-p2p-communication"], False),
 ])
 def test_pipeline_matches_no_pipeline(world, extra, bidir):
-    ref = run_distributed(_train, 1, [], False)[0]
+    # flags that change the model itself also apply to the one-rank oracle
+    model_flags = [extra[i + j] for i, x in enumerate(extra) if x in ("--vocab-size", "--num-layers") for j in (0, 1)]
+    ref = run_distributed(_train, 1, model_flags, False)[0]
     res = run_distributed(_train, world, extra, bidir)
     have = [r for r in res if r[0] is not None]
     # bidirectional schedules compute half of the micro-batches' losses at each end of the pipeline
