@@ -64,7 +64,6 @@ UNSUPPORTED: Dict[str, str] = {
     "moe-model-type": "the DeepSpeed-style MoE is selected through mindspeed_b200.legacy_moe, not through this flag",
     "moe-bmm-mc2": "use --moe-alltoall-mc2 (peer-memory dispatch / combine) with --moe-grouped-gemm",
     "moe-unperm2-mem-optim-swap": "host swap of the unpermute buffer is not implemented; use --moe-zero-memory",
-    "quant-grads": "quantised gradient buffers are not implemented (quantised optimizer states: --quant-states)",
     "adaptive-recompute-device-swap": "adaptive recompute decides recompute only; combine it with --swap-attention for host swap",
     "adaptive-cp-dynamic-attn-mask": "adaptive CP takes one mask per run",
     "adaptive-cp-manually-set-mask-list": "adaptive CP derives its mask list itself",

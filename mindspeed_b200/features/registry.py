@@ -610,6 +610,12 @@ class OptimizerFeature(Feature):
                                                           getattr(args, "use_fused_dist_opt", False) or getattr(args, "virtual_optimizer", None)):
             raise AssertionError("--compress-optimizer keeps the moments encoded between steps; it is not combined with "
                                  "--swap-optimizer, --quant-states, --virtual-optimizer or --use-fused-dist-opt")
+        if getattr(args, "quant_grads", False):
+            if getattr(args, "gradient_accumulation_fusion", False):
+                raise AssertionError("--quant-grads keeps 16-bit gradient buffers; the GEMM epilogue accumulates into fp32 "
+                                     "buffers: add --no-gradient-accumulation-fusion")
+            if args.swap_optimizer or getattr(args, "use_fused_dist_opt", False):
+                raise AssertionError("--quant-grads is not combined with --swap-optimizer or --use-fused-dist-opt")
         if args.swap_optimizer and args.quant_states:
             raise AssertionError("--swap-optimizer is incompatible with the low-precision optimizer")
         if args.quant_states == "hif8":

@@ -20,6 +20,7 @@ from .buffers import ParamAndGradBuffer
 @dataclass
 class DistributedDataParallelConfig:
     grad_reduce_in_fp32: bool = False
+    quant_grads: bool = False            # gradient buffers (accumulation and reduction) in fp16 instead of fp32 / the parameter type
     overlap_grad_reduce: bool = False
     overlap_param_gather: bool = False
     align_param_gather: bool = False
@@ -59,7 +60,9 @@ class DistributedDataParallel(nn.Module):
             for p in params:
                 by_dtype.setdefault(p.dtype, []).append(p)
             for dt, ps_ in by_dtype.items():
-                gdt = torch.float32 if ddp_config.grad_reduce_in_fp32 else dt
+                # --quant-grads: 16-bit gradient buffers halve gradient memory and reduce-scatter traffic (reference:
+                # mindspeed/core/optimizer/low_precision/param_and_grad_buffer.py:23-33, dtype fp16)
+                gdt = torch.float16 if ddp_config.quant_grads else (torch.float32 if ddp_config.grad_reduce_in_fp32 else dt)
                 out.append(ParamAndGradBuffer(ddp_config, dt, gdt, ps_, group, bucket_size, scale))
 
         dp_group = ps.get_data_parallel_group(with_context_parallel=True)

@@ -113,6 +113,7 @@ def get_model(model_provider_func, wrap_with_ddp=True):
         return [FullyShardedDataParallel(m, plan, dp_group_ranks=ranks) for m in models]
     ddp_cfg = DistributedDataParallelConfig(
         grad_reduce_in_fp32=args.accumulate_allreduce_grads_in_fp32, overlap_grad_reduce=args.overlap_grad_reduce,
+        quant_grads=bool(getattr(args, "quant_grads", False)),
         overlap_param_gather=args.overlap_param_gather, use_distributed_optimizer=args.use_distributed_optimizer,
         check_for_nan_in_grad=args.check_for_nan_in_loss_and_grad, bucket_size=args.ddp_bucket_size,
         average_in_collective=args.ddp_average_in_collective, param_and_grad_buffer_pad=args.param_and_grad_buffer_pad,

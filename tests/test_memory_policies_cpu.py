@@ -176,3 +176,13 @@ def test_automated_pipeline_gives_the_output_stage_fewer_layers():
     a.adaptive_recompute_device_size = 40 * 1024
     _, tight = plan_from_args(a)
     assert tight.feasible and tight.recompute_per_stage[0] >= tight.recompute_per_stage[-1] and sum(tight.recompute_per_stage) > 0
+
+
+def test_quant_grads_uses_16_bit_gradient_buffers():
+    """``--quant-grads``: gradient accumulation and data-parallel reduction in fp16 buffers; the trajectory stays close."""
+    from dist_utils import run_distributed
+    ref = run_distributed(_train_compress, 2, ["--use-distributed-optimizer"])[0][0]
+    got = run_distributed(_train_compress, 2, ["--use-distributed-optimizer", "--quant-grads"])[0][0]
+    assert got != ref                                   # the buffers really are 16-bit
+    for a, b in zip(ref, got):
+        assert abs(a - b) < 5e-3 * max(1.0, abs(a)), (ref, got)
