@@ -8,6 +8,9 @@ import os
 from .cost_model import Estimate, estimate, memory_gib, step_ms
 from .hardware import Hardware, probe, probe_collectives
 from .search_space import ModelDesc, SearchConfig, build_search_space
+from .comm_predictors import CommPredictors
+from .operator_db import OperatorDB
+from .profiling_parse import ProfileSummary, parse_chrome_trace, summarize
 from .searcher import black_search, mixed_search, white_search
 
 
@@ -25,14 +28,21 @@ class AutoSettings:
         except Exception:
             pass
         kind = args.auto_settings_type
+        os.makedirs(args.auto_settings_work_dir, exist_ok=True)
+        # what profiled runs taught earlier searches in this work directory is reused: measured operator times and the
+        # per-dimension communication lines
+        from .comm_predictors import CommPredictors
+        from .operator_db import OperatorDB
+        db = OperatorDB(os.path.join(args.auto_settings_work_dir, "operator_db.sqlite"))
+        comm = CommPredictors(hw)
         if kind == "white":
-            best = white_search(model, world, hw)
+            best = white_search(model, world, hw, db=db if len(db) else None)
         else:
             from .executor import TorchrunExecutor
             base = self._base_flags(args)
-            ex = TorchrunExecutor(base, world, master_port=args.master_port + 7)
-            best = black_search(model, world, hw, ex) if kind == "black" else mixed_search(model, world, hw, ex)
-        os.makedirs(args.auto_settings_work_dir, exist_ok=True)
+            ex = TorchrunExecutor(base, world, master_port=args.master_port + 7,
+                                  profile_dir=os.path.join(args.auto_settings_work_dir, "profiles") if kind == "mixed" else None)
+            best = black_search(model, world, hw, ex) if kind == "black" else mixed_search(model, world, hw, ex, db=db, comm=comm)
         out = [{"rank": i, "config": e.config.as_dict(), "flags": e.config.to_flags(), "step_ms": e.step_ms, "memory_gib": e.memory_gib,
                 "detail": e.detail} for i, e in enumerate(best)]
         with open(os.path.join(args.auto_settings_work_dir, "auto_settings_result.json"), "w") as f:

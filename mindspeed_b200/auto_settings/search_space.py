@@ -110,3 +110,34 @@ def build_search_space(model: ModelDesc, world: int, gpus_per_node: int = 8, min
                         for rl in sorted({0, per_stage // 2, per_stage}):
                             out.append(SearchConfig(tp=tp, cp=cp, pp=pp, dp=dp, ep=ep, mbs=mbs, recompute_layers=rl))
     return out
+
+
+def stage_1_prune(configs: List[SearchConfig], model: ModelDesc, memory_fn, budget_gib: float) -> List[SearchConfig]:
+    """First-stage pruning before anything is timed (reference rules: mindspeed/auto_settings/module/search/
+    stage_1_prune.py:33-102):
+      * drop what cannot fit: configurations whose modelled memory exceeds the budget even with every layer recomputed;
+      * among configurations that differ only in the number of recomputed layers keep the smallest count that fits
+        (more recompute is never faster);
+      * drop pipeline splits with fewer micro-batches than 2 x stages (bubble above one third) when a configuration with the
+        same tensor / context sizes and a shallower pipeline fits;
+      * drop context parallelism when the same configuration without it fits (it only adds ring traffic)."""
+    by_key = {}
+    for c in configs:
+        mem = memory_fn(model, c)["total"]
+        if mem > budget_gib:
+            continue
+        k = (c.tp, c.cp, c.pp, c.vpp, c.dp, c.ep, c.mbs, c.sequence_parallel, c.use_distributed_optimizer, c.fused_tp_comm)
+        if k not in by_key or c.recompute_layers < by_key[k].recompute_layers:
+            by_key[k] = c
+    kept = list(by_key.values())
+    fits = {(c.tp, c.cp, c.pp, c.ep, c.mbs) for c in kept}
+    out = []
+    for c in kept:
+        n_mb = model.global_batch_size // (c.dp * c.mbs)
+        shallower = any((c.tp, c.cp, p, c.ep, c.mbs) in fits for p in range(1, c.pp))
+        if c.pp > 1 and n_mb < 2 * c.pp and shallower:
+            continue
+        if c.cp > 1 and any((c.tp, q, c.pp, e, c.mbs) in fits for q in range(1, c.cp) for e in (c.ep, max(1, c.ep // 2))):
+            continue
+        out.append(c)
+    return out
