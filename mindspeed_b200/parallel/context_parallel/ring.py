@@ -11,8 +11,9 @@ reference: mindspeed/core/context_parallel/ring_context_parallel/ring_context_pa
 bookkeeping mindspeed/core/context_parallel/utils.py:122-206,300-340; KV cache policy
 context_parallel_kv_cache.py:5-133; double ring groups model_parallel_utils.py:121-212.
 
-On one NVSwitch domain every peer is one hop away, so the ring order carries no locality; the window
-(``--cp-window-size``) is accepted and arranges the same exchanges as inner / outer rings.
+``--cp-window-size w`` turns the ring into a double ring (``ring_schedule``): w - 1 hops inside a window of w ranks, then one
+hop to the next window.  On one NVSwitch domain every peer is one hop away and the order carries no locality; across nodes the
+window is the node, so only every w-th hop crosses the slower links.
 """
 from __future__ import annotations
 
@@ -41,7 +42,14 @@ class RingP2P:
         self.reqs = []
         self.even = i % 2 == 0
 
-    def async_send_recv(self, send_tensor, recv_tensor):
+    def async_send_recv(self, send_tensor, recv_tensor, dst=None, src=None):
+        """Send to ``dst`` and receive from ``src`` (global ranks; default: the ring neighbours).  With explicit peers the
+        two transfers go out as one batched call, which needs no even / odd ordering."""
+        if dst is not None or src is not None:
+            ops = [dist.P2POp(dist.isend, send_tensor, self.next if dst is None else dst, self.group),
+                   dist.P2POp(dist.irecv, recv_tensor, self.prev if src is None else src, self.group)]
+            self.reqs.extend(dist.batch_isend_irecv(ops))
+            return
         g_send = self.group
         g_recv = self.group_overlap if self.group_overlap is not None else self.group
         if self.group_overlap is not None and not self.even:
@@ -65,22 +73,46 @@ def _halves(t):
     return t[:c], t[c:]
 
 
+def _pack_kv(k, v):
+    """K and V travel as one message: stacked when they have the same shape, else concatenated along the head dimension
+    (multi-latent attention: K carries the rotary part, so its head dimension is larger than V's; reference:
+    mindspeed/core/context_parallel/utils.py:143-197)."""
+    if k.shape == v.shape:
+        return torch.stack((k, v)).contiguous()
+    return torch.cat((k, v), dim=-1).contiguous()
+
+
+def _unpack_kv(kv, dk, same):
+    if same:
+        return kv[0], kv[1]
+    return kv[..., :dk].contiguous(), kv[..., dk:].contiguous()
+
+
+def _pack_grads(gk, gv, same):
+    return torch.stack((gk, gv)).float() if same else torch.cat((gk, gv), dim=-1).float()
+
+
 class _RingAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, group, ranks, group_overlap, causal, scale, cache_kv):
+    def forward(ctx, q, k, v, group, ranks, group_overlap, causal, scale, cache_kv, window=1):
         cp = len(ranks)
         rank = ranks.index(dist.get_rank())
         ring = RingP2P(ranks, group, group_overlap)
-        kv = torch.stack((k, v)).contiguous()           # [2, s, b, nkv, d]
+        srcs, send_to, recv_from, _ = ring_schedule(cp, rank, window)
+        same, dk = k.shape == v.shape, k.shape[-1]
+        kv = _pack_kv(k, v)                               # [2, s, b, nkv, d], or [s, b, nkv, dk + dv]
         nxt = torch.empty_like(kv)
         out = lse = None
         blocks = []                                       # what each step needs for backward
         kv_cache = []
         for i in range(cp):
             if i < cp - 1:
-                ring.async_send_recv(kv, nxt)
-            src = (rank - i) % cp
-            kk, vv = kv[0], kv[1]
+                if window > 1:
+                    ring.async_send_recv(kv, nxt, ranks[send_to[i]], ranks[recv_from[i]])
+                else:
+                    ring.async_send_recv(kv, nxt)
+            src = srcs[i]
+            kk, vv = _unpack_kv(kv, dk, same)
             if not causal or i == 0:
                 o, l, c = A.attn_fwd_block(q, kk, vv, causal and i == 0, scale)
                 mode = 0
@@ -106,21 +138,23 @@ class _RingAttention(torch.autograd.Function):
                 ring.wait()
                 kv, nxt = nxt, kv
         ctx.save_for_backward(q, k, v, out, lse, *(kv_cache if cache_kv else []))
-        ctx.meta = (group, ranks, group_overlap, causal, scale, blocks, cache_kv)
+        ctx.meta = (group, ranks, group_overlap, causal, scale, blocks, cache_kv, window)
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        group, ranks, group_overlap, causal, scale, blocks, cache_kv = ctx.meta
+        group, ranks, group_overlap, causal, scale, blocks, cache_kv, window = ctx.meta
         saved = ctx.saved_tensors
         q, k, v, out, lse = saved[:5]
         cache = list(saved[5:])
         cp = len(ranks)
         rank = ranks.index(dist.get_rank())
+        srcs, send_to, recv_from, home_from = ring_schedule(cp, rank, window)
+        same, dk = k.shape == v.shape, k.shape[-1]
         dout = dout.contiguous()
         kv_ring = RingP2P(ranks, group, group_overlap)
         dkv_ring = RingP2P(ranks, group, group_overlap)
-        kv = torch.stack((k, v)).contiguous()
+        kv = _pack_kv(k, v)
         nxt = torch.empty_like(kv)
         dq = torch.zeros_like(q, dtype=torch.float32)
         dkv = torch.zeros_like(kv, dtype=torch.float32)  # gradient of the block currently held; travels with it
@@ -130,42 +164,91 @@ class _RingAttention(torch.autograd.Function):
             if cache_kv:
                 kv = cache[i]
             elif i < cp - 1:
-                kv_ring.async_send_recv(kv, nxt)
+                if window > 1:
+                    kv_ring.async_send_recv(kv, nxt, ranks[send_to[i]], ranks[recv_from[i]])
+                else:
+                    kv_ring.async_send_recv(kv, nxt)
             mode, c = blocks[i]
-            kk, vv = kv[0], kv[1]
+            kk, vv = _unpack_kv(kv, dk, same)
             if mode == 0:
                 gq, gk, gv = A.attn_bwd_block(dout, q, kk, vv, out, lse, causal and i == 0, scale, c)
                 dq += gq.float()
-                blk = torch.stack((gk, gv)).float()
+                blk = _pack_grads(gk, gv, same)
             elif mode == 1:
                 gq, gk, gv = A.attn_bwd_block(dout, q, _halves(kk)[0], _halves(vv)[0], out, lse, False, scale, c)
                 dq += gq.float()
                 blk = torch.zeros_like(dkv)
-                blk[0, :h], blk[1, :h] = gk.float(), gv.float()
+                if same:
+                    blk[0, :h], blk[1, :h] = gk.float(), gv.float()
+                else:
+                    blk[:h] = torch.cat((gk, gv), dim=-1).float()
             else:
                 gq, gk, gv = A.attn_bwd_block(dout[h:], q[h:], kk, vv, out[h:], lse[..., h:].contiguous(), False, scale, c)
                 dq[h:] += gq.float()
-                blk = torch.stack((gk, gv)).float()
+                blk = _pack_grads(gk, gv, same)
             if i > 0:
                 dkv_ring.wait()
                 dkv = dkv_recv + blk
                 dkv_recv = torch.empty_like(dkv)
             else:
                 dkv = blk
-            # pass the accumulated gradient of this block on, together with the block itself
-            dkv_ring.async_send_recv(dkv, dkv_recv)
+            # pass the accumulated gradient of this block on, together with the block itself; after the last step it goes
+            # straight to the block's origin
+            if window > 1:
+                if i < cp - 1:
+                    dkv_ring.async_send_recv(dkv, dkv_recv, ranks[send_to[i]], ranks[recv_from[i]])
+                else:
+                    dkv_ring.async_send_recv(dkv, dkv_recv, ranks[srcs[i]], ranks[home_from])
+            else:
+                dkv_ring.async_send_recv(dkv, dkv_recv)
             if not cache_kv and i < cp - 1:
                 kv_ring.wait()
                 kv, nxt = nxt, kv
         dkv_ring.wait()
-        dkv = dkv_recv  # after cp hops the gradient of the local block is home
-        return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None, None, None, None, None, None
+        dkv = dkv_recv  # the gradient of the local block is home
+        if same:
+            gk_home, gv_home = dkv[0], dkv[1]
+        else:
+            gk_home, gv_home = dkv[..., :dk], dkv[..., dk:]
+        return dq.to(q.dtype), gk_home.to(k.dtype), gv_home.to(v.dtype), None, None, None, None, None, None, None
 
 
-def _double_ring_order(ranks, window):
-    """Visiting order for a double ring: the inner ring turns inside a window, the outer ring shifts by whole
-    windows.  On NVSwitch the sequence of sources is what matters; it is a permutation of the plain ring."""
-    return ranks
+def ring_schedule(cp: int, rank: int, window: int = 1):
+    """Who holds what, step by step.  Returns (src, send_to, recv_from, home_from): at step i this rank works on the block
+    that originated on ``src[i]``; after the step it passes the block to ``send_to[i]`` and receives the next one from
+    ``recv_from[i]`` (i < cp - 1); ``home_from`` is the rank that holds this rank's own block at the last step, i.e. where
+    its dK / dV come home from.  All values are indices into the group's rank list.
+
+    window == 1: the plain ring.  window = w > 1 (``--cp-window-size``): a double ring - w - 1 hops around the inner ring of
+    the rank's window, then one hop on the outer ring to the same inner position of the next window, and so on; on
+    multi-node jobs the window is chosen as the node so that only every w-th hop leaves it
+    (reference: mindspeed/core/context_parallel/model_parallel_utils.py:121-212 builds the two ring groups,
+    ring_context_parallel.py:918-1028 alternates them)."""
+    w = max(1, int(window))
+    if cp % w != 0:
+        raise ValueError(f"cp_window_size {w} does not divide the context-parallel size {cp}")
+    W = cp // w
+
+    def walk(r):
+        """The sequence of ranks that the block starting on r visits."""
+        win, pos = divmod(r, w)
+        seq = [r]
+        for i in range(cp - 1):
+            if w > 1 and i % w != w - 1:
+                pos = (pos + 1) % w                  # inner hop
+            elif w > 1:
+                win = (win + 1) % W                  # outer hop
+            else:
+                pos, win = 0, (win + 1) % W          # plain ring over single-rank windows
+            seq.append(win * w + pos)
+        return seq
+
+    walks = [walk(r) for r in range(cp)]
+    src = [next(o for o in range(cp) if walks[o][i] == rank) for i in range(cp)]
+    send_to = [walks[src[i]][i + 1] for i in range(cp - 1)]
+    recv_from = [walks[src[i + 1]][i] for i in range(cp - 1)]
+    home_from = walks[rank][cp - 1]
+    return src, send_to, recv_from, home_from
 
 
 def ring_attention(q, k, v, config=None, causal=True, softmax_scale=None, layer_number=1, group=None, ranks=None,
@@ -178,5 +261,8 @@ def ring_attention(q, k, v, config=None, causal=True, softmax_scale=None, layer_
     policy = getattr(config, "context_parallel_kv_cache_policy", None) if config is not None else None
     interval = getattr(config, "context_parallel_cache_interval", 0) if config is not None else 0
     cache = policy in ("full", "half") and (interval == 0 or (layer_number - 1) % (interval + 1) == 0)
+    window = int(getattr(config, "cp_window_size", 1) or 1) if config is not None else 1
+    if window >= len(ranks) or len(ranks) % max(window, 1) != 0:
+        window = 1
     return _RingAttention.apply(q.contiguous(), k.contiguous(), v.contiguous(), group, list(ranks), group_overlap, causal,
-                                softmax_scale, cache)
+                                softmax_scale, cache, window)

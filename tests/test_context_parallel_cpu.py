@@ -37,8 +37,11 @@ def _run(rank, world, algo, nq, nkv, causal, extra):
     cfg.context_parallel_cache_interval = 0
     cfg.use_ulysses_allgather_kv = bool(extra.get("allgather_kv", False))
     cfg.hamilton_path_num = extra.get("paths", 0)
+    cfg.cp_window_size = extra.get("window", 1)
     s, b, d = 32 * world, 2, 16
     q, k, v, w = _full(3, s, b, nq, nkv, d)
+    if extra.get("dv"):
+        v, w = v[..., :extra["dv"]].contiguous(), w[..., :extra["dv"]].contiguous()
     qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
     ref = attention_ref(qf, kf, vf, causal=causal)
     (ref * w).sum().backward()
@@ -63,6 +66,13 @@ def _run(rank, world, algo, nq, nkv, causal, extra):
     ("ulysses_cp_algo", 4, 4, 2, True, {}),
     ("ulysses_cp_algo", 4, 4, 2, True, {"allgather_kv": True}),       # fewer KV heads than ranks: K/V gathered along the sequence
     ("ulysses_cp_algo", 2, 4, 1, True, {"allgather_kv": True}),
+    # double ring: hops inside windows of 2, then across windows; gradients return straight to the block's origin
+    ("megatron_cp_algo", 4, 4, 2, True, {"window": 2}),
+    ("megatron_cp_algo", 6, 2, 2, True, {"window": 3}),
+    ("megatron_cp_algo", 4, 4, 4, False, {"window": 2}),
+    # K and V with different head dimensions (multi-latent attention) travel as one concatenated message
+    ("megatron_cp_algo", 4, 4, 4, True, {"dv": 8}),
+    ("megatron_cp_algo", 4, 4, 4, True, {"dv": 8, "window": 2}),
     ("kvallgather_cp_algo", 2, 4, 2, True, {}),
     ("hybrid_cp_algo", 4, 4, 4, True, {}),
     # Hamilton: the KV block split over edge-disjoint cycles (strides coprime to the group size), full attention
@@ -148,3 +158,21 @@ def test_hamilton_cycles_are_hamiltonian_and_edge_disjoint():
             assert len(seen) == n and r == 0        # visits every rank once and closes
     with pytest.raises(ValueError):
         hamilton_strides(8, 5)                      # 8 ranks have 4 such cycles
+
+
+def test_double_ring_schedule_is_consistent():
+    from mindspeed_b200.parallel.context_parallel.ring import ring_schedule
+    for cp, w in ((4, 1), (4, 2), (8, 4), (8, 2), (6, 3)):
+        sch = [ring_schedule(cp, r, w) for r in range(cp)]
+        for r in range(cp):
+            src, send_to, recv_from, home = sch[r]
+            assert sorted(src) == list(range(cp)) and src[0] == r          # every block once, the local one first
+            for i in range(cp - 1):
+                assert sch[send_to[i]][2][i] == r                          # my receiver expects me
+                assert sch[recv_from[i]][0][i] == src[i + 1]               # and I get the block my sender was working on
+                if w > 1:
+                    same_window = send_to[i] // w == r // w
+                    assert same_window == (i % w != w - 1)                 # w - 1 inner hops, then one outer hop
+            assert sch[home][0][cp - 1] == r                               # my block's gradient comes home from its last holder
+    with pytest.raises(ValueError):
+        ring_schedule(6, 0, 4)
