@@ -165,14 +165,20 @@ def finalize_async_save(blocking: bool = True):
 
 def generate_state_dict(model, optimizer, opt_param_scheduler, iteration, args=None, rng=True):
     sharded: Dict[str, ShardedTensor] = {}
+    from ..parallel.distributed.fsdp import FullyShardedDataParallel
     for chunk in model:      # keys carry global layer numbers, so chunks of one model never collide
-        sharded.update(model_sharded_state_dict(chunk, ""))
+        if isinstance(chunk, FullyShardedDataParallel):
+            sharded.update(chunk.sharded_state_dict(""))       # flat per-parameter pieces of the rank's shard
+        else:
+            sharded.update(model_sharded_state_dict(chunk, ""))
     common = {"iteration": iteration, "checkpoint_version": 3.0}
     if args is not None:
         common["args"] = {k: v for k, v in vars(args).items() if isinstance(v, (int, float, str, bool, list, tuple, type(None)))}
     if optimizer is not None and hasattr(optimizer, "sharded_state_dict"):
         sharded.update(optimizer.sharded_state_dict())
-        common["optimizer"] = {"step": optimizer.step_count, "param_groups": [dict(g) for g in optimizer.param_groups]}
+        step = optimizer.step_count if hasattr(optimizer, "step_count") else optimizer.param_groups[0].get("step", 0)
+        common["optimizer"] = {"step": step, "param_groups": [{k: v for k, v in g.items() if not torch.is_tensor(v)}
+                                                              for g in optimizer.param_groups]}
     if opt_param_scheduler is not None:
         common["opt_param_scheduler"] = opt_param_scheduler.state_dict()
     if rng:
@@ -254,9 +260,13 @@ def load_checkpoint(model, optimizer, opt_param_scheduler, load_dir=None, args=N
     load_optim = optimizer is not None and not getattr(args, "no_load_optim", False)
     sharded, _ = generate_state_dict(model, optimizer if load_optim else None, None, it, None, rng=False)
     _load_sharded(sharded, path, strict=strict)
+    for chunk in model:
+        if hasattr(chunk, "post_load"):
+            chunk.post_load()
     common = torch.load(os.path.join(path, "common.pt"), weights_only=False)
     if load_optim and "optimizer" in common:
-        optimizer.step_count = common["optimizer"]["step"]
+        if hasattr(optimizer, "step_count"):
+            optimizer.step_count = common["optimizer"]["step"]
         for g, s in zip(optimizer.param_groups, common["optimizer"]["param_groups"]):
             g.update(s)
         # fp32 params update in place; bf16 models keep their master copy in the optimizer (already loaded)

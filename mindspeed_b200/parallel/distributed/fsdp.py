@@ -103,6 +103,13 @@ class ShardedUnit:
         self.params: List[nn.Parameter] = [p for p in module.parameters(recurse=True) if not getattr(p, "_fsdp_owned", False)]
         for p in self.params:
             p._fsdp_owned = True
+        ids = {id(p): n for n, p in module.named_parameters(recurse=True)}
+        self.param_names = [ids.get(id(p), f"param{i}") for i, p in enumerate(self.params)]
+        # tensor-parallel bookkeeping: a parameter split over the tensor-parallel ranks holds different values on each of
+        # them; the rest is duplicated there (its gradient norm counts once), and the duplicated ones that see only a
+        # sequence slice per rank (norm weights under sequence parallelism) need their gradients summed over those ranks
+        self.tp_sharded = [bool(getattr(p, "tensor_model_parallel", False)) or not getattr(p, "allreduce", True) for p in self.params]
+        self.seq_replicated = [bool(getattr(p, "sequence_parallel", False)) for p in self.params]
         self.shapes = [p.shape for p in self.params]
         self.numels = [p.numel() for p in self.params]
         total = sum(self.numels)
@@ -216,6 +223,7 @@ class ShardedUnit:
             return
         self._reduced = True
         dev = self.flat_shard.device
+        self._sum_sequence_parallel_grads()
         flat = torch.zeros(self.padded, dtype=self.reduce_dtype, device=dev)
         off = 0
         for p, n in zip(self.params, self.numels):
@@ -236,6 +244,52 @@ class ShardedUnit:
             self.opt_param.grad = g
         else:
             self.opt_param.grad.add_(g)
+
+    def _sum_sequence_parallel_grads(self):
+        """Parameters that every tensor-parallel rank holds in full but applies to its own slice of the sequence (norm
+        weights under sequence parallelism): their gradient is the sum over the tensor-parallel ranks."""
+        from .. import parallel_state as ps
+        if not ps.model_parallel_is_initialized() or ps.get_tensor_model_parallel_world_size() == 1:
+            return
+        grads = [p.grad for p, sr in zip(self.params, self.seq_replicated) if sr and p.grad is not None]
+        if not grads:
+            return
+        flat = torch.cat([g.reshape(-1).float() for g in grads])
+        dist.all_reduce(flat, group=ps.get_tensor_model_parallel_group())
+        off = 0
+        for g in grads:
+            g.copy_(flat[off:off + g.numel()].view_as(g))
+            off += g.numel()
+
+    def local_range(self):
+        """[lo, hi) of the flat (padded) parameter space that this rank's optimizer parameter covers."""
+        lo = self.s_rank * self.per
+        if self.plan.zero1_over_replicas and self.R > 1:
+            lo += self.r_rank * self.own
+        return lo, lo + self.own
+
+    def param_slices(self, lo: int, hi: int):
+        """(index, name, start inside the parameter, start inside [lo, hi), length) for every parameter that overlaps the
+        flat range [lo, hi)."""
+        out, off = [], 0
+        for i, (name, n) in enumerate(zip(self.param_names, self.numels)):
+            a, b = max(lo, off), min(hi, off + n)
+            if b > a:
+                out.append((i, name, a - off, a - lo, b - a))
+            off += n
+        return out
+
+    def norm_weight_mask(self):
+        """1 where an element of the local optimizer parameter counts towards the global gradient norm on this rank:
+        parameters duplicated over the tensor-parallel ranks count on tensor-parallel rank 0 only; padding never."""
+        from .. import parallel_state as ps
+        lo, hi = self.local_range()
+        mask = torch.zeros(hi - lo, dtype=torch.float32, device=self.flat_shard.device)
+        tp_rank = ps.get_tensor_model_parallel_rank() if ps.model_parallel_is_initialized() else 0
+        for i, _, _, at, n in self.param_slices(lo, hi):
+            if self.tp_sharded[i] or tp_rank == 0:
+                mask[at:at + n] = 1.0
+        return mask
 
     def post_step(self):
         """LayerZeRO: rebuild the parameter shard from the slices the replicas own."""
@@ -342,6 +396,37 @@ class FullyShardedDataParallel(nn.Module):
                     out[names[id(p)]] = t
         return out
 
+    def post_load(self):
+        """After a checkpoint has been read into the parameter shards: the optimizer's own slice (a separate tensor in the
+        LayerZeRO layout) follows."""
+        for u in self.units:
+            if u.plan.zero1_over_replicas and u.R > 1:
+                u.opt_param.data.copy_(u.flat_shard[u.r_rank * u.own:(u.r_rank + 1) * u.own])
+
+    def sharded_state_dict(self, prefix: str = ""):
+        """Every parameter as a flat 1-D global tensor of which this rank holds one contiguous piece: written with
+        ``torch.distributed.checkpoint`` and readable under any other shard-group / replica-group size.  Parameters that are
+        split over tensor-parallel ranks (and everything of another pipeline stage) get the rank in their key: resharding
+        across those dimensions is left to the DDP checkpoint path."""
+        from ...checkpointing.sharded import ShardedTensor
+        from .. import parallel_state as ps
+        mp = ps.model_parallel_is_initialized()
+        tp, tpr = (ps.get_tensor_model_parallel_world_size(), ps.get_tensor_model_parallel_rank()) if mp else (1, 0)
+        ppr = ps.get_pipeline_model_parallel_rank() if mp and ps.get_pipeline_model_parallel_world_size() > 1 else None
+        out = {}
+        for u in self.units:
+            lo, hi = u.s_rank * u.per, (u.s_rank + 1) * u.per            # the parameter shard (complete on every replica)
+            for i, name, start, at, n in u.param_slices(lo, hi):
+                qual = name if u.name == "<root>" else f"{u.name}.{name}"
+                key = f"{prefix}fsdp.{qual}"
+                if tp > 1 and u.tp_sharded[i]:
+                    key += f".tp{tpr}of{tp}"
+                if ppr is not None:
+                    key += f".pp{ppr}"
+                replica = u.r_rank + (0 if (u.tp_sharded[i] or tp == 1) else tpr * 1000)
+                out[key] = ShardedTensor(key, u.flat_shard[at:at + n], (u.numels[i],), (start,), replica_id=replica)
+        return out
+
     def memory_summary(self) -> Dict[str, int]:
         shard = sum(u.flat_shard.numel() * u.flat_shard.element_size() for u in self.units)
         opt = sum(u.opt_param.numel() * u.opt_param.element_size() for u in self.units)
@@ -383,7 +468,7 @@ class ShardedAdamW:
                 if u.plan.zero1_over_replicas and u.R > 1:
                     m = m[u.r_rank * u.own:(u.r_rank + 1) * u.own]
                 self.state.append(dict(unit=u, wd_mask=m.clone(), m=torch.zeros_like(u.opt_param, dtype=torch.float32),
-                                       v=torch.zeros_like(u.opt_param, dtype=torch.float32)))
+                                       v=torch.zeros_like(u.opt_param, dtype=torch.float32), norm_mask=u.norm_weight_mask()))
 
     def zero_grad(self, set_to_none=True):
         for w in self.wrappers:
@@ -407,12 +492,17 @@ class ShardedAdamW:
             for st in self.state:
                 gr = st["unit"].opt_param.grad
                 if gr is not None:
-                    sq += gr.float().pow(2).sum()
+                    sq += (gr.float().pow(2) * st["norm_mask"]).sum()
             u0 = self.state[0]["unit"]
             if u0.S > 1:
                 dist.all_reduce(sq, group=u0.shard_group)
             if u0.plan.zero1_over_replicas and u0.R > 1:
                 dist.all_reduce(sq, group=u0.replica_group)
+            from .. import parallel_state as ps
+            if ps.model_parallel_is_initialized():
+                mpg = ps.get_model_parallel_group()
+                if mpg is not None and dist.get_world_size(mpg) > 1:
+                    dist.all_reduce(sq, group=mpg)       # tensor- and pipeline-parallel ranks hold other parameters
             grad_norm = float(sq.sqrt())
             coef = min(1.0, self.clip_grad / (grad_norm + 1e-6))
         bc1, bc2 = 1.0 - b1 ** t, 1.0 - b2 ** t
@@ -429,6 +519,27 @@ class ShardedAdamW:
         for w in self.wrappers:
             w.post_step()
         return True, grad_norm, None
+
+    def sharded_state_dict(self, prefix: str = "optimizer."):
+        """Adam moments laid out like ``FullyShardedDataParallel.sharded_state_dict``: flat per-parameter pieces."""
+        from ...checkpointing.sharded import ShardedTensor
+        from .. import parallel_state as ps
+        mp = ps.model_parallel_is_initialized()
+        tp, tpr = (ps.get_tensor_model_parallel_world_size(), ps.get_tensor_model_parallel_rank()) if mp else (1, 0)
+        ppr = ps.get_pipeline_model_parallel_rank() if mp and ps.get_pipeline_model_parallel_world_size() > 1 else None
+        out = {}
+        for st in self.state:
+            u = st["unit"]
+            lo, hi = u.local_range()
+            split = u.plan.zero1_over_replicas and u.R > 1
+            for i, name, start, at, n in u.param_slices(lo, hi):
+                qual = name if u.name == "<root>" else f"{u.name}.{name}"
+                suffix = (f".tp{tpr}of{tp}" if tp > 1 and u.tp_sharded[i] else "") + (f".pp{ppr}" if ppr is not None else "")
+                replica = (0 if split else u.r_rank) + (0 if (u.tp_sharded[i] or tp == 1) else tpr * 1000)
+                for kind, buf in (("exp_avg", st["m"]), ("exp_avg_sq", st["v"])):
+                    key = f"{prefix}fsdp.{kind}.{qual}{suffix}"
+                    out[key] = ShardedTensor(key, buf[at:at + n], (u.numels[i],), (start,), replica_id=replica)
+        return out
 
     def state_dict(self):
         return {"step": self.param_groups[0]["step"], "m": [s["m"] for s in self.state], "v": [s["v"] for s in self.state]}

@@ -104,13 +104,20 @@ def get_model(model_provider_func, wrap_with_ddp=True):
     cfg = models[0].config
     if getattr(args, "layerzero", False) or getattr(args, "fsdp2_config_path", None):
         # fully sharded data parallel instead of bucketed DDP (+ optional ZeRO-1 of the optimizer state across replicas)
-        if ps.get_tensor_model_parallel_world_size() > 1 or pp > 1:
-            raise NotImplementedError("--layerzero / --fsdp2-config-path run with tensor and pipeline parallel size 1")
+        if pp > 1 and not args.untie_embeddings_and_output_weights:
+            raise NotImplementedError("--layerzero / --fsdp2-config-path with pipeline parallelism need "
+                                      "--untie-embeddings-and-output-weights (a tied weight lives on two stages)")
         from ..parallel.distributed.fsdp import FSDPPlan, FullyShardedDataParallel
         path = getattr(args, "fsdp2_config_path", None) or getattr(args, "layerzero_config", None)
         plan = FSDPPlan.from_yaml(path) if path else FSDPPlan(zero1_over_replicas=bool(getattr(args, "layerzero", False)))
         ranks = ps._ranks("dp")
-        return [FullyShardedDataParallel(m, plan, dp_group_ranks=ranks) for m in models]
+        # group creation is collective over the job: every rank creates the shard / replica groups of every data-parallel
+        # group (one per tensor- and pipeline-parallel coordinate) in the same order; chunks of one rank share theirs
+        from ..parallel.distributed.fsdp import build_groups
+        shard_g, rep_g = build_groups(ranks, plan.shard_size, ps.get_all_ranks("dp"))
+        if shard_g is None and rep_g is None and len(ranks) == 1:
+            shard_g = "local"
+        return [FullyShardedDataParallel(m, plan, dp_group_ranks=ranks, shard_group=shard_g, replica_group=rep_g) for m in models]
     ddp_cfg = DistributedDataParallelConfig(
         grad_reduce_in_fp32=args.accumulate_allreduce_grads_in_fp32, overlap_grad_reduce=args.overlap_grad_reduce,
         quant_grads=bool(getattr(args, "quant_grads", False)),
