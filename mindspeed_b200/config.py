@@ -36,6 +36,10 @@ class ModelParallelConfig:
     params_dtype: torch.dtype = torch.float32
     timers: Optional[Callable] = None
     finalize_model_grads_func: Optional[Callable] = None
+    # 2-D tensor parallelism: tensor_model_parallel_size = tp_x * tp_y
+    tp_2d: bool = False
+    tp_x: int = 1
+    tp_y: int = 1
     grad_scale_func: Optional[Callable] = None
     no_sync_func: Optional[Callable] = None
     grad_sync_func: Optional[Callable] = None
@@ -223,9 +227,10 @@ class TransformerConfig(ModelParallelConfig):
             self.kv_channels = self.hidden_size // self.num_attention_heads
         if self.num_query_groups is None:
             self.num_query_groups = self.num_attention_heads
-        if self.num_query_groups and self.num_query_groups % max(1, self.tensor_model_parallel_size) != 0 \
+        head_split = self.tp_x if self.tp_2d else self.tensor_model_parallel_size     # 2-D: heads split over tp-x only
+        if self.num_query_groups and self.num_query_groups % max(1, head_split) != 0 \
                 and not getattr(self, "unaligned_linear", False):
-            raise ValueError("num_query_groups must be divisible by tensor_model_parallel_size")
+            raise ValueError("num_query_groups must be divisible by tensor_model_parallel_size (tp_x with --tp-2d)")
         if self.apply_query_key_layer_scaling:
             self.attention_softmax_in_fp32 = True
         if self.expert_model_parallel_size > 1 and self.num_moe_experts is None:

@@ -112,8 +112,16 @@ class TransformerLayer(nn.Module):
         self.layer_number = layer_number + get_transformer_layer_offset(config)
         self.hidden_dropout = config.hidden_dropout if hidden_dropout is None else hidden_dropout
         self.input_layernorm = build_norm(config, config.hidden_size)
-        attn_cls = MLASelfAttention if config.multi_latent_attention else SelfAttention
-        self.self_attention = attn_cls(config, self.layer_number, attn_mask_type=getattr(config, "attention_mask_type", "causal"))
+        tp2d = bool(getattr(config, "tp_2d", False))
+        if tp2d:
+            # 2-D tensor parallelism: activations between blocks are [s/x, b, h/y] (parallel/tp2d/layers_2d.py)
+            if config.multi_latent_attention or getattr(config, "attention_mask_type", "causal") != "causal":
+                raise NotImplementedError("--tp-2d supports causal multi-head / grouped-query attention")
+            from ..parallel.tp2d import MLP2D, SelfAttention2D
+            self.self_attention = SelfAttention2D(config, self.layer_number)
+        else:
+            attn_cls = MLASelfAttention if config.multi_latent_attention else SelfAttention
+            self.self_attention = attn_cls(config, self.layer_number, attn_mask_type=getattr(config, "attention_mask_type", "causal"))
         self.pre_mlp_layernorm = build_norm(config, config.hidden_size)
         if is_moe is None:
             is_moe = _is_moe_layer(config, self.layer_number)
@@ -121,6 +129,8 @@ class TransformerLayer(nn.Module):
         if is_moe:
             from ..parallel.moe.moe_layer import MoELayer
             self.mlp = MoELayer(config, layer_number=self.layer_number)
+        elif tp2d:
+            self.mlp = MLP2D(config)
         else:
             self.mlp = MLP(config)
         sel = getattr(config, "compress_activation", None) or []
@@ -263,6 +273,10 @@ class TransformerBlock(nn.Module):
     def forward(self, hidden_states, attention_mask=None, rotary_pos_emb=None, packed_seq_params=None, **kwargs):
         if not self.pre_process:
             hidden_states = self.input_tensor
+        tp2d = bool(getattr(self.config, "tp_2d", False))
+        if tp2d and self.pre_process:
+            from ..parallel.tp2d import to_2d_layout
+            hidden_states = to_2d_layout(hidden_states)          # [s, b, h] from the embedding -> this rank's [s/x, b, h/y]
         if self.fb_overlap is not None and self.training and torch.is_grad_enabled():
             # forward of this micro-batch interleaved with the layer backward of the previous one (--moe-fb-overlap);
             # returns a detached leaf: the schedule's loss backward stops there and seeds the next interleaved backward
@@ -276,4 +290,7 @@ class TransformerBlock(nn.Module):
                                          packed_seq_params=packed_seq_params)
         if self.final_layernorm is not None:
             hidden_states = self.final_layernorm(hidden_states)
+        if tp2d and self.post_process:
+            from ..parallel.tp2d import from_2d_layout
+            hidden_states = from_2d_layout(hidden_states)        # back to [s, b, h] for the output layer
         return hidden_states

@@ -253,6 +253,8 @@ def get_tensor_shapes(*, seq_length, micro_batch_size, config, decoder_seq_lengt
     s = seq_length // ps.get_context_parallel_world_size()
     if config.sequence_parallel:
         s //= ps.get_tensor_model_parallel_world_size()
+    if getattr(config, "tp_2d", False):            # stages hand over the [s/x, b, h/y] tile
+        return [(s // config.tp_x, micro_batch_size, config.hidden_size // config.tp_y)]
     return [(s, micro_batch_size, config.hidden_size)]
 
 
