@@ -9,6 +9,14 @@ def _rel(a, b):
     return (a.float() - b.float()).abs().max().item() / max(1e-6, b.float().abs().max().item())
 
 
+def _elementwise(y, ref, k):
+    """Every element against the fp32 result rounded to the output type: two units in the last place of bf16, plus an
+    absolute term for elements that cancel to near zero (fp32 accumulation order over ``k`` products)."""
+    want = ref.to(y.dtype).float() if y.dtype != torch.float32 else ref
+    rtol = 2.0 ** -7 if y.dtype == torch.bfloat16 else 1e-4
+    torch.testing.assert_close(y.float(), want, rtol=rtol, atol=1e-5 * k + 1e-3)
+
+
 SHAPES = [(128, 256, 64), (256, 512, 128), (1000, 776, 520), (8192, 768, 512), (384, 128, 4096), (130, 264, 72)]
 
 
@@ -23,6 +31,7 @@ def test_linear_fwd(M, N, K):
     G.check_status()
     ref = x.float() @ w.float().t()
     assert _rel(y, ref) < 1e-2, _rel(y, ref)
+    _elementwise(y, ref, K)
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
@@ -36,6 +45,7 @@ def test_linear_dgrad(M, N, K):
     G.check_status()
     ref = dy.float() @ w.float()
     assert _rel(dx, ref) < 1e-2, _rel(dx, ref)
+    _elementwise(dx, ref, N)
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
@@ -53,6 +63,8 @@ def test_linear_wgrad(M, N, K):
     G.check_status()
     assert _rel(dw, ref) < 1e-2
     assert _rel(acc, 1 + 2 * ref) < 1e-2
+    _elementwise(dw, ref, M)
+    _elementwise(acc, 1 + 2 * ref, 2 * M)
 
 
 def test_bias_epilogue_and_determinism():
