@@ -454,6 +454,9 @@ def pretrain(train_valid_test_dataset_provider, model_provider, model_type=None,
                 save_fault_dump(args.iteration, model, optimizer, args.ttp_dump_dir, save_optimizer=args.ttp_save_optimizer,
                                 save_rng=args.ttp_save_rng, keep=args.ttp_max_dump_ckpt_to_keep)
         install_ttp(args, dump_fn=dump)
+        # a kernel that waits for a peer which has died must give up before the heartbeat declares this rank dead too
+        from ..ops import fused_comm
+        fused_comm.WAIT_LIMIT_MS = min(fused_comm.WAIT_LIMIT_MS, max(200, int(args.ttp_heartbeat_timeout_ms * 2 // 3)))
         if not args.load and os.path.isdir(args.ttp_dump_dir) and os.listdir(args.ttp_dump_dir):
             # restart after a fault: wait for the dump of this rank to be complete, then resume from it
             found = wait_for_fault_dump(args.ttp_dump_dir, [args.rank], timeout_s=args.ttp_wait_dump_file_timeout)
