@@ -220,3 +220,32 @@ def test_scaled_masked_softmax_and_ring_update_and_quant():
     assert (q.float() - qr.float()).abs().max() <= 32          # at most one fp8 step apart (rounding of the division)
     h, yn = misc.add_rmsnorm(po, co, torch.ones(d, device="cuda", dtype=torch.bfloat16))
     torch.testing.assert_close(h, po + co)
+
+
+@pytest.mark.parametrize("experts", [False, True])
+def test_fused_ffn_op(experts):
+    """ffn(): both GEMMs on the tcgen05 kernels (dense or one grouped launch), SwiGLU on the fused kernel."""
+    from mindspeed_b200.ops.ffn import ffn
+    torch.manual_seed(5)
+    K, Fh, N = 512, 768, 256
+    if experts:
+        counts = [300, 0, 129, 451]
+        x = torch.randn(sum(counts), K, device="cuda", dtype=torch.bfloat16)
+        w1 = (torch.randn(4, K, 2 * Fh, device="cuda") * 0.05).bfloat16()
+        w2 = (torch.randn(4, Fh, N, device="cuda") * 0.05).bfloat16()
+        y = ffn(x, w1, w2, "swiglu", expert_tokens=torch.tensor(counts, device="cuda"))
+        outs, r = [], 0
+        for e, n in enumerate(counts):
+            h = x[r:r + n].float() @ w1[e].float()
+            outs.append((torch.nn.functional.silu(h[:, :Fh]) * h[:, Fh:]).bfloat16().float() @ w2[e].float())
+            r += n
+        ref = torch.cat(outs)
+    else:
+        x = torch.randn(640, K, device="cuda", dtype=torch.bfloat16)
+        w1 = (torch.randn(K, 2 * Fh, device="cuda") * 0.05).bfloat16()
+        w2 = (torch.randn(Fh, N, device="cuda") * 0.05).bfloat16()
+        y = ffn(x, w1, w2, "swiglu")
+        h = x.float() @ w1.float()
+        ref = (torch.nn.functional.silu(h[:, :Fh]) * h[:, Fh:]).bfloat16().float() @ w2.float()
+    torch.cuda.synchronize()
+    _close(y, ref, torch.bfloat16, 4)
