@@ -513,9 +513,12 @@ class MoEFeature(Feature):
                 raise AssertionError("--moe-fb-overlap needs expert tensor parallel size 1")
             if getattr(args, "moe_pad_expert_input_to_capacity", False):
                 raise AssertionError("--moe-fb-overlap does not support drop-and-pad")
-            if getattr(args, "pipeline_model_parallel_size", 1) > 1:
-                raise AssertionError("--moe-fb-overlap interleaves micro-batches inside one rank's layer stack: it needs "
-                                     "pipeline parallel size 1")
+            if getattr(args, "pipeline_model_parallel_size", 1) > 1 and (
+                    getattr(args, "recompute_in_bubble", False) or getattr(args, "recompute_in_advance", False) or
+                    getattr(args, "schedules_method", None) in ("dualpipe", "chimera") or
+                    getattr(args, "use_multiparameter_pipeline_model_parallel", False)):
+                raise AssertionError("--moe-fb-overlap with pipeline parallelism runs on the 1F1B, interleaved and DualPipeV "
+                                     "schedules, without scheduler-placed recompute or list-valued stage interfaces")
             if getattr(args, "recompute_granularity", None) == "full" or getattr(args, "noop_layers", None):
                 raise AssertionError("--moe-fb-overlap keeps the staged layer graphs: no full recompute, no no-op layers")
         if args.moe_alltoall_mc2 and getattr(args, "use_ascend_mc2", False) and ne:

@@ -222,6 +222,7 @@ class TransformerBlock(nn.Module):
                 layers.append(TransformerLayer(config, layer_number=i + 1))
         self.layers = nn.ModuleList(layers)
         self.num_layers_per_pipeline_rank = n
+        self.fb_state, self.fb_partner = None, None      # pipeline schedules: parallel/moe/fb_overlap.StagedBlockState
         self.fb_overlap = None           # set by the schedule for the duration of one step (parallel/moe/fb_overlap.BlockOverlap)
         self.final_layernorm = build_norm(config, config.hidden_size) if (post_process and post_layer_norm) else None
 
@@ -277,7 +278,14 @@ class TransformerBlock(nn.Module):
         if tp2d and self.pre_process:
             from ..parallel.tp2d import to_2d_layout
             hidden_states = to_2d_layout(hidden_states)          # [s, b, h] from the embedding -> this rank's [s/x, b, h/y]
-        if self.fb_overlap is not None and self.training and torch.is_grad_enabled():
+        if self.fb_state is not None and self.training and torch.is_grad_enabled():
+            # pipeline form of --moe-fb-overlap: staged graphs per (chunk, micro-batch); a partner's backward may ride along
+            from ..parallel.pipeline.executor import current_microbatch
+            cur = current_microbatch()
+            hidden_states = self.fb_state.forward((cur["chunk"], cur["mb"]), hidden_states, partner=self.fb_partner,
+                                                  attention_mask=attention_mask, rotary_pos_emb=rotary_pos_emb,
+                                                  packed_seq_params=packed_seq_params)
+        elif self.fb_overlap is not None and self.training and torch.is_grad_enabled():
             # forward of this micro-batch interleaved with the layer backward of the previous one (--moe-fb-overlap);
             # returns a detached leaf: the schedule's loss backward stops there and seeds the next interleaved backward
             hidden_states = self.fb_overlap.forward(hidden_states, attention_mask=attention_mask, rotary_pos_emb=rotary_pos_emb,

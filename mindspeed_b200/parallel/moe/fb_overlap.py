@@ -331,3 +331,65 @@ class BlockOverlap:
         for g in reversed(graphs):
             grad = backward_layer_staged(g, grad)
         self._finish_input(p_in, grad)
+
+
+class StagedBlockState:
+    """Pipeline form of the overlap: a model chunk's layer stack keeps the staged graphs of every (chunk, micro-batch) whose
+    backward is still to come, and a forward can be given a PARTNER - another chunk's pending micro-batch on the same rank -
+    whose layer backward is then interleaved with it stage by stage (the F || B slots of a pipeline schedule).
+
+        forward(key, hidden, partner=None)   staged forward; with partner = (state, key) the partner's layers run backward
+                                             in between (last layer of the partner against the first layer of this one)
+        backward(key)                        the layer backward of ``key`` if no forward has done it, then the gradient goes
+                                             into the block input (the received activation's ``.grad`` or the embedding)
+    The seed of a backward is the ``.grad`` of the detached output leaf, put there by the stage's own post-processing (loss
+    backward on the last stage, ``torch.autograd.backward(output, received gradient)`` elsewhere).
+    reference: mindspeed/core/transformer/moe/moe_feature/fb_overlap/vpp_schedules.py:300-990 (F || B pairing in the
+    interleaved schedule) and dualpipev/dualpipev_schedules.py:310-346 (overlap phase)."""
+
+    def __init__(self, layers: Sequence):
+        self.staged = [StagedMoELayer(l) for l in layers]
+        self.streams: Optional[_Streams] = None
+        self.records = {}
+
+    def forward(self, key, hidden: torch.Tensor, partner=None, **attn_kw) -> torch.Tensor:
+        if self.streams is None:
+            self.streams = _Streams(hidden.device)
+        graphs: List[LayerGraph] = []
+        h = hidden.detach()
+        if partner is None:
+            for s in self.staged:
+                h, g = forward_layer_staged(s, h, self.streams, **attn_kw)
+                graphs.append(g)
+        else:
+            pstate, pkey = partner
+            p_graphs, p_in, p_leaf = pstate.records[pkey]
+            grad = p_leaf.grad
+            if grad is None:
+                raise RuntimeError("forward/backward overlap: the partner micro-batch has no output gradient yet")
+            n = min(len(self.staged), len(p_graphs))
+            for k in range(n):
+                h, g, grad = forward_backward_overlapped(self.staged[k], h, p_graphs[len(p_graphs) - 1 - k], grad, self.streams, **attn_kw)
+                graphs.append(g)
+            for s in self.staged[n:]:
+                h, g = forward_layer_staged(s, h, self.streams, **attn_kw)
+                graphs.append(g)
+            for g in reversed(p_graphs[:len(p_graphs) - n]):
+                grad = backward_layer_staged(g, grad)
+            pstate.records[pkey] = (None, p_in, grad)                   # layers done: only the block input is left
+        leaf = h.detach().requires_grad_(True)
+        self.records[key] = (graphs, hidden, leaf)
+        return leaf
+
+    def backward(self, key):
+        graphs, block_input, x = self.records.pop(key)
+        if graphs is None:
+            grad = x
+        else:
+            grad = x.grad
+            if grad is None:
+                return
+            for g in reversed(graphs):
+                grad = backward_layer_staged(g, grad)
+        if isinstance(block_input, torch.Tensor) and block_input.requires_grad and grad is not None:
+            block_input.backward(grad)

@@ -151,6 +151,103 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
                 ten = ten.contiguous()
                 pending_send.append((dist.isend(ten, pp_ranks[m.dst], group=comm_of(m)), ten))   # keep the tensor alive
 
+    # ---- forward/backward overlap (--moe-fb-overlap): every chunk's layer stack keeps staged graphs; a slot that holds an F
+    # and a B runs the B's layer backward interleaved with the F's layer forward on two streams ----
+    fb_mode = bool(getattr(config, "moe_fb_overlap", False)) and not forward_only
+    blocks = []
+    if fb_mode:
+        from ...models.transformer import TransformerBlock
+        from ..moe.fb_overlap import StagedBlockState
+        for chunk in model:
+            blk = next(m for m in chunk.modules() if isinstance(m, TransformerBlock))
+            blk.fb_state, blk.fb_partner = StagedBlockState(blk.layers), None
+            blocks.append(blk)
+
+    def enter(op):
+        pipe, stage = pl.stage_of[(rank, op.chunk)]
+        _CURRENT.update(chunk=op.chunk, mb=op.mb, pipe=pipe)
+        ps.set_virtual_pipeline_model_parallel_world_size(None)
+        ps.set_stage_override(stage == 0, stage == Sn - 1)
+        return pipe, stage
+
+    def fb_forward(op, partner=None):
+        nonlocal total_tokens
+        pipe, stage = enter(op)
+        inp = None
+        if stage > 0:
+            inp = inbox.pop(("act", op.chunk, op.mb))
+            for x in inp:
+                if x.is_floating_point():
+                    x.requires_grad_(True)
+            inp = unwrap(inp)
+        blocks[op.chunk].fb_partner = partner
+        try:
+            out, nt = S.forward_step(forward_step_func, data_iterator[op.chunk], model[op.chunk], num_microbatches, inp, store,
+                                     config, collect_non_loss_data, current_microbatch=op.mb)
+        finally:
+            blocks[op.chunk].fb_partner = None
+        total_tokens += nt.cpu() if torch.is_tensor(nt) else nt
+        inputs[(op.chunk, op.mb)], outputs[(op.chunk, op.mb)] = inp, out
+        if stage < Sn - 1:
+            dr, dc = pl.holder(pipe, stage + 1)
+            outs = list(out) if isinstance(out, (list, tuple)) else [out]
+            if dr == rank:
+                inbox[("act", dc, op.mb)] = [o.detach().clone() for o in outs]
+            else:
+                outbox[("act", op.chunk, op.mb)] = [o.detach() for o in outs]
+
+    def fb_seed(op):
+        """The part of a backward that lies after the layer stack (loss, output layer, final norm - or nothing): leaves the
+        gradient of the stack's output in its detached leaf."""
+        pipe, stage = enter(op)
+        out = outputs.pop((op.chunk, op.mb))
+        if stage == Sn - 1:
+            loss = out
+            if getattr(config, "grad_scale_func", None) is not None:
+                loss = config.grad_scale_func(loss)
+            loss.backward()
+        else:
+            og = inbox.pop(("grad", op.chunk, op.mb))
+            torch.autograd.backward(out, unwrap(og))
+
+    def fb_finish(op):
+        pipe, stage = enter(op)
+        inp = inputs.pop((op.chunk, op.mb))
+        blocks[op.chunk].fb_state.backward((op.chunk, op.mb))
+        if stage > 0:
+            g = inp.grad if inp.grad is not None else torch.zeros_like(inp)
+            dr, dc = pl.holder(pipe, stage - 1)
+            if dr == rank:
+                inbox[("grad", dc, op.mb)] = [g]
+            else:
+                outbox[("grad", op.chunk, op.mb)] = [g]
+
+    def fb_slot(ops):
+        fs = [o for o in ops if o.kind == "F"]
+        bs = [o for o in ops if o.kind == "B"]
+        if has_w and bs:
+            WeightGradStore.enable(True)
+        if len(fs) == 1 and len(bs) == 1:
+            b = bs[0]
+            fb_seed(b)
+            fb_forward(fs[0], partner=(blocks[b.chunk].fb_state, (b.chunk, b.mb)))
+            fb_finish(b)
+        else:
+            for o in ops:
+                if o.kind == "F":
+                    fb_forward(o)
+                elif o.kind == "B":
+                    fb_seed(o)
+                    fb_finish(o)
+        if has_w and bs:
+            WeightGradStore.flush()
+            WeightGradStore.enable(False)
+        for o in ops:
+            if o.kind == "W":
+                WeightGradStore.pop()
+            elif o.kind == "R":
+                raise RuntimeError("scheduler-placed recompute is not combined with --moe-fb-overlap")
+
     try:
         if overlap:
             post_recvs(0)
@@ -182,7 +279,9 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
                         r.wait()
                 for m, buf in bufs:
                     inbox[(m.kind, m.dst_chunk, m.mb)] = buf
-            for op in plan.table[rank][t]:
+            if fb_mode:
+                fb_slot(plan.table[rank][t])
+            for op in ([] if fb_mode else plan.table[rank][t]):
                 if forward_only and op.kind != "F":
                     continue
                 pipe, stage = pl.stage_of[(rank, op.chunk)]
@@ -259,6 +358,8 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
         ps.set_stage_override(None, None)
         ps.set_virtual_pipeline_model_parallel_rank(saved_vpp[0])
         ps.set_virtual_pipeline_model_parallel_world_size(saved_vpp[1])
+        for blk in blocks:
+            blk.fb_state, blk.fb_partner = None, None
         if has_w:
             WeightGradStore.pop_all()
             WeightGradStore.enable(False)

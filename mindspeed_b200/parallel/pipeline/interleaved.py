@@ -6,10 +6,17 @@ from .plan import build_plan
 _CACHE = {}
 
 
-def _plan(name, pp, n, vpp=None, split_w=True):
-    k = (name, pp, n, vpp, split_w)
+def _plan(name, pp, n, vpp=None, split_w=True, pair_fb=None):
+    """``pair_fb`` None: follow ``--moe-fb-overlap`` (F and B of different micro-batches share a slot and are interleaved)."""
+    if pair_fb is None:
+        try:
+            from ...training.global_vars import get_args
+            pair_fb = bool(getattr(get_args(), "moe_fb_overlap", False))
+        except RuntimeError:
+            pair_fb = False
+    k = (name, pp, n, vpp, split_w, pair_fb)
     if k not in _CACHE:
-        _CACHE[k] = build_plan(name, pp, n, vpp=vpp, split_w=split_w)
+        _CACHE[k] = build_plan(name, pp, n, vpp=vpp, split_w=split_w, pair_fb=pair_fb)
     return _CACHE[k]
 
 

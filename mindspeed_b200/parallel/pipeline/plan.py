@@ -342,6 +342,22 @@ def assign_slots(placement: Placement, orders: List[List[Op]], n_mb: int, pair_f
                     ptr[r] += 1
                     remaining -= 1
                     progressed = True
+                    # forward/backward overlap: an F directly followed by a B of another micro-batch (or the other way round)
+                    # shares the slot when that op's inputs are ready too - the executor interleaves the two
+                    if pair_fb and op.kind in ("F", "B") and ptr[r] < len(orders[r]):
+                        nx = orders[r][ptr[r]]
+                        if {nx.kind, op.kind} == {"F", "B"} and (nx.chunk, nx.mb) != (op.chunk, op.mb):
+                            npipe, nstage = placement.stage_of[(r, nx.chunk)]
+                            if nx.kind == "F":
+                                nok = nstage == 0 or done.get((npipe, nstage - 1, "F", nx.mb), 1 << 30) < t
+                            else:
+                                nok = done.get((npipe, nstage, "F", nx.mb), 1 << 30) < t and \
+                                    (nstage == S - 1 or done.get((npipe, nstage + 1, "B", nx.mb), 1 << 30) < t)
+                            if nok:
+                                ops_here.append(nx)
+                                finished_now.append((npipe, nstage, nx.kind, nx.mb, r))
+                                ptr[r] += 1
+                                remaining -= 1
                     # a W directly after its B may share the slot (same rank, no communication in between)
                     while ptr[r] < len(orders[r]) and orders[r][ptr[r]].kind == "W":
                         w = orders[r][ptr[r]]
@@ -486,7 +502,7 @@ def recomputed_forwards(orders: List[List[Op]]) -> List[set]:
 
 
 def build_plan(name: str, pp: int, n_mb: int, vpp: Optional[int] = None, split_w: bool = True,
-               recompute: Optional[str] = None) -> Plan:
+               recompute: Optional[str] = None, pair_fb: bool = False) -> Plan:
     if name == "1f1b":
         pl, orders = placement_1f1b(pp), order_1f1b(pp, n_mb)
     elif name == "interleaved":
@@ -506,4 +522,4 @@ def build_plan(name: str, pp: int, n_mb: int, vpp: Optional[int] = None, split_w
         raise ValueError(name)
     if recompute:
         orders = insert_recompute(orders, recompute)
-    return assign_slots(pl, orders, n_mb)
+    return assign_slots(pl, orders, n_mb, pair_fb=pair_fb)

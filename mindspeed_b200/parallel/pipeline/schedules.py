@@ -262,8 +262,8 @@ def forward_backward_pipelining_without_interleaving(*, forward_step_func, data_
                                                      seq_length, micro_batch_size, decoder_seq_length=None,
                                                      forward_only=False, collect_non_loss_data=False, first_val_step=None):
     """Non-interleaved 1F1B: warm-up forwards, steady 1F1B, cool-down backwards."""
-    if is_multi_parameter(_cfg(model)):
-        # list-valued stage interfaces are handled by the plan executor (same 1F1B order, as data)
+    if is_multi_parameter(_cfg(model)) or (getattr(_cfg(model), "moe_fb_overlap", False) and not forward_only):
+        # list-valued stage interfaces and forward/backward overlap are handled by the plan executor (same 1F1B order, as data)
         from .executor import run_plan
         from .interleaved import _plan
         plan = _plan("1f1b", ps.get_pipeline_model_parallel_world_size(), num_microbatches)

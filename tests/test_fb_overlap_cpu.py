@@ -116,3 +116,46 @@ def test_training_with_hot_expert_replicas_matches_plain_dispatch():
                                              "--trans-hot-expert-group-num", "2"])[0]
     for a, b in zip(ref, got):
         assert abs(a - b) < 1e-5 * max(1.0, abs(a)), (ref, got)
+
+
+def _train_pp(rank, world, extra):
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import io
+    from contextlib import redirect_stdout
+    import pretrain_gpt as pg
+    from test_pipeline_cpu import BASE
+    from mindspeed_b200.training import pretrain
+    moe = ["--num-experts", "4", "--moe-router-topk", "2", "--moe-token-dispatcher-type", "alltoall", "--moe-grouped-gemm",
+           "--moe-aux-loss-coeff", "0.01", "--expert-model-parallel-size", "2", "--pipeline-model-parallel-size", "2"]
+    with redirect_stdout(io.StringIO()):
+        hist = pretrain(pg.train_valid_test_datasets_provider, pg.model_provider, forward_step_func=pg.forward_step,
+                        args_list=BASE + moe + list(extra))
+    return [h.get("lm loss") for h in hist]
+
+
+@pytest.mark.parametrize("schedule", [[], ["--num-layers-per-virtual-pipeline-stage", "1"], ["--schedules-method", "dualpipev"]])
+def test_pipeline_schedules_with_fb_overlap_match_plain(schedule):
+    """Pipeline 2 x expert parallel 2 on four ranks: with ``--moe-fb-overlap`` the schedules put an F and a B of different
+    micro-batches into one slot and interleave them stage by stage; the losses are those of the unpaired schedule."""
+    ref = run_distributed(_train_pp, 4, schedule)
+    got = run_distributed(_train_pp, 4, schedule + ["--moe-fb-overlap"])
+    ref_l = [r for r in ref if r[0] is not None][0]
+    got_l = [r for r in got if r[0] is not None][0]
+    assert len(ref_l) == 3
+    for a, b in zip(ref_l, got_l):
+        assert abs(a - b) < 1e-5 * max(1.0, abs(a)), (ref_l, got_l)
+
+
+def test_paired_plans_are_valid():
+    from mindspeed_b200.parallel.pipeline.plan import build_plan, validate
+    for name, vpp in (("1f1b", None), ("interleaved", 2), ("dualpipev", None)):
+        for pp in (2, 4):
+            plain, paired = build_plan(name, pp, 8, vpp=vpp), build_plan(name, pp, 8, vpp=vpp, pair_fb=True)
+            validate(paired)
+            assert paired.num_slots < plain.num_slots
+            assert any({o.kind for o in slot} >= {"F", "B"} for r in range(pp) for slot in paired.table[r])
+            for r in range(pp):      # a pair never holds the forward and the backward of one micro-batch of one chunk
+                for slot in paired.table[r]:
+                    fs = {(o.chunk, o.mb) for o in slot if o.kind == "F"}
+                    bs = {(o.chunk, o.mb) for o in slot if o.kind == "B"}
+                    assert not (fs & bs) and len(fs) <= 1 and len(bs) <= 1
