@@ -58,7 +58,16 @@ class CoreAttention(nn.Module):
 
     def forward(self, q, k, v, attention_mask=None, packed_seq_params=None):
         cp = ps.get_context_parallel_world_size()
-        if cp > 1:
+        cu = packed_seq_params.get("cu_seqlens") if isinstance(packed_seq_params, dict) else getattr(packed_seq_params, "cu_seqlens_q", None)
+        if cu is not None:
+            # packed documents (--reset-attention-mask): every document attends to itself only
+            if cp > 1:
+                raise NotImplementedError("packed-sequence attention is not combined with context parallelism")
+            want = getattr(self.config, "attention_backend", "auto")
+            backend = "library" if want == "library" else ("sm100" if self.config.optimization_level >= 1 else None)
+            out = attn_ops.varlen_attention(q, k, v, cu.tolist() if torch.is_tensor(cu) else cu, causal=self.causal,
+                                            softmax_scale=self.softmax_scale, backend=backend)
+        elif cp > 1:
             from ..parallel.context_parallel import dispatch_context_parallel_attention
             out = dispatch_context_parallel_attention(q, k, v, self.config, causal=self.causal,
                                                       softmax_scale=self.softmax_scale, attention_mask=attention_mask,

@@ -111,6 +111,12 @@ class GPTModel(nn.Module):
             s_local = inp.shape[0] * (ps.get_tensor_model_parallel_world_size() if self.config.sequence_parallel else 1)
             dev = inp.device
         rpe = self._rotary(s_local, dev)
+        pos_reset = packed_seq_params.get("position_ids") if isinstance(packed_seq_params, dict) else None
+        if pos_reset is not None and self.rotary_pos_emb is not None:
+            # positions restart at every document (--reset-position-ids): the rotary angles follow them
+            if pos_reset.dim() == 2 and pos_reset.shape[0] != 1:
+                raise NotImplementedError("per-document rotary positions take micro-batch size 1")
+            rpe = self.rotary_pos_emb.get_cos_sin(s_local, dev, positions=pos_reset.reshape(-1).to(dev))
         hidden = self.decoder(decoder_input, attention_mask=attention_mask, rotary_pos_emb=rpe,
                               packed_seq_params=packed_seq_params)
         if not self.post_process:

@@ -184,3 +184,22 @@ def merge_lse(out1, lse1, out2, lse2):
     w2 = torch.exp(lse2 - lse).permute(2, 0, 1).unsqueeze(-1)
     out = out1.float() * w1 + out2.float() * w2
     return out.to(out1.dtype), lse
+
+
+def varlen_attention(q, k, v, cu_seqlens, causal=True, softmax_scale=None, backend=None):
+    """Attention over packed sequences: q / k / v [s, 1, n, d] hold several documents back to back, ``cu_seqlens`` (host
+    integers, first 0, last s) their boundaries; every document attends only to itself.  One attention call per document on
+    the configured backend (the tcgen05 kernels on a GPU), so the cost is the sum of the documents' squares instead of s^2.
+    reference semantics: actual_seq_qlen / actual_seq_kvlen of npu_fusion_attention in the TND layout
+    (mindspeed/ops/fusion_attention_v2.py:22-114) as used by the reset-attention-mask path
+    (mindspeed/core/transformer/flash_attention/reset_attention_mask/adaptor.py:218-759)."""
+    if q.shape[1] != 1:
+        raise ValueError("packed-sequence attention takes micro-batch size 1 (documents are concatenated along the sequence)")
+    bounds = [int(x) for x in cu_seqlens]
+    if bounds[0] != 0 or bounds[-1] != q.shape[0]:
+        raise ValueError(f"cu_seqlens must run from 0 to the sequence length {q.shape[0]}, got {bounds[0]}..{bounds[-1]}")
+    outs = []
+    for a, b in zip(bounds[:-1], bounds[1:]):
+        if b > a:
+            outs.append(flash_attention(q[a:b], k[a:b], v[a:b], causal=causal, softmax_scale=softmax_scale, backend=backend))
+    return torch.cat(outs, dim=0)

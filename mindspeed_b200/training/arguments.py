@@ -235,6 +235,14 @@ def _core_validate(args):
     args.params_dtype = torch.bfloat16 if args.bf16 else torch.float16 if args.fp16 else torch.float32
     if args.bf16:
         args.accumulate_allreduce_grads_in_fp32 = True
+    if getattr(args, "reset_attention_mask", False):
+        # packed documents: each attends to itself only; documents are concatenated along the sequence of one sample
+        if args.micro_batch_size != 1:
+            raise AssertionError("--reset-attention-mask takes --micro-batch-size 1 (packed documents share one sequence)")
+        if getattr(args, "context_parallel_size", 1) > 1:
+            raise AssertionError("--reset-attention-mask is not combined with context parallelism")
+        if not getattr(args, "data_path", None):
+            raise AssertionError("--reset-attention-mask needs --data-path: synthetic data has no document boundaries")
     if args.sequence_parallel and args.tensor_model_parallel_size == 1:
         args.sequence_parallel = False
     if args.recompute_activations:

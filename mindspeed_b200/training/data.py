@@ -48,10 +48,23 @@ class BatchIterator:
         return batch
 
 
-def get_batch(data_iterator, device=None):
-    """tokens, labels, loss_mask, attention_mask(None: causal), position_ids for this cp rank."""
+def get_batch(data_iterator, device=None, return_packed=False):
+    """tokens, labels, loss_mask, attention_mask(None: causal), position_ids for this cp rank; with ``return_packed`` a sixth
+    value: None, or for batches that carry ``document_ids`` (packed documents, --reset-attention-mask) a dict with the
+    documents' boundaries ``cu_seqlens`` (host integers) and, when the positions restart per document, ``position_ids``."""
     batch = next(data_iterator)
+    packed = None
+    doc = batch.pop("document_ids", None) if isinstance(batch, dict) else None
+    if doc is not None:
+        if doc.shape[0] != 1:
+            raise ValueError("packed documents (--reset-attention-mask) take micro-batch size 1")
+        d = doc[0].cpu()
+        starts = torch.nonzero(d[1:] != d[:-1]).flatten() + 1
+        packed = {"cu_seqlens": [0] + starts.tolist() + [int(d.numel())]}
     if device is not None:
         batch = {k: v.to(device, non_blocking=True) for k, v in batch.items()}
     batch = get_batch_on_this_cp_rank(batch)
-    return batch["tokens"], batch["labels"], batch["loss_mask"], None, batch["position_ids"]
+    if packed is not None and bool((batch["position_ids"][0, 1:] < batch["position_ids"][0, :-1]).any()):
+        packed["position_ids"] = batch["position_ids"]
+    out = (batch["tokens"], batch["labels"], batch["loss_mask"], None, batch["position_ids"])
+    return out + (packed,) if return_packed else out

@@ -39,8 +39,8 @@ def loss_func(loss_mask, output_tensor):
 
 def forward_step(data_iterator, model):
     dev = next(model.parameters()).device
-    tokens, labels, loss_mask, attention_mask, position_ids = get_batch(data_iterator, dev)
-    out = model(tokens, position_ids, attention_mask, labels=labels)
+    tokens, labels, loss_mask, attention_mask, position_ids, packed = get_batch(data_iterator, dev, return_packed=True)
+    out = model(tokens, position_ids, attention_mask, labels=labels, packed_seq_params=packed)
     return out, partial(loss_func, loss_mask)
 
 
@@ -50,12 +50,12 @@ def train_valid_test_datasets_provider(args):
         from mindspeed_b200.training.gpt_dataset import build_train_valid_test_datasets
         n_train = args.train_iters * args.global_batch_size if args.train_iters else None
         eod = None
-        if args.reset_position_ids or args.eod_mask_loss:
+        if args.reset_position_ids or args.eod_mask_loss or args.reset_attention_mask:
             from mindspeed_b200.tokenizer.tokenizer import build_tokenizer
             eod = build_tokenizer(args).eod        # the end-of-document id the corpus was tokenised with
         train, _, _ = build_train_valid_test_datasets(args.data_path, args.split, args.seq_length, args.seed, (n_train, None, None),
                                                       eod_token=eod, reset_position_ids=args.reset_position_ids,
-                                                      reset_attention_mask=False, eod_mask_loss=args.eod_mask_loss)
+                                                      reset_attention_mask=args.reset_attention_mask, eod_mask_loss=args.eod_mask_loss)
         if train is None:
             raise ValueError("--split leaves no documents for training")
         return BatchIterator(train, args.micro_batch_size, ps.get_data_parallel_rank(), ps.get_data_parallel_world_size(),

@@ -106,3 +106,61 @@ def test_pretrain_reads_data_path():
         _corpus(os.path.join(d, "c"), n_docs=120, vocab=100)
         losses = run_distributed(_train_on_files, 2, os.path.join(d, "c"))[0]
         assert len(losses) == 6 and losses[-1] < losses[0]
+
+
+def test_varlen_attention_matches_document_mask():
+    from mindspeed_b200.ops.attention import attention_ref, varlen_attention
+    torch.manual_seed(0)
+    s, n, d = 24, 2, 8
+    q, k, v = (torch.randn(s, 1, n, d, requires_grad=True) for _ in range(3))
+    cu = [0, 5, 6, 17, 24]
+    doc = torch.zeros(s, dtype=torch.long)
+    for i, (a, b) in enumerate(zip(cu[:-1], cu[1:])):
+        doc[a:b] = i
+    masked = ~(torch.tril(torch.ones(s, s, dtype=torch.bool)) & (doc.view(-1, 1) == doc.view(1, -1)))
+    ref = attention_ref(q, k, v, causal=False, mask=masked.view(1, 1, s, s))
+    w = torch.randn_like(ref)
+    gr = torch.autograd.grad((ref * w).sum(), (q, k, v))
+    out = varlen_attention(q, k, v, cu, causal=True)
+    gg = torch.autograd.grad((out * w).sum(), (q, k, v))
+    torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5)
+    for a, b in zip(gg, gr):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-5)
+
+
+def _train_packed(rank, world, prefix, extra):
+    import io
+    from contextlib import redirect_stdout
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import pretrain_gpt as pg
+    from test_pipeline_cpu import BASE
+    from mindspeed_b200.models import attention as MA
+    from mindspeed_b200.ops import attention as OA
+    from mindspeed_b200.training import pretrain
+    calls = {"n": 0, "docs": 0}
+    orig = OA.varlen_attention
+
+    def counted(q, k, v, cu, *a, **kw):
+        calls["n"] += 1
+        calls["docs"] += len(cu) - 1
+        return orig(q, k, v, cu, *a, **kw)
+    OA.varlen_attention = counted
+    with redirect_stdout(io.StringIO()):
+        hist = pretrain(pg.train_valid_test_datasets_provider, pg.model_provider, forward_step_func=pg.forward_step,
+                        args_list=BASE + ["--data-path", prefix, "--split", "100,0,0", "--train-iters", "3", "--tokenizer-type",
+                                          "NullTokenizer", "--vocab-size", "127", "--make-vocab-size-divisible-by", "128"] + list(extra))
+    return [h["lm loss"] for h in hist], calls
+
+
+def test_training_with_reset_attention_mask_uses_packed_attention():
+    """--reset-attention-mask --reset-position-ids: attention runs per document (and the rotary positions restart), which
+    changes the loss relative to attending across documents."""
+    from dist_utils import run_distributed
+    with tempfile.TemporaryDirectory() as d:
+        # NullTokenizer(vocab 127): eod id 127 -> the corpus closes documents with 127; the model's vocabulary is 128
+        _corpus(os.path.join(d, "c"), n_docs=80, vocab=100, eod=127)
+        plain, c0 = run_distributed(_train_packed, 1, os.path.join(d, "c"), [])[0]
+        packed, c1 = run_distributed(_train_packed, 1, os.path.join(d, "c"), ["--reset-attention-mask", "--reset-position-ids",
+                                                                              "--eod-mask-loss"])[0]
+        assert c0["n"] == 0 and c1["n"] > 0 and c1["docs"] > c1["n"]          # several documents per sample
+        assert plain != packed and all(abs(a - b) < 0.5 for a, b in zip(plain, packed))
