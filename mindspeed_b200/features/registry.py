@@ -493,6 +493,8 @@ class MoEFeature(Feature):
                 raise AssertionError("the overlapped / fused alltoall dispatcher needs --moe-grouped-gemm")
             if getattr(args, "moe_token_dispatcher_type", "alltoall") not in ("alltoall", "alltoall_seq"):
                 raise AssertionError("alltoall overlap needs --moe-token-dispatcher-type alltoall")
+        if args.enable_fine_grained_expert_placement and not args.enable_expert_placement:
+            raise AssertionError("--enable-fine-grained-expert-placement refines --enable-expert-placement: set both")
         if args.balanced_moe_experts:
             if getattr(args, "expert_model_parallel_size", 1) <= 1 or not getattr(args, "moe_grouped_gemm", False):
                 raise AssertionError("--balanced-moe-experts needs expert parallel size > 1 and --moe-grouped-gemm")

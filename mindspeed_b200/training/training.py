@@ -414,7 +414,10 @@ def _expert_load_step(args, model, optimizer, routers, planners, iteration):
         if getattr(args, "print_expert_load", False):
             print_rank_0(f" iteration {iteration:8d} | moe layer {li} tokens per expert: {[int(x) for x in load.tolist()]}")
         if getattr(args, "enable_expert_placement", False) and ep > 1 and iteration % args.expert_placement_freq == 0:
-            pl = planners.setdefault(li, ExpertPlacementPlanner(r.num_experts, ep))
+            # --enable-fine-grained-expert-placement: experts only move when the heaviest rank is more than the threshold
+            # above the mean (reference: expert_placement/executor.py, fine_grained_expert_placement_thre)
+            thr = args.fine_grained_expert_placement_thre if getattr(args, "enable_fine_grained_expert_placement", False) else None
+            pl = planners.setdefault(li, ExpertPlacementPlanner(r.num_experts, ep, thr))
             pl.record(load)
             new = pl.plan()
             if new != pl.placement:

@@ -52,3 +52,17 @@ def test_hot_split():
     assert hot == [0] or hot == [2]
     cold_map, cold_p, hot_map, hot_p = split_hot_routing(rm, pr, [2])
     assert cold_map[:, 2].sum() == 0 and hot_map.shape == (3, 1) and hot_map.sum() == 2
+
+
+def test_fine_grained_threshold_keeps_a_nearly_balanced_placement():
+    """With a threshold the planner leaves the placement alone while the heaviest rank is within it of the mean."""
+    from mindspeed_b200.parallel.moe.expert_placement import ExpertPlacementPlanner
+    load = torch.tensor([100.0, 100.0, 104.0, 100.0, 100.0, 100.0, 100.0, 100.0])
+    coarse, fine = ExpertPlacementPlanner(8, 4), ExpertPlacementPlanner(8, 4, fine_grained_threshold=0.08)
+    coarse.record(load)
+    fine.record(load)
+    assert fine.imbalance() < 0.08 and fine.plan() == list(range(8))
+    skew = torch.tensor([400.0, 300.0, 10.0, 10.0, 10.0, 10.0, 10.0, 10.0])
+    fine.commit(fine.plan())
+    fine.record(skew)
+    assert fine.imbalance() > 0.08 and fine.plan() != list(range(8))
