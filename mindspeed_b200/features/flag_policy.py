@@ -79,7 +79,6 @@ UNSUPPORTED: Dict[str, str] = {
     "kl-loss-reduction": "only used by the lightning-indexer KL loss, which is not wired into training",
     "fix-sub-seq-length": "fixed-length sub-sequence packing for EOD-reset CP is not implemented",
     "no-qad-enable": "distillation is driven through mindspeed_b200.qat.distill, not through this switch",
-    "recompute-module-list": "module-level recompute is selected with --recompute-granularity / --recompute-activation-function / --recompute-norm",
 }
 
 

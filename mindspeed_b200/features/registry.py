@@ -387,7 +387,12 @@ class PipelineMiscFeature(Feature):
         add_arg(g, "--pipeline-num-transformer-layers", type=str, default=None)
         add_arg(g, "--automated-pipeline", action="store_true")
         add_arg(g, "--automated-pipeline-perf", action="store_true")
-        add_arg(g, "--recompute-module-list", type=str, default=None)
+        add_arg(g, "--recompute-module-list", type=str, default=None,
+                help="per pipeline rank: how many modules recompute, e.g. '[4,2,0,0]' (the policy an automated-pipeline run prints)")
+        add_arg(g, "--recompute-type", type=int, default=2, choices=[0, 1, 2],
+                help="what --recompute-module-list counts: 0 the MLP block, 1 the attention block, 2 whole transformer layers")
+        add_arg(g, "--num-layer-list", type=str, default=None,
+                help="transformer layers per pipeline rank, e.g. '[8,9,9,6]' (the layer policy an automated-pipeline run prints)")
 
     def validate_args(self, args):
         if args.use_multiparameter_pipeline_model_parallel and not getattr(args, "pipeline_tensor_shapes", None):
@@ -413,6 +418,30 @@ class PipelineMiscFeature(Feature):
         if isinstance(args.pipeline_num_transformer_layers, str):
             import ast
             args.pipeline_num_transformer_layers = ast.literal_eval(args.pipeline_num_transformer_layers)
+        for name in ("recompute_module_list", "num_layer_list"):
+            v = getattr(args, name, None)
+            if isinstance(v, str):
+                import ast
+                v = ast.literal_eval(v) if v.strip().startswith("[") else [int(x) for x in v.split(",") if x.strip() != ""]
+                setattr(args, name, [int(x) for x in v])
+        pp_ = getattr(args, "pipeline_model_parallel_size", 1)
+        if args.num_layer_list:
+            # a stored layer policy: same effect as --pipeline-num-transformer-layers
+            if len(args.num_layer_list) != pp_ or sum(args.num_layer_list) != args.num_layers:
+                raise AssertionError("--num-layer-list needs one entry per pipeline rank, summing to --num-layers")
+            if not args.pipeline_num_transformer_layers:
+                args.pipeline_num_transformer_layers = list(args.num_layer_list)
+        if args.recompute_module_list:
+            if len(args.recompute_module_list) != pp_:
+                raise AssertionError("--recompute-module-list needs one entry per pipeline rank")
+            if args.recompute_type == 2:
+                if getattr(args, "recompute_granularity", None) not in (None, "full"):
+                    raise AssertionError("--recompute-module-list with --recompute-type 2 is full-layer recompute")
+                args.recompute_granularity, args.recompute_method = "full", "block"
+                args.enable_recompute_layers_per_pp_rank = True
+                args.recompute_num_layers = list(args.recompute_module_list)
+            elif getattr(args, "recompute_granularity", None) == "full":
+                raise AssertionError("--recompute-type 0 / 1 recompute one block of a layer; do not combine with full recompute")
         if args.automated_pipeline or args.automated_pipeline_perf:
             # layers per stage (and layers to recompute per stage) from the model shape, so that the stage that also holds
             # the output layer gets fewer transformer layers (reference: mindspeed/core/memory/auto_pipeline/*,

@@ -133,6 +133,13 @@ class TransformerLayer(nn.Module):
             self.mlp = MLP2D(config)
         else:
             self.mlp = MLP(config)
+        # --recompute-module-list with --recompute-type 0 / 1: the first N layers of this pipeline rank recompute only their
+        # MLP block / attention block in backward (reference: the module-level policy of mindspeed/core/memory/auto_pipeline)
+        rml, rtype = getattr(config, "recompute_module_list", None), getattr(config, "recompute_type", 2)
+        n_blk = rml[ps.get_pipeline_model_parallel_rank()] if isinstance(rml, (list, tuple)) and rtype in (0, 1) else 0
+        plain_residual = not config.apply_residual_connection_post_layernorm      # the block's norm lives inside the checkpoint
+        self.recompute_mlp_block = rtype == 0 and layer_number <= n_blk and plain_residual
+        self.recompute_attn_block = rtype == 1 and layer_number <= n_blk and plain_residual
         sel = getattr(config, "compress_activation", None) or []
         self.compress_saved = isinstance(sel, (list, tuple)) and self.layer_number in sel
         self.recompute_norm = bool(getattr(config, "recompute_norm", False))
@@ -164,6 +171,15 @@ class TransformerLayer(nn.Module):
                                                       packed_seq_params=packed_seq_params)
             ck.discard_output()
             attn_out.register_hook(ck.recompute)
+        elif self.recompute_attn_block and self.training and hidden_states.requires_grad:
+            from ..parallel.random import checkpoint
+
+            def attn_block(h):
+                o, b_ = self.self_attention(self.input_layernorm(h), attention_mask=attention_mask, rotary_pos_emb=rotary_pos_emb,
+                                            packed_seq_params=packed_seq_params)
+                return o if b_ is None else o + b_
+            ln = None
+            attn_out, attn_bias = checkpoint(attn_block, False, hidden_states), None
         else:
             ln = self.input_layernorm(hidden_states)
             attn_out, attn_bias = self.self_attention(ln, attention_mask=attention_mask, rotary_pos_emb=rotary_pos_emb,
@@ -172,13 +188,20 @@ class TransformerLayer(nn.Module):
             residual = ln
         ln2 = None
         if (attn_bias is None and not (self.hidden_dropout > 0.0 and self.training) and not self.recompute_norm
-                and not self.config.apply_residual_connection_post_layernorm and hasattr(self.pre_mlp_layernorm, "forward_add")):
+                and not self.recompute_mlp_block and not self.config.apply_residual_connection_post_layernorm and hasattr(self.pre_mlp_layernorm, "forward_add")):
             # residual add and the MLP's norm in one pass over the row (and one kernel in backward)
             hidden_states, ln2 = self.pre_mlp_layernorm.forward_add(attn_out, residual)
         else:
             hidden_states = _bda(attn_out, attn_bias, residual, self.hidden_dropout, self.training)
         residual = hidden_states
-        if ln2 is not None:
+        if self.recompute_mlp_block and self.training and hidden_states.requires_grad and not self.is_moe:
+            from ..parallel.random import checkpoint
+
+            def mlp_block(h):
+                o, b_ = self.mlp(self.pre_mlp_layernorm(h))
+                return o if b_ is None else o + b_
+            mlp_out, mlp_bias = checkpoint(mlp_block, False, hidden_states), None
+        elif ln2 is not None:
             mlp_out, mlp_bias = self.mlp(ln2)
         elif self.recompute_norm and self.training and hidden_states.requires_grad and not self.is_moe:
             ck2 = CheckpointWithoutOutput()

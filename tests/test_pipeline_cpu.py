@@ -151,6 +151,11 @@ def _train(rank, world, extra, bidirectional):
     (2, ["--pipeline-model-parallel-size", "2", "--recompute-in-bubble"], False),
     # layers per stage chosen from the model shape (the stage with the output layer gets fewer transformer layers)
     (2, ["--pipeline-model-parallel-size", "2", "--automated-pipeline", "--vocab-size", "2048", "--num-layers", "5"], False),
+    # a stored automated-pipeline policy: layers per rank, and per rank how many layers recompute their MLP / attention block
+    (2, ["--pipeline-model-parallel-size", "2", "--num-layers", "5", "--num-layer-list", "[3,2]", "--recompute-module-list", "[2,1]",
+         "--recompute-type", "0"], False),
+    (2, ["--pipeline-model-parallel-size", "2", "--recompute-module-list", "2,0", "--recompute-type", "1"], False),
+    (2, ["--pipeline-model-parallel-size", "2", "--recompute-module-list", "[1,2]"], False),
     # list-valued stage interface with its default content (the one hidden-state tensor), through the plan executor
     (2, ["--pipeline-model-parallel-size", "2", "--use-multiparameter-pipeline-model-parallel"], False),
     (2, ["--pipeline-model-parallel-size", "2", "--num-layers-per-virtual-pipeline-stage", "1", "--recompute-in-advance"], False),
