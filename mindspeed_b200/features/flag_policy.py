@@ -58,10 +58,6 @@ NO_EFFECT: Dict[str, str] = {
 
 UNSUPPORTED: Dict[str, str] = {
     "ampipe-degree": "attention-MoE micro-pipelining (ampipe) is not implemented; use --moe-fb-overlap",
-    "use-pipe-experts": "pipelined experts are part of the legacy DeepSpeed-style MoE only (mindspeed_b200.legacy_moe)",
-    "pipe-experts-multi-data": "pipelined experts are part of the legacy DeepSpeed-style MoE only (mindspeed_b200.legacy_moe)",
-    "pipe-experts-multi-stream": "pipelined experts are part of the legacy DeepSpeed-style MoE only (mindspeed_b200.legacy_moe)",
-    "moe-model-type": "the DeepSpeed-style MoE is selected through mindspeed_b200.legacy_moe, not through this flag",
     "moe-bmm-mc2": "use --moe-alltoall-mc2 (peer-memory dispatch / combine) with --moe-grouped-gemm",
     "moe-unperm2-mem-optim-swap": "host swap of the unpermute buffer is not implemented; use --moe-zero-memory",
     "adaptive-recompute-device-swap": "adaptive recompute decides recompute only; combine it with --swap-attention for host swap",

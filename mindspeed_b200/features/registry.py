@@ -522,6 +522,17 @@ class MoEFeature(Feature):
                 raise AssertionError("the overlapped / fused alltoall dispatcher needs --moe-grouped-gemm")
             if getattr(args, "moe_token_dispatcher_type", "alltoall") not in ("alltoall", "alltoall_seq"):
                 raise AssertionError("alltoall overlap needs --moe-token-dispatcher-type alltoall")
+        legacy = getattr(args, "moe_model_type", "megatron_moe") == "deepspeed_moe"
+        if (args.use_pipe_experts or args.pipe_experts_multi_data > 1 or args.pipe_experts_multi_stream) and not legacy:
+            raise AssertionError("pipelined experts (--use-pipe-experts, --pipe-experts-*) belong to --moe-model-type deepspeed_moe")
+        if legacy:
+            if not ne:
+                raise AssertionError("--moe-model-type deepspeed_moe needs --num-experts")
+            if getattr(args, "moe_router_topk", 2) not in (1, 2):
+                raise AssertionError("the DeepSpeed-style gate supports --moe-router-topk 1 or 2")
+            if args.moe_alltoall_mc2 or args.moe_alltoall_overlap_comm or args.moe_fb_overlap or args.balanced_moe_experts:
+                raise AssertionError("--moe-model-type deepspeed_moe has its own dispatch (einsum + all-to-all); the core "
+                                     "dispatcher options do not apply to it")
         if args.enable_fine_grained_expert_placement and not args.enable_expert_placement:
             raise AssertionError("--enable-fine-grained-expert-placement refines --enable-expert-placement: set both")
         if args.balanced_moe_experts:

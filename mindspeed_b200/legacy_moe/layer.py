@@ -16,7 +16,12 @@ class Experts(nn.Module):
 
     def __init__(self, expert: nn.Module, num_local_experts: int = 1):
         super().__init__()
-        self.experts = nn.ModuleList([copy.deepcopy(expert) for _ in range(num_local_experts)])
+        # ``expert`` is a module (copied, as DeepSpeed does) or a zero-argument factory (modules that hold process groups
+        # cannot be deep-copied)
+        if isinstance(expert, nn.Module):
+            self.experts = nn.ModuleList([copy.deepcopy(expert) for _ in range(num_local_experts)])
+        else:
+            self.experts = nn.ModuleList([expert() for _ in range(num_local_experts)])
         for e in self.experts:
             for p in e.parameters():
                 p.allreduce = False
@@ -35,11 +40,27 @@ class MOELayer(nn.Module):
         self.gate, self.experts = gate, experts
         self.ep_group, self.ep_size, self.num_local_experts = ep_group, ep_size, num_local_experts
         self.pipe_experts = max(1, pipe_experts)
+        self.multi_stream = False            # chunks' all-to-alls on a second CUDA stream (--pipe-experts-multi-stream)
+        self._comm_stream = None
         self.l_aux = None
         self.exp_counts = None
 
     def _a2a(self, x):
-        return M.all_to_all(self.ep_group, x) if self.ep_size > 1 else x
+        if self.ep_size <= 1:
+            return x
+        if self.multi_stream and x.is_cuda and self.pipe_experts > 1:
+            # the exchange of this chunk runs beside the expert computation of the previous one
+            if self._comm_stream is None:
+                self._comm_stream = torch.cuda.Stream(device=x.device)
+            main = torch.cuda.current_stream()
+            self._comm_stream.wait_stream(main)
+            x.record_stream(self._comm_stream)
+            with torch.cuda.stream(self._comm_stream):
+                y = M.all_to_all(self.ep_group, x)
+            y.record_stream(main)
+            main.wait_stream(self._comm_stream)
+            return y
+        return M.all_to_all(self.ep_group, x)
 
     def forward(self, x):
         d = x.shape[-1]

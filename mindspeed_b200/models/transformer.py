@@ -126,7 +126,10 @@ class TransformerLayer(nn.Module):
         if is_moe is None:
             is_moe = _is_moe_layer(config, self.layer_number)
         self.is_moe = is_moe
-        if is_moe:
+        if is_moe and getattr(config, "moe_model_type", "megatron_moe") == "deepspeed_moe":
+            from ..legacy_moe.adapter import LegacyMoEBlock
+            self.mlp = LegacyMoEBlock(config, layer_number=self.layer_number)
+        elif is_moe:
             from ..parallel.moe.moe_layer import MoELayer
             self.mlp = MoELayer(config, layer_number=self.layer_number)
         elif tp2d:

@@ -89,3 +89,40 @@ def _moe_rank(rank, world):
 
 def test_legacy_moe_expert_parallel_matches_local():
     assert all(run_distributed(_moe_rank, 2))
+
+
+def _train_legacy(rank, world, prefix, extra):
+    import io
+    import os
+    import sys
+    from contextlib import redirect_stdout
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    import pretrain_gpt as pg
+    from test_pipeline_cpu import BASE
+    from mindspeed_b200.training import pretrain
+    flags = ["--num-experts", "4", "--moe-router-topk", "2", "--moe-model-type", "deepspeed_moe", "--moe-aux-loss-coeff", "0.01",
+             "--expert-model-parallel-size", str(world), "--moe-no-drop", "--data-path", prefix, "--split", "100,0,0",
+             "--train-iters", "8", "--lr", "1e-2"]
+    with redirect_stdout(io.StringIO()):
+        hist = pretrain(pg.train_valid_test_datasets_provider, pg.model_provider, forward_step_func=pg.forward_step,
+                        args_list=BASE + flags + list(extra))
+    return [h["lm loss"] for h in hist]
+
+
+def test_deepspeed_style_moe_trains_and_pipelined_experts_change_nothing(tmp_path):
+    """--moe-model-type deepspeed_moe in the transformer layer: learns a small corpus; cutting the capacity dimension into
+    chunks (--use-pipe-experts --pipe-experts-multi-data 2) is the same computation."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from dist_utils import run_distributed
+    from test_gpt_dataset_cpu import _corpus
+    prefix = str(tmp_path / "c")
+    _corpus(prefix, n_docs=60, vocab=100)
+    plain = run_distributed(_train_legacy, 2, prefix, [])[0]
+    piped = run_distributed(_train_legacy, 2, prefix, ["--use-pipe-experts", "--pipe-experts-multi-data", "2",
+                                                       "--pipe-experts-multi-stream"])[0]
+    assert plain[-1] < plain[0] - 0.1, plain
+    for a, b in zip(plain, piped):
+        assert abs(a - b) < 1e-5 * max(1.0, abs(a)), (plain, piped)
