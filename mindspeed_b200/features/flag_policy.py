@@ -58,8 +58,6 @@ NO_EFFECT: Dict[str, str] = {
 
 UNSUPPORTED: Dict[str, str] = {
     "ampipe-degree": "attention-MoE micro-pipelining (ampipe) is not implemented; use --moe-fb-overlap",
-    "moe-bmm-mc2": "use --moe-alltoall-mc2 (peer-memory dispatch / combine) with --moe-grouped-gemm",
-    "moe-unperm2-mem-optim-swap": "host swap of the unpermute buffer is not implemented; use --moe-zero-memory",
     "adaptive-recompute-device-swap": "adaptive recompute decides recompute only; combine it with --swap-attention for host swap",
     "adaptive-cp-dynamic-attn-mask": "adaptive CP takes one mask per run",
     "adaptive-cp-manually-set-mask-list": "adaptive CP derives its mask list itself",

@@ -522,6 +522,12 @@ class MoEFeature(Feature):
                 raise AssertionError("the overlapped / fused alltoall dispatcher needs --moe-grouped-gemm")
             if getattr(args, "moe_token_dispatcher_type", "alltoall") not in ("alltoall", "alltoall_seq"):
                 raise AssertionError("alltoall overlap needs --moe-token-dispatcher-type alltoall")
+        if args.moe_bmm_mc2:
+            # the reference's fused all-to-all + batched-matmul op pair; here the same role is played by the peer-memory
+            # dispatch / combine kernels around the one-launch grouped GEMM
+            if getattr(args, "expert_model_parallel_size", 1) <= 1 or not getattr(args, "moe_grouped_gemm", False):
+                raise AssertionError("--moe-bmm-mc2 needs expert parallel size > 1 and --moe-grouped-gemm")
+            args.moe_alltoall_mc2 = True
         legacy = getattr(args, "moe_model_type", "megatron_moe") == "deepspeed_moe"
         if (args.use_pipe_experts or args.pipe_experts_multi_data > 1 or args.pipe_experts_multi_stream) and not legacy:
             raise AssertionError("pipelined experts (--use-pipe-experts, --pipe-experts-*) belong to --moe-model-type deepspeed_moe")

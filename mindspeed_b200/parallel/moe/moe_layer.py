@@ -54,6 +54,7 @@ class MoELayer(nn.Module):
         self.hot_experts = []
         self._load = None
         self._hot_w1 = self._hot_w2 = None
+        self.unperm_swap = bool(getattr(config, "moe_unperm2_mem_optim_swap", False))
         self.zero_memory = getattr(config, "moe_zero_memory", "disable")
         n_zm = getattr(config, "moe_zero_memory_num_layers", None)
         if n_zm is not None and layer_number > n_zm:
@@ -79,7 +80,13 @@ class MoELayer(nn.Module):
                 probs, routing_map, hot_out = self._hot_path(hidden_states, probs, routing_map)
         dispatched, tokens_per_expert, pprobs = self.token_dispatcher.token_permutation(hidden_states, probs.to(hidden_states.dtype), routing_map)
         expert_out, _ = self.experts(dispatched, tokens_per_expert, pprobs)
-        out, _ = self.token_dispatcher.token_unpermutation(expert_out)
+        if self.unperm_swap and self.training and expert_out.is_cuda:
+            # --moe-unperm2-mem-optim-swap: what the un-permute saves for backward (the expert output rows) waits in host memory
+            from ...memory.host_offload import OffloadSaved
+            with OffloadSaved():
+                out, _ = self.token_dispatcher.token_unpermutation(expert_out)
+        else:
+            out, _ = self.token_dispatcher.token_unpermutation(expert_out)
         if hot_out is not None:
             out = out + hot_out
         if self.shared_experts is not None:
