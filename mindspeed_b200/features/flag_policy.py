@@ -37,6 +37,8 @@ NO_EFFECT: Dict[str, str] = {
     "transformer-impl": "one implementation (this package's modules with the TE-compatible surface)",
     "use-mcore-models": "the core model classes are the only ones",
     # --- always-on behaviours ---
+    "adaptive-cp-only-reschedule": "adaptive CP here always keeps the sequence order and only schedules the exchanges",
+    "adaptive-cp-without-coarse": "the mask is coarsened to context-parallel rank granularity for scheduling only; nothing else uses the coarse form",
     "gemm-gradient-accumulation-fusion": "weight gradients always accumulate into main_grad inside the GEMM epilogue",
     "no-bias-swiglu-fusion": "SwiGLU is fused whenever the optimisation level allows; level 0 gives the unfused path",
     "coc-mode": "sub-mode of the chunk-pipelining path; --use-ascend-coc / --coc-fused-kernel select the back end",
@@ -59,10 +61,6 @@ NO_EFFECT: Dict[str, str] = {
 UNSUPPORTED: Dict[str, str] = {
     "ampipe-degree": "attention-MoE micro-pipelining (ampipe) is not implemented; use --moe-fb-overlap",
     "adaptive-recompute-device-swap": "adaptive recompute decides recompute only; combine it with --swap-attention for host swap",
-    "adaptive-cp-dynamic-attn-mask": "adaptive CP takes one mask per run",
-    "adaptive-cp-manually-set-mask-list": "adaptive CP derives its mask list itself",
-    "adaptive-cp-only-reschedule": "adaptive CP always remaps and reschedules",
-    "adaptive-cp-without-coarse": "adaptive CP always uses the coarsened search",
     "alibi-fusion-attn-type": "ALiBi runs on the reference (eager) attention path only; the fused kernels have no bias input",
     "alibi-diagonal-opposite": "ALiBi runs on the reference (eager) attention path only; the fused kernels have no bias input",
     "square-alibi-mask": "ALiBi runs on the reference (eager) attention path only; the fused kernels have no bias input",

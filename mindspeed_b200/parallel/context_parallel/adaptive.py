@@ -21,12 +21,22 @@ from ...ops import attention as A
 from ...utils.host_lib import host_lib
 from .. import parallel_state as ps
 
-_GLOBAL_MASK = {"mask": None}
+_GLOBAL_MASK = {"mask": None, "blocks": None}
+_SCHEDULE_CACHE = {}
 
 
 def set_global_attention_mask(mask: torch.Tensor):
-    """[S, S] bool, True = masked out (``--adaptive-cp-manually-set-mask-list`` style explicit setting)."""
+    """[S, S] bool, True = masked out."""
     _GLOBAL_MASK["mask"] = mask
+
+
+def set_block_mask_list(blocks):
+    """``--adaptive-cp-manually-set-mask-list``: the mask given block by block instead of as one [S, S] tensor.
+    ``blocks[i][j]`` is the [s_local, s_local] bool mask (True = masked out) between the queries of context-parallel rank i
+    and the keys of rank j, or None when no query of rank i sees any key of rank j; the exchange schedule is derived from
+    which entries exist, so a long sequence never needs its full mask in one piece
+    (reference: mindspeed/core/context_parallel/utils.py, the manually set mask list of adaptive CP)."""
+    _GLOBAL_MASK["blocks"] = blocks
 
 
 def coarsen_mask(visible: torch.Tensor, block: int, threads: int = 4) -> torch.Tensor:
@@ -98,18 +108,38 @@ def adaptive_attention(q, k, v, config=None, attention_mask=None, softmax_scale=
     group = ps.get_context_parallel_group()
     ranks = ps.get_context_parallel_global_ranks()
     cp, r = len(ranks), ps.get_context_parallel_rank()
-    mask = attention_mask if attention_mask is not None and attention_mask.dim() == 2 else _GLOBAL_MASK["mask"]
-    if mask is None:
-        raise RuntimeError("adaptive context parallelism needs the global [S, S] attention mask")
     s_local = q.shape[0]
-    visible = ~mask.bool()
-    need = coarsen_mask(visible, s_local)                       # [cp, cp]
-    limit = comm_limit or int(getattr(config, "adaptive_cp_comm_limit", 1) or 1)
-    n_rounds, round_of = schedule_rounds(need, limit)
     dev = q.device
+    limit = comm_limit or int(getattr(config, "adaptive_cp_comm_limit", 1) or 1)
+    dynamic = bool(getattr(config, "adaptive_cp_dynamic_attn_mask", False))
+    blocks = _GLOBAL_MASK["blocks"] if bool(getattr(config, "adaptive_cp_manually_set_mask_list", False)) or \
+        (attention_mask is None and _GLOBAL_MASK["mask"] is None) else None
+    if blocks is not None:
+        need = torch.tensor([[0 if blocks[i][j] is None else 1 for j in range(cp)] for i in range(cp)], dtype=torch.uint8)
+        key = ("blocks", id(blocks), limit)
 
-    def sub_mask(qr, kr):
-        return mask[qr * s_local:(qr + 1) * s_local, kr * s_local:(kr + 1) * s_local].to(dev).view(1, 1, s_local, s_local)
+        def sub_mask(qr, kr):
+            return blocks[qr][kr].to(dev).view(1, 1, s_local, s_local)
+    else:
+        mask = attention_mask if attention_mask is not None and attention_mask.dim() == 2 else _GLOBAL_MASK["mask"]
+        if mask is None:
+            raise RuntimeError("adaptive context parallelism needs the global [S, S] attention mask or a block mask list")
+        key = ("mask", mask.data_ptr(), mask._version, tuple(mask.shape), s_local, limit)
+        if not dynamic and key in _SCHEDULE_CACHE:
+            need = _SCHEDULE_CACHE[key][2]
+        else:
+            need = coarsen_mask(~mask.bool(), s_local)              # [cp, cp]
+
+        def sub_mask(qr, kr):
+            return mask[qr * s_local:(qr + 1) * s_local, kr * s_local:(kr + 1) * s_local].to(dev).view(1, 1, s_local, s_local)
+    if not dynamic and key in _SCHEDULE_CACHE:
+        n_rounds, round_of, _ = _SCHEDULE_CACHE[key]
+    else:
+        n_rounds, round_of = schedule_rounds(need, limit)
+        if not dynamic:
+            if len(_SCHEDULE_CACHE) > 16:
+                _SCHEDULE_CACHE.clear()
+            _SCHEDULE_CACHE[key] = (n_rounds, round_of, need)
 
     out = lse = None
     if need[r, r]:

@@ -107,6 +107,19 @@ def _run_adaptive(rank, world):
     ql, kl, vl = (sl(t).requires_grad_(True) for t in (q, k, v))
     out = adaptive_attention(ql, kl, vl, None, mask)
     (out * sl(w)).sum().backward()
+    # the same mask handed over block by block (--adaptive-cp-manually-set-mask-list): same result, schedule from the list
+    from mindspeed_b200.parallel.context_parallel import adaptive as AD
+    import types
+    blocks = [[None if bool(mask[i * per:(i + 1) * per, j * per:(j + 1) * per].all()) else
+               mask[i * per:(i + 1) * per, j * per:(j + 1) * per].clone() for j in range(world)] for i in range(world)]
+    AD.set_block_mask_list(blocks)
+    cfg = types.SimpleNamespace(adaptive_cp_manually_set_mask_list=True, adaptive_cp_dynamic_attn_mask=True, adaptive_cp_comm_limit=1)
+    q2, k2, v2 = (sl(t).requires_grad_(True) for t in (q, k, v))
+    out2 = adaptive_attention(q2, k2, v2, cfg, None)
+    assert (out2.detach() - out.detach()).abs().max().item() < 1e-6
+    n_cached = len(AD._SCHEDULE_CACHE)
+    adaptive_attention(sl(q), sl(k), sl(v), None, mask)           # static mask: the schedule is reused
+    assert len(AD._SCHEDULE_CACHE) == n_cached
     res = {"out": (out.detach() - sl(ref.detach())).abs().max().item(), "dq": (ql.grad - sl(qf.grad)).abs().max().item(),
            "dk": (kl.grad - sl(kf.grad)).abs().max().item(), "dv": (vl.grad - sl(vf.grad)).abs().max().item()}
     ps.destroy_model_parallel()
