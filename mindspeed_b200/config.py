@@ -121,6 +121,13 @@ class TransformerConfig(ModelParallelConfig):
     test_mode: bool = False
     calculate_per_token_loss: bool = False
     multi_latent_attention: bool = False
+    experimental_attention_variant: Optional[str] = None     # "dsa": lightning indexer + top-k sparse attention (MLA only)
+    dsa_indexer_n_heads: int = 64
+    dsa_indexer_head_dim: int = 128
+    dsa_indexer_topk: int = 2048
+    dsa_indexer_loss_coeff: float = 1.0
+    use_dsa_absorb: bool = False
+    kl_loss_reduction: str = "batchmean"
     softmax_scale: Optional[float] = None
     attention_softmax_in_fp32: bool = True
     apply_query_key_layer_scaling: bool = False

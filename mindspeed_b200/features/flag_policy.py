@@ -37,6 +37,9 @@ NO_EFFECT: Dict[str, str] = {
     "transformer-impl": "one implementation (this package's modules with the TE-compatible surface)",
     "use-mcore-models": "the core model classes are the only ones",
     # --- always-on behaviours ---
+    "use-fused-lightning-indexer": "the indexer, the sparse attention and the KL loss of --experimental-attention-variant dsa are one implementation (ops/lightning_indexer.py, ops/sparse_attention.py); there is no separate unfused path to switch from",
+    "use-fused-sparse-flash-attention": "the indexer, the sparse attention and the KL loss of --experimental-attention-variant dsa are one implementation (ops/lightning_indexer.py, ops/sparse_attention.py); there is no separate unfused path to switch from",
+    "use-fused-lightning-indexer-kl-loss": "the indexer, the sparse attention and the KL loss of --experimental-attention-variant dsa are one implementation (ops/lightning_indexer.py, ops/sparse_attention.py); there is no separate unfused path to switch from",
     "adaptive-cp-only-reschedule": "adaptive CP here always keeps the sequence order and only schedules the exchanges",
     "adaptive-cp-without-coarse": "the mask is coarsened to context-parallel rank granularity for scheduling only; nothing else uses the coarse form",
     "gemm-gradient-accumulation-fusion": "weight gradients always accumulate into main_grad inside the GEMM epilogue",
@@ -64,11 +67,6 @@ UNSUPPORTED: Dict[str, str] = {
     "alibi-fusion-attn-type": "ALiBi runs on the reference (eager) attention path only; the fused kernels have no bias input",
     "alibi-diagonal-opposite": "ALiBi runs on the reference (eager) attention path only; the fused kernels have no bias input",
     "square-alibi-mask": "ALiBi runs on the reference (eager) attention path only; the fused kernels have no bias input",
-    "use-dsa-absorb": "DeepSeek sparse attention is not implemented (lightning indexer only, ops/lightning_indexer.py)",
-    "use-fused-lightning-indexer": "the lightning indexer is a PyTorch op (ops/lightning_indexer.py); no fused kernel yet",
-    "use-fused-lightning-indexer-kl-loss": "the lightning indexer is a PyTorch op (ops/lightning_indexer.py); no fused kernel yet",
-    "use-fused-sparse-flash-attention": "sparse flash attention is not implemented",
-    "kl-loss-reduction": "only used by the lightning-indexer KL loss, which is not wired into training",
     "fix-sub-seq-length": "fixed-length sub-sequence packing for EOD-reset CP is not implemented",
     "no-qad-enable": "distillation is driven through mindspeed_b200.qat.distill, not through this switch",
 }

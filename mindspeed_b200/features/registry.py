@@ -311,11 +311,49 @@ class FlashAttentionFeature(Feature):
         add_arg(g, "--alibi-diagonal-opposite", action="store_true")
         add_arg(g, "--reset-attention-mask", action="store_true")
         add_arg(g, "--fix-sub-seq-length", type=int, default=None)
+
+
+class SparseAttentionFeature(Feature):
+    """DeepSeek sparse attention (reference: mindspeed/features_manager/transformer/experimental_attention_variant/dsa.py:5-50)."""
+
+    def __init__(self):
+        super().__init__("experimental-attention-variant", optimization_level=0)
+
+    def is_need_apply(self, args) -> bool:
+        return bool(args.experimental_attention_variant or args.use_dsa_absorb or args.use_fused_lightning_indexer
+                    or args.use_fused_sparse_flash_attention or args.use_fused_lightning_indexer_kl_loss)
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
         add_arg(g, "--experimental-attention-variant", type=str, default=None, choices=[None, "dsa"])
         add_arg(g, "--use-dsa-absorb", action="store_true")
         add_arg(g, "--use-fused-lightning-indexer", action="store_true")
         add_arg(g, "--use-fused-sparse-flash-attention", action="store_true")
         add_arg(g, "--use-fused-lightning-indexer-kl-loss", action="store_true")
+        add_arg(g, "--dsa-indexer-n-heads", type=int, default=64)
+        add_arg(g, "--dsa-indexer-head-dim", type=int, default=128)
+        add_arg(g, "--dsa-indexer-topk", type=int, default=2048)
+        add_arg(g, "--dsa-indexer-loss-coeff", type=float, default=1.0)
+
+    def validate_args(self, args):
+        fused = (args.use_fused_lightning_indexer, args.use_fused_sparse_flash_attention, args.use_fused_lightning_indexer_kl_loss)
+        if args.experimental_attention_variant != "dsa":
+            if args.use_dsa_absorb or any(fused):
+                raise AssertionError("--use-dsa-absorb / --use-fused-lightning-indexer* / --use-fused-sparse-flash-attention "
+                                     "need --experimental-attention-variant dsa")
+            return
+        if not getattr(args, "multi_head_latent_attention", False):
+            raise AssertionError("--experimental-attention-variant dsa is built on --multi-head-latent-attention")
+        if not args.qk_layernorm:
+            raise AssertionError("--experimental-attention-variant dsa needs --qk-layernorm (the latent query / key norms)")
+        if any(fused) and not (all(fused) and args.use_dsa_absorb):
+            raise AssertionError("the fused sparse-attention operators come as a set: give --use-dsa-absorb, "
+                                 "--use-fused-lightning-indexer, --use-fused-sparse-flash-attention and "
+                                 "--use-fused-lightning-indexer-kl-loss together")
+        if args.context_parallel_size > 1:
+            raise AssertionError("--experimental-attention-variant dsa is not combined with context parallelism")
+        if args.kl_loss_reduction not in ("batchmean", "sum", "mean"):
+            raise AssertionError("--kl-loss-reduction is one of batchmean, sum, mean")
 
 
 class MLAFeature(Feature):
@@ -761,7 +799,7 @@ def create_features_list():
         RequirementsBasicFeature(), MegatronBasicFeature(), TransformerEngineBasicFeature(), ProfileFeature(),
         TflopsCalculateFeature(), DeterministicFeature(), TokenizerFeature(),
         FusedTPCommFeature(), ChunkedTPCommFeature(), TP2DFeature(), UnalignedLinearFeature(),
-        ContextParallelFeature(), FlashAttentionFeature(), MLAFeature(),
+        ContextParallelFeature(), FlashAttentionFeature(), SparseAttentionFeature(), MLAFeature(),
         DualpipeVFeature(), PipelineMiscFeature(), MoEFeature(), MemoryFeature(), OptimizerFeature(),
         DistributedFeature(), AutoSettingsFeature(), TTPFeature(),
     ]

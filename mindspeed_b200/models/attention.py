@@ -192,6 +192,12 @@ class MLASelfAttention(nn.Module):
         self.linear_proj = RowParallelLinear(config.num_attention_heads * self.v_dim, h, config=config,
                                              init_method=config.output_layer_init_method, bias=config.add_bias_linear,
                                              input_is_parallel=True, skip_bias_add=True)
+        self.dsa = getattr(config, "experimental_attention_variant", None) == "dsa"
+        if self.dsa:
+            from .dsa import DSAIndexer
+            if ps.get_context_parallel_world_size() > 1:
+                raise NotImplementedError("DeepSeek sparse attention is not combined with context parallelism")
+            self.indexer = DSAIndexer(config)
 
     def forward(self, hidden_states, attention_mask=None, rotary_pos_emb=None, packed_seq_params=None, **_):
         from ..parallel import mappings as M
@@ -199,6 +205,7 @@ class MLASelfAttention(nn.Module):
         x = hidden_states
         sp = cfg.sequence_parallel and ps.get_tensor_model_parallel_world_size() > 1
         if cfg.q_lora_rank is None:
+            qc = x
             q, _ = self.linear_q_proj(x)
         else:
             qc = self.q_layernorm(self.linear_q_down_proj(x))
@@ -210,13 +217,11 @@ class MLASelfAttention(nn.Module):
             kvc = M.gather_from_sequence_parallel_region(kvc, tensor_parallel_output_grad=True)
         kv_lat, k_pe = kvc.split([cfg.kv_lora_rank, self.qk_rope], dim=-1)
         kv_lat = self.kv_layernorm(kv_lat.contiguous())
-        if sp:
-            kv_in = M.scatter_to_sequence_parallel_region(kv_lat)
-        else:
-            kv_in = kv_lat
-        kv, _ = self.linear_kv_up_proj(kv_in)
-        kv = kv.view(s, b, self.n, self.qk_nope + self.v_dim)
-        k_nope, v = kv.split([self.qk_nope, self.v_dim], dim=-1)
+        if not self.dsa:                            # the sparse path applies the up-projection weight itself
+            kv_in = M.scatter_to_sequence_parallel_region(kv_lat) if sp else kv_lat
+            kv, _ = self.linear_kv_up_proj(kv_in)
+            kv = kv.view(s, b, self.n, self.qk_nope + self.v_dim)
+            k_nope, v = kv.split([self.qk_nope, self.v_dim], dim=-1)
         q_nope, q_pe = q.split([self.qk_nope, self.qk_rope], dim=-1)
         k_pe = k_pe.reshape(s, b, 1, self.qk_rope)
         if rotary_pos_emb is not None:
@@ -224,6 +229,14 @@ class MLASelfAttention(nn.Module):
             q_pe = apply_rope(q_pe, cos, sin, cfg.rotary_interleaved, fused=False)
             k_pe = apply_rope(k_pe, cos, sin, cfg.rotary_interleaved, fused=False)
         qf = torch.cat((q_nope, q_pe), dim=-1)
+        if self.dsa:
+            from .dsa import dsa_attention
+            xf, qcf = x.detach(), qc.detach()
+            if sp:                                  # the indexer scores the whole sequence on every rank
+                xf = M.gather_from_sequence_parallel_region(xf, tensor_parallel_output_grad=False)
+                qcf = M.gather_from_sequence_parallel_region(qcf, tensor_parallel_output_grad=False)
+            ctx = dsa_attention(self, xf, qcf, qf, kv_lat, k_pe, rotary_pos_emb)
+            return self.linear_proj(ctx)
         kf = torch.cat((k_nope, k_pe.expand(s, b, self.n, self.qk_rope)), dim=-1)
         ctx = self.core_attention(qf, kf, v.contiguous(), attention_mask, packed_seq_params)
         return self.linear_proj(ctx)

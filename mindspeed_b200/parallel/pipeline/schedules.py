@@ -109,10 +109,30 @@ def forward_step(forward_step_func, data_iterator, model, num_microbatches, inpu
             forward_data_store.append(loss_reduced)
         else:
             forward_data_store.append(loss_func(output_tensor, non_loss_data=True))
-    if getattr(config, "timers", None) is not None:
-        pass
-    # MoE auxiliary losses are attached to the graph by the router with their own scale
+    _set_aux_loss_scale(config, num_microbatches, output_tensor)
     return output_tensor, num_tokens
+
+
+def _set_aux_loss_scale(config, num_microbatches, like):
+    """Losses attached inside the model (MoE load balancing / z-loss, the sparse-attention indexer's KL loss) get the
+    gradient scale of the main loss: the loss scaler's factor, divided by the micro-batch count when the main loss is
+    averaged over micro-batches."""
+    moe = getattr(config, "num_moe_experts", None) is not None
+    dsa = getattr(config, "experimental_attention_variant", None) == "dsa"
+    if not (moe or dsa):
+        return
+    dev = like.device if torch.is_tensor(like) else (like[0].device if like else "cpu")
+    scale = torch.ones(1, device=dev)
+    if getattr(config, "grad_scale_func", None) is not None:
+        scale = config.grad_scale_func(scale)
+    if not getattr(config, "calculate_per_token_loss", False):
+        scale = scale / num_microbatches
+    if moe:
+        from ..moe.moe_utils import MoEAuxLossAutoScaler
+        MoEAuxLossAutoScaler.set_loss_scale(scale)
+    if dsa:
+        from ...models.dsa import DSAIndexerLossScaler
+        DSAIndexerLossScaler.set_loss_scale(scale)
 
 
 def is_multi_parameter(config) -> bool:
