@@ -127,7 +127,7 @@ class TransformerConfig(ModelParallelConfig):
     dsa_indexer_topk: int = 2048
     dsa_indexer_loss_coeff: float = 1.0
     use_dsa_absorb: bool = False
-    kl_loss_reduction: str = "batchmean"
+    kl_loss_reduction: str = "mean"
     softmax_scale: Optional[float] = None
     attention_softmax_in_fp32: bool = True
     apply_query_key_layer_scaling: bool = False

@@ -68,7 +68,6 @@ UNSUPPORTED: Dict[str, str] = {
     "alibi-diagonal-opposite": "ALiBi runs on the reference (eager) attention path only; the fused kernels have no bias input",
     "square-alibi-mask": "ALiBi runs on the reference (eager) attention path only; the fused kernels have no bias input",
     "fix-sub-seq-length": "fixed-length sub-sequence packing for EOD-reset CP is not implemented",
-    "no-qad-enable": "distillation is driven through mindspeed_b200.qat.distill, not through this switch",
 }
 
 

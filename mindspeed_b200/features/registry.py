@@ -69,14 +69,43 @@ class TransformerEngineBasicFeature(Feature):
         add_arg(g, "--fp8-reuse-quantized-weight", action="store_true")
         add_arg(g, "--qat-scheme", type=str, default=None, choices=[None, "w4a16", "w8a16", "w4a4"])
         add_arg(g, "--qat-quant-block-size", type=int, default=128)
+        add_arg(g, "--qad-enable", action="store_true", default=False)
         add_arg(g, "--no-qad-enable", action="store_false", dest="qad_enable")
-        add_arg(g, "--kl-loss-reduction", type=str, default="batchmean")
+        add_arg(g, "--qad-teacher-load", type=str, default="")
+        add_arg(g, "--kl-temperature", type=float, default=1.0)
+        add_arg(g, "--kl-loss-weight", type=float, default=1.0)
+        add_arg(g, "--kl-loss-reduction", type=str, default="mean", choices=["mean", "sum"])
 
     def validate_args(self, args):
         if args.fp8_format == "hif8":
             raise AssertionError("hif8 is an Ascend number format with no Blackwell tensor-core mode; use e4m3/hybrid")
         if args.fp8_format and args.fp8_recipe == "delayed" and getattr(args, "moe_grouped_gemm", False):
             pass
+
+
+class QADFeature(Feature):
+    """Quantisation-aware distillation (reference: mindspeed/features_manager/qad/qad_quant_engine.py:17-175)."""
+
+    def __init__(self):
+        super().__init__("qad-enable", optimization_level=0)
+
+    def is_need_apply(self, args) -> bool:
+        return bool(getattr(args, "qad_enable", False))
+
+    def validate_args(self, args):
+        if not args.qad_teacher_load:
+            raise AssertionError("--qad-enable needs --qad-teacher-load (the teacher's checkpoint directory)")
+        if args.kl_temperature <= 0:
+            raise AssertionError(f"--kl-temperature must be positive, got {args.kl_temperature}")
+        if args.kl_loss_weight < 0:
+            raise AssertionError(f"--kl-loss-weight must not be negative, got {args.kl_loss_weight}")
+        if getattr(args, "num_experts", None):
+            raise AssertionError("--qad-enable covers dense models only (--num-experts is set)")
+        if args.pipeline_model_parallel_size > 1:
+            raise AssertionError("--qad-enable needs --pipeline-model-parallel-size 1: the loss compares the teacher's and "
+                                 "the student's logits of one micro-batch on one rank")
+        if getattr(args, "context_parallel_size", 1) > 1:
+            raise AssertionError("--qad-enable is not combined with context parallelism")
 
 
 class ProfileFeature(Feature):
@@ -352,8 +381,6 @@ class SparseAttentionFeature(Feature):
                                  "--use-fused-lightning-indexer-kl-loss together")
         if args.context_parallel_size > 1:
             raise AssertionError("--experimental-attention-variant dsa is not combined with context parallelism")
-        if args.kl_loss_reduction not in ("batchmean", "sum", "mean"):
-            raise AssertionError("--kl-loss-reduction is one of batchmean, sum, mean")
 
 
 class MLAFeature(Feature):
@@ -796,7 +823,7 @@ class TTPFeature(Feature):
 
 def create_features_list():
     return [
-        RequirementsBasicFeature(), MegatronBasicFeature(), TransformerEngineBasicFeature(), ProfileFeature(),
+        RequirementsBasicFeature(), MegatronBasicFeature(), TransformerEngineBasicFeature(), QADFeature(), ProfileFeature(),
         TflopsCalculateFeature(), DeterministicFeature(), TokenizerFeature(),
         FusedTPCommFeature(), ChunkedTPCommFeature(), TP2DFeature(), UnalignedLinearFeature(),
         ContextParallelFeature(), FlashAttentionFeature(), SparseAttentionFeature(), MLAFeature(),

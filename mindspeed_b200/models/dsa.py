@@ -139,7 +139,7 @@ def dsa_attention(self, x_full, qc_full, q, kv_lat, k_pe, rotary_pos_emb):
             p_all = p.detach().clone()
             torch.distributed.all_reduce(p_all, group=ps.get_tensor_model_parallel_group())
             p_all /= ps.get_tensor_model_parallel_world_size()
-        loss = SA.selected_kl_loss(sc, idx, p_all, getattr(cfg, "kl_loss_reduction", "batchmean"))
+        loss = SA.selected_kl_loss(sc, idx, p_all, getattr(cfg, "kl_loss_reduction", "mean"))
         _LOSSES[self.layer_number] = loss.detach()
         ctx = DSAIndexerLossScaler.apply(ctx, loss, float(cfg.dsa_indexer_loss_coeff))
     return ctx

@@ -80,12 +80,11 @@ def sparse_latent_attention(q_lat, q_pe, kv, k_pe, idx, softmax_scale: float, bl
     return _blocks(one, q_lat.shape[1], block, recompute, q_lat, q_pe, idx, shared=(kv, k_pe))
 
 
-def selected_kl_loss(scores, idx, p_target, reduction: str = "batchmean"):
+def selected_kl_loss(scores, idx, p_target, reduction: str = "mean"):
     """KL(p_target || softmax over the selected keys of the indexer scores).
 
     scores [B, T, S] (the indexer's, -inf where a key is not visible); idx [B, T, K]; p_target [B, T, K] (detached here).
-    ``reduction``: "batchmean" averages over query tokens, "sum" adds them, "mean" also divides by K (the conventions
-    of ``torch.nn.functional.kl_div``)."""
+    ``reduction``: "mean" (alias "batchmean") averages the per-query divergences over query tokens, "sum" adds them."""
     valid = idx >= 0
     sc = torch.gather(scores, 2, idx.clamp_min(0)).masked_fill(~valid, float("-inf"))
     m = sc.amax(dim=-1, keepdim=True)
@@ -98,8 +97,6 @@ def selected_kl_loss(scores, idx, p_target, reduction: str = "batchmean"):
     tot = kl.sum()
     if reduction == "sum":
         return tot
-    if reduction == "mean":
-        return tot / kl.numel()
-    if reduction == "batchmean":
+    if reduction in ("mean", "batchmean"):
         return tot / (kl.shape[0] * kl.shape[1])
     raise ValueError(f"unknown KL reduction {reduction!r}")

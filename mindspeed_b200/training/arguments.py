@@ -167,6 +167,8 @@ def _core_args(p: argparse.ArgumentParser):
     g.add_argument("--no-save-rng", action="store_true")
     g.add_argument("--no-load-optim", action="store_true")
     g.add_argument("--no-load-rng", action="store_true")
+    g.add_argument("--finetune", action="store_true",
+                   help="load the model weights only (no optimizer, scheduler or RNG state) and start counting iterations at 0")
     g.add_argument("--ckpt-format", type=str, default="torch_dist", choices=["torch", "torch_dist"])
     g.add_argument("--use-dist-ckpt", action="store_true")
     g.add_argument("--async-save", action="store_true")

@@ -170,9 +170,21 @@ def setup_model_and_optimizer(model_provider_func, no_wd_decay_cond=None, scale_
         qcfg = QATConfig(scheme=args.qat_scheme.upper(), weight_group=getattr(args, "qat_quant_block_size", 128))
         for m in model:
             apply_qat(m, qcfg)
+    if getattr(args, "qad_enable", False):
+        from ..qat.qad import setup_teacher
+        setup_teacher(model_provider_func, args)      # full precision, frozen; not touched by --qat-scheme
     _MEMORY_MANAGERS.clear()
     _MEMORY_MANAGERS.extend(build_memory_managers(args, model))
-    if args.load:
+    if args.load and getattr(args, "finetune", False):
+        from ..qat.qad import load_model_weights
+        load_model_weights(model, args.load)
+        for chunk in model:
+            if hasattr(chunk, "post_load"):
+                chunk.post_load()
+        if hasattr(optimizer, "reload_model_params"):
+            optimizer.reload_model_params()
+        args.iteration = 0
+    elif args.load:
         from ..checkpointing import load_checkpoint
         args.iteration = load_checkpoint(model, optimizer, sched)
     else:

@@ -40,6 +40,11 @@ def loss_func(loss_mask, output_tensor):
 def forward_step(data_iterator, model):
     dev = next(model.parameters()).device
     tokens, labels, loss_mask, attention_mask, position_ids, packed = get_batch(data_iterator, dev, return_packed=True)
+    args = get_args()
+    if getattr(args, "qad_enable", False):
+        # quantisation-aware distillation: the loss is the KL divergence from a frozen teacher's logits
+        from mindspeed_b200.qat.qad import qad_forward_step
+        return qad_forward_step(tokens, labels, loss_mask, attention_mask, position_ids, packed, model, args)
     out = model(tokens, position_ids, attention_mask, labels=labels, packed_seq_params=packed)
     return out, partial(loss_func, loss_mask)
 
