@@ -121,6 +121,9 @@ class TransformerConfig(ModelParallelConfig):
     test_mode: bool = False
     calculate_per_token_loss: bool = False
     multi_latent_attention: bool = False
+    position_embedding_type: str = "learned_absolute"        # "alibi": attention adds the per-head linear distance bias
+    alibi_fusion_attn_type: Optional[int] = None             # None / 0 / 2: -slope * |i - j|; 3: -slope * sqrt|i - j|
+    alibi_diagonal_opposite: bool = False                    # bias slope * (j - i): opposite signs on the two sides
     experimental_attention_variant: Optional[str] = None     # "dsa": lightning indexer + top-k sparse attention (MLA only)
     dsa_indexer_n_heads: int = 64
     dsa_indexer_head_dim: int = 128

@@ -28,6 +28,7 @@ NO_EFFECT: Dict[str, str] = {
     "attention-mask-on-cpu": "the causal mask is generated inside the attention kernels, no mask tensor is built",
     "pre-tockens": "sliding-window bounds of the vendor attention op; attention here is full or causal",
     "next-tockens": "sliding-window bounds of the vendor attention op; attention here is full or causal",
+    "square-alibi-mask": "shape of the ALiBi bias tensor on the unfused path; the bias here is evaluated from the head slopes block by block, no bias tensor of either shape exists",
     "fill-neg-inf": "mask fill value of the unfused softmax path; masked scores are -inf in every kernel here",
     "te-comparison-with-bf16": "debug comparison hook of the reference's TE shim",
     "te-comparison-with-cpu": "debug comparison hook of the reference's TE shim",
@@ -64,9 +65,6 @@ NO_EFFECT: Dict[str, str] = {
 UNSUPPORTED: Dict[str, str] = {
     "ampipe-degree": "attention-MoE micro-pipelining (ampipe) is not implemented; use --moe-fb-overlap",
     "adaptive-recompute-device-swap": "adaptive recompute decides recompute only; combine it with --swap-attention for host swap",
-    "alibi-fusion-attn-type": "ALiBi runs on the reference (eager) attention path only; the fused kernels have no bias input",
-    "alibi-diagonal-opposite": "ALiBi runs on the reference (eager) attention path only; the fused kernels have no bias input",
-    "square-alibi-mask": "ALiBi runs on the reference (eager) attention path only; the fused kernels have no bias input",
     "fix-sub-seq-length": "fixed-length sub-sequence packing for EOD-reset CP is not implemented",
 }
 

@@ -342,6 +342,27 @@ class FlashAttentionFeature(Feature):
         add_arg(g, "--fix-sub-seq-length", type=int, default=None)
 
 
+class AlibiFeature(Feature):
+    """ALiBi position bias (reference: mindspeed/features_manager/transformer/flash_attention/alibi_feature.py:9-90)."""
+
+    def __init__(self):
+        super().__init__("position-embedding-type", optimization_level=0)
+
+    def is_need_apply(self, args) -> bool:
+        return getattr(args, "position_embedding_type", None) == "alibi" or args.alibi_fusion_attn_type is not None \
+            or args.alibi_diagonal_opposite
+
+    def validate_args(self, args):
+        if args.position_embedding_type != "alibi":
+            raise AssertionError("--alibi-fusion-attn-type / --alibi-diagonal-opposite need --position-embedding-type alibi")
+        if args.alibi_diagonal_opposite and args.alibi_fusion_attn_type == 3:
+            raise AssertionError("--alibi-diagonal-opposite applies to the linear bias (--alibi-fusion-attn-type 0 or 2)")
+        if args.context_parallel_size > 1:
+            raise AssertionError("--position-embedding-type alibi is not combined with context parallelism")
+        if getattr(args, "reset_attention_mask", False):
+            raise AssertionError("--position-embedding-type alibi is not combined with --reset-attention-mask")
+
+
 class SparseAttentionFeature(Feature):
     """DeepSeek sparse attention (reference: mindspeed/features_manager/transformer/experimental_attention_variant/dsa.py:5-50)."""
 
@@ -826,7 +847,7 @@ def create_features_list():
         RequirementsBasicFeature(), MegatronBasicFeature(), TransformerEngineBasicFeature(), QADFeature(), ProfileFeature(),
         TflopsCalculateFeature(), DeterministicFeature(), TokenizerFeature(),
         FusedTPCommFeature(), ChunkedTPCommFeature(), TP2DFeature(), UnalignedLinearFeature(),
-        ContextParallelFeature(), FlashAttentionFeature(), SparseAttentionFeature(), MLAFeature(),
+        ContextParallelFeature(), FlashAttentionFeature(), AlibiFeature(), SparseAttentionFeature(), MLAFeature(),
         DualpipeVFeature(), PipelineMiscFeature(), MoEFeature(), MemoryFeature(), OptimizerFeature(),
         DistributedFeature(), AutoSettingsFeature(), TTPFeature(),
     ]

@@ -55,11 +55,27 @@ class CoreAttention(nn.Module):
         if config.apply_query_key_layer_scaling:
             self.softmax_scale /= layer_number
         self.dropout_p = config.attention_dropout
+        self.alibi_slopes = None
+        if getattr(config, "position_embedding_type", None) == "alibi":
+            from .attention_masks import alibi_slopes
+            tp, r = ps.get_tensor_model_parallel_world_size(), ps.get_tensor_model_parallel_rank()
+            per = config.num_attention_heads // tp
+            self.alibi_slopes = alibi_slopes(config.num_attention_heads)[r * per:(r + 1) * per]
+
+    def _alibi(self, q, k, v, packed):
+        if packed or ps.get_context_parallel_world_size() > 1:
+            raise NotImplementedError("ALiBi attention is not combined with packed sequences or context parallelism")
+        cfg = self.config
+        self.alibi_slopes = self.alibi_slopes.to(q.device)
+        return attn_ops.alibi_attention(q, k, v, self.alibi_slopes, causal=self.causal, softmax_scale=self.softmax_scale,
+                                        mode=cfg.alibi_fusion_attn_type or 0, signed=bool(cfg.alibi_diagonal_opposite))
 
     def forward(self, q, k, v, attention_mask=None, packed_seq_params=None):
         cp = ps.get_context_parallel_world_size()
         cu = packed_seq_params.get("cu_seqlens") if isinstance(packed_seq_params, dict) else getattr(packed_seq_params, "cu_seqlens_q", None)
-        if cu is not None:
+        if self.alibi_slopes is not None:
+            out = self._alibi(q, k, v, cu is not None)
+        elif cu is not None:
             # packed documents (--reset-attention-mask): every document attends to itself only
             if cp > 1:
                 raise NotImplementedError("packed-sequence attention is not combined with context parallelism")

@@ -34,6 +34,8 @@ class GPTModel(nn.Module):
         self.parallel_output = parallel_output
         self.share_embeddings_and_output_weights = share_embeddings_and_output_weights
         self.position_embedding_type = position_embedding_type
+        if position_embedding_type == "alibi":
+            config.position_embedding_type = "alibi"            # read by the attention layers (bias from head slopes)
         self.fp16_lm_cross_entropy = fp16_lm_cross_entropy
         self.vp_stage = vp_stage
         if pre_process:

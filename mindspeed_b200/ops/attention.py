@@ -203,3 +203,49 @@ def varlen_attention(q, k, v, cu_seqlens, causal=True, softmax_scale=None, backe
         if b > a:
             outs.append(flash_attention(q[a:b], k[a:b], v[a:b], causal=causal, softmax_scale=softmax_scale, backend=backend))
     return torch.cat(outs, dim=0)
+
+
+def alibi_attention(q, k, v, slopes, causal=True, softmax_scale=None, mode=0, signed=False, block=1024):
+    """Attention with the ALiBi position bias evaluated from the per-head ``slopes [n]`` (no [n, s, s] bias tensor is built).
+
+    q [sq, b, n, d]; k, v [sk, b, nkv, d].  ``mode`` 0 / 2: bias = -slope * |i - j| (0 is the reference's dense-bias form,
+    2 its in-kernel form: the same values); 3: -slope * sqrt|i - j|.  ``signed`` (the reference's diagonal-opposite option,
+    modes 0 / 2): bias = slope * (j - i), negative for past keys and positive for future ones - the same as the default under
+    a causal mask.  Query rows are processed in blocks, each re-computed in backward, so one block's [b, n, tb, sk]
+    scores are the largest temporary.  fp32 math.
+    reference: mindspeed/core/transformer/flash_attention/alibi/alibi.py:28-124, dot_product_attention.py:19-106."""
+    from torch.utils.checkpoint import checkpoint
+    sq, b, nq, d = q.shape
+    sk, nkv = k.shape[0], k.shape[2]
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
+    rep = nq // nkv
+    off = sk - sq
+    sl = slopes.float().view(1, nq, 1, 1)
+
+    def one(qb, k, v, t0):
+        tb = qb.shape[0]
+        kf = k.permute(1, 2, 0, 3).float().repeat_interleave(rep, dim=1)
+        vf = v.permute(1, 2, 0, 3).float().repeat_interleave(rep, dim=1)
+        s = torch.matmul(qb.permute(1, 2, 0, 3).float(), kf.transpose(-1, -2)) * scale
+        qi = torch.arange(t0, t0 + tb, device=q.device).view(tb, 1) + off
+        kj = torch.arange(sk, device=q.device).view(1, sk)
+        rel = (kj - qi).float()
+        if mode == 3:
+            bias = -sl * rel.abs().sqrt().view(1, 1, tb, sk)
+        elif signed:
+            bias = sl * rel.view(1, 1, tb, sk)
+        else:
+            bias = -sl * rel.abs().view(1, 1, tb, sk)
+        s = s + bias
+        if causal:
+            s = s.masked_fill((kj > qi).view(1, 1, tb, sk), float("-inf"))
+        p = torch.softmax(s, dim=-1)
+        return torch.matmul(p, vf).permute(2, 0, 1, 3).to(q.dtype)
+
+    outs = []
+    need = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
+    for t0 in range(0, sq, block):
+        qb = q[t0:t0 + block]
+        outs.append(checkpoint(one, qb, k, v, t0, use_reentrant=False) if need and sq > block else one(qb, k, v, t0))
+    return torch.cat(outs, dim=0).contiguous()
+
