@@ -339,7 +339,7 @@ class FlashAttentionFeature(Feature):
         add_arg(g, "--alibi-fusion-attn-type", type=int, default=None, choices=[None, 0, 2, 3])
         add_arg(g, "--alibi-diagonal-opposite", action="store_true")
         add_arg(g, "--reset-attention-mask", action="store_true")
-        add_arg(g, "--fix-sub-seq-length", type=int, default=None)
+        add_arg(g, "--fix-sub-seq-length", type=int, default=-1)
 
 
 class AlibiFeature(Feature):

@@ -187,17 +187,27 @@ def merge_lse(out1, lse1, out2, lse2):
 
 
 def varlen_attention(q, k, v, cu_seqlens, causal=True, softmax_scale=None, backend=None):
-    """Attention over packed sequences: q / k / v [s, 1, n, d] hold several documents back to back, ``cu_seqlens`` (host
-    integers, first 0, last s) their boundaries; every document attends only to itself.  One attention call per document on
-    the configured backend (the tcgen05 kernels on a GPU), so the cost is the sum of the documents' squares instead of s^2.
+    """Attention over packed sequences: q / k / v [s, b, n, d] hold several documents back to back, ``cu_seqlens`` (host
+    integers, first 0, last s) their boundaries, the same for every batch row (b = 1 when they come from the data);
+    every document attends only to itself.  One attention call per document on the configured backend (the tcgen05
+    kernels on a GPU), so the cost is the sum of the documents' squares instead of s^2; documents of one common length
+    are folded into the batch axis and take a single call.
     reference semantics: actual_seq_qlen / actual_seq_kvlen of npu_fusion_attention in the TND layout
     (mindspeed/ops/fusion_attention_v2.py:22-114) as used by the reset-attention-mask path
     (mindspeed/core/transformer/flash_attention/reset_attention_mask/adaptor.py:218-759)."""
-    if q.shape[1] != 1:
-        raise ValueError("packed-sequence attention takes micro-batch size 1 (documents are concatenated along the sequence)")
     bounds = [int(x) for x in cu_seqlens]
     if bounds[0] != 0 or bounds[-1] != q.shape[0]:
         raise ValueError(f"cu_seqlens must run from 0 to the sequence length {q.shape[0]}, got {bounds[0]}..{bounds[-1]}")
+    lens = {b - a for a, b in zip(bounds[:-1], bounds[1:])}
+    if len(lens) == 1 and len(bounds) > 2:
+        # equal sub-sequences: fold them into the batch axis, one attention call for all of them
+        L, m = lens.pop(), len(bounds) - 1
+        s, b = q.shape[0], q.shape[1]
+
+        def fold(x):
+            return x.reshape(m, L, b, x.shape[2], x.shape[3]).transpose(0, 1).reshape(L, m * b, x.shape[2], x.shape[3])
+        o = flash_attention(fold(q), fold(k), fold(v), causal=causal, softmax_scale=softmax_scale, backend=backend)
+        return o.reshape(L, m, b, o.shape[2], o.shape[3]).transpose(0, 1).reshape(s, b, o.shape[2], o.shape[3])
     outs = []
     for a, b in zip(bounds[:-1], bounds[1:]):
         if b > a:

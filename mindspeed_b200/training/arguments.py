@@ -239,11 +239,14 @@ def _core_validate(args):
         args.accumulate_allreduce_grads_in_fp32 = True
     if getattr(args, "reset_attention_mask", False):
         # packed documents: each attends to itself only; documents are concatenated along the sequence of one sample
-        if args.micro_batch_size != 1:
+        # --fix-sub-seq-length L replaces the documents' own boundaries by sub-sequences of L tokens (the last takes the
+        # rest): every row of a batch then has the same boundaries, so any micro-batch size and synthetic data work
+        fixed = 0 < (getattr(args, "fix_sub_seq_length", None) or -1) <= args.seq_length
+        if args.micro_batch_size != 1 and not fixed:
             raise AssertionError("--reset-attention-mask takes --micro-batch-size 1 (packed documents share one sequence)")
         if getattr(args, "context_parallel_size", 1) > 1:
             raise AssertionError("--reset-attention-mask is not combined with context parallelism")
-        if not getattr(args, "data_path", None):
+        if not getattr(args, "data_path", None) and not fixed:
             raise AssertionError("--reset-attention-mask needs --data-path: synthetic data has no document boundaries")
     if args.sequence_parallel and args.tensor_model_parallel_size == 1:
         args.sequence_parallel = False

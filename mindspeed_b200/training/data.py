@@ -48,6 +48,25 @@ class BatchIterator:
         return batch
 
 
+def fixed_sub_seq_boundaries(seq_length: int, sub_seq_length: int):
+    """[0, L, 2L, ..., seq_length]: sub-sequences of L tokens, the last one taking what is left
+    (reference: mindspeed/core/transformer/flash_attention/reset_attention_mask/utils.py:206-211)."""
+    return list(range(0, seq_length, sub_seq_length)) + [seq_length]
+
+
+def _fixed_sub_seq_boundaries(seq_length):
+    """Boundaries set by ``--reset-attention-mask --fix-sub-seq-length L`` (0 < L <= seq_length), else None."""
+    try:
+        from .global_vars import get_args
+        args = get_args()
+    except RuntimeError:
+        return None
+    L = getattr(args, "fix_sub_seq_length", None)
+    if not getattr(args, "reset_attention_mask", False) or L is None or not (0 < L <= seq_length):
+        return None
+    return fixed_sub_seq_boundaries(seq_length, L)
+
+
 def get_batch(data_iterator, device=None, return_packed=False):
     """tokens, labels, loss_mask, attention_mask(None: causal), position_ids for this cp rank; with ``return_packed`` a sixth
     value: None, or for batches that carry ``document_ids`` (packed documents, --reset-attention-mask) a dict with the
@@ -55,7 +74,10 @@ def get_batch(data_iterator, device=None, return_packed=False):
     batch = next(data_iterator)
     packed = None
     doc = batch.pop("document_ids", None) if isinstance(batch, dict) else None
-    if doc is not None:
+    fixed = _fixed_sub_seq_boundaries(batch["tokens"].shape[1]) if return_packed else None
+    if fixed is not None:
+        packed = {"cu_seqlens": fixed}                 # the same for every row of the batch
+    elif doc is not None:
         if doc.shape[0] != 1:
             raise ValueError("packed documents (--reset-attention-mask) take micro-batch size 1")
         d = doc[0].cpu()
@@ -64,7 +86,15 @@ def get_batch(data_iterator, device=None, return_packed=False):
     if device is not None:
         batch = {k: v.to(device, non_blocking=True) for k, v in batch.items()}
     batch = get_batch_on_this_cp_rank(batch)
-    if packed is not None and bool((batch["position_ids"][0, 1:] < batch["position_ids"][0, :-1]).any()):
+    if fixed is not None:
+        # positions restart in every sub-sequence (the rotary embedding of a packed layout follows the boundaries)
+        pos = torch.arange(fixed[-1], device=batch["position_ids"].device)
+        start = torch.zeros_like(pos)
+        for a in fixed[1:-1]:
+            start[a:] = a
+        batch["position_ids"] = (pos - start).unsqueeze(0).expand_as(batch["position_ids"]).contiguous()
+        packed["position_ids"] = batch["position_ids"][:1]            # one row: the same for the whole batch
+    elif packed is not None and bool((batch["position_ids"][0, 1:] < batch["position_ids"][0, :-1]).any()):
         packed["position_ids"] = batch["position_ids"]
     out = (batch["tokens"], batch["labels"], batch["loss_mask"], None, batch["position_ids"])
     return out + (packed,) if return_packed else out

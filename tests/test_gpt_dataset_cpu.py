@@ -164,3 +164,66 @@ def test_training_with_reset_attention_mask_uses_packed_attention():
                                                                               "--eod-mask-loss"])[0]
         assert c0["n"] == 0 and c1["n"] > 0 and c1["docs"] > c1["n"]          # several documents per sample
         assert plain != packed and all(abs(a - b) < 0.5 for a, b in zip(plain, packed))
+
+
+def test_equal_sub_sequences_fold_into_the_batch_axis():
+    from mindspeed_b200.ops.attention import attention_ref, varlen_attention
+    from mindspeed_b200.training.data import fixed_sub_seq_boundaries
+    assert fixed_sub_seq_boundaries(32, 8) == [0, 8, 16, 24, 32]
+    assert fixed_sub_seq_boundaries(30, 8) == [0, 8, 16, 24, 30]
+    assert fixed_sub_seq_boundaries(8, 8) == [0, 8]
+    torch.manual_seed(0)
+    s, b, n, d = 32, 3, 2, 8
+    q, k, v = (torch.randn(s, b, n, d, requires_grad=True) for _ in range(3))
+    for cu in ([0, 8, 16, 24, 32], [0, 12, 24, 32]):                 # folded path / one call per sub-sequence, batch of 3
+        doc = torch.zeros(s, dtype=torch.long)
+        for i, (a, e) in enumerate(zip(cu[:-1], cu[1:])):
+            doc[a:e] = i
+        masked = ~(torch.tril(torch.ones(s, s, dtype=torch.bool)) & (doc.view(-1, 1) == doc.view(1, -1)))
+        ref = attention_ref(q, k, v, causal=False, mask=masked.view(1, 1, s, s))
+        out = varlen_attention(q, k, v, cu, causal=True)
+        w = torch.randn_like(ref)
+        torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5)
+        for a, e in zip(torch.autograd.grad((out * w).sum(), (q, k, v)), torch.autograd.grad((ref * w).sum(), (q, k, v))):
+            torch.testing.assert_close(a, e, rtol=1e-5, atol=1e-5)
+
+
+def _train_fixed(rank, world, extra):
+    import io
+    from contextlib import redirect_stdout
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import pretrain_gpt as pg
+    from test_pipeline_cpu import BASE
+    from mindspeed_b200.training import pretrain
+    seen = []
+    orig = pg.get_batch
+
+    def spy(*a, **kw):
+        out = orig(*a, **kw)
+        seen.append((out[5], out[4][:, :12].tolist()))
+        return out
+    pg.get_batch = spy
+    base = list(BASE)
+    base[base.index("--micro-batch-size") + 1] = "2"
+    with redirect_stdout(io.StringIO()):
+        hist = pretrain(pg.train_valid_test_datasets_provider, pg.model_provider, forward_step_func=pg.forward_step,
+                        args_list=base + list(extra))
+    pg.get_batch = orig
+    return [h["lm loss"] for h in hist], seen[0]
+
+
+def test_fixed_sub_sequence_length_sets_boundaries_and_positions_for_any_batch():
+    """--reset-attention-mask --fix-sub-seq-length 8 on synthetic data with micro-batch 2: attention and rotary positions
+    restart every 8 tokens (sequence length 32 -> four sub-sequences per row)."""
+    from dist_utils import run_distributed
+    plain, (p0, _) = run_distributed(_train_fixed, 1, [])[0]
+    fixed, (p1, pos) = run_distributed(_train_fixed, 1, ["--reset-attention-mask", "--fix-sub-seq-length", "8"])[0]
+    assert p0 is None and p1["cu_seqlens"] == [0, 8, 16, 24, 32]
+    assert pos == [[0, 1, 2, 3, 4, 5, 6, 7, 0, 1, 2, 3]] * 2
+    assert plain != fixed and all(abs(a - b) < 0.5 for a, b in zip(plain, fixed))
+    # a sub-sequence length above the sequence length leaves the documents' own boundaries (none here): refused without data
+    from mindspeed_b200.training.arguments import parse_args, validate_args
+    with pytest.raises(AssertionError, match="data-path"):
+        validate_args(parse_args(args_list=["--num-layers", "2", "--hidden-size", "64", "--num-attention-heads", "4", "--seq-length",
+                                            "32", "--micro-batch-size", "1", "--vocab-size", "128", "--reset-attention-mask",
+                                            "--fix-sub-seq-length", "64"]))
