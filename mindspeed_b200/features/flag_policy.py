@@ -64,7 +64,6 @@ NO_EFFECT: Dict[str, str] = {
 
 UNSUPPORTED: Dict[str, str] = {
     "ampipe-degree": "attention-MoE micro-pipelining (ampipe) is not implemented; use --moe-fb-overlap",
-    "adaptive-recompute-device-swap": "adaptive recompute decides recompute only; combine it with --swap-attention for host swap",
 }
 
 

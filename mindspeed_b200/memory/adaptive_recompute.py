@@ -10,6 +10,13 @@
 
 Budget = ``--adaptive-recompute-device-size`` (MiB of device memory the job may use) minus the static footprint
 (parameters, gradients, optimizer state) measured at the end of profiling.
+
+``--adaptive-recompute-device-swap`` (``swap_while_profiling``): the profiling steps themselves must not run out of
+memory, so while profiling every large activation saved for backward is parked in pinned host memory and fetched back
+when backward needs it (``memory/host_offload.OffloadSaved``); the byte counts are unchanged by that.  Without an explicit
+device size the budget is then ``auto_budget_fraction`` of the device's memory.  After the decision the swap stops and the
+chosen modules recompute.  (The reference reaches the same end from the other side: its allocator swaps tensors out when
+an allocation fails during profiling and the swapped volume tells the solver how much to free.)
 reference: mindspeed/core/memory/adaptive_recomputing/adaptive_recompute.py (profiling + hooks),
 adaptive_recompute_solver.py (knapsack over the module tree).
 """
@@ -102,8 +109,17 @@ class _Ckpt(nn.Module):
 
 class AdaptiveRecompute:
     def __init__(self, model: nn.Module, candidates: Optional[Sequence[str]] = None, profiling_steps: int = 2,
-                 device_budget_bytes: Optional[int] = None, child_names: Sequence[str] = ("self_attention", "mlp")):
+                 device_budget_bytes: Optional[int] = None, child_names: Sequence[str] = ("self_attention", "mlp"),
+                 swap_while_profiling: bool = False, auto_budget_fraction: float = 0.9, swap_min_bytes: int = 1 << 20):
         self.model, self.profiling_steps, self.budget = model, profiling_steps, device_budget_bytes
+        self.swap = None
+        if swap_while_profiling:
+            from .host_offload import OffloadSaved
+            self.swap = OffloadSaved(min_bytes=swap_min_bytes)
+            if self.budget is None and torch.cuda.is_available():
+                total = torch.cuda.get_device_properties(torch.cuda.current_device()).total_memory
+                self.budget = int(auto_budget_fraction * total)
+        self.swapped_bytes = 0                       # bytes parked on the host during profiling (all steps)
         self.step = 0
         self.profiles: Dict[str, ModuleProfile] = {}
         self.chosen: List[str] = []
@@ -168,8 +184,14 @@ class AdaptiveRecompute:
                 if mgr.step < mgr.profiling_steps:
                     def pack(t):
                         mgr._saved_counter += t.numel() * t.element_size()
-                        return t
-                    mgr._hooks_ctx = torch.autograd.graph.saved_tensors_hooks(pack, lambda t: t)
+                        if mgr.swap is None:
+                            return t
+                        out = mgr.swap._pack(t)
+                        if out is not t:
+                            mgr.swapped_bytes += t.numel() * t.element_size()
+                        return out
+                    unpack = (lambda t: t) if mgr.swap is None else mgr.swap._unpack
+                    mgr._hooks_ctx = torch.autograd.graph.saved_tensors_hooks(pack, unpack)
                     mgr._hooks_ctx.__enter__()
                 return self_inner
 

@@ -200,11 +200,13 @@ def build_memory_managers(args, model):
     (profiling or executing its policy through saved-tensor hooks) and is told when the step ends."""
     out = []
     budget_mb = getattr(args, "adaptive_recompute_device_size", -1)
-    if budget_mb and budget_mb > 0 and not getattr(args, "smart_swap", False):
+    dev_swap = bool(getattr(args, "adaptive_recompute_device_swap", False))
+    if ((budget_mb and budget_mb > 0) or dev_swap) and not getattr(args, "smart_swap", False):
         from ..memory.adaptive_recompute import AdaptiveRecompute
         for m in model:
             out.append(AdaptiveRecompute(m, profiling_steps=getattr(args, "adaptive_recompute_profiling_step", 10),
-                                         device_budget_bytes=budget_mb << 20))
+                                         device_budget_bytes=(budget_mb << 20) if budget_mb and budget_mb > 0 else None,
+                                         swap_while_profiling=dev_swap))
     if getattr(args, "smart_swap", False):
         from ..memory.smart_swap import SmartSwapManager
         if torch.cuda.is_available():

@@ -97,6 +97,50 @@ def test_adaptive_recompute_end_to_end():
     assert all(torch.allclose(a, b, atol=1e-6) for a, b in zip(got, gref))
 
 
+def test_adaptive_recompute_parks_activations_on_the_host_while_profiling():
+    """``swap_while_profiling``: during the profiling steps saved tensors go through the host-offload hooks (here a stand-in
+    that wraps them, as CPU tensors are passed through by the real one); after the decision the hooks are gone."""
+    net = _net(3)
+    x = torch.randn(128, 64, requires_grad=True)
+    ar = AR.AdaptiveRecompute(net, candidates=["0", "1", "2"], profiling_steps=1, device_budget_bytes=200_000,
+                              swap_while_profiling=True, swap_min_bytes=1024)
+    assert ar.swap is not None and ar.swap.min_bytes == 1024
+    parked = {"out": 0, "back": 0}
+
+    class Box:
+        def __init__(self, t):
+            self.t = t
+
+    class FakeSwap:
+        def _pack(self, t):
+            if t.numel() * t.element_size() < 1024:
+                return t
+            parked["out"] += 1
+            return Box(t.clone())
+
+        def _unpack(self, o):
+            if isinstance(o, Box):
+                parked["back"] += 1
+                return o.t
+            return o
+    ar.swap = FakeSwap()
+    with ar.step_context():
+        loss = net(x).pow(2).sum()
+    loss.backward()
+    gref = [p.grad.clone() for p in net.parameters()]
+    net.zero_grad()
+    assert parked["out"] > 0 and parked["back"] == parked["out"] and ar.swapped_bytes > 0
+    ar.end_step(static_bytes=0)
+    assert ar.chosen and all(ar.profiles[n].saved_bytes > 0 for n in ("0", "1", "2"))      # byte counts unaffected by the swap
+    n_out = parked["out"]
+    with ar.step_context():
+        loss2 = net(x).pow(2).sum()
+    loss2.backward()
+    assert parked["out"] == n_out                                                           # no swap after profiling
+    assert torch.allclose(loss, loss2)
+    assert all(torch.allclose(a.grad, b, atol=1e-6) for a, b in zip(net.parameters(), gref))
+
+
 def test_auto_pipeline_balances_time_under_memory():
     LP = AP.LayerProfile
     layers = [LP(1.0, 2.0, 100, 10, 50) for _ in range(8)]
