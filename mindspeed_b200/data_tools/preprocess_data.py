@@ -1,6 +1,6 @@
 """``python -m mindspeed_b200.data_tools.preprocess_data --input data.jsonl --output-prefix out/corpus
        --tokenizer-type PretrainedFromHF --tokenizer-name-or-path DIR --handler-name AlpacaHandler``
-Tokenises a JSON / JSON-lines file with the chosen handler and writes indexed datasets next to ``--output-prefix``.
+Tokenises a JSON / JSON-lines / CSV / text / Parquet file (or a directory of them) with the chosen handler and writes indexed datasets next to ``--output-prefix``.
 reference: mindspeed/tools/preprocess_data.py:172."""
 from __future__ import annotations
 
@@ -22,13 +22,23 @@ def main(argv=None) -> int:
     ap.add_argument("--vocab-size", type=int, default=None)
     ap.add_argument("--seq-length", type=int, default=None)
     ap.add_argument("--no-append-eod", action="store_true")
-    ap.add_argument("--json-key", default="text")
+    ap.add_argument("--json-key", "--json-keys", dest="json_key", default="text", help="text field(s), comma separated")
+    ap.add_argument("--split-sentences", action="store_true", help="pretrain handlers: one stored item per sentence")
+    ap.add_argument("--pad-to-multiple-of", type=int, default=1,
+                    help="pretrain handlers: pad every document to a multiple of this many tokens")
+    ap.add_argument("--train-on-inputs", action="store_true", help="instruction handlers: loss on the prompt tokens too")
     a = ap.parse_args(argv)
     a.padded_vocab_size = 1          # not needed here; stops build_tokenizer from touching parallel sizes
     tok = build_tokenizer(a)
     kw = dict(seq_length=a.seq_length, append_eod=not a.no_append_eod)
-    if a.handler_name == "GeneralPretrainHandler":
-        kw["text_key"] = a.json_key
+    from .data_handler import HANDLERS, GeneralInstructionHandler, GeneralPretrainHandler
+    cls = HANDLERS.get(a.handler_name)
+    if cls is not None and issubclass(cls, GeneralPretrainHandler):
+        kw.update(split_sentences=a.split_sentences, pad_to_multiple_of=a.pad_to_multiple_of)
+        if cls is GeneralPretrainHandler:
+            kw["text_key"] = a.json_key
+    if cls is not None and issubclass(cls, GeneralInstructionHandler):
+        kw["train_on_inputs"] = a.train_on_inputs
     h = get_handler(a.handler_name, tok, **kw)
     stats = h.serialize_to_disk(h.records(a.input), a.output_prefix)
     print(json.dumps(stats))

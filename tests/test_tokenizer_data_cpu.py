@@ -1,6 +1,7 @@
 """Tokenizers, indexed datasets, data handlers, preprocessing CLI and mask / position utilities."""
 import json
 import math
+import os
 from types import SimpleNamespace
 
 import numpy as np
@@ -70,6 +71,76 @@ def test_handlers_and_cli(tmp_path):
     assert preprocess_data.main(["--input", str(src), "--output-prefix", str(tmp_path / "out")]) == 0
     ds = MMapIndexedDataset(str(tmp_path / "out_input_ids_document"))
     assert len(ds) == 2 and ds[0].tolist() == list(b"abc") + [tok.eod]
+
+
+def test_handler_family(tmp_path):
+    from mindspeed_b200.data_tools import MMapIndexedDataset, get_handler, preprocess_data
+    from mindspeed_b200.data_tools.data_handler import data_files, read_records, split_sentences
+    from mindspeed_b200.tokenizer import ByteLevelTokenizer
+    tok = ByteLevelTokenizer()
+    dec = lambda ids: bytes(i for i in ids if 0 <= i < 256).decode()
+    trained = lambda e: dec([t for t, l in zip(e["input_ids"], e["labels"]) if l != -100])
+
+    # pretrain-style handlers: text built from the record, every token trained
+    e = get_handler("AlpacaPretrainHandler", tok).encode({"instruction": "Add", "input": "1 2", "output": "3"})
+    t = dec(e["input_ids"])
+    assert "### Instruction:\nAdd" in t and "### Input:\n1 2" in t and t.endswith("ASSISTANT: 3") and e["input_ids"][-1] == tok.eod
+    assert "### Input" not in dec(get_handler("AlpacaPretrainHandler", tok).encode({"instruction": "Hi", "output": "x"})["input_ids"])
+    e = get_handler("StackOverflowPythonPretrainHandler", tok).encode({"title": "sort a list", "question_body": "how?", "answer_body": "sorted(x)"})
+    assert dec(e["input_ids"]) == "In python, sort a list\n### Question:\nhow?\n### Response:\nsorted(x)\n"
+    # several text fields, sentence splitting, padding to a multiple with the id one past the vocabulary
+    h = get_handler("GeneralPretrainHandler", tok, text_key="title,body", split_sentences=True, pad_to_multiple_of=8)
+    e = h.encode({"title": "One. Two!", "body": "Three? Four"})
+    assert [dec(p) for p in e["sentences"]] == ["One.", "Two!", "Three?", "Four"]
+    assert len(e["input_ids"]) % 8 == 0 and e["input_ids"][-1] == tok.eod and e["input_ids"][-2] == tok.vocab_size
+    assert split_sentences("a b. c d\ne") == ["a b.", "c d", "e"]
+
+    # instruction handlers: loss on the final response only
+    g = get_handler("GeneralInstructionHandler", tok)
+    e = g.encode({"instruction": "Translate", "input": "chat", "output": "cat"})
+    assert dec(e["input_ids"]) == "USER: Translate\nchat\nASSISTANT: cat" and trained(e) == "cat"
+    assert trained(get_handler("GeneralInstructionHandler", tok, train_on_inputs=True).encode(
+        {"instruction": "a", "output": "b"})) == "USER: a\nASSISTANT: b"
+    b = get_handler("BelleMultiTurnInstructionHandler", tok).encode(
+        {"instruction": "Human: hi\nAssistant: hello\nHuman: bye\nAssistant:", "output": "see you"})
+    assert dec(b["input_ids"]) == "USER: hi\nASSISTANT: hello\nUSER: bye\nASSISTANT: see you" and trained(b) == "see you"
+    l = get_handler("LeetcodePythonInstructionHandler", tok).encode(
+        {"code_with_problem": "Two sum.\n```python\nx```", "code_only": "def f(): pass", "explanation_only": "hash map"})
+    assert dec(l["input_ids"]) == "USER: Two sum.\nASSISTANT: def f(): pass\nhash map" and trained(l) == "def f(): pass\nhash map"
+
+    # MOSS dialogues: one sample per turn with the history as prompt / one sample per dialogue with role marker ids
+    rec = {"chat": {"turn_1": {"Human": "<|Human|>: q1<eoh>", "MOSS": "<|MOSS|>: a1<eom>"},
+                    "turn_2": {"Human": "<|Human|>: q2<eoh>", "MOSS": "<|MOSS|>: a2<eom>"}}}
+    per_turn = get_handler("MOSSInstructionHandler", tok).encode(rec)
+    assert [trained(x) for x in per_turn] == ["a1", "a2"]
+    assert dec(per_turn[1]["input_ids"]) == "USER: q1\nASSISTANT: a1\nUSER: q2\nASSISTANT: a2"
+    m = get_handler("MOSSMultiTurnHandler", tok, user_token=(300,), assistant_token=(301,)).encode(rec)
+    assert m["input_ids"] == [300] + list(b"q1") + [301] + list(b"a1") + [300] + list(b"q2") + [301] + list(b"a2") + [tok.eod]
+    assert [x for x in m["labels"] if x != -100] == list(b"a1") + list(b"a2") + [tok.eod]
+
+    # input formats: a directory of text files (majority format wins), csv, parquet; the CLI writes one dataset per turn
+    d = tmp_path / "corpus"
+    d.mkdir()
+    (d / "a.txt").write_text("first doc\nsecond doc\n")
+    (d / "b.txt").write_text("third doc\n")
+    (d / "c.json").write_text(json.dumps([{"text": "ignored"}]))
+    assert [os.path.basename(f) for f in data_files(str(d))] == ["a.txt", "b.txt"]
+    assert [r["text"] for r in read_records(str(d))] == ["first doc", "second doc", "third doc"]
+    (tmp_path / "x.csv").write_text("instruction,output\nsay a,a\nsay b,b\n")
+    assert [r["output"] for r in read_records(str(tmp_path / "x.csv"))] == ["a", "b"]
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+    pq.write_table(pa.table({"text": ["p1", "p2"]}), str(tmp_path / "y.parquet"))
+    assert [r["text"] for r in read_records(str(tmp_path / "y.parquet"))] == ["p1", "p2"]
+    src = tmp_path / "moss.jsonl"
+    src.write_text(json.dumps(rec))
+    assert preprocess_data.main(["--input", str(src), "--output-prefix", str(tmp_path / "moss"), "--handler-name",
+                                 "MOSSInstructionHandler"]) == 0
+    ids, lab = MMapIndexedDataset(str(tmp_path / "moss_input_ids_document")), MMapIndexedDataset(str(tmp_path / "moss_labels_document"))
+    assert len(ids) == 2 and len(lab) == 2 and len(ids[1]) == len(lab[1]) > len(ids[0])
+    assert preprocess_data.main(["--input", str(d), "--output-prefix", str(tmp_path / "sent"), "--split-sentences"]) == 0
+    sd = MMapIndexedDataset(str(tmp_path / "sent_input_ids_document"))
+    assert len(sd) == 3 and sd.doc_idx.tolist() == [0, 1, 2, 3]
 
 
 def test_alibi_masks_and_eod_reset():
