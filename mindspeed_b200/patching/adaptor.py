@@ -47,13 +47,8 @@ def _surface():
 
 
 def _optional_dependency_stubs():
-    from .compat import FusedAdamStub, multi_tensor_applier, multi_tensor_l2norm, multi_tensor_scale
-    return [
-        ("apex.optimizers.FusedAdam", FusedAdamStub),
-        ("apex.multi_tensor_apply.multi_tensor_applier", multi_tensor_applier),
-        ("amp_C.multi_tensor_l2norm", multi_tensor_l2norm),
-        ("amp_C.multi_tensor_scale", multi_tensor_scale),
-    ]
+    from .compat import optional_dependency_stubs
+    return optional_dependency_stubs()
 
 
 def delete_lock_file(directory: Optional[str] = None):
