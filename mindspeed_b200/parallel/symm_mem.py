@@ -27,6 +27,61 @@ class _RawCuda:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
 
 
+GUARD_BYTES = 1024
+GUARD_PATTERN = 0xA5
+
+
+class HeapLayout:
+    """Offsets of named buffers inside a heap of ``nbytes`` (the first ``FLAG_BYTES`` are the synchronisation words).
+    With ``guard`` > 0 every buffer is followed by ``guard`` canary bytes that no kernel may touch: ``fill_guards`` writes
+    the pattern, ``check_guards`` names the buffers whose canary has been overwritten (a write past the buffer's end by a
+    local kernel or by a peer's store).  The sizes and offsets are the same on every rank because allocation calls are SPMD."""
+
+    def __init__(self, nbytes: int, guard: int = 0):
+        self.nbytes, self.guard = nbytes, guard
+        self.cursor = FLAG_BYTES
+        self.named: Dict[str, Tuple[int, int]] = {}
+
+    def alloc(self, name: str, nbytes: int) -> Tuple[int, bool]:
+        """(offset, newly allocated)."""
+        if name in self.named:
+            off, size = self.named[name]
+            if size >= nbytes:
+                return off, False
+            raise RuntimeError(f"symmetric buffer '{name}' of {size} bytes is too small for {nbytes}")
+        off = self.cursor
+        size = ((nbytes + 1023) // 1024) * 1024
+        if off + size + self.guard > self.nbytes:
+            raise RuntimeError(f"symmetric heap exhausted: need {size + self.guard} more bytes at {off} of {self.nbytes}")
+        self.cursor += size + self.guard
+        self.named[name] = (off, size)
+        return off, True
+
+    def guard_range(self, name: str) -> Tuple[int, int]:
+        off, size = self.named[name]
+        return off + size, off + size + self.guard
+
+    def fill_guard(self, raw: torch.Tensor, name: str):
+        if self.guard:
+            a, b = self.guard_range(name)
+            raw[a:b].fill_(GUARD_PATTERN)
+
+    def check_guards(self, raw: torch.Tensor) -> List[str]:
+        """Names of the buffers whose canary no longer holds the pattern (one device-to-host read per buffer)."""
+        bad = []
+        if self.guard:
+            for name in self.named:
+                a, b = self.guard_range(name)
+                if bool((raw[a:b] != GUARD_PATTERN).any()):
+                    bad.append(name)
+        return bad
+
+
+def canaries_enabled() -> bool:
+    import os
+    return os.environ.get("MSB200_HEAP_CANARIES", "0") == "1"
+
+
 class SymmetricHeap:
     def __init__(self, group, nbytes: int):
         L = loader.require_lib()
@@ -53,26 +108,28 @@ class SymmetricHeap:
                 loader.check(L.msb_symm_import(buf, ctypes.byref(q)), "symm_import")
                 self.peer_ptrs.append(q.value)
         self._raw = torch.as_tensor(_RawCuda(self.local_ptr, self.nbytes), device=torch.device("cuda", torch.cuda.current_device()))
-        self._cursor = FLAG_BYTES
-        self._named: Dict[str, Tuple[int, int]] = {}
+        # MSB200_HEAP_CANARIES=1 (debugging): guard bytes behind every buffer, verified by check_canaries(); the heap itself is
+        # not enlarged, so a configuration that fills it exactly needs a larger heap in this mode
+        self.layout = HeapLayout(self.nbytes, GUARD_BYTES if canaries_enabled() else 0)
         self.epoch = 0
         dist.barrier(group=group)
 
     # ---- layout ----
     def alloc(self, name: str, nbytes: int) -> int:
         """Offset of a named buffer (allocated once; same offset on every rank because calls are SPMD)."""
-        if name in self._named:
-            off, size = self._named[name]
-            if size >= nbytes:
-                return off
-            raise RuntimeError(f"symmetric buffer '{name}' of {size} bytes is too small for {nbytes}")
-        off = self._cursor
-        size = ((nbytes + 1023) // 1024) * 1024
-        if off + size > self.nbytes:
-            raise RuntimeError(f"symmetric heap exhausted: need {size} more bytes at {off} of {self.nbytes}")
-        self._cursor += size
-        self._named[name] = (off, size)
+        off, new = self.layout.alloc(name, nbytes)
+        if new:
+            self.layout.fill_guard(self._raw, name)
         return off
+
+    def check_canaries(self):
+        """Debug mode only: raise if a kernel (of this rank or a peer) wrote past the end of a named buffer."""
+        if not self.layout.guard:
+            return
+        torch.cuda.synchronize()
+        bad = self.layout.check_guards(self._raw)
+        if bad:
+            raise RuntimeError(f"symmetric heap of rank {self.rank}: guard bytes overwritten behind {bad}")
 
     def tensor(self, offset: int, shape, dtype) -> torch.Tensor:
         n = 1
@@ -118,6 +175,12 @@ def get_heap(group, nbytes: int, tag: str = "tp") -> SymmetricHeap:
         h = SymmetricHeap(group, nbytes)
         _HEAPS[key] = h
     return h
+
+
+def check_all_canaries():
+    """Debug mode (``MSB200_HEAP_CANARIES=1``): verify the guard bytes of every heap; called by the training loop after a step."""
+    for h in _HEAPS.values():
+        h.check_canaries()
 
 
 def destroy_heaps():

@@ -227,6 +227,10 @@ def train_step(forward_step_func, data_iterator, model, optimizer, opt_param_sch
         out = _train_step_inner(forward_step_func, data_iterator, model, optimizer, opt_param_scheduler, config)
     for mgr in _MEMORY_MANAGERS:
         mgr.end_step()
+    if torch.cuda.is_available():
+        from ..parallel import symm_mem
+        if symm_mem.canaries_enabled():
+            symm_mem.check_all_canaries()           # debugging aid: a write past a symmetric buffer stops the run here
     return out
 
 
