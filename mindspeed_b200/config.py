@@ -115,7 +115,10 @@ class TransformerConfig(ModelParallelConfig):
     activation_func_fp8_input_store: bool = False
     num_moe_experts: Optional[int] = None
     rotary_interleaved: bool = False
-    window_size: Optional[Tuple[int, int]] = None
+    window_size: Optional[Tuple[int, int]] = None            # (left, right) keys a query sees; -1 = unbounded
+    pre_tockens: int = 65536                                 # the reference's spelling of the same bounds: keys before ...
+    next_tockens: int = 0                                    # ... and after the query (sparse_mode 0 / 4)
+    sparse_mode: int = 0                                     # 0 / 4: honour the bounds; 2 / 3: plain causal
     normalization: str = "LayerNorm"
     qk_layernorm: bool = False
     test_mode: bool = False

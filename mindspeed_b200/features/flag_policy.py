@@ -26,8 +26,6 @@ NO_EFFECT: Dict[str, str] = {
     "use-fusion-attn-v2": "selects between two vendor attention ops; there is one attention kernel family here",
     "megatron-cp-in-bnsd": "layout hint for the vendor attention op; the tcgen05 kernels read strided [s, b, n, d] directly",
     "attention-mask-on-cpu": "the causal mask is generated inside the attention kernels, no mask tensor is built",
-    "pre-tockens": "sliding-window bounds of the vendor attention op; attention here is full or causal",
-    "next-tockens": "sliding-window bounds of the vendor attention op; attention here is full or causal",
     "square-alibi-mask": "shape of the ALiBi bias tensor on the unfused path; the bias here is evaluated from the head slopes block by block, no bias tensor of either shape exists",
     "fill-neg-inf": "mask fill value of the unfused softmax path; masked scores are -inf in every kernel here",
     "te-comparison-with-bf16": "debug comparison hook of the reference's TE shim",

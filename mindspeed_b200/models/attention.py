@@ -70,11 +70,31 @@ class CoreAttention(nn.Module):
         return attn_ops.alibi_attention(q, k, v, self.alibi_slopes, causal=self.causal, softmax_scale=self.softmax_scale,
                                         mode=cfg.alibi_fusion_attn_type or 0, signed=bool(cfg.alibi_diagonal_opposite))
 
+    def _window(self, sq, sk):
+        """(keys before, keys after) a query may see, or None when that is all of them (full / plain causal attention)."""
+        cfg = self.config
+        if cfg.window_size is not None:
+            pre, nxt = (x if x >= 0 else sk for x in cfg.window_size)
+        elif getattr(cfg, "sparse_mode", 0) in (0, 4) and (cfg.pre_tockens != 65536 or cfg.next_tockens != 0):
+            pre, nxt = cfg.pre_tockens, cfg.next_tockens          # bounds the user has set (the defaults mean "no window")
+        else:
+            return None
+        if self.causal:
+            nxt = 0
+        if pre >= sk - 1 and (self.causal or nxt >= sk - 1):
+            return None
+        return pre, nxt
+
     def forward(self, q, k, v, attention_mask=None, packed_seq_params=None):
         cp = ps.get_context_parallel_world_size()
         cu = packed_seq_params.get("cu_seqlens") if isinstance(packed_seq_params, dict) else getattr(packed_seq_params, "cu_seqlens_q", None)
+        win = self._window(q.shape[0] * cp, k.shape[0] * cp)
         if self.alibi_slopes is not None:
             out = self._alibi(q, k, v, cu is not None)
+        elif win is not None:
+            if cp > 1 or cu is not None:
+                raise NotImplementedError("sliding-window attention is not combined with context parallelism or packed sequences")
+            out = attn_ops.band_attention(q, k, v, win[0], win[1], softmax_scale=self.softmax_scale)
         elif cu is not None:
             # packed documents (--reset-attention-mask): every document attends to itself only
             if cp > 1:

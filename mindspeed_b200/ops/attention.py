@@ -259,3 +259,35 @@ def alibi_attention(q, k, v, slopes, causal=True, softmax_scale=None, mode=0, si
         outs.append(checkpoint(one, qb, k, v, t0, use_reentrant=False) if need and sq > block else one(qb, k, v, t0))
     return torch.cat(outs, dim=0).contiguous()
 
+
+def band_attention(q, k, v, pre: int, nxt: int, softmax_scale=None, block: int = 512):
+    """Sliding-window attention: query i (bottom-right aligned when sk > sq) sees keys j with i - pre <= j <= i + nxt.
+
+    q [sq, b, n, d]; k, v [sk, b, nkv, d].  Query rows are taken ``block`` at a time and only the keys a block can see are
+    sliced out, so the work is O(s * (pre + nxt + block)) instead of O(s^2); every block is re-computed in backward.
+    fp32 math.  The window bounds of the reference's attention op: ``pre_tockens`` / ``next_tockens`` with ``sparse_mode`` 0 / 4
+    (mindspeed/ops/fusion_attention_v2.py:22-114)."""
+    from torch.utils.checkpoint import checkpoint
+    sq, sk = q.shape[0], k.shape[0]
+    off = sk - sq
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(q.shape[-1])
+
+    def one(qb, kb, vb, t0, lo):
+        tb, kb_n = qb.shape[0], kb.shape[0]
+        qi = torch.arange(t0, t0 + tb, device=q.device).view(tb, 1) + off
+        kj = torch.arange(lo, lo + kb_n, device=q.device).view(1, kb_n)
+        hidden = (kj < qi - pre) | (kj > qi + nxt)
+        return attention_ref(qb, kb, vb, causal=False, softmax_scale=scale, mask=hidden.view(1, 1, tb, kb_n))
+
+    need = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
+    outs = []
+    for t0 in range(0, sq, block):
+        t1 = min(sq, t0 + block)
+        lo, hi = max(0, t0 + off - pre), min(sk, t1 - 1 + off + nxt + 1)
+        if hi <= lo:                                   # no visible key: zero rows
+            outs.append(q.new_zeros(t1 - t0, q.shape[1], q.shape[2], v.shape[-1]))
+            continue
+        args = (q[t0:t1], k[lo:hi], v[lo:hi], t0, lo)
+        outs.append(checkpoint(one, *args, use_reentrant=False) if need and sq > block else one(*args))
+    return torch.cat(outs, dim=0).contiguous()
+

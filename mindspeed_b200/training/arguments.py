@@ -43,6 +43,8 @@ def _core_args(p: argparse.ArgumentParser):
     g.add_argument("--disable-bias-linear", action="store_false", dest="add_bias_linear")
     g.add_argument("--add-qkv-bias", action="store_true")
     g.add_argument("--qk-layernorm", action="store_true")
+    g.add_argument("--window-size", type=lambda t: tuple(int(x) for x in t.split(",")), default=None,
+                   help="sliding-window attention: 'left,right' keys a query sees (-1 = unbounded)")
     g.add_argument("--untie-embeddings-and-output-weights", action="store_true")
     g.add_argument("--make-vocab-size-divisible-by", type=int, default=128)
     g.add_argument("--vocab-size", type=int, default=None)

@@ -89,3 +89,53 @@ def test_flags_validate():
     with pytest.raises(AssertionError, match="linear bias"):
         validate_args(parse_args(args_list=base + ["--position-embedding-type", "alibi", "--alibi-fusion-attn-type", "3",
                                                    "--alibi-diagonal-opposite"]))
+
+
+@pytest.mark.parametrize("pre,nxt,sk", [(5, 0, 40), (3, 2, 40), (100, 0, 40), (4, 0, 52), (0, 0, 40)])
+def test_sliding_window_attention_equals_band_masked_attention(pre, nxt, sk):
+    from mindspeed_b200.ops.attention import attention_ref, band_attention
+    g = torch.Generator().manual_seed(1)
+    sq, B, n, d = 40, 2, 4, 8
+    q = torch.randn(sq, B, n, d, generator=g, requires_grad=True)
+    k = torch.randn(sk, B, 2, d, generator=g, requires_grad=True)
+    v = torch.randn(sk, B, 2, d, generator=g, requires_grad=True)
+    i = torch.arange(sq).view(sq, 1) + (sk - sq)
+    j = torch.arange(sk).view(1, sk)
+    hidden = (j < i - pre) | (j > i + nxt)
+    ref = attention_ref(q, k, v, causal=False, mask=hidden.view(1, 1, sq, sk))
+    out = band_attention(q, k, v, pre, nxt, block=16)
+    assert torch.allclose(out, ref, atol=1e-5)
+    go = torch.randn(out.shape, generator=g)
+    for a, b in zip(torch.autograd.grad(out, (q, k, v), go), torch.autograd.grad(ref, (q, k, v), go)):
+        assert torch.allclose(a, b, atol=1e-5)
+
+
+def _train_window(rank, world, extra):
+    import io
+    from contextlib import redirect_stdout
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import pretrain_gpt as pg
+    from test_pipeline_cpu import BASE
+    from mindspeed_b200.ops import attention as OA
+    from mindspeed_b200.training import pretrain
+    calls = []
+    orig = OA.band_attention
+    OA.band_attention = lambda q, k, v, pre, nxt, **kw: (calls.append((pre, nxt)), orig(q, k, v, pre, nxt, **kw))[1]
+    with redirect_stdout(io.StringIO()):
+        hist = pretrain(pg.train_valid_test_datasets_provider, pg.model_provider, forward_step_func=pg.forward_step,
+                        args_list=BASE + list(extra))
+    OA.band_attention = orig
+    return [h["lm loss"] for h in hist], sorted(set(calls))
+
+
+def test_window_flags_select_sliding_window_attention():
+    from dist_utils import run_distributed
+    plain, c0 = run_distributed(_train_window, 1, [])[0]
+    assert c0 == []                                                   # default bounds: plain causal attention
+    a, ca = run_distributed(_train_window, 1, ["--pre-tockens", "8", "--sparse-mode", "4"])[0]
+    b, cb = run_distributed(_train_window, 1, ["--window-size", "8,0"])[0]
+    assert ca == [(8, 0)] and cb == [(8, 0)] and a == pytest.approx(b, abs=1e-6) and a != pytest.approx(plain, abs=1e-6)
+    c, cc = run_distributed(_train_window, 1, ["--pre-tockens", "8", "--sparse-mode", "2"])[0]
+    assert cc == [] and c == pytest.approx(plain, abs=1e-6)           # mode 2: causal, the bounds are not used
+    d, cd = run_distributed(_train_window, 1, ["--window-size", "64,0"])[0]
+    assert cd == [] and d == pytest.approx(plain, abs=1e-6)           # a window that covers the sequence
