@@ -39,6 +39,9 @@ NO_EFFECT: Dict[str, str] = {
     "use-fused-lightning-indexer": "the indexer, the sparse attention and the KL loss of --experimental-attention-variant dsa are one implementation (ops/lightning_indexer.py, ops/sparse_attention.py); there is no separate unfused path to switch from",
     "use-fused-sparse-flash-attention": "the indexer, the sparse attention and the KL loss of --experimental-attention-variant dsa are one implementation (ops/lightning_indexer.py, ops/sparse_attention.py); there is no separate unfused path to switch from",
     "use-fused-lightning-indexer-kl-loss": "the indexer, the sparse attention and the KL loss of --experimental-attention-variant dsa are one implementation (ops/lightning_indexer.py, ops/sparse_attention.py); there is no separate unfused path to switch from",
+    "shape-order": "layout hint for the vendor attention op; the kernels here read strided [s, b, n, d] directly",
+    "enable-token-rearrange-opt": "the DeepSpeed-style MoE here always dispatches through index arithmetic on the one-hot routing; there is no slower einsum path to switch from",
+    "skip-bias-add": "every parallel linear here returns its bias separately when the caller fuses the add; there is no switch",
     "adaptive-cp-only-reschedule": "adaptive CP here always keeps the sequence order and only schedules the exchanges",
     "adaptive-cp-without-coarse": "the mask is coarsened to context-parallel rank granularity for scheduling only; nothing else uses the coarse form",
     "gemm-gradient-accumulation-fusion": "weight gradients always accumulate into main_grad inside the GEMM epilogue",
@@ -61,7 +64,12 @@ NO_EFFECT: Dict[str, str] = {
 }
 
 UNSUPPORTED: Dict[str, str] = {
-    "ampipe-degree": "attention-MoE micro-pipelining (ampipe) is not implemented; use --moe-fb-overlap",
+    "ampipe-tp-sp-comm-overlap": "option of --ampipe-degree, for which the reference ships no forward path any more",
+    "optimized-mbs-list": "stored policy of --automated-pipeline-perf with per-micro-batch batch sizes; micro-batches of one step have one size here (--automated-pipeline-perf chooses that size)",
+    "mbs-idx": "index into --optimized-mbs-list, which is not implemented",
+    "pp-schedule-list": "stored forward / backward order of --automated-pipeline-perf; schedules here are generated by parallel/pipeline/plan.py from --schedules-method and the virtual-pipeline flags",
+    "optimized-mbs-mode": "switch of --optimized-mbs-list, which is not implemented",
+    "ampipe-degree": "attention-MoE micro-pipelining: the reference registers and validates the flag (mindspeed/arguments.py:336-340, 803-820) but ships no forward path for it any more; here --moe-fb-overlap and --use-pipe-experts cover the overlap of MoE communication with compute",
 }
 
 

@@ -108,6 +108,85 @@ class QADFeature(Feature):
             raise AssertionError("--qad-enable is not combined with context parallelism")
 
 
+class LegacySpellingsFeature(Feature):
+    """Older spellings of current features and stored policies of the automated pipeline (reference: mindspeed/arguments.py:
+    27-976, the argument groups that predate the feature classes).  ``pre_validate_args`` rewrites them onto the flags
+    the framework reads, so both spellings run the same code."""
+
+    def __init__(self):
+        super().__init__("legacy-spellings", optimization_level=0)
+        self.default_patches = True
+
+    def register_args(self, parser):
+        g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--use-nd-matmul", action="store_true", help="older name of --tp-2d")
+        add_arg(g, "--nd1-dim1-size", type=int, default=1, help="with --use-nd-matmul: --tp-x")
+        add_arg(g, "--nd2-dim1-size", type=int, default=1, help="with --use-nd-matmul: --tp-y")
+        add_arg(g, "--optimize-vpp-send-recv-comm", action="store_true",
+                help="--optimize-send-recv-comm for the interleaved schedule (one switch covers both here)")
+        add_arg(g, "--enable-zero3", action="store_true", help="parameters, gradients and optimizer state sharded over "
+                "the data-parallel group: the same as --layerzero")
+        add_arg(g, "--shape-order", type=str, default="SBH", choices=["SBH", "BSH", "BSND", "BNSD"])
+        add_arg(g, "--yarn-scaling-factor", type=float, default=1.0, help="older name of --rope-scaling-factor with yarn")
+        add_arg(g, "--add-dense-bias", action="store_true", help="bias on the attention output projection even with --disable-bias-linear")
+        add_arg(g, "--skip-bias-add", action="store_false", default=True)
+        add_arg(g, "--additional-config", type=str, default=None,
+                help="JSON / YAML file of {argument name: value} applied on top of the command line")
+        add_arg(g, "--save-memory-ratio", type=float, default=0.20,
+                help="--automated-pipeline: fraction of device memory the plan must leave free")
+        add_arg(g, "--optimized-mbs-list", type=str, default=None)
+        add_arg(g, "--mbs-idx", type=int, default=None)
+        add_arg(g, "--pp-schedule-list", type=str, default=None)
+        add_arg(g, "--optimized-mbs-mode", action="store_false")
+
+    def pre_validate_args(self, args):
+        if args.additional_config:
+            import json
+            with open(args.additional_config) as f:
+                txt = f.read()
+            try:
+                extra = json.loads(txt)
+            except ValueError:
+                import yaml
+                extra = yaml.safe_load(txt)
+            if not isinstance(extra, dict):
+                raise AssertionError("--additional-config must hold a mapping of argument names to values")
+            for k, v in extra.items():
+                k = k.lstrip("-").replace("-", "_")
+                if not hasattr(args, k):
+                    raise AssertionError(f"--additional-config: unknown argument {k!r}")
+                setattr(args, k, v)
+        if args.use_nd_matmul:
+            if args.tp_2d:
+                raise AssertionError("--use-nd-matmul is the older name of --tp-2d; give one of them")
+            tp = args.tensor_model_parallel_size
+            if tp % args.nd1_dim1_size or tp % args.nd2_dim1_size:
+                raise AssertionError("tensor_model_parallel_size must be divisible by nd1_dim1_size and by nd2_dim1_size")
+            if args.nd1_dim1_size * args.nd2_dim1_size != tp:
+                raise AssertionError("--nd1-dim1-size x --nd2-dim1-size must equal --tensor-model-parallel-size (the x and y "
+                                     "extents of the 2-D tensor-parallel grid)")
+            args.tp_2d, args.tp_x, args.tp_y = True, args.nd1_dim1_size, args.nd2_dim1_size
+        if args.optimize_vpp_send_recv_comm:
+            args.optimize_send_recv_comm = True
+        if args.enable_zero3:
+            args.layerzero = True
+        if args.yarn_scaling_factor != 1.0 and getattr(args, "rope_scaling_factor", 1.0) == 1.0:
+            args.rope_scaling_factor = args.yarn_scaling_factor
+        if getattr(args, "expert_interval", 1) > 1:
+            if getattr(args, "moe_model_type", "megatron_moe") != "deepspeed_moe":
+                raise AssertionError("--expert-interval belongs to --moe-model-type deepspeed_moe; use --moe-layer-freq otherwise")
+            n = args.expert_interval
+            args.moe_layer_freq = str([1 if (i + 1) % n == 0 else 0 for i in range(args.num_layers)])
+
+    def validate_args(self, args):
+        if getattr(args, "moe_adaptive_recompute_activation", False) and not args.num_experts:
+            raise AssertionError("--moe-adaptive-recompute-activation needs a MoE model (--num-experts)")
+        if getattr(args, "moe_adaptive_recompute_activation_scale", 2.0) <= 0:
+            raise AssertionError("--moe-adaptive-recompute-activation-scale must be positive")
+        if not (0.0 <= args.save_memory_ratio < 1.0):
+            raise AssertionError("--save-memory-ratio is a fraction in [0, 1)")
+
+
 class ProfileFeature(Feature):
     def __init__(self):
         super().__init__("profile", optimization_level=0)
@@ -464,6 +543,10 @@ class PipelineMiscFeature(Feature):
 
     def register_args(self, parser):
         g = parser.add_argument_group(title=self.feature_name)
+        add_arg(g, "--use-nanopipe", action="store_true",
+                help="interleaved schedule: the first weight-gradient GEMMs of each rank run behind its last backward")
+        add_arg(g, "--use-nanopipe-swap", action="store_true",
+                help="--use-nanopipe: what the deferred weight gradients need waits in pinned host memory")
         add_arg(g, "--recompute-in-bubble", action="store_true")
         add_arg(g, "--recompute-in-advance", action="store_true")
         add_arg(g, "--noop-layers", type=str, default=None)
@@ -490,6 +573,18 @@ class PipelineMiscFeature(Feature):
                 s_ //= args.tensor_model_parallel_size
             dt = torch.bfloat16 if getattr(args, "bf16", False) else torch.float16 if getattr(args, "fp16", False) else torch.float32
             args.pipeline_tensor_shapes = [{"shape": (s_, args.micro_batch_size, args.hidden_size), "dtype": dt}]
+        if args.use_nanopipe_swap and not args.use_nanopipe:
+            raise AssertionError("--use-nanopipe-swap needs --use-nanopipe")
+        if args.use_nanopipe:
+            if getattr(args, "pipeline_model_parallel_size", 1) < 2 or not getattr(args, "num_layers_per_virtual_pipeline_stage", None):
+                raise AssertionError("--use-nanopipe splits the backward of the interleaved schedule: it needs pipeline parallelism "
+                                     "with --num-layers-per-virtual-pipeline-stage")
+            for other in ("moe_fb_overlap", "tp_2d", "recompute_in_bubble", "recompute_in_advance"):
+                if getattr(args, other, False):
+                    raise AssertionError(f"--use-nanopipe is not combined with --{other.replace('_', '-')}")
+            if getattr(args, "schedules_method", None) not in (None, "", "1f1b", "interleaved"):
+                raise AssertionError("--use-nanopipe belongs to the interleaved schedule, not to --schedules-method "
+                                     f"{args.schedules_method}")
         if args.recompute_in_bubble and args.recompute_in_advance:
             raise AssertionError("--recompute-in-bubble and --recompute-in-advance are exclusive")
         if (args.recompute_in_bubble or args.recompute_in_advance):
@@ -568,6 +663,16 @@ class MoEFeature(Feature):
     def register_args(self, parser):
         g = parser.add_argument_group(title=self.feature_name)
         add_arg(g, "--moe-tp-extend-ep", action="store_true")
+        add_arg(g, "--expert-interval", type=int, default=1,
+                help="--moe-model-type deepspeed_moe: every expert-interval-th layer is a MoE layer")
+        add_arg(g, "--enable-token-rearrange-opt", action="store_true")
+        add_arg(g, "--use-rts", action="store_true", default=False,
+                help="deepspeed_moe top-1 gate: over-capacity experts keep a random selection of their tokens")
+        add_arg(g, "--no-use-rts", action="store_false", dest="use_rts")
+        add_arg(g, "--moe-adaptive-recompute-activation", action="store_true",
+                help="recompute a MoE layer in backward only on steps where its busiest expert is over scale x the balanced load")
+        add_arg(g, "--moe-adaptive-recompute-activation-scale", type=float, default=2.0)
+        add_arg(g, "--ampipe-tp-sp-comm-overlap", action="store_true")
         add_arg(g, "--moe-permutation-async-comm", action="store_true")
         add_arg(g, "--moe-alltoall-overlap-comm", action="store_true")
         add_arg(g, "--moe-allgather-overlap-comm", action="store_true")
@@ -844,7 +949,7 @@ class TTPFeature(Feature):
 
 def create_features_list():
     return [
-        RequirementsBasicFeature(), MegatronBasicFeature(), TransformerEngineBasicFeature(), QADFeature(), ProfileFeature(),
+        RequirementsBasicFeature(), MegatronBasicFeature(), TransformerEngineBasicFeature(), LegacySpellingsFeature(), QADFeature(), ProfileFeature(),
         TflopsCalculateFeature(), DeterministicFeature(), TokenizerFeature(),
         FusedTPCommFeature(), ChunkedTPCommFeature(), TP2DFeature(), UnalignedLinearFeature(),
         ContextParallelFeature(), FlashAttentionFeature(), AlibiFeature(), SparseAttentionFeature(), MLAFeature(),

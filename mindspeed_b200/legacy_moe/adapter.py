@@ -37,7 +37,8 @@ class LegacyMoEBlock(nn.Module):
             return MLP(config, ffn_hidden_size=ffn, is_expert=True)
         self.moe = MoE(config.hidden_size, expert, num_experts=config.num_moe_experts, ep_size=ep, k=k, capacity_factor=cf,
                        eval_capacity_factor=cf, noisy_gate_policy=getattr(config, "noisy_gate_policy", None),
-                       ep_group=ps.get_expert_model_parallel_group(check_initialized=False) if ep > 1 else None, pipe_experts=pipe)
+                       ep_group=ps.get_expert_model_parallel_group(check_initialized=False) if ep > 1 else None, pipe_experts=pipe,
+                       use_rts=bool(getattr(config, "use_rts", False)))
         self.moe.moe_layer.multi_stream = bool(getattr(config, "pipe_experts_multi_stream", False))
         self.aux_coeff = float(getattr(config, "moe_aux_loss_coeff", 0.0) or 0.0)
 

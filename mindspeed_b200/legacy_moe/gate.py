@@ -18,8 +18,10 @@ def _locations(mask):
     return torch.cumsum(mask, dim=0) - mask
 
 
-def top1gating(logits, capacity_factor=1.0, min_capacity=4, noisy_gate_policy=None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
-    """logits [S, E] -> (aux loss, combine weights [S, E, C], dispatch mask [S, E, C] bool, tokens per expert [E])."""
+def top1gating(logits, capacity_factor=1.0, min_capacity=4, noisy_gate_policy=None, use_rts=False) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """logits [S, E] -> (aux loss, combine weights [S, E, C], dispatch mask [S, E, C] bool, tokens per expert [E]).
+    ``use_rts`` (random token selection): when an expert is over capacity the tokens it keeps are drawn at random instead
+    of being the first ones in sequence order, which removes the bias towards early positions."""
     S, E = logits.shape
     gates = F.softmax(logits.float(), dim=1)
     C = _capacity(S, E, capacity_factor, min_capacity)
@@ -29,8 +31,16 @@ def top1gating(logits, capacity_factor=1.0, min_capacity=4, noisy_gate_policy=No
     exp_counts = mask.sum(0).detach()
     me, ce = gates.mean(0), mask.mean(0)
     l_aux = (me * ce).sum() * E
-    loc = _locations(mask)
-    mask = mask * (loc < C)
+    if use_rts:
+        prio = mask * torch.rand_like(mask)                      # a random priority for every (token, chosen expert)
+        keep = torch.zeros_like(mask)
+        top = torch.topk(prio, k=min(C, S), dim=0).indices       # per expert: its C highest priorities
+        keep.scatter_(0, top, 1.0)
+        mask = mask * keep
+        loc = _locations(mask)
+    else:
+        loc = _locations(mask)
+        mask = mask * (loc < C)
     loc_s = (loc * mask).sum(1).long()
     gate_s = (gates * mask).sum(1)
     combine = gate_s.view(S, 1, 1) * mask.unsqueeze(-1) * F.one_hot(loc_s, C).to(gates.dtype).unsqueeze(1)
@@ -64,8 +74,9 @@ def top2gating(logits, capacity_factor=1.0, min_capacity=4) -> Tuple[torch.Tenso
 
 class TopKGate(nn.Module):
     def __init__(self, model_dim, num_experts, k=1, capacity_factor=1.0, eval_capacity_factor=1.0, min_capacity=4,
-                 noisy_gate_policy=None):
+                 noisy_gate_policy=None, use_rts=False):
         super().__init__()
+        self.use_rts = use_rts
         if k not in (1, 2):
             raise ValueError("only top-1 and top-2 gating are supported")
         self.wg = nn.Linear(model_dim, num_experts, bias=False)
@@ -75,5 +86,5 @@ class TopKGate(nn.Module):
         logits = self.wg(x.float())
         cf = self.cf if self.training else self.ecf
         if self.k == 1:
-            return top1gating(logits, cf, self.min_capacity, self.noisy if self.training else None)
+            return top1gating(logits, cf, self.min_capacity, self.noisy if self.training else None, self.use_rts and self.training)
         return top2gating(logits, cf, self.min_capacity)

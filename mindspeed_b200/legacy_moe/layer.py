@@ -87,12 +87,12 @@ class MoE(nn.Module):
     """User-facing wrapper: returns (output, auxiliary loss, tokens per expert)."""
 
     def __init__(self, hidden_size, expert: nn.Module, num_experts=1, ep_size=1, k=1, capacity_factor=1.0, eval_capacity_factor=1.0,
-                 min_capacity=4, noisy_gate_policy: Optional[str] = None, ep_group=None, pipe_experts: int = 1):
+                 min_capacity=4, noisy_gate_policy: Optional[str] = None, ep_group=None, pipe_experts: int = 1, use_rts: bool = False):
         super().__init__()
         if num_experts % ep_size != 0:
             raise ValueError("num_experts must be divisible by ep_size")
         self.num_local_experts = num_experts // ep_size
-        gate = TopKGate(hidden_size, num_experts, k, capacity_factor, eval_capacity_factor, min_capacity, noisy_gate_policy)
+        gate = TopKGate(hidden_size, num_experts, k, capacity_factor, eval_capacity_factor, min_capacity, noisy_gate_policy, use_rts)
         self.moe_layer = MOELayer(gate, Experts(expert, self.num_local_experts), ep_group, ep_size, self.num_local_experts, pipe_experts)
 
     def forward(self, hidden_states):

@@ -166,13 +166,15 @@ def analytic_layer_profiles(args, micro_batch_size: Optional[int] = None, peak_f
 
 def plan_from_args(args, budget_bytes: Optional[int] = None, search_micro_batch_size: bool = False) -> Tuple[int, PipelinePlan]:
     """(micro-batch size, plan) for the configured model: layers per pipeline stage and layers to recompute per stage.
-    The memory budget is ``--adaptive-recompute-device-size`` (MiB) when given, else 90 % of 180 GB."""
+    The memory budget is ``--adaptive-recompute-device-size`` (MiB) when given, else 180 GB less the share
+    ``--save-memory-ratio`` asks to keep free (10 % when the arguments carry no such value)."""
     pp = args.pipeline_model_parallel_size
     world = getattr(args, "world_size", None) or 1
     dp = max(1, world // (pp * max(1, args.tensor_model_parallel_size) * max(1, getattr(args, "context_parallel_size", 1))))
     if budget_bytes is None:
         mib = getattr(args, "adaptive_recompute_device_size", -1) or -1
-        budget_bytes = int(mib) * (1 << 20) if mib and mib > 0 else int(0.9 * 180e9)
+        free = float(getattr(args, "save_memory_ratio", 0.1))          # --save-memory-ratio: the share of the device left free
+        budget_bytes = int(mib) * (1 << 20) if mib and mib > 0 else int((1.0 - free) * 180e9)
     # bytes of training state per byte of 16-bit parameter: fp32 gradient (2x) + fp32 master and two moments (6x), the
     # latter divided over the data-parallel ranks by the distributed optimizer
     mult = 1.0 + 2.0 + 6.0 / (dp if getattr(args, "use_distributed_optimizer", False) else 1)

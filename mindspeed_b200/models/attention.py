@@ -152,7 +152,8 @@ class SelfAttention(nn.Module):
         self.linear_qkv.weight.qkv_row_blocks = blocks
         self.core_attention = CoreAttention(config, layer_number, attn_mask_type)
         self.linear_proj = Row(self.nq_total * self.d, config.hidden_size, config=config,
-                                             init_method=config.output_layer_init_method, bias=config.add_bias_linear,
+                                             init_method=config.output_layer_init_method,
+                                             bias=config.add_bias_linear or bool(getattr(config, "add_dense_bias", False)),
                                              input_is_parallel=True, skip_bias_add=True)
         if config.qk_layernorm:
             self.q_layernorm = build_norm(config, self.d)
@@ -226,7 +227,8 @@ class MLASelfAttention(nn.Module):
         self.core_attention = CoreAttention(config, layer_number, attn_mask_type, softmax_scale=scale,
                                             k_channels=self.q_head_dim, v_channels=self.v_dim)
         self.linear_proj = RowParallelLinear(config.num_attention_heads * self.v_dim, h, config=config,
-                                             init_method=config.output_layer_init_method, bias=config.add_bias_linear,
+                                             init_method=config.output_layer_init_method,
+                                             bias=config.add_bias_linear or bool(getattr(config, "add_dense_bias", False)),
                                              input_is_parallel=True, skip_bias_add=True)
         self.dsa = getattr(config, "experimental_attention_variant", None) == "dsa"
         if self.dsa:

@@ -60,6 +60,24 @@ class MoELayer(nn.Module):
         if n_zm is not None and layer_number > n_zm:
             self.zero_memory = "disable"       # --moe-zero-memory-num-layers: only the first N MoE layers of a stage trade recompute for memory
 
+        # --moe-adaptive-recompute-activation: recompute this layer in backward only on steps where its busiest local expert
+        # received more than ``scale`` times the balanced share of tokens (judged by the previous forward; the first one
+        # recomputes).  reference: mindspeed/core/transformer/moe/moe_layer.py:59-66, 106-112
+        self.adaptive_recompute = bool(getattr(config, "moe_adaptive_recompute_activation", False))
+        self.adaptive_scale = float(getattr(config, "moe_adaptive_recompute_activation_scale", 2.0))
+        gather = ep * (ps.get_tensor_model_parallel_world_size() if kind == "allgather" and config.sequence_parallel else 1)
+        self._share = gather * config.moe_router_topk / config.num_moe_experts        # balanced tokens per expert per local token
+        self._max_tokens_per_expert = None
+        self.recomputed_steps = 0
+
+    def _recompute_this_step(self, hidden_states) -> bool:
+        if not self.adaptive_recompute:
+            return False
+        if self._max_tokens_per_expert is None:
+            return True
+        n = hidden_states.shape[0] * hidden_states.shape[1]
+        return float(self._max_tokens_per_expert) > n * self._share * self.adaptive_scale
+
     def _forward(self, hidden_states):
         if hasattr(self.token_dispatcher, "pre_gather"):
             self.token_dispatcher.pre_gather(hidden_states)      # in flight while the router computes
@@ -79,6 +97,9 @@ class MoELayer(nn.Module):
             if self.hot_experts:
                 probs, routing_map, hot_out = self._hot_path(hidden_states, probs, routing_map)
         dispatched, tokens_per_expert, pprobs = self.token_dispatcher.token_permutation(hidden_states, probs.to(hidden_states.dtype), routing_map)
+        if self.adaptive_recompute:
+            with torch.no_grad():
+                self._max_tokens_per_expert = torch.as_tensor(tokens_per_expert).max()
         expert_out, _ = self.experts(dispatched, tokens_per_expert, pprobs)
         if self.unperm_swap and self.training and expert_out.is_cuda:
             # --moe-unperm2-mem-optim-swap: what the un-permute saves for backward (the expert output rows) waits in host memory
@@ -153,6 +174,10 @@ class MoELayer(nn.Module):
         self._hot_w1.grad = self._hot_w2.grad = None
 
     def forward(self, hidden_states):
+        if self.training and torch.is_grad_enabled() and self._recompute_this_step(hidden_states):
+            from ..random import checkpoint
+            self.recomputed_steps += 1
+            return checkpoint(self._forward, False, hidden_states), None
         if self.training and (self.config.moe_layer_recompute or self.zero_memory != "disable"):
             # zero-memory levels: drop dispatcher intermediates and recompute them in backward
             # (reference: --moe-zero-memory level0/level1, moe_layer_overlap_all2all.py:157-409)

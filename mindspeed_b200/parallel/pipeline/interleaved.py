@@ -24,7 +24,17 @@ def forward_backward_interleaved(*, forward_step_func, data_iterator, model, num
                                  forward_only=False, collect_non_loss_data=False, **_):
     pp = ps.get_pipeline_model_parallel_world_size()
     vpp = len(model)
-    plan = _plan("interleaved", pp, num_microbatches, vpp)
+    nano, swap = False, False
+    try:
+        from ...training.global_vars import get_args
+        nano, swap = bool(getattr(get_args(), "use_nanopipe", False)), bool(getattr(get_args(), "use_nanopipe_swap", False))
+    except RuntimeError:
+        pass
+    # --use-nanopipe: weight gradients of the first backward steps of every rank move to the end of its schedule;
+    # --use-nanopipe-swap parks what they need (layer inputs and output gradients) in pinned host memory meanwhile
+    from ..weight_grad_store import WeightGradStore
+    WeightGradStore.swap_to_host = nano and swap and not forward_only
+    plan = _plan("nanopipe" if nano and not forward_only else "interleaved", pp, num_microbatches, vpp)
     return run_plan(plan, forward_step_func=forward_step_func, data_iterator=data_iterator, model=model,
                     num_microbatches=num_microbatches, seq_length=seq_length, micro_batch_size=micro_batch_size,
                     forward_only=forward_only, collect_non_loss_data=collect_non_loss_data)

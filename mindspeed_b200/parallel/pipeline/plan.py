@@ -94,8 +94,14 @@ def order_1f1b(pp, n_mb) -> List[List[Op]]:
     return out
 
 
-def order_interleaved(pp, v, n_mb) -> List[List[Op]]:
-    """Megatron interleaved 1F1B: micro-batches advance in groups of pp through the v chunks."""
+def order_interleaved(pp, v, n_mb, nano: bool = False) -> List[List[Op]]:
+    """Megatron interleaved 1F1B: micro-batches advance in groups of pp through the v chunks.
+
+    ``nano`` (``--use-nanopipe``): backward is split into the input-gradient part B and the weight-gradient part W.  On rank
+    r the first 2 r backward steps run B only - the ranks before it in the pipeline get their output gradients one
+    weight-gradient GEMM earlier per step, which is what shortens the start of the backward wave - and their W parts run
+    after the rank's last backward, in what would be its tail bubble; every other backward is followed by a W at once
+    (reference: mindspeed/core/pipeline_parallel/ripipe_schedules.py:166-170, 542-552, 738-744)."""
     if n_mb % pp != 0:
         raise ValueError("interleaved schedule needs the number of micro-batches to be a multiple of the pipeline size")
     total = n_mb * v
@@ -115,12 +121,22 @@ def order_interleaved(pp, v, n_mb) -> List[List[Op]]:
         f = b = 0
         for _ in range(warm):
             c, m = fwd_id(f); ops.append(Op("F", c, m)); f += 1
+        num_dx = min(2 * r, total) if nano else 0
+        late: List[Op] = []
+
+        def back():
+            nonlocal b
+            c, m = bwd_id(b)
+            ops.append(Op("B", c, m))
+            if nano:
+                (late if b < num_dx else ops).append(Op("W", c, m))
+            b += 1
         for _ in range(total - warm):
             c, m = fwd_id(f); ops.append(Op("F", c, m)); f += 1
-            c, m = bwd_id(b); ops.append(Op("B", c, m)); b += 1
+            back()
         while b < total:
-            c, m = bwd_id(b); ops.append(Op("B", c, m)); b += 1
-        out.append(ops)
+            back()
+        out.append(ops + late)
     return out
 
 
@@ -505,8 +521,8 @@ def build_plan(name: str, pp: int, n_mb: int, vpp: Optional[int] = None, split_w
                recompute: Optional[str] = None, pair_fb: bool = False) -> Plan:
     if name == "1f1b":
         pl, orders = placement_1f1b(pp), order_1f1b(pp, n_mb)
-    elif name == "interleaved":
-        pl, orders = placement_interleaved(pp, vpp), order_interleaved(pp, vpp, n_mb)
+    elif name in ("interleaved", "nanopipe"):
+        pl, orders = placement_interleaved(pp, vpp), order_interleaved(pp, vpp, n_mb, nano=(name == "nanopipe"))
     elif name == "dualpipev":
         pl = placement_v(pp)
         orders = order_dualpipev(pp, n_mb, split_w)

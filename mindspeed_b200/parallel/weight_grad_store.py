@@ -21,6 +21,26 @@ class WeightGradStore:
     _cache: List[tuple] = []
     _queue: "queue.Queue[List[tuple]]" = queue.Queue()
     _gather_stream = None
+    swap_to_host = False           # park the stored inputs / output gradients in pinned host memory between flush and pop
+    _offload = None
+    _fresh = None                  # swap mode: the most recently flushed micro-batch, still on the device
+
+    @classmethod
+    def _park(cls, entries):
+        if not cls.swap_to_host:
+            return entries
+        if cls._offload is None:
+            from ..memory.host_offload import OffloadSaved
+            cls._offload = OffloadSaved(min_bytes=1 << 16)
+        pk = cls._offload._pack
+        return [(pk(x), pk(dy), w, sp, g, f) for x, dy, w, sp, g, f in entries]
+
+    @classmethod
+    def _fetch(cls, entries):
+        if cls._offload is None:
+            return entries
+        up = cls._offload._unpack
+        return [(up(x), up(dy), w, sp, g, f) for x, dy, w, sp, g, f in entries]
 
     @classmethod
     def enable(cls, flag: bool = True):
@@ -37,16 +57,24 @@ class WeightGradStore:
     @classmethod
     def flush(cls):
         """Close the current micro-batch: everything put since the last flush pops together."""
-        cls._queue.put(cls._cache)
+        if cls.swap_to_host:
+            # the newest micro-batch stays on the device: if its W comes next it is popped as it is; it is parked only when
+            # another backward arrives first, i.e. when its W has been deferred
+            if cls._fresh is not None:
+                cls._queue.put(cls._park(cls._fresh))
+            cls._fresh = cls._cache
+        else:
+            cls._queue.put(cls._cache)
         cls._cache = []
 
     @classmethod
     def is_empty(cls) -> bool:
-        return cls._queue.empty()
+        return cls._queue.empty() and cls._fresh is None
 
     @classmethod
     def clear(cls):
         cls._cache = []
+        cls._fresh = None
         cls._queue = queue.Queue()
 
     @classmethod
@@ -70,11 +98,15 @@ class WeightGradStore:
         """Run the weight-gradient GEMMs of one flushed micro-batch (or ``num`` entries of it)."""
         from .comm_ops import get_ops
         from .layers import _wgrad
-        if cls._queue.empty():
-            if not cls._cache:
-                return 0
-            cls.flush()
-        entries = cls._queue.get()
+        if cls._fresh is not None:
+            entries, cls._fresh = cls._fresh, None
+        else:
+            if cls._queue.empty():
+                if not cls._cache:
+                    return 0
+                cls.flush()
+                return cls.pop(num)
+            entries = cls._fetch(cls._queue.get())
         if 0 <= num < len(entries):
             rest = entries[num:]
             entries = entries[:num]
@@ -110,6 +142,6 @@ class WeightGradStore:
     @classmethod
     def pop_all(cls):
         n = 0
-        while not cls._queue.empty() or cls._cache:
+        while not cls._queue.empty() or cls._cache or cls._fresh is not None:
             n += cls.pop()
         return n

@@ -1,0 +1,126 @@
+"""Older spellings and small legacy options: each is rewritten onto, or implemented next to, the feature it names."""
+import json
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+BASE = ["--num-layers", "4", "--hidden-size", "64", "--num-attention-heads", "4", "--seq-length", "32",
+        "--micro-batch-size", "1", "--vocab-size", "128"]
+
+
+def _args(extra, world=1, monkeypatch=None):
+    from mindspeed_b200.training.arguments import parse_args, validate_args
+    if monkeypatch is not None:
+        monkeypatch.setenv("WORLD_SIZE", str(world))
+    return validate_args(parse_args(args_list=BASE + list(extra)))
+
+
+def test_older_spellings_are_rewritten(monkeypatch, tmp_path):
+    a = _args(["--tensor-model-parallel-size", "4", "--use-nd-matmul", "--nd1-dim1-size", "2", "--nd2-dim1-size", "2"], 4, monkeypatch)
+    assert a.tp_2d and (a.tp_x, a.tp_y) == (2, 2)
+    with pytest.raises(AssertionError, match="must equal"):
+        _args(["--tensor-model-parallel-size", "4", "--use-nd-matmul", "--nd1-dim1-size", "2", "--nd2-dim1-size", "1"], 4, monkeypatch)
+    a = _args(["--pipeline-model-parallel-size", "2", "--num-layers-per-virtual-pipeline-stage", "1", "--optimize-vpp-send-recv-comm"],
+              2, monkeypatch)
+    assert a.optimize_send_recv_comm
+    a = _args(["--enable-zero3"], 2, monkeypatch)
+    assert a.layerzero
+    a = _args(["--multi-head-latent-attention", "--rope-scaling-type", "yarn", "--yarn-scaling-factor", "8"], 1, monkeypatch)
+    assert a.rope_scaling_factor == 8
+    a = _args(["--num-experts", "4", "--moe-model-type", "deepspeed_moe", "--expert-interval", "2"], 1, monkeypatch)
+    assert a.moe_layer_freq == [0, 1, 0, 1]
+    with pytest.raises(AssertionError, match="deepspeed_moe"):
+        _args(["--num-experts", "4", "--expert-interval", "2"], 1, monkeypatch)
+    cfgf = tmp_path / "more.json"
+    cfgf.write_text(json.dumps({"--add-dense-bias": True, "kl_temperature": 2.5}))
+    a = _args(["--additional-config", str(cfgf)], 1, monkeypatch)
+    assert a.add_dense_bias is True and a.kl_temperature == 2.5
+    cfgf.write_text("no_such_argument: 1\n")
+    with pytest.raises(AssertionError, match="unknown argument"):
+        _args(["--additional-config", str(cfgf)], 1, monkeypatch)
+    with pytest.raises(NotImplementedError, match="optimized-mbs-list"):
+        _args(["--optimized-mbs-list", "[2,1,1]"], 1, monkeypatch)
+    with pytest.raises(AssertionError, match="use-nanopipe"):
+        _args(["--use-nanopipe"], 1, monkeypatch)
+
+
+def test_random_token_selection_keeps_capacity_and_is_not_position_biased():
+    from mindspeed_b200.legacy_moe.gate import top1gating
+    torch.manual_seed(0)
+    S, E = 64, 2
+    logits = torch.zeros(S, E)
+    logits[:, 0] = 1.0                                             # every token wants expert 0: capacity 32 * cf
+    _, comb, mask, counts = top1gating(logits, capacity_factor=0.5, min_capacity=4)
+    kept = mask.any(-1)[:, 0].nonzero().flatten()
+    assert kept.tolist() == list(range(16))                        # sequence order: the first 16
+    picks = []
+    for _ in range(4):
+        _, comb, mask, _ = top1gating(logits, capacity_factor=0.5, min_capacity=4, use_rts=True)
+        m = mask[:, 0]                                             # [S, C]
+        assert int(m.any(-1).sum()) == 16 and int(m.sum(0).max()) == 1          # 16 kept, one token per capacity slot
+        picks.append(tuple(m.any(-1).nonzero().flatten().tolist()))
+    assert len(set(picks)) > 1 and any(max(p) >= 32 for p in picks)
+    # under capacity nothing is dropped either way
+    lg = torch.randn(16, 4)
+    a = top1gating(lg, capacity_factor=4.0)[1]
+    b = top1gating(lg, capacity_factor=4.0, use_rts=True)[1]
+    assert torch.equal(a.sum(-1), b.sum(-1))
+
+
+def _train_moe(rank, world, extra):
+    import io
+    from contextlib import redirect_stdout
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import pretrain_gpt as pg
+    from test_pipeline_cpu import BASE as TB
+    from mindspeed_b200.parallel.moe.moe_layer import MoELayer
+    from mindspeed_b200.training import pretrain
+    layers = []
+    orig = MoELayer.__init__
+
+    def spy(self, *a, **kw):
+        orig(self, *a, **kw)
+        layers.append(self)
+    MoELayer.__init__ = spy
+    flags = ["--num-experts", "4", "--moe-router-topk", "2", "--moe-token-dispatcher-type", "alltoall", "--moe-grouped-gemm",
+             "--moe-aux-loss-coeff", "0.01", "--train-iters", "4"]
+    with redirect_stdout(io.StringIO()):
+        hist = pretrain(pg.train_valid_test_datasets_provider, pg.model_provider, forward_step_func=pg.forward_step,
+                        args_list=TB + flags + list(extra))
+    MoELayer.__init__ = orig
+    return [h["lm loss"] for h in hist], [l.recomputed_steps for l in layers]
+
+
+def test_moe_recompute_only_on_unbalanced_steps_changes_no_numbers():
+    from dist_utils import run_distributed
+    plain, r0 = run_distributed(_train_moe, 1, [])[0]
+    assert set(r0) == {0}
+    # an unreachable threshold: only the very first forward of every layer (no history yet) recomputes
+    hi, r1 = run_distributed(_train_moe, 1, ["--moe-adaptive-recompute-activation", "--moe-adaptive-recompute-activation-scale", "100"])[0]
+    assert set(r1) == {1} and hi == pytest.approx(plain, abs=1e-6)
+    # a threshold every step exceeds: every forward (4 steps x 8 micro-batches) recomputes
+    lo, r2 = run_distributed(_train_moe, 1, ["--moe-adaptive-recompute-activation", "--moe-adaptive-recompute-activation-scale", "0.01"])[0]
+    assert set(r2) == {32} and lo == pytest.approx(plain, abs=1e-6)
+
+
+def test_dense_bias_flag_adds_the_projection_bias():
+    from mindspeed_b200.config import TransformerConfig
+    from mindspeed_b200.models.attention import SelfAttention
+    from mindspeed_b200.parallel import parallel_state as ps
+    import torch.distributed as dist
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", "29878")
+    if not dist.is_initialized():
+        dist.init_process_group("gloo", rank=0, world_size=1)
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(1, 1)
+    kw = dict(num_layers=1, hidden_size=32, num_attention_heads=4, use_cpu_initialization=True, optimization_level=0, add_bias_linear=False)
+    cfg = TransformerConfig(**kw)
+    assert SelfAttention(cfg).linear_proj.bias is None
+    cfg2 = TransformerConfig(**kw)
+    cfg2.add_dense_bias = True
+    assert SelfAttention(cfg2).linear_proj.bias is not None and SelfAttention(cfg2).linear_qkv.bias is None
+    ps.destroy_model_parallel()

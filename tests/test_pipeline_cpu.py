@@ -9,7 +9,7 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 from dist_utils import run_distributed  # noqa: E402
 
 
-@pytest.mark.parametrize("name,vpp", [("1f1b", None), ("interleaved", 2), ("interleaved", 4), ("dualpipev", None),
+@pytest.mark.parametrize("name,vpp", [("1f1b", None), ("interleaved", 2), ("interleaved", 4), ("nanopipe", 2), ("dualpipev", None),
                                       ("dualpipev_greedy", None), ("dualpipe", None), ("chimera", None)])
 @pytest.mark.parametrize("pp", [2, 4, 8])
 def test_plans_are_valid_and_matched(name, vpp, pp):
@@ -52,6 +52,29 @@ def test_recompute_ops_fill_bubbles(mode):
     t_naive, _ = simulate_orders(pl, orders, {"F": 1, "B": 3, "W": 0})
     t_ri, _ = simulate_orders(pl, insert_recompute(orders, mode), {"F": 1, "B": 2, "W": 0, "R": 1})
     assert t_none <= t_ri < t_naive, (t_none, t_ri, t_naive)
+
+
+def test_nanopipe_defers_the_first_weight_gradients_of_each_rank_and_shortens_the_step():
+    from mindspeed_b200.parallel.pipeline.plan import order_interleaved, placement_interleaved, simulate_orders
+    pp, v, n = 4, 2, 8
+    plain, nano = order_interleaved(pp, v, n), order_interleaved(pp, v, n, nano=True)
+    for r in range(pp):
+        ops = nano[r]
+        assert [o for o in ops if o.kind != "W"] == plain[r]                   # same forward / backward order
+        bs = [o for o in ops if o.kind == "B"]
+        ws = [o for o in ops if o.kind == "W"]
+        assert sorted((o.chunk, o.mb) for o in bs) == sorted((o.chunk, o.mb) for o in ws)
+        last_b = max(i for i, o in enumerate(ops) if o.kind == "B")
+        late = [o for o in ops[last_b + 1:] if o.kind == "W"]
+        assert len(late) == 2 * r + 1                                            # the last backward's own, then the deferred ones
+        assert [(o.chunk, o.mb) for o in late[1:]] == [(o.chunk, o.mb) for o in bs[:2 * r]]
+    # with backward split into equal input- and weight-gradient parts the deferral shortens the step
+    cost = {"F": 1, "B": 1, "W": 1}
+    pl = placement_interleaved(pp, v)
+    both = [[x for o in ops for x in ((o, type(o)("W", o.chunk, o.mb)) if o.kind == "B" else (o,))] for ops in plain]
+    t_plain, _ = simulate_orders(pl, both, cost)
+    t_nano, _ = simulate_orders(pl, nano, cost)
+    assert t_nano < t_plain, (t_nano, t_plain)
 
 
 def test_1f1b_bubble_matches_theory():
@@ -159,6 +182,9 @@ def _train(rank, world, extra, bidirectional):
     # list-valued stage interface with its default content (the one hidden-state tensor), through the plan executor
     (2, ["--pipeline-model-parallel-size", "2", "--use-multiparameter-pipeline-model-parallel"], False),
     (2, ["--pipeline-model-parallel-size", "2", "--num-layers-per-virtual-pipeline-stage", "1", "--recompute-in-advance"], False),
+    # interleaved schedule with the first weight-gradient GEMMs of each rank moved behind its last backward
+    (2, ["--pipeline-model-parallel-size", "2", "--num-layers-per-virtual-pipeline-stage", "1", "--use-nanopipe"], False),
+    (2, ["--pipeline-model-parallel-size", "2", "--num-layers-per-virtual-pipeline-stage", "1", "--use-nanopipe", "--use-nanopipe-swap"], False),
     (2, ["--pipeline-model-parallel-size", "2", "--schedules-method", "chimera"], True),
     (2, ["--pipeline-model-parallel-size", "2", "--schedules-method", "dualpipe"], True),
     # receives of the next slot posted before this slot's compute, sends right after it, one communicator per direction
