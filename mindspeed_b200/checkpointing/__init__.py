@@ -202,6 +202,21 @@ def save_checkpoint(iteration, model, optimizer, opt_param_scheduler, args=None,
     sharded, common = generate_state_dict(model, optimizer if not getattr(args, "no_save_optim", False) else None,
                                           opt_param_scheduler, iteration, args, rng=not getattr(args, "no_save_rng", False))
     rank = dist.get_rank() if dist.is_initialized() else 0
+    from ..parallel.distributed.fsdp import FullyShardedDataParallel as _FSDP
+    if any(isinstance(c, _FSDP) for c in model):
+        # the flat per-parameter tensors of a fully sharded model carry no shapes: keep them next to the checkpoint so that
+        # checkpointing/convert_fsdp.py can rebuild the parameters without the model
+        mine = {}
+        for c in model:
+            if isinstance(c, _FSDP):
+                mine.update(c.layout(""))
+        if _use_dist():
+            parts = [None] * dist.get_world_size()
+            dist.all_gather_object(parts, mine)
+            mine = {k: v for part in parts for k, v in part.items()}
+        common["fsdp_layout"] = mine
+        inner = model[0].module
+        common["num_layers"] = int(getattr(getattr(inner, "config", None), "num_layers", 0) or 0)
     os.makedirs(path, exist_ok=True)
     rng_state = {"rng_state": common.pop("rng_state", None)}
 

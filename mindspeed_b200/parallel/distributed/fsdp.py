@@ -112,6 +112,9 @@ class ShardedUnit:
         self.seq_replicated = [bool(getattr(p, "sequence_parallel", False)) for p in self.params]
         self.shapes = [p.shape for p in self.params]
         self.numels = [p.numel() for p in self.params]
+        # where a tensor-parallel parameter is split (axis, and 2 for the gated FC1 whose rows are [gate; up] per rank)
+        self.tp_dims = [int(getattr(p, "partition_dim", -1)) if getattr(p, "tensor_model_parallel", False) else None for p in self.params]
+        self.tp_strides = [int(getattr(p, "partition_stride", 1)) for p in self.params]
         total = sum(self.numels)
         div = self.S * (self.R if plan.zero1_over_replicas else 1)
         self.padded = ((total + div - 1) // div) * div
@@ -425,6 +428,40 @@ class FullyShardedDataParallel(nn.Module):
                     key += f".pp{ppr}"
                 replica = u.r_rank + (0 if (u.tp_sharded[i] or tp == 1) else tpr * 1000)
                 out[key] = ShardedTensor(key, u.flat_shard[at:at + n], (u.numels[i],), (start,), replica_id=replica)
+        return out
+
+    def layout(self, prefix: str = "") -> Dict[str, dict]:
+        """What a reader of ``sharded_state_dict`` needs to turn the flat tensors back into parameters, per checkpoint key:
+        the qualified parameter name, the local shape, the tensor-parallel split (rank, size, axis, stride) or None, and the
+        global number of the layer the parameter belongs to (pipeline stages number their layers locally)."""
+        from .. import parallel_state as ps
+        mp = ps.model_parallel_is_initialized()
+        tp, tpr = (ps.get_tensor_model_parallel_world_size(), ps.get_tensor_model_parallel_rank()) if mp else (1, 0)
+        ppr = ps.get_pipeline_model_parallel_rank() if mp and ps.get_pipeline_model_parallel_world_size() > 1 else None
+        inner = self.module
+        numbers = {}
+        if hasattr(inner, "decoder"):
+            numbers = {i: l.layer_number - 1 for i, l in enumerate(inner.decoder.layers) if hasattr(l, "layer_number")}
+        out = {}
+        for u in self.units:
+            for i, name in enumerate(u.param_names):
+                qual = name if u.name == "<root>" else f"{u.name}.{name}"
+                key = f"{prefix}fsdp.{qual}"
+                split = None
+                if tp > 1 and u.tp_sharded[i]:
+                    key += f".tp{tpr}of{tp}"
+                    split = (tpr, tp, u.tp_dims[i], u.tp_strides[i])
+                if ppr is not None:
+                    key += f".pp{ppr}"
+                parts = qual.split(".")
+                layer = None
+                if "layers" in parts:
+                    j = parts.index("layers")
+                    if j + 1 < len(parts) and parts[j + 1].isdigit():
+                        layer = numbers.get(int(parts[j + 1]))
+                        parts = parts[:j + 1] + parts[j + 2:]
+                out[key] = {"name": ".".join(parts), "shape": tuple(u.shapes[i]), "tp": split, "layer": layer,
+                            "expert": not getattr(u.params[i], "allreduce", True)}
         return out
 
     def memory_summary(self) -> Dict[str, int]:

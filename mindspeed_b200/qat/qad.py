@@ -43,7 +43,17 @@ def load_model_weights(model, load_dir, iteration=None, strict=True):
     if it is None:
         raise FileNotFoundError(f"no checkpoint under {load_dir!r} (latest_checkpointed_iteration.txt is missing)")
     sharded, _ = C.generate_state_dict(model, None, None, it, None, rng=False)
-    C._load_sharded(sharded, C.get_checkpoint_name(load_dir, it), strict=strict)
+    missing = C._load_sharded(sharded, C.get_checkpoint_name(load_dir, it), strict=False)
+    if strict and missing:
+        # persistent buffers (rotary frequencies and the like) are rebuilt by the model and may be absent from converted
+        # checkpoints; a missing parameter is an error
+        buffers = set()
+        for chunk in model:
+            inner = chunk.module if hasattr(chunk, "module") and not hasattr(chunk, "decoder") else chunk
+            buffers.update(n for n, _ in inner.named_buffers())
+        bad = [k for k in missing if k.split("@")[0] not in buffers]
+        if bad:
+            raise KeyError(f"keys missing from checkpoint: {bad[:5]} ...")
     return it
 
 

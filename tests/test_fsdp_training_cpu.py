@@ -121,3 +121,71 @@ def test_fsdp_sharded_checkpoint_reloads_under_another_shard_size(tmp_path):
     for (l0, w0), (l1, w1) in zip(saved, loaded):
         assert abs(l0 - l1) < 1e-5 * max(1.0, abs(l0)), (saved, loaded)
         assert abs(w0 - w1) < 1e-4 * max(1.0, abs(w0)), (saved, loaded)
+
+
+def _probe(rank, world, extra, save_dir, steps):
+    """Train ``steps`` steps (optionally save), then report the loss of one more step on fixed samples."""
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import pretrain_gpt as pg
+    from mindspeed_b200.checkpointing import save_checkpoint
+    from mindspeed_b200.parallel import parallel_state as ps
+    from mindspeed_b200.training import initialize_megatron, setup_model_and_optimizer, train_step
+    from mindspeed_b200.training.data import SyntheticGPTDataset
+    base = [a for a in BASE if a != "--no-gradient-accumulation-fusion"]
+    base[base.index("--global-batch-size") + 1] = "4"
+    base[base.index("--num-layers") + 1] = "2"
+    args = initialize_megatron(args_list=base + ["--clip-grad", "1.0"] + list(extra))
+    model, opt, sched = setup_model_and_optimizer(pg.model_provider)
+    ds = SyntheticGPTDataset(args.padded_vocab_size, args.seq_length, 4096, seed=args.seed)
+    dp_r, dp_n = ps.get_data_parallel_rank(), ps.get_data_parallel_world_size()
+
+    class It:
+        base, m = 0, 0
+
+        def __iter__(self):
+            return self
+
+        def __next__(self):
+            i = It.base + It.m * dp_n + dp_r                      # the same global samples for every parallel layout
+            It.m += 1
+            return {k: v.unsqueeze(0) for k, v in ds[i].items()}
+
+    for s in range(steps):
+        It.base, It.m = 4 * s, 0
+        train_step(pg.forward_step, It(), model, opt, sched)
+    if save_dir and steps:
+        save_checkpoint(steps, model, opt, sched, args, save_dir=save_dir)
+    It.base, It.m = 1000, 0
+    ld, *_ = train_step(pg.forward_step, It(), model, opt, sched)
+    return float(ld["lm loss"])
+
+
+@pytest.mark.parametrize("world,tp", [(2, 1), (4, 2)])
+def test_fully_sharded_checkpoint_converts_to_the_regular_layout(tmp_path, world, tp):
+    """A LayerZeRO checkpoint (flat per-parameter shards; with tensor parallelism one set per tensor-parallel rank) is
+    converted offline and read by a plain single-rank model: the loss on fixed samples is the sharded run's."""
+    import torch
+    from mindspeed_b200.checkpointing import convert_fsdp
+    src, dst = str(tmp_path / "fsdp"), str(tmp_path / "plain")
+    flags = ["--layerzero", "--lr", "1e-2"] + (["--tensor-model-parallel-size", str(tp), "--sequence-parallel"] if tp > 1 else [])
+    sharded = run_distributed(_probe, world, flags, src, 2)[0]
+    assert convert_fsdp.main(["--input_folder", src, "--output_folder", dst, "--target_tp", "1", "--target_pp", "1"]) == 0
+    common = torch.load(os.path.join(dst, "iter_0000002", "common.pt"), weights_only=False)
+    assert common["args"]["tensor_model_parallel_size"] == 1 and "fsdp_layout" not in common
+    assert common["converted_from"]["source_tp"] == tp
+    plain = run_distributed(_probe, 1, ["--load", dst, "--finetune"], None, 0)[0]
+    assert abs(plain - sharded) < 2e-5 * max(1.0, abs(sharded)), (sharded, plain)
+    untrained = run_distributed(_probe, 1, [], None, 0)[0]
+    assert abs(untrained - sharded) > 1e-3                        # the probe does depend on the trained weights
+
+
+def test_gated_projection_rows_regroup_between_tensor_parallel_sizes():
+    import torch
+    from mindspeed_b200.checkpointing.convert_fsdp import regroup_gated
+    gate, up = torch.arange(8.0).view(8, 1), 100 + torch.arange(8.0).view(8, 1)
+    per_rank = lambda tp: torch.cat([torch.cat((g, u)) for g, u in zip(gate.chunk(tp), up.chunk(tp))])
+    for a in (1, 2, 4):
+        for b in (1, 2, 4):
+            assert torch.equal(regroup_gated(per_rank(a), a, b), per_rank(b)), (a, b)
+    w = torch.randn(3, 8)
+    assert torch.equal(regroup_gated(regroup_gated(w, 2, 4, dim=1), 4, 2, dim=1), w)
