@@ -153,6 +153,29 @@ def topk_softmax_with_capacity(logits, topk, capacity_factor=None, pad_to_capaci
     return probs, routing_map, tokens_per_expert
 
 
+def reduce_moe_metrics(tracker, calls_per_layer: int, clear: bool = True):
+    """{name: per-layer means [num_layers]} of what ``track_moe_metrics`` accumulated since the last call: layers live on
+    different pipeline stages (summed over the pipeline group), every layer added one value per forward (``calls_per_layer``
+    = micro-batches x steps) and data-parallel ranks see different tokens (averaged).  Collective over the pipeline and
+    data-parallel groups: every rank must call it (reference: Megatron ``reduce_aux_losses_tracker_across_ranks`` as used by
+    mindspeed/core/transformer/moe/moe_utils.py track_moe_metrics)."""
+    import torch.distributed as dist
+    from .. import parallel_state as ps
+    out = {}
+    for name in sorted(tracker):
+        v = tracker[name]["values"].float().clone() / max(1, calls_per_layer)
+        if dist.is_initialized() and ps.model_parallel_is_initialized():
+            if ps.get_pipeline_model_parallel_world_size() > 1:
+                dist.all_reduce(v, group=ps.get_pipeline_model_parallel_group())
+            if ps.get_data_parallel_world_size() > 1:
+                dist.all_reduce(v, group=ps.get_data_parallel_group())
+                v /= ps.get_data_parallel_world_size()
+        out[name] = v
+        if clear:
+            tracker[name]["values"].zero_()
+    return out
+
+
 def track_moe_metrics(tracker, name, value, layer_number, num_layers):
     if name not in tracker:
         tracker[name] = {"values": torch.zeros(num_layers, device=value.device)}

@@ -387,6 +387,22 @@ def train(forward_step_func, model, optimizer, opt_param_scheduler, train_data_i
         if prof is not None:
             prof.step()
         if iteration % args.log_interval == 0:
+            if args.num_experts and args.moe_aux_loss_coeff > 0 and getattr(args, "moe_model_type", "") != "deepspeed_moe":
+                # auxiliary losses the routers attached inside the model: mean over the MoE layers (and per layer with
+                # --moe-per-layer-logging), averaged over the micro-batches and steps since the last log line
+                from ..parallel.moe.moe_utils import reduce_moe_metrics
+                calls = get_num_microbatches() * min(args.log_interval, iteration)
+                tracker = ps.get_moe_layer_wise_logging_tracker()
+                if "load_balancing_loss" not in tracker:         # a stage without MoE layers still joins the reduction
+                    dev = next(model[0].parameters()).device
+                    tracker["load_balancing_loss"] = {"values": torch.zeros(args.num_layers, device=dev)}
+                for name, per_layer in reduce_moe_metrics(tracker, calls).items():
+                    n_moe = max(1, int((per_layer != 0).sum()))
+                    loss_dict[name] = per_layer.sum() / n_moe
+                    if getattr(args, "moe_per_layer_logging", False):
+                        for i, x in enumerate(per_layer.tolist()):
+                            if x != 0:
+                                loss_dict[f"{name} layer {i + 1}"] = x
             training_log(loss_dict, iteration, elapsed, grad_norm, skipped, optimizer.param_groups[0]["lr"])
             if writer is not None:
                 for k, v in loss_dict.items():

@@ -92,19 +92,27 @@ def _train_moe(rank, world, extra):
         hist = pretrain(pg.train_valid_test_datasets_provider, pg.model_provider, forward_step_func=pg.forward_step,
                         args_list=TB + flags + list(extra))
     MoELayer.__init__ = orig
-    return [h["lm loss"] for h in hist], [l.recomputed_steps for l in layers]
+    return [h.get("lm loss") for h in hist], [l.recomputed_steps for l in layers], [{k: float(v) for k, v in h.items() if "balancing" in k} for h in hist]
 
 
 def test_moe_recompute_only_on_unbalanced_steps_changes_no_numbers():
     from dist_utils import run_distributed
-    plain, r0 = run_distributed(_train_moe, 1, [])[0]
+    plain, r0, aux = run_distributed(_train_moe, 1, [])[0]
+    # the routers' load-balancing loss is reported per log line: mean over the MoE layers, >= 1 x coefficient when unbalanced
+    assert all(set(a) == {"load_balancing_loss"} and 0.0099 < a["load_balancing_loss"] < 0.05 for a in aux), aux
     assert set(r0) == {0}
     # an unreachable threshold: only the very first forward of every layer (no history yet) recomputes
-    hi, r1 = run_distributed(_train_moe, 1, ["--moe-adaptive-recompute-activation", "--moe-adaptive-recompute-activation-scale", "100"])[0]
+    hi, r1, _ = run_distributed(_train_moe, 1, ["--moe-adaptive-recompute-activation", "--moe-adaptive-recompute-activation-scale", "100"])[0]
     assert set(r1) == {1} and hi == pytest.approx(plain, abs=1e-6)
     # a threshold every step exceeds: every forward (4 steps x 8 micro-batches) recomputes
-    lo, r2 = run_distributed(_train_moe, 1, ["--moe-adaptive-recompute-activation", "--moe-adaptive-recompute-activation-scale", "0.01"])[0]
+    lo, r2, _ = run_distributed(_train_moe, 1, ["--moe-adaptive-recompute-activation", "--moe-adaptive-recompute-activation-scale", "0.01"])[0]
     assert set(r2) == {32} and lo == pytest.approx(plain, abs=1e-6)
+    # two pipeline stages: every stage joins the reduction, every layer is reported once
+    pp, _, aux_pp = run_distributed(_train_moe, 2, ["--pipeline-model-parallel-size", "2", "--moe-per-layer-logging"])[1]
+    # (the two stages draw their initial weights independently, so the values differ from the one-stage run)
+    assert all(0.0099 < a["load_balancing_loss"] < 0.05 for a in aux_pp), aux_pp
+    per_layer = [aux_pp[0][f"load_balancing_loss layer {i}"] for i in (1, 2, 3, 4)]
+    assert abs(sum(per_layer) / 4 - aux_pp[0]["load_balancing_loss"]) < 1e-6 and all(x > 0.0099 for x in per_layer)
 
 
 def test_dense_bias_flag_adds_the_projection_bias():
