@@ -118,3 +118,40 @@ def parse_chrome_trace(path: str) -> ProfileSummary:
     with open(path) as f:
         d = json.load(f)
     return summarize(d["traceEvents"] if isinstance(d, dict) else d)
+
+
+# --- what a search needs to know about a job without running it --------------------------------------------------------
+def dump_settings(args, save_path: str) -> str:
+    """Write the parsed, validated arguments of this launch (plain values only) to ``<save_path>/auto_settings_args.json``.
+    A launcher started with ``OOTB_OPTIMIZER_PARSE_ARGS=TRUE`` does this and exits: the search reads the file instead of
+    re-implementing argument parsing (reference: mindspeed/training.py:185-195, auto_settings/module/parse/profiling_parse)."""
+    import json
+    import os
+    os.makedirs(save_path, exist_ok=True)
+    plain = {k: v for k, v in vars(args).items() if isinstance(v, (int, float, str, bool, list, tuple, type(None))) and not k.startswith("_")}
+    out = os.path.join(save_path, "auto_settings_args.json")
+    if getattr(args, "rank", 0) == 0:
+        with open(out, "w") as f:
+            json.dump(plain, f, indent=1, sort_keys=True)
+    return out
+
+
+def dump_model_params(model, pp_rank: int, save_path: str) -> str:
+    """Write name, shape, element count and tensor-parallel split of every parameter this pipeline rank holds to
+    ``<save_path>/model_params_pp<rank>.json`` (``OOTB_OPTIMIZER_PARSE_MODEL=TRUE``; reference: mindspeed/training.py:273-277).
+    One file per pipeline rank, written by the first data- and tensor-parallel rank of the stage."""
+    import json
+    import os
+    os.makedirs(save_path, exist_ok=True)
+    rows = []
+    for ci, chunk in enumerate(model):
+        inner = chunk.module if hasattr(chunk, "module") and not hasattr(chunk, "decoder") else chunk
+        for name, p in inner.named_parameters():
+            rows.append({"chunk": ci, "name": name, "shape": list(p.shape), "numel": p.numel(), "dtype": str(p.dtype).replace("torch.", ""),
+                         "tensor_parallel": bool(getattr(p, "tensor_model_parallel", False)),
+                         "partition_dim": int(getattr(p, "partition_dim", -1)), "expert": not getattr(p, "allreduce", True)})
+    out = os.path.join(save_path, f"model_params_pp{pp_rank}.json")
+    with open(out, "w") as f:
+        json.dump({"pp_rank": pp_rank, "parameters": rows, "total_numel": sum(r["numel"] for r in rows)}, f, indent=1)
+    return out
+

@@ -477,10 +477,22 @@ def pretrain(train_valid_test_dataset_provider, model_provider, model_type=None,
              process_non_loss_data_func=None, extra_args_provider=None, args_defaults=None, args_list=None):
     """Full entry: initialise, (optionally) run the auto-settings search and return, build, train, save."""
     args = initialize_megatron(extra_args_provider, args_defaults, args_list=args_list)
+    if os.getenv("OOTB_OPTIMIZER_PARSE_ARGS", "FALSE") == "TRUE":
+        # a search asks what this launch resolves to: write the validated arguments and stop
+        from ..auto_settings.profiling_parse import dump_settings
+        dump_settings(args, args.profile_save_path)
+        print_rank_0("OOTB_OPTIMIZER_PARSE_ARGS: arguments written, exiting")
+        return []
     if args.auto_settings:
         from ..auto_settings import AutoSettings
         return AutoSettings().auto_setting_fun(args)
     model, optimizer, sched = setup_model_and_optimizer(model_provider)
+    if os.getenv("OOTB_OPTIMIZER_PARSE_MODEL", "FALSE") == "TRUE":
+        from ..auto_settings.profiling_parse import dump_model_params
+        if ps.get_data_parallel_rank() == 0 and ps.get_tensor_model_parallel_rank() == 0:
+            dump_model_params(model, ps.get_pipeline_model_parallel_rank(), args.profile_save_path)
+        print_rank_0("OOTB_OPTIMIZER_PARSE_MODEL: parameter tables written, exiting")
+        return []
     if args.ttp_enabled:
         from ..checkpointing import load_fault_dump, save_fault_dump, wait_for_fault_dump
         from ..ttp import install_ttp

@@ -114,3 +114,41 @@ def test_learn_from_profile_feeds_db_and_lines():
     learn_from_profile(summarize(_trace()), model, cfg, hw, db, comm)
     assert db.exact("gemm", (2048, 1024, 1)) is not None and db.exact("attention", (2048, 2048, 8)) is not None
     assert len(comm.total["ep"].samples) == 1 and comm.exposed["ep"].samples[0][1] < comm.total["ep"].samples[0][1]
+
+
+def _ootb(rank, world, save, env):
+    import io
+    import os
+    import sys
+    from contextlib import redirect_stdout
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    os.environ[env] = "TRUE"
+    import pretrain_gpt as pg
+    from test_pipeline_cpu import BASE
+    from mindspeed_b200.training import pretrain
+    with redirect_stdout(io.StringIO()):
+        hist = pretrain(pg.train_valid_test_datasets_provider, pg.model_provider, forward_step_func=pg.forward_step,
+                        args_list=BASE + ["--pipeline-model-parallel-size", str(world), "--profile-save-path", save])
+    return hist
+
+
+def test_launch_can_report_its_arguments_and_parameters_without_training(tmp_path):
+    """OOTB_OPTIMIZER_PARSE_ARGS / OOTB_OPTIMIZER_PARSE_MODEL: the launcher writes what it resolved and stops."""
+    import json
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from dist_utils import run_distributed
+    d = str(tmp_path)
+    assert run_distributed(_ootb, 2, d, "OOTB_OPTIMIZER_PARSE_ARGS") == [[], []]
+    a = json.load(open(os.path.join(d, "auto_settings_args.json")))
+    assert a["pipeline_model_parallel_size"] == 2 and a["hidden_size"] == 64 and a["data_parallel_size"] == 1
+    assert run_distributed(_ootb, 2, d, "OOTB_OPTIMIZER_PARSE_MODEL") == [[], []]
+    p0 = json.load(open(os.path.join(d, "model_params_pp0.json")))
+    p1 = json.load(open(os.path.join(d, "model_params_pp1.json")))
+    n0, n1 = {r["name"] for r in p0["parameters"]}, {r["name"] for r in p1["parameters"]}
+    assert "embedding.word_embeddings.weight" in n0 and "output_layer.weight" in n1 and "output_layer.weight" not in n0
+    qkv = next(r for r in p0["parameters"] if r["name"].endswith("linear_qkv.weight"))
+    assert qkv["tensor_parallel"] and qkv["partition_dim"] == 0 and qkv["numel"] == qkv["shape"][0] * qkv["shape"][1]
+    assert p0["total_numel"] == sum(r["numel"] for r in p0["parameters"])
