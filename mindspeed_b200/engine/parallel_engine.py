@@ -61,9 +61,13 @@ class MindSpeedParallelEngine(nn.Module):
                     if rank in sub:
                         self.ep_group = g
         self.stats = {}
-        if config.quantization == "fp8-block":
-            from ..models.te_compat import quantize_linears
-            self.stats["quantized"] = quantize_linears(model, recipe="blockwise")
+        if config.quantization is not None:
+            from .quantization import convert_linears
+            self.stats["quantized"] = convert_linears(model, config.quantization)
+        if config.memory_plan.swap_activation_modules:
+            from .memory import swap_activations
+            self.stats["swap_activation"] = swap_activations(model, config.memory_plan.swap_activation_modules,
+                                                             config.memory_plan.swap_min_bytes)
         self.stats["tp_modules"] = apply_tp_plan(model, config.tp_plan.rules, self.tp_group, config.tp_plan.sequence_parallel) \
             if tp > 1 else 0
         self.stats["ep_blocks"] = shard_experts(model, config.ep_plan.moe_modules, self.ep_group) \
@@ -134,6 +138,14 @@ class MindSpeedParallelEngine(nn.Module):
             if self.expert_fsdp is not None:
                 self.expert_fsdp.finish_grad_sync()
             self.model.finish_grad_sync()
+
+    def wrap_optimizer(self, optimizer):
+        """Apply the memory plan to an optimizer built over ``optimizer_params()``: with ``swap_optimizer`` its state is kept
+        in pinned host memory between steps."""
+        if self.config.memory_plan.swap_optimizer:
+            from .memory import HostStateOptimizer
+            return HostStateOptimizer(optimizer, self.config.memory_plan.swap_optimizer_chunk_bytes)
+        return optimizer
 
     def post_step(self):
         if self.sharded:

@@ -114,11 +114,24 @@ class BlockwiseScaling(Recipe):
 
 @dataclasses.dataclass
 class MXFP8Scaling(Recipe):
+    """Micro-scaling fp8: blocks of 32 elements ALONG THE CONTRACTION AXIS of the GEMM that consumes the tensor share one
+    power-of-two (e8m0) scale.  The three GEMMs of a linear contract over different axes - forward over the input features,
+    the data gradient over the output features, the weight gradient over the tokens - so every operand is quantised twice,
+    once per axis it is contracted over (``axis_aware``; reference: the dual-axis quantisation of
+    mindspeed/te/pytorch/fp8/recipes/mxfp8_scaling_recipe.py:68-132).  An axis whose length is not a multiple of 32 is
+    zero-padded for the quantisation."""
     name = "mxfp8"
+    axis_aware = True
 
-    def round_trip(self, t, key, state=None):
-        q, e = Q.quant_mx(t, axis=-1, dtype=self.dtype_for(key))
-        return Q.dequant_mx(q, e, axis=-1).to(t.dtype)
+    def round_trip(self, t, key, state=None, axis: int = -1):
+        n = t.shape[axis]
+        pad = -n % 32
+        if pad:
+            t2 = torch.nn.functional.pad(t.movedim(axis, -1), (0, pad))
+            q, e = Q.quant_mx(t2, axis=-1, dtype=self.dtype_for(key))
+            return Q.dequant_mx(q, e, axis=-1)[..., :n].movedim(-1, axis).to(t.dtype)
+        q, e = Q.quant_mx(t, axis=axis, dtype=self.dtype_for(key))
+        return Q.dequant_mx(q, e, axis=axis).to(t.dtype)
 
 
 RECIPES = {"delayed": DelayedScaling, "tensorwise": TensorwiseScaling, "blockwise": BlockwiseScaling, "mxfp8": MXFP8Scaling,
@@ -166,14 +179,27 @@ class _FakeQuantLinearFn(torch.autograd.Function):
     def forward(ctx, x, w, recipe, state):
         xq = recipe.round_trip(x, "inputs", state)
         wq = recipe.round_trip(w, "weight", state)
-        ctx.save_for_backward(xq, wq)
         ctx.recipe, ctx.state = recipe, state
+        if getattr(recipe, "axis_aware", False):
+            ctx.save_for_backward(x, w)                 # backward re-quantises along the axes its GEMMs contract over
+        else:
+            ctx.save_for_backward(xq, wq)
         return torch.matmul(xq, wq.t())
 
     @staticmethod
     def backward(ctx, dy):
+        r, st = ctx.recipe, ctx.state
+        if getattr(r, "axis_aware", False):
+            x, w = ctx.saved_tensors
+            dx = dw = None
+            if ctx.needs_input_grad[0]:                 # dx = dy @ w: contraction over the output features
+                dx = torch.matmul(r.round_trip(dy, "grads", st, axis=-1), r.round_trip(w, "weight", st, axis=0))
+            if ctx.needs_input_grad[1]:                 # dw = dy^T @ x: contraction over the tokens
+                d2, x2 = dy.reshape(-1, dy.shape[-1]), x.reshape(-1, x.shape[-1])
+                dw = torch.matmul(r.round_trip(d2, "grads", st, axis=0).t(), r.round_trip(x2, "inputs", st, axis=0))
+            return dx, dw, None, None
         xq, wq = ctx.saved_tensors
-        dq = ctx.recipe.round_trip(dy, "grads", ctx.state)
+        dq = r.round_trip(dy, "grads", st)
         dx = torch.matmul(dq, wq) if ctx.needs_input_grad[0] else None
         dw = torch.matmul(dq.reshape(-1, dq.shape[-1]).t(), xq.reshape(-1, xq.shape[-1])) if ctx.needs_input_grad[1] else None
         return dx, dw, None, None

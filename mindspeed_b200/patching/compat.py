@@ -184,6 +184,17 @@ def optional_dependency_stubs() -> List[tuple]:
 
     class _Format:
         E4M3, HYBRID = "e4m3", "hybrid"
+
+    class TELinear(TE.Fp8Linear):
+        """``transformer_engine.pytorch.Linear(in_features, out_features, bias=True)``: fp8 under ``fp8_autocast``."""
+
+        def __init__(self, in_features, out_features, bias=True, params_dtype=None, device=None, **_):
+            super().__init__(torch.nn.Linear(in_features, out_features, bias=bias, device=device, dtype=params_dtype), None)
+
+        def forward(self, x):
+            if not TE.fp8_enabled():
+                return torch.nn.functional.linear(x, self.weight, self.bias)
+            return super().forward(x)
     return [
         ("amp_C.multi_tensor_l2norm", multi_tensor_l2norm),
         ("amp_C.multi_tensor_scale", multi_tensor_scale),
@@ -196,7 +207,7 @@ def optional_dependency_stubs() -> List[tuple]:
         ("apex.normalization.FusedRMSNorm", FusedRMSNorm),
         ("apex.normalization.MixedFusedRMSNorm", FusedRMSNorm),
         ("fused_layer_norm_cuda.available", True),
-        ("transformer_engine.pytorch.Linear", TE.Fp8Linear),
+        ("transformer_engine.pytorch.Linear", TELinear),
         ("transformer_engine.pytorch.LayerNorm", FusedLayerNorm),
         ("transformer_engine.pytorch.RMSNorm", FusedRMSNorm),
         ("transformer_engine.pytorch.LayerNormLinear", TE.TELayerNormColumnParallelLinear),

@@ -166,3 +166,113 @@ def test_chunked_loss_matches_dense():
         g2h, g2w = torch.autograd.grad(out * 2.0, (h, w))
         assert torch.allclose(out, ref, atol=1e-5)
         assert torch.allclose(g2h, 2 * gh, atol=1e-5) and torch.allclose(g2w, 2 * gw, atol=1e-5)
+
+
+def test_mxfp8_linear_quantises_every_operand_along_the_axis_its_gemm_contracts_over():
+    from mindspeed_b200.engine.quantization import MXFP8GroupedLinear, MXFP8Linear
+    from mindspeed_b200.ops import quant as Q
+    torch.manual_seed(0)
+    rt = lambda t, axis, dt=torch.float8_e4m3fn: Q.dequant_mx(*Q.quant_mx(t, axis=axis, dtype=dt), axis=axis)
+    lin = MXFP8Linear(64, 96, bias=True)
+    x = torch.randn(32, 64, requires_grad=True)
+    y = lin(x)
+    assert torch.allclose(y, rt(x.detach(), 1) @ rt(lin.weight.detach(), 1).t() + lin.bias, atol=1e-5)
+    dy = torch.randn(32, 96)
+    y.backward(dy)
+    e5 = torch.float8_e5m2                                         # "hybrid": gradients in e5m2
+    assert torch.allclose(x.grad, rt(dy, 1, e5) @ rt(lin.weight.detach(), 0), atol=1e-5)          # contraction over out features
+    assert torch.allclose(lin.weight.grad, rt(dy, 0, e5).t() @ rt(x.detach(), 0), atol=1e-4)      # contraction over tokens
+    # close to the exact linear, not equal to it
+    exact = torch.nn.functional.linear(x.detach(), lin.weight.detach(), lin.bias)
+    err = (y.detach() - exact).norm() / exact.norm()
+    assert 1e-4 < float(err) < 0.08
+    # a token count that is not a multiple of 32 is padded for the weight-gradient quantisation
+    x2 = torch.randn(20, 64, requires_grad=True)
+    lin(x2).sum().backward()
+    assert torch.isfinite(x2.grad).all()
+    # grouped: every expert is the single linear on its rows
+    g = MXFP8GroupedLinear(3, 64, 32)
+    xs = torch.randn(40, 64)
+    out = g(xs, [10, 0, 30])
+    one = MXFP8Linear(64, 32, bias=False)
+    with torch.no_grad():
+        one.weight.copy_(g.weight[2])
+    assert out.shape == (40, 32) and torch.allclose(out[10:], one(xs[10:]), atol=1e-6)
+    with pytest.raises(ValueError):
+        g(xs, [10, 10, 10])
+
+
+def test_quantisation_plan_selects_linears_by_pattern():
+    from mindspeed_b200.engine import MindSpeedParallelEngine, ParallelEngineConfig, QuantizeConfig
+    from mindspeed_b200.models.te_compat import Fp8Linear, MXFP8Scaling
+    torch.manual_seed(0)
+    model = TinyLM()
+    cfg = ParallelEngineConfig(quantization=QuantizeConfig(recipe_name="mxfp8", apply_modules=["layers.*.moe.**", "layers.*.up"],
+                                                           ignored_modules=["**.down", "**gate"]))
+    eng = MindSpeedParallelEngine(cfg, model)
+    kinds = {n: type(m).__name__ for n, m in model.named_modules() if isinstance(m, torch.nn.Linear)}
+    assert eng.stats["quantized"] == sum(v == "Fp8Linear" for v in kinds.values()) > 0
+    assert all((v == "Fp8Linear") == n.endswith(".up") for n, v in kinds.items()), kinds
+    q = next(m for m in model.modules() if isinstance(m, Fp8Linear))
+    assert isinstance(q.recipe, MXFP8Scaling)
+    assert ParallelEngineConfig(quantization="fp8-block").validate(1).quantization.recipe().name == "blockwise"
+    with pytest.raises(ValueError):
+        ParallelEngineConfig(quantization="int3").validate(1)
+
+
+def test_memory_plan_parks_activations_and_optimizer_state():
+    from mindspeed_b200.engine.memory import HostStateOptimizer, swap_activations
+    torch.manual_seed(0)
+    model = TinyLM()
+    seen = {"enter": 0}
+
+    class Ctx:
+        def __enter__(self):
+            seen["enter"] += 1
+
+        def __exit__(self, *a):
+            return False
+    n = swap_activations(model, ["layers.*"], context=Ctx)
+    assert n == len(model.layers) and swap_activations(model, ["layers.*"], context=Ctx) == 0       # wrapped once
+    ids = torch.randint(0, V, (2, 5))
+    h = model(ids)
+    assert seen["enter"] == n
+    with torch.no_grad():
+        model(ids)
+    assert seen["enter"] == n                                       # nothing is saved without a graph
+
+    # optimizer state on the "host" between steps: same trajectory as the plain optimizer
+    a, b = TinyLM(), TinyLM()
+    b.load_state_dict(a.state_dict())
+    ref = torch.optim.AdamW(a.parameters(), lr=1e-2, weight_decay=0.1)
+    moved = {"out": 0, "back": 0}
+
+    class Host:                                                    # stand-in for pinned memory
+        def __init__(self, t):
+            self.t = t.clone()
+
+    def to_host(t):
+        moved["out"] += 1
+        box = t.clone()
+        box._parked = True
+        return box
+
+    def to_device(hst, like):
+        moved["back"] += 1
+        assert getattr(hst, "_parked", False)
+        return hst.clone()
+    opt = HostStateOptimizer(torch.optim.AdamW(b.parameters(), lr=1e-2, weight_decay=0.1), chunk_bytes=40_000,
+                             to_host=to_host, to_device=to_device)
+    for step in range(3):
+        for m, o in ((a, ref), (b, opt)):
+            o.zero_grad()
+            m(ids).pow(2).mean().backward()
+            o.step()
+    for p, q in zip(a.parameters(), b.parameters()):
+        assert torch.allclose(p, q, atol=1e-7)
+    n_state = sum(1 for st in opt.opt.state.values() for v in st.values() if torch.is_tensor(v) and v.numel() > 1)
+    assert moved["out"] == 3 * n_state and moved["back"] == 2 * n_state and opt.moved_bytes > 0
+    assert all(getattr(v, "_on_host", False) for st in opt.opt.state.values() for v in st.values() if torch.is_tensor(v) and v.numel() > 1)
+    assert len(list(opt._slices())) > 1                            # the state visits the device in several slices
+    opt.zero_grad()
+    assert len(list(opt._slices())) == 0                           # no gradients pending -> nothing to step
