@@ -84,3 +84,40 @@ def test_async_save_resume_matches_uninterrupted_run():
         run_distributed(_run, 2, 2, 2, d, None, ["--async-save"])
         second = run_distributed(_run, 2, 2, 4, None, d)[0]
         assert second == pytest.approx(full[2:], abs=1e-5)
+
+
+def _load_foreign(rank, world, tp, load):
+    """Build the model under ``tp`` ranks, read a checkpoint some other writer produced, return the loss of one step."""
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import pretrain_gpt as pg
+    from mindspeed_b200.training import pretrain
+    extra = ["--tensor-model-parallel-size", str(tp), "--train-iters", "1", "--load", load, "--finetune", "--lr", "0.0"]
+    hist = pretrain(pg.train_valid_test_datasets_provider, pg.model_provider, forward_step_func=pg.forward_step,
+                    args_list=ARGS + extra)
+    return hist[0]["lm loss"]
+
+
+def test_checkpoint_written_by_plain_torch_dcp_with_megatron_key_names_loads():
+    """A directory produced by nothing but ``torch.distributed.checkpoint.save`` over a {Megatron key: full tensor} dict -
+    what a Megatron-core ``torch_dist`` writer stores for a model without tensor parallelism - is read under tensor
+    parallelism 1 and 2: the loss equals the one of the model whose weights were written."""
+    import torch.distributed.checkpoint as dcp
+    from torch.distributed.checkpoint import FileSystemReader, FileSystemWriter
+    with tempfile.TemporaryDirectory() as own, tempfile.TemporaryDirectory() as foreign:
+        run_distributed(_run, 1, 1, 2, own, None)                               # train two steps, save in this framework
+        src = os.path.join(own, "iter_0000002")
+        md = FileSystemReader(src).read_metadata().state_dict_metadata
+        weights = {k: torch.empty(tuple(v.size), dtype=v.properties.dtype) for k, v in md.items()
+                   if not k.startswith("optimizer.") and hasattr(v, "size")}
+        dcp.load(weights, storage_reader=FileSystemReader(src), no_dist=True)   # full tensors under Megatron names
+        assert "decoder.layers.mlp.linear_fc1.weight" in weights and weights["decoder.layers.mlp.linear_fc1.weight"].dim() == 3
+        dst = os.path.join(foreign, "iter_0000007")
+        os.makedirs(dst)
+        dcp.save(weights, storage_writer=FileSystemWriter(dst), no_dist=True)   # the foreign writer: stock DCP only
+        with open(os.path.join(foreign, "latest_checkpointed_iteration.txt"), "w") as f:
+            f.write("7")
+        ref = run_distributed(_load_foreign, 1, 1, own)[0]
+        for tp in (1, 2):
+            got = run_distributed(_load_foreign, tp, tp, foreign)[0]
+            assert got == pytest.approx(ref, abs=2e-5), (tp, ref, got)
+        assert ref != pytest.approx(run_distributed(_run, 1, 1, 1, None, None)[0][0], abs=1e-4)   # not the initial weights
