@@ -188,7 +188,7 @@ def test_flags_validate():
 
 
 MLA = ["--multi-head-latent-attention", "--qk-layernorm", "--q-lora-rank", "32", "--kv-lora-rank", "24", "--qk-nope-head-dim", "16",
-       "--qk-rope-head-dim", "8", "--v-head-dim", "16", "--train-iters", "6", "--global-batch-size", "4", "--lr", "3e-3"]
+       "--qk-rope-head-dim", "8", "--v-head-dim", "16", "--train-iters", "3", "--global-batch-size", "4", "--lr", "3e-3"]
 DSA = ["--experimental-attention-variant", "dsa", "--dsa-indexer-n-heads", "2", "--dsa-indexer-head-dim", "16",
        "--dsa-indexer-topk", "8"]
 
