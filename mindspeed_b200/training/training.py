@@ -201,7 +201,16 @@ def build_memory_managers(args, model):
     out = []
     budget_mb = getattr(args, "adaptive_recompute_device_size", -1)
     dev_swap = bool(getattr(args, "adaptive_recompute_device_swap", False))
-    if ((budget_mb and budget_mb > 0) or dev_swap) and not getattr(args, "smart_swap", False):
+    if getattr(args, "adaptive_memory_optimization", False) and not getattr(args, "smart_swap", False):
+        # recompute / host swap / keep chosen per module from a profile (memory/adaptive_memory.py)
+        from ..memory.adaptive_memory import AdaptiveMemory
+        pp = ps.get_pipeline_model_parallel_world_size()
+        in_flight = 1 if pp <= 1 else min(pp - ps.get_pipeline_model_parallel_rank(), get_num_microbatches())
+        for m in model:
+            out.append(AdaptiveMemory(m, profiling_steps=getattr(args, "adaptive_recompute_profiling_step", 10),
+                                      device_budget_bytes=(budget_mb << 20) if budget_mb and budget_mb > 0 else None,
+                                      in_flight=in_flight))
+    elif ((budget_mb and budget_mb > 0) or dev_swap) and not getattr(args, "smart_swap", False):
         from ..memory.adaptive_recompute import AdaptiveRecompute
         for m in model:
             out.append(AdaptiveRecompute(m, profiling_steps=getattr(args, "adaptive_recompute_profiling_step", 10),

@@ -141,6 +141,67 @@ def test_adaptive_recompute_parks_activations_on_the_host_while_profiling():
     assert all(torch.allclose(a.grad, b, atol=1e-6) for a, b in zip(net.parameters(), gref))
 
 
+def test_adaptive_memory_chooses_between_recompute_and_host_swap():
+    from mindspeed_b200.memory import adaptive_memory as AM
+    MP = AR.ModuleProfile
+    MB = 1 << 20
+    layers = [MP(f"l{i}", forward_time=0.010, saved_bytes=400 * MB, input_bytes=40 * MB) for i in range(4)]
+    fast, slow = AM.HostLink(bytes_per_s=60e9, latency_s=2e-5), AM.HostLink(bytes_per_s=2e9, latency_s=2e-5)
+    # a fast link hides the copies behind the layer's own compute: swapping is (nearly) free and frees more than recompute
+    pol = AM.solve_memory_policy(layers, 700 * MB, fast)
+    assert sorted(pol.values()) == ["swap", "swap"]
+    # a slow link exposes 2 * (0.2 s - 0.01 s) per layer: one more forward (10 ms) is cheaper
+    pol = AM.solve_memory_policy(layers, 700 * MB, slow)
+    assert sorted(pol.values()) == ["recompute", "recompute"]
+    assert AM.solve_memory_policy(layers, 700 * MB, fast, allow_swap=False) == pol
+    assert AM.solve_memory_policy(layers, 0, fast) == {}
+    # activations of several micro-batches in flight on a pipeline stage: one layer's action frees in_flight times as much
+    assert len(AM.solve_memory_policy(layers, 700 * MB, fast, in_flight=2)) == 1
+    # children are an alternative to the whole layer: only the attention part is cheap to swap here
+    tree = [MP("l0", 0.010, 400 * MB, 40 * MB), MP("l0.attn", 0.008, 100 * MB, 40 * MB, parent="l0"),
+            MP("l0.mlp", 0.002, 300 * MB, 40 * MB, parent="l0")]
+    mid = AM.HostLink(bytes_per_s=20e9, latency_s=2e-5)            # attn: 5 ms copy < 8 ms compute; mlp: 15 ms copy > 2 ms
+    assert AM.solve_memory_policy(tree, 90 * MB, mid) == {"l0.attn": "swap"}
+    assert AM.solve_memory_policy(tree, 250 * MB, mid) == {"l0.mlp": "recompute"}
+    # unreachable target: everything that frees the most
+    assert set(AM.solve_memory_policy(layers, 10_000 * MB, slow).values()) == {"swap"}
+
+
+def test_adaptive_memory_end_to_end_applies_both_wrappers():
+    from mindspeed_b200.memory import adaptive_memory as AM
+    net = _net(3)
+    x = torch.randn(128, 64, requires_grad=True)
+    parked = {"n": 0}
+
+    class Ctx:
+        def __enter__(self):
+            parked["n"] += 1
+
+        def __exit__(self, *a):
+            return False
+    # layer "0" gets a huge compute time through a fast fake link -> swap; the link is slow for the rest -> recompute
+    am = AM.AdaptiveMemory(net, candidates=["0", "1", "2"], profiling_steps=1, device_budget_bytes=1, allow_swap=True,
+                           link=AM.HostLink(bytes_per_s=1e6, latency_s=0.0), swap_context=Ctx, granularity=1024)
+    with am.step_context():
+        loss = net(x).pow(2).sum()
+    loss.backward()
+    gref = [p.grad.clone() for p in net.parameters()]
+    net.zero_grad()
+    am.profiles["0"].forward_time = 10.0                           # its copies hide completely
+    pr = am.profiles
+    total = sum(p.saved_bytes for p in pr.values())
+    # what must go: all of layer 0 (only a swap frees that much) and the recomputable part of the other two
+    am.budget = total - (pr["0"].saved_bytes + sum(pr[n].saved_bytes - pr[n].input_bytes for n in ("1", "2"))) + 1024
+    am.end_step(static_bytes=0)
+    assert am.policy["0"] == "swap" and isinstance(getattr(net, "0"), AM._Swap)
+    assert all(am.policy[n] == "recompute" and isinstance(getattr(net, n), AR._Ckpt) for n in ("1", "2"))
+    with am.step_context():
+        loss2 = net(x).pow(2).sum()
+    loss2.backward()
+    assert parked["n"] == 1 and torch.allclose(loss, loss2)
+    assert all(torch.allclose(a.grad, b, atol=1e-6) for a, b in zip(net.parameters(), gref))
+
+
 def test_auto_pipeline_balances_time_under_memory():
     LP = AP.LayerProfile
     layers = [LP(1.0, 2.0, 100, 10, 50) for _ in range(8)]

@@ -13,6 +13,7 @@ from test_pipeline_cpu import _train  # noqa: E402
 @pytest.mark.parametrize("extra,exact", [
     (["--adaptive-recompute-device-size", "1", "--adaptive-recompute-profiling-step", "1"], True),
     (["--adaptive-recompute-device-swap", "--adaptive-recompute-device-size", "1", "--adaptive-recompute-profiling-step", "2"], True),
+    (["--adaptive-memory-optimization", "--adaptive-recompute-device-size", "1", "--adaptive-recompute-profiling-step", "1"], True),
     (["--smart-swap"], True),
     (["--qat-scheme", "w8a16"], False),
 ])
