@@ -42,6 +42,7 @@ NO_EFFECT: Dict[str, str] = {
     "shape-order": "layout hint for the vendor attention op; the kernels here read strided [s, b, n, d] directly",
     "enable-token-rearrange-opt": "the DeepSpeed-style MoE here always dispatches through index arithmetic on the one-hot routing; there is no slower einsum path to switch from",
     "skip-bias-add": "every parallel linear here returns its bias separately when the caller fuses the add; there is no switch",
+    "use-fused-ring-attention-update": "ring attention carries log-sum-exp values and merges partial results inside its own autograd function; the max / sum form of the update is the stand-alone op ops/misc.ring_attention_update",
     "adaptive-cp-only-reschedule": "adaptive CP here always keeps the sequence order and only schedules the exchanges",
     "adaptive-cp-without-coarse": "the mask is coarsened to context-parallel rank granularity for scheduling only; nothing else uses the coarse form",
     "gemm-gradient-accumulation-fusion": "weight gradients always accumulate into main_grad inside the GEMM epilogue",

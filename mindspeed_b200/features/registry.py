@@ -46,7 +46,7 @@ class MegatronBasicFeature(Feature):
     def post_validate_args(self, args):
         if args.optimization_level >= 1:
             for k in ("use_fused_rmsnorm", "use_fused_swiglu", "use_fused_rotary_pos_emb",
-                      "use_fused_moe_token_permute_and_unpermute", "use_fused_ring_attention_update"):
+                      "use_fused_moe_token_permute_and_unpermute"):
                 setattr(args, k, True)
 
 
