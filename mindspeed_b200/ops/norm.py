@@ -117,3 +117,54 @@ def rms_norm(x, weight, eps=1e-5, zero_centered=False, fused=True):
     if fused and x.is_cuda and loader.use_kernels(x) and weight.dtype == x.dtype:
         return _RMSNormFn.apply(x, weight, eps, zero_centered)
     return rms_norm_ref(x, weight, eps, zero_centered)
+
+
+def dropout_add_norm(x0, residual, weight, bias, dropout_p, epsilon, rowscale=None, layerscale=None, prenorm=False,
+                     residual_in_fp32=False, return_dropout_mask=False, is_rms_norm=False, training=True):
+    """out = norm(dropout(x0 * rowscale * layerscale) + residual) * weight (+ bias).
+
+    ``rowscale`` [batch, seq] scales whole token rows (stochastic depth), ``layerscale`` [hidden] scales channels, both
+    before the dropout; ``prenorm`` also returns the un-normalised sum (the next residual stream, in fp32 when
+    ``residual_in_fp32``); ``return_dropout_mask`` appends the keep mask.  Without dropout and scales the RMSNorm form on a
+    GPU is the one-pass add + norm kernel (``add_rms_norm``); every other combination is composed from PyTorch ops.
+    reference: mindspeed/ops/dropout_add_layer_norm.py:8-76, mindspeed/ops/dropout_add_rms_norm.py (same arguments;
+    mindspeed/ops/csrc/cann/npu_dropout_add_layer_norm.cpp)."""
+    h = x0
+    if rowscale is not None:
+        h = h * rowscale.reshape(*x0.shape[:-1], 1).to(h.dtype)
+    if layerscale is not None:
+        h = h * layerscale.reshape(*([1] * (x0.dim() - 1)), -1).to(h.dtype)
+    mask = None
+    p = float(dropout_p) if training else 0.0
+    if p > 0.0:
+        mask = torch.rand_like(h, dtype=torch.float32) >= p
+        h = h * mask.to(h.dtype) / (1.0 - p)
+    plain = p == 0.0 and rowscale is None and layerscale is None
+    if (plain and is_rms_norm and residual is not None and bias is None and h.is_cuda and not residual_in_fp32
+            and h.dtype == residual.dtype and loader.lib() is not None):
+        pre, out = add_rms_norm(h, residual, weight, epsilon)
+    else:
+        pre = h if residual is None else (h.float() + residual.float() if residual_in_fp32 else h + residual.to(h.dtype))
+        if is_rms_norm:
+            out = rms_norm_ref(pre.to(x0.dtype), weight, epsilon)
+        else:
+            out = torch.nn.functional.layer_norm(pre.to(x0.dtype), (x0.shape[-1],), weight, None, epsilon)
+        if bias is not None:
+            out = out + bias
+    ret = (out, pre) if prenorm else (out,)
+    if return_dropout_mask:
+        ret = ret + (mask if mask is not None else torch.ones_like(x0, dtype=torch.bool),)
+    return ret[0] if len(ret) == 1 else ret
+
+
+def dropout_add_layer_norm(x0, residual, weight, bias, dropout_p, epsilon, rowscale=None, layerscale=None, prenorm=False,
+                           residual_in_fp32=False, return_dropout_mask=False, training=True):
+    return dropout_add_norm(x0, residual, weight, bias, dropout_p, epsilon, rowscale, layerscale, prenorm, residual_in_fp32,
+                            return_dropout_mask, False, training)
+
+
+def dropout_add_rms_norm(x0, residual, weight, bias, dropout_p, epsilon, rowscale=None, layerscale=None, prenorm=False,
+                         residual_in_fp32=False, return_dropout_mask=False, training=True):
+    return dropout_add_norm(x0, residual, weight, bias, dropout_p, epsilon, rowscale, layerscale, prenorm, residual_in_fp32,
+                            return_dropout_mask, True, training)
+

@@ -53,3 +53,32 @@ def test_quantised_grouped_gemms():
     ref = torch.cat(outs) * tok.unsqueeze(1)
     got = quant_grouped_gemm(qx, q, scale, tok, torch.tensor(counts), out_dtype=torch.float32)
     torch.testing.assert_close(got, ref, rtol=1e-5, atol=1e-5)
+
+
+def test_dropout_add_norm_ops():
+    import torch
+    from mindspeed_b200.ops.norm import dropout_add_layer_norm, dropout_add_rms_norm
+    g = torch.Generator().manual_seed(0)
+    B, S, H = 2, 5, 16
+    x0, res = torch.randn(B, S, H, generator=g), torch.randn(B, S, H, generator=g)
+    w, b = torch.randn(H, generator=g), torch.randn(H, generator=g)
+    rows, chans = torch.rand(B, S, generator=g), torch.rand(H, generator=g)
+    # the oracle of the reference's test: scales, residual add, then the norm
+    h = x0 * rows.view(B, S, 1) * chans.view(1, 1, H) + res
+    rms = h / torch.sqrt((h * h).sum(-1, keepdim=True) / H + 1e-5) * w
+    out, pre = dropout_add_rms_norm(x0, res, w, None, 0.0, 1e-5, rowscale=rows, layerscale=chans, prenorm=True)
+    assert torch.allclose(out, rms, atol=1e-5) and torch.allclose(pre, h, atol=1e-6)
+    ln = torch.nn.functional.layer_norm(x0 + res, (H,), w, b, 1e-5)
+    assert torch.allclose(dropout_add_layer_norm(x0, res, w, b, 0.0, 1e-5), ln, atol=1e-5)
+    assert torch.allclose(dropout_add_layer_norm(x0, None, w, b, 0.0, 1e-5), torch.nn.functional.layer_norm(x0, (H,), w, b, 1e-5), atol=1e-5)
+    # dropout: the returned mask reproduces the output; kept entries are scaled by 1 / (1 - p)
+    torch.manual_seed(3)
+    out, pre, mask = dropout_add_rms_norm(x0, res, w, None, 0.5, 1e-5, prenorm=True, return_dropout_mask=True, residual_in_fp32=True)
+    assert mask.dtype == torch.bool and 0.2 < float(mask.float().mean()) < 0.8 and pre.dtype == torch.float32
+    assert torch.allclose(pre, x0 * mask / 0.5 + res, atol=1e-6)
+    # evaluation mode: no dropout
+    assert torch.allclose(dropout_add_layer_norm(x0, res, w, b, 0.5, 1e-5, training=False), ln, atol=1e-5)
+    # differentiable
+    xg = x0.clone().requires_grad_(True)
+    dropout_add_rms_norm(xg, res, w, None, 0.0, 1e-5).sum().backward()
+    assert torch.isfinite(xg.grad).all() and xg.grad.abs().sum() > 0
