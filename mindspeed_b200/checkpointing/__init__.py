@@ -292,6 +292,11 @@ def load_checkpoint(model, optimizer, opt_param_scheduler, load_dir=None, args=N
     elif optimizer is not None and hasattr(optimizer, "reload_model_params"):
         optimizer.reload_model_params()
     if opt_param_scheduler is not None and "opt_param_scheduler" in common:
+        # the schedule's shape (peak, warm-up, decay length) comes from this launch's flags; the checkpoint supplies the step
+        # count, and with --use-checkpoint-opt_param-scheduler also the flags the schedule was saved with
+        if getattr(args, "use_checkpoint_opt_param_scheduler", False) and "schedule" in common["opt_param_scheduler"]:
+            for k, v in common["opt_param_scheduler"]["schedule"].items():
+                setattr(opt_param_scheduler, k, v)
         opt_param_scheduler.load_state_dict(common["opt_param_scheduler"])
     rank = dist.get_rank() if dist.is_initialized() else 0
     rp = os.path.join(path, f"rng_{rank}.pt")

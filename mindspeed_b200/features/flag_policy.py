@@ -43,6 +43,20 @@ NO_EFFECT: Dict[str, str] = {
     "enable-token-rearrange-opt": "the DeepSpeed-style MoE here always dispatches through index arithmetic on the one-hot routing; there is no slower einsum path to switch from",
     "skip-bias-add": "every parallel linear here returns its bias separately when the caller fuses the add; there is no switch",
     "use-fused-ring-attention-update": "ring attention carries log-sum-exp values and merges partial results inside its own autograd function; the max / sum form of the update is the stand-alone op ops/misc.ring_attention_update",
+    "use-legacy-models": "the core model classes are the only ones",
+    "spec": "layer specifications are chosen from the model flags (MLA, MoE, TE-compatible modules); there is no module-spec import",
+    "timing-log-level": "step time and throughput are always logged; there are no nested timers to select",
+    "timing-log-option": "step time and throughput are always logged; there are no nested timers to select",
+    "no-barrier-with-level-1-timing": "step time and throughput are always logged; there are no nested timers to select",
+    "no-bias-gelu-fusion": "bias + GeLU run unfused unless the optimisation level enables the fused activation kernels",
+    "no-rope-fusion": "the rotary kernel follows --optimization-level / --use-fused-rotary-pos-emb",
+    "auto-detect-ckpt-format": "one checkpoint format (torch.distributed.checkpoint) is read and written",
+    "dist-ckpt-format": "one checkpoint format (torch.distributed.checkpoint) is read and written",
+    "no-shared-storage": "every rank writes its own shard files and reads what it needs; no rank relies on another's local disk",
+    "short-seq-prob": "option of the BERT-style sample builder; GPT samples are packed to the full sequence length",
+    "img-h": "read by vision-language model definitions built on this package (parallel/multimodal), not by the GPT entry point",
+    "img-w": "read by vision-language model definitions built on this package (parallel/multimodal), not by the GPT entry point",
+    "patch-dim": "read by vision-language model definitions built on this package (parallel/multimodal), not by the GPT entry point",
     "adaptive-cp-only-reschedule": "adaptive CP here always keeps the sequence order and only schedules the exchanges",
     "adaptive-cp-without-coarse": "the mask is coarsened to context-parallel rank granularity for scheduling only; nothing else uses the coarse form",
     "gemm-gradient-accumulation-fusion": "weight gradients always accumulate into main_grad inside the GEMM epilogue",

@@ -494,13 +494,13 @@ class MLAFeature(Feature):
         add_arg(g, "--q-lora-rank", type=int, default=None)
         add_arg(g, "--kv-lora-rank", type=int, default=512)
         add_arg(g, "--v-head-dim", type=int, default=128)
-        add_arg(g, "--qk-rope-head-dim", type=int, default=64)
-        add_arg(g, "--qk-nope-head-dim", type=int, default=128)
+        add_arg(g, "--qk-rope-head-dim", "--qk-pos-emb-head-dim", dest="qk_rope_head_dim", type=int, default=64)
+        add_arg(g, "--qk-nope-head-dim", "--qk-head-dim", dest="qk_nope_head_dim", type=int, default=128)
         add_arg(g, "--rope-scaling-type", type=str, default=None, choices=[None, "yarn"])
-        add_arg(g, "--rope-scaling-factor", type=float, default=1.0)
+        add_arg(g, "--rope-scaling-factor", "--rotary-scaling-factor", dest="rope_scaling_factor", type=float, default=1.0)
         add_arg(g, "--rope-scaling-original-max-position-embeddings", type=int, default=4096)
-        add_arg(g, "--rope-scaling-beta-fast", type=int, default=32)
-        add_arg(g, "--rope-scaling-beta-slow", type=int, default=1)
+        add_arg(g, "--rope-scaling-beta-fast", "--beta-fast", dest="rope_scaling_beta_fast", type=int, default=32)
+        add_arg(g, "--rope-scaling-beta-slow", "--beta-slow", dest="rope_scaling_beta_slow", type=int, default=1)
         add_arg(g, "--rope-scaling-mscale", type=float, default=1.0)
         add_arg(g, "--rope-scaling-mscale-all-dim", type=float, default=0.0)
 

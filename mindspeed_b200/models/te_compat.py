@@ -142,7 +142,12 @@ def recipe_from_args(args) -> Optional[Recipe]:
     fmt = getattr(args, "fp8_format", None) or getattr(args, "fp8", None)
     if not fmt:
         return None
-    return RECIPES[getattr(args, "fp8_recipe", "delayed")](fp8_format="hybrid" if fmt == "hybrid" else "e4m3")
+    cls = RECIPES[getattr(args, "fp8_recipe", "delayed")]
+    kw = {}
+    if cls is DelayedScaling:                       # --fp8-amax-history-len / --fp8-amax-compute-algo / --fp8-margin
+        kw = dict(amax_history_len=int(getattr(args, "fp8_amax_history_len", 16) or 16),
+                  amax_compute_algo=getattr(args, "fp8_amax_compute_algo", "max") or "max", margin=int(getattr(args, "fp8_margin", 0) or 0))
+    return cls(fp8_format="hybrid" if fmt == "hybrid" else "e4m3", **kw)
 
 
 # ---- global fp8 state ------------------------------------------------------------------------------------------

@@ -53,7 +53,9 @@ class TopKRouter(nn.Module):
         return out
 
     def gating(self, x):
-        return torch.nn.functional.linear(x.float(), self.weight.float())
+        # --moe-router-dtype: the logits (and everything routing derives from them) in fp32 (default) or fp64
+        dt = torch.float64 if getattr(self.config, "moe_router_dtype", None) == "fp64" else torch.float32
+        return torch.nn.functional.linear(x.to(dt), self.weight.to(dt))
 
     def _aux(self, probs_for_loss, routing_map, tokens_per_expert, activation, seq_shape):
         cfg = self.config

@@ -151,6 +151,77 @@ class PretrainedFromHF(_Base):
         return self.tokenizer.eos_token_id
 
 
+class GPT2BPETokenizer(_Base):
+    """Byte-level BPE from a ``vocab.json`` (token -> id) and a ``merges.txt`` (one merge per line, highest priority first), the
+    file pair GPT-2 style models ship (``--tokenizer-type GPT2BPETokenizer --vocab-file ... --merge-file ...``).  Text is cut
+    into words by the GPT-2 pattern, every word's UTF-8 bytes are mapped to printable code points, and adjacent symbols are
+    merged in priority order.  The end-of-document token is ``<|endoftext|>``."""
+    name = "GPT2BPETokenizer"
+    PATTERN = r"""'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+"""
+
+    def __init__(self, vocab_file: str, merge_file: str):
+        import json
+        import regex
+        with open(vocab_file, encoding="utf-8") as f:
+            self.encoder = json.load(f)
+        self.decoder = {v: k for k, v in self.encoder.items()}
+        with open(merge_file, encoding="utf-8") as f:
+            lines = [l.rstrip("\n") for l in f if l.strip() and not l.startswith("#version")]
+        self.ranks = {tuple(l.split()): i for i, l in enumerate(lines)}
+        bs = list(range(ord("!"), ord("~") + 1)) + list(range(0xA1, 0xAD)) + list(range(0xAE, 0x100))
+        cs, n = bs[:], 0
+        for b in range(256):                       # bytes without a printable form get code points above 255
+            if b not in bs:
+                bs.append(b)
+                cs.append(256 + n)
+                n += 1
+        self.byte_enc = {b: chr(c) for b, c in zip(bs, cs)}
+        self.byte_dec = {c: b for b, c in self.byte_enc.items()}
+        self.pat = regex.compile(self.PATTERN)
+        self.cache: Dict[str, List[str]] = {}
+        if "<|endoftext|>" not in self.encoder:
+            raise ValueError("vocab file has no <|endoftext|> token")
+
+    def _bpe(self, word: str) -> List[str]:
+        if word in self.cache:
+            return self.cache[word]
+        sym = list(word)
+        while len(sym) > 1:
+            best = min(zip(sym, sym[1:]), key=lambda pr: self.ranks.get(pr, float("inf")))
+            if best not in self.ranks:
+                break
+            out, i = [], 0                         # merge every occurrence of the best-ranked pair, left to right
+            while i < len(sym):
+                if i + 1 < len(sym) and (sym[i], sym[i + 1]) == best:
+                    out.append(sym[i] + sym[i + 1])
+                    i += 2
+                else:
+                    out.append(sym[i])
+                    i += 1
+            sym = out
+        self.cache[word] = sym
+        return sym
+
+    def tokenize(self, text):
+        ids = []
+        for w in self.pat.findall(text):
+            mapped = "".join(self.byte_enc[b] for b in w.encode("utf-8"))
+            ids.extend(self.encoder[t] for t in self._bpe(mapped))
+        return ids
+
+    def detokenize(self, ids):
+        text = "".join(self.decoder[int(i)] for i in ids)
+        return bytearray(self.byte_dec[c] for c in text).decode("utf-8", errors="replace")
+
+    @property
+    def vocab_size(self):
+        return len(self.encoder)
+
+    @property
+    def eod(self):
+        return self.encoder["<|endoftext|>"]
+
+
 def build_tokenizer(args):
     """Build from ``--tokenizer-type`` and set ``args.padded_vocab_size`` when it is not fixed yet."""
     kind = getattr(args, "tokenizer_type", "NullTokenizer")
@@ -160,6 +231,10 @@ def build_tokenizer(args):
             raise ValueError("--tokenizer-name-or-path is required for PretrainedFromHF")
         tok = PretrainedFromHF(path, getattr(args, "vocab_extra_ids", 0), getattr(args, "seq_length", None),
                                not getattr(args, "tokenizer_not_use_fast", False))
+    elif kind == "GPT2BPETokenizer":
+        if not getattr(args, "vocab_file", None) or not getattr(args, "merge_file", None):
+            raise ValueError("GPT2BPETokenizer needs --vocab-file and --merge-file")
+        tok = GPT2BPETokenizer(args.vocab_file, args.merge_file)
     elif kind == "ByteLevelTokenizer":
         tok = ByteLevelTokenizer()
     elif kind == "NullTokenizer":

@@ -61,6 +61,9 @@ def _core_args(p: argparse.ArgumentParser):
     g = p.add_argument_group("moe")
     g.add_argument("--num-experts", type=int, default=None)
     g.add_argument("--moe-router-topk", type=int, default=2)
+    g.add_argument("--moe-router-dtype", type=str, default=None, choices=[None, "fp32", "fp64"],
+                   help="precision of the router's logits, softmax and top-k (fp32 when unset)")
+    g.add_argument("--seq-aux", action="store_true", help="the same as --moe-router-load-balancing-type seq_aux_loss")
     g.add_argument("--moe-router-load-balancing-type", type=str, default="aux_loss",
                    choices=["aux_loss", "seq_aux_loss", "sinkhorn", "none"])
     g.add_argument("--moe-router-score-function", type=str, default="softmax", choices=["softmax", "sigmoid"])
@@ -155,6 +158,34 @@ def _core_args(p: argparse.ArgumentParser):
     g.add_argument("--no-bias-dropout-fusion", action="store_false", dest="bias_dropout_fusion")
     g.add_argument("--no-bias-swiglu-fusion", action="store_false", dest="bias_swiglu_fusion")
     g.add_argument("--yaml-cfg", type=str, default=None)
+    # --- further Megatron training flags that launch scripts of the reference pass ---
+    g.add_argument("--train-samples", type=int, default=None, help="length of training in samples (instead of --train-iters)")
+    g.add_argument("--skip-train", action="store_true", help="build, load and evaluate / save without training steps")
+    g.add_argument("--start-weight-decay", type=float, default=None)
+    g.add_argument("--end-weight-decay", type=float, default=None)
+    g.add_argument("--weight-decay-incr-style", type=str, default="constant", choices=["constant", "linear", "cosine"])
+    g.add_argument("--log-num-zeros-in-grad", action="store_true")
+    g.add_argument("--log-params-norm", action="store_true")
+    g.add_argument("--manual-gc", action="store_true", help="collect garbage only every --manual-gc-interval steps, on all ranks at once")
+    g.add_argument("--manual-gc-interval", type=int, default=0)
+    g.add_argument("--timing-log-level", type=int, default=0, choices=[0, 1, 2])
+    g.add_argument("--timing-log-option", type=str, default="minmax", choices=["max", "minmax", "all"])
+    g.add_argument("--no-barrier-with-level-1-timing", action="store_false", dest="barrier_with_L1_time")
+    g.add_argument("--no-bias-gelu-fusion", action="store_false", dest="bias_gelu_fusion")
+    g.add_argument("--no-rope-fusion", action="store_false", dest="apply_rope_fusion")
+    g.add_argument("--no-position-embedding", action="store_false", dest="add_position_embedding")
+    g.add_argument("--use-legacy-models", action="store_true")
+    g.add_argument("--spec", type=str, nargs="*", default=None)
+    g.add_argument("--use-torch-fsdp2", action="store_true", help="parameters sharded over data-parallel ranks (the --layerzero path)")
+    g.add_argument("--use-custom-fsdp", action="store_true", help="with --data-parallel-sharding-strategy: the --layerzero path")
+    g.add_argument("--data-parallel-sharding-strategy", type=str, default="no_shard",
+                   choices=["no_shard", "optim", "optim_grads", "optim_grads_params"])
+    g.add_argument("--fp8-amax-history-len", type=int, default=1024)
+    g.add_argument("--fp8-amax-compute-algo", type=str, default="max", choices=["max", "most_recent"])
+    g.add_argument("--short-seq-prob", type=float, default=0.1)
+    g.add_argument("--img-h", type=int, default=224)
+    g.add_argument("--img-w", type=int, default=224)
+    g.add_argument("--patch-dim", type=int, default=16)
 
     g = p.add_argument_group("data / checkpoint")
     g.add_argument("--data-path", nargs="*", default=None)
@@ -162,6 +193,15 @@ def _core_args(p: argparse.ArgumentParser):
     g.add_argument("--split", type=str, default="100,0,0")
     g.add_argument("--tokenizer-type", type=str, default="NullTokenizer")
     g.add_argument("--tokenizer-model", type=str, default=None)
+    g.add_argument("--vocab-file", type=str, default=None, help="GPT2BPETokenizer: vocab.json")
+    g.add_argument("--merge-file", type=str, default=None, help="GPT2BPETokenizer: merges.txt")
+    g.add_argument("--auto-detect-ckpt-format", action="store_true")
+    g.add_argument("--dist-ckpt-format", type=str, default="torch_dist", choices=["torch_dist"])
+    g.add_argument("--exit-on-missing-checkpoint", action="store_true",
+                   help="stop when --load is given and holds no checkpoint (instead of starting from scratch)")
+    g.add_argument("--use-checkpoint-opt_param-scheduler", "--use-checkpoint-opt-param-scheduler", action="store_true",
+                   dest="use_checkpoint_opt_param_scheduler", help="take the schedule's settings from the checkpoint")
+    g.add_argument("--no-shared-storage", action="store_false", dest="shared_storage")
     g.add_argument("--save", type=str, default=None)
     g.add_argument("--load", type=str, default=None)
     g.add_argument("--save-interval", type=int, default=None)
@@ -236,6 +276,28 @@ def _core_validate(args):
         raise AssertionError("--group-query-attention needs --num-query-groups")
     if args.use_rotary_position_embeddings:
         args.position_embedding_type = "rope"
+    if getattr(args, "seq_aux", False):
+        args.moe_router_load_balancing_type = "seq_aux_loss"
+    if not args.add_position_embedding and args.position_embedding_type == "learned_absolute":
+        args.position_embedding_type = "none"                     # --no-position-embedding
+    if args.train_samples is not None:
+        if args.train_iters is not None:
+            raise AssertionError("give --train-iters or --train-samples, not both")
+        args.train_iters = args.train_samples // args.global_batch_size
+    if args.start_weight_decay is None:
+        args.start_weight_decay = args.end_weight_decay = args.weight_decay
+    elif args.end_weight_decay is None:
+        raise AssertionError("--start-weight-decay needs --end-weight-decay")
+    elif args.weight_decay_incr_style == "constant" and args.start_weight_decay != args.end_weight_decay:
+        raise AssertionError("--weight-decay-incr-style constant needs equal start and end weight decay")
+    else:
+        args.weight_decay = args.start_weight_decay
+    if args.use_torch_fsdp2 or (args.use_custom_fsdp and args.data_parallel_sharding_strategy == "optim_grads_params"):
+        args.layerzero = True                                        # parameters, gradients and optimizer state sharded
+    elif args.use_custom_fsdp and args.data_parallel_sharding_strategy in ("optim", "optim_grads"):
+        args.use_distributed_optimizer = True                        # optimizer state (and reduce-scattered gradients) sharded
+    if args.manual_gc and args.manual_gc_interval < 0:
+        raise AssertionError("--manual-gc-interval must not be negative")
     args.params_dtype = torch.bfloat16 if args.bf16 else torch.float16 if args.fp16 else torch.float32
     if args.bf16:
         args.accumulate_allreduce_grads_in_fp32 = True

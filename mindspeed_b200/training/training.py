@@ -28,10 +28,20 @@ from .initialize import initialize_megatron
 class OptimizerParamScheduler:
     """Learning-rate schedule: warmup then constant / linear / cosine / inverse-sqrt decay."""
 
-    def __init__(self, optimizer, max_lr, min_lr, warmup_steps, decay_steps, style):
+    def __init__(self, optimizer, max_lr, min_lr, warmup_steps, decay_steps, style, start_wd=None, end_wd=None, wd_incr_steps=0,
+                 wd_incr_style="constant"):
         self.opt, self.max_lr, self.min_lr = optimizer, max_lr, min_lr
         self.warmup, self.decay, self.style, self.num_steps = warmup_steps, decay_steps, style, 0
+        # weight decay moves from start_wd to end_wd over wd_incr_steps (--start/--end-weight-decay, --weight-decay-incr-style)
+        self.start_wd, self.end_wd, self.wd_steps, self.wd_style = start_wd, end_wd, wd_incr_steps, wd_incr_style
         self.step(0)
+
+    def get_wd(self):
+        if self.start_wd is None or self.wd_style == "constant" or not self.wd_steps:
+            return self.end_wd
+        r = min(1.0, self.num_steps / self.wd_steps)
+        c = r if self.wd_style == "linear" else 0.5 * (math.cos(math.pi * (1.0 - r)) + 1.0)
+        return self.start_wd + c * (self.end_wd - self.start_wd)
 
     def get_lr(self):
         n = self.num_steps
@@ -55,11 +65,19 @@ class OptimizerParamScheduler:
     def step(self, increment=1):
         self.num_steps += increment
         lr = self.get_lr()
+        wd = self.get_wd()
+        scheduled = wd is not None and self.wd_style != "constant"
         for g in self.opt.param_groups:
             g["lr"] = lr
+            if scheduled and "weight_decay" in g:
+                # groups that were built without decay (biases, norm gains in torch-style optimizers) stay without
+                if g.setdefault("wd_scheduled", g["weight_decay"] != 0.0 or self.start_wd == 0.0 and len(self.opt.param_groups) == 1):
+                    g["weight_decay"] = wd
 
     def state_dict(self):
-        return {"num_steps": self.num_steps}
+        return {"num_steps": self.num_steps,
+                "schedule": {k: getattr(self, k) for k in ("max_lr", "min_lr", "warmup", "decay", "style", "start_wd", "end_wd",
+                                                           "wd_steps", "wd_style")}}
 
     def load_state_dict(self, sd):
         self.num_steps = sd["num_steps"]
@@ -159,7 +177,9 @@ def setup_model_and_optimizer(model_provider_func, no_wd_decay_cond=None, scale_
     warmup = args.lr_warmup_iters
     if getattr(args, "lr_warmup_fraction", None) is not None:
         warmup = int(args.lr_warmup_fraction * decay_iters)          # --lr-warmup-fraction overrides --lr-warmup-iters
-    sched = OptimizerParamScheduler(optimizer, args.lr, args.min_lr, warmup, decay_iters, args.lr_decay_style)
+    sched = OptimizerParamScheduler(optimizer, args.lr, args.min_lr, warmup, decay_iters, args.lr_decay_style,
+                                    start_wd=getattr(args, "start_weight_decay", None), end_wd=getattr(args, "end_weight_decay", None),
+                                    wd_incr_steps=args.train_iters or 0, wd_incr_style=getattr(args, "weight_decay_incr_style", "constant"))
     cfg = model[0].module.config
     cfg.finalize_model_grads_func = finalize_model_grads
     if args.swap_attention:
@@ -258,7 +278,15 @@ def _train_step_inner(forward_step_func, data_iterator, model, optimizer, opt_pa
         losses_reduced = fb(forward_step_func=forward_step_func, data_iterator=data_iterator, model=model,
                             num_microbatches=get_num_microbatches(), seq_length=args.seq_length,
                             micro_batch_size=args.micro_batch_size, decoder_seq_length=None, forward_only=False)
+    if getattr(args, "log_num_zeros_in_grad", False):
+        # exact zeros in the reduced gradients, counted before the step consumes them (--log-num-zeros-in-grad)
+        from ..patching.compat import count_zeros_fp32
+        params = [p for m in model for p in m.parameters() if p.requires_grad]
+        mpg = ps.get_model_parallel_group()
+        zeros = count_zeros_fp32(params, mpg if dist.is_initialized() and dist.get_world_size(mpg) > 1 else None)
     ok, grad_norm, num_zeros = optimizer.step()
+    if getattr(args, "log_num_zeros_in_grad", False):
+        num_zeros = zeros
     if getattr(args, "balanced_moe_experts", False):
         # the experts that were busiest in this step are replicated on every expert-parallel rank for the next one
         from ..parallel.moe.moe_layer import MoELayer
@@ -370,10 +398,39 @@ def check_kernel_status():
     G.check_status()
 
 
+def calc_params_l2_norm(model) -> float:
+    """L2 norm of all parameters of the job: tensor-parallel duplicates and shared embeddings counted once, summed over
+    the model-parallel group (and the expert-parallel ranks for expert weights)."""
+    dense = torch.zeros(1, dtype=torch.float32, device=next(model[0].parameters()).device)
+    expert = torch.zeros_like(dense)
+    tp_rank = ps.get_tensor_model_parallel_rank()
+    for chunk in model:
+        for p in chunk.parameters():
+            if getattr(p, "shared", False) or (not getattr(p, "tensor_model_parallel", False) and getattr(p, "allreduce", True) and tp_rank != 0):
+                continue
+            sq = p.detach().float().pow(2).sum()
+            if getattr(p, "allreduce", True):
+                dense += sq
+            else:
+                expert += sq
+    if dist.is_initialized():
+        mpg = ps.get_model_parallel_group()
+        if dist.get_world_size(mpg) > 1:
+            dist.all_reduce(dense, group=mpg)
+            dist.all_reduce(expert, group=mpg)
+        if ps.get_expert_model_parallel_world_size() > 1:
+            dist.all_reduce(expert, group=ps.get_expert_model_parallel_group())
+    return float((dense + expert).sqrt())
+
+
 def train(forward_step_func, model, optimizer, opt_param_scheduler, train_data_iterator, process_non_loss_data_func=None):
     args = get_args()
     for m in model:
         m.train()
+    if getattr(args, "manual_gc", False):
+        import gc
+        gc.disable()                         # collections happen only where the loop asks for them
+        gc.collect()
     iteration = args.iteration
     prof = None
     if args.profile and (args.profile_ranks == [-1] or args.rank in args.profile_ranks):
@@ -386,9 +443,12 @@ def train(forward_step_func, model, optimizer, opt_param_scheduler, train_data_i
     planners = {}
     while iteration < args.train_iters:
         t0 = time.time()
-        loss_dict, skipped, grad_norm, _ = train_step(forward_step_func, train_data_iterator, model, optimizer,
-                                                      opt_param_scheduler)
+        loss_dict, skipped, grad_norm, num_zeros = train_step(forward_step_func, train_data_iterator, model, optimizer,
+                                                              opt_param_scheduler)
         iteration += 1
+        if getattr(args, "manual_gc", False) and args.manual_gc_interval and iteration % args.manual_gc_interval == 0:
+            import gc
+            gc.collect()                     # every rank at the same step: no rank stalls the others at a random moment
         if torch.cuda.is_available() and next(model[0].parameters()).is_cuda:
             torch.cuda.synchronize()
         check_kernel_status()
@@ -396,6 +456,10 @@ def train(forward_step_func, model, optimizer, opt_param_scheduler, train_data_i
         if prof is not None:
             prof.step()
         if iteration % args.log_interval == 0:
+            if getattr(args, "log_num_zeros_in_grad", False) and num_zeros is not None:
+                loss_dict["num zeros"] = float(num_zeros)
+            if getattr(args, "log_params_norm", False):
+                loss_dict["params norm"] = calc_params_l2_norm(model)
             if args.num_experts and args.moe_aux_loss_coeff > 0 and getattr(args, "moe_model_type", "") != "deepspeed_moe":
                 # auxiliary losses the routers attached inside the model: mean over the MoE layers (and per layer with
                 # --moe-per-layer-logging), averaged over the micro-batches and steps since the last log line
@@ -521,7 +585,20 @@ def pretrain(train_valid_test_dataset_provider, model_provider, model_type=None,
             if found is not None:
                 args.iteration = load_fault_dump(model, optimizer if args.ttp_save_optimizer else None, found)
     train_iter = train_valid_test_dataset_provider(args)
-    history = train(forward_step_func, model, optimizer, sched, train_iter, process_non_loss_data_func)
+    if getattr(args, "exit_on_missing_checkpoint", False) and args.load and not args.iteration:
+        from ..checkpointing import read_latest_iteration
+        if read_latest_iteration(args.load) is None:
+            print_rank_0(f"--exit-on-missing-checkpoint: no checkpoint under {args.load}, exiting")
+            return []
+    if getattr(args, "skip_train", False):
+        # --skip-train: no training steps; evaluate if asked to, then fall through to the final save
+        history = []
+        if args.eval_iters:
+            ev = evaluate(forward_step_func, train_iter, model, args.eval_iters)
+            print_rank_last(" validation loss (no training): " + " | ".join(f"{k}: {v:.6E}" for k, v in ev.items()))
+            history.append({f"validation {k}": v for k, v in ev.items()})
+    else:
+        history = train(forward_step_func, model, optimizer, sched, train_iter, process_non_loss_data_func)
     if args.save:
         from ..checkpointing import finalize_async_save, save_checkpoint
         save_checkpoint(args.iteration, model, optimizer, sched)
