@@ -702,7 +702,7 @@ class MoEFeature(Feature):
         add_arg(g, "--use-pipe-experts", action="store_true")
         add_arg(g, "--pipe-experts-multi-data", type=int, default=1)
         add_arg(g, "--pipe-experts-multi-stream", action="store_true")
-        add_arg(g, "--ampipe-degree", type=int, default=0)
+        add_arg(g, "--ampipe-degree", type=int, default=1)
 
     def validate_args(self, args):
         ne = getattr(args, "num_experts", None)

@@ -161,3 +161,49 @@ def test_router_dtype_and_seq_aux(monkeypatch):
     probs, rmap = r(x)
     assert rmap.sum(-1).tolist() == [2] * 6 and torch.isfinite(probs).all()
     ps.destroy_model_parallel()
+
+
+def test_yaml_file_with_megatron_sections_and_config_field_names(tmp_path, monkeypatch):
+    """Sections ``language_model`` / ``model_parallel`` are flattened and configuration field names are translated to the
+    arguments that carry them; nulls keep the defaults."""
+    monkeypatch.setenv("WORLD_SIZE", "8")
+    from mindspeed_b200.training.arguments import core_transformer_config_from_args, parse_args, validate_args
+    y = tmp_path / "cfg.yaml"
+    y.write_text("""
+language_model:
+  num_layers: 4
+  hidden_size: 256
+  num_attention_heads: 8
+  num_query_groups: 4
+  ffn_hidden_size: 512
+  kv_channels: 32
+  layernorm_epsilon: 0.00002
+  layernorm_zero_centered_gamma: True
+  add_bias_linear: False
+  activation_func: swiglu
+  num_moe_experts: null
+  normalization: 'RMSNorm'
+  window_size: null
+  moe_router_topk: 2
+  recompute_granularity: null
+model_parallel:
+  tensor_model_parallel_size: 2
+  context_parallel_size: 4
+  sequence_parallel: True
+  bf16: True
+  use_cpu_initialization: null
+group_query_attention: True
+seq_length: 64
+micro_batch_size: 1
+vocab_size: 128
+adam_beta2: 0.95
+ampipe_degree: 1
+position_embedding_type: rope
+""")
+    a = validate_args(parse_args(args_list=["--yaml-cfg", str(y)]))
+    assert (a.tensor_model_parallel_size, a.context_parallel_size, a.data_parallel_size) == (2, 4, 1)
+    assert a.norm_epsilon == 0.00002 and a.apply_layernorm_1p and a.swiglu and a.num_experts is None and a.adam_beta2 == 0.95
+    assert a.use_cpu_initialization is False                       # null: the default stays
+    cfg = core_transformer_config_from_args(a)
+    assert cfg.layernorm_epsilon == 0.00002 and cfg.layernorm_zero_centered_gamma and cfg.gated_linear_unit
+    assert cfg.num_query_groups == 4 and cfg.sequence_parallel and not cfg.add_bias_linear and cfg.num_moe_experts is None
