@@ -251,13 +251,103 @@ def ring_schedule(cp: int, rank: int, window: int = 1):
     return src, send_to, recv_from, home_from
 
 
+class _RingAttentionUnaligned(torch.autograd.Function):
+    """Ring attention without a causal mask for sequence slices of different lengths per rank (``shapes[r]`` tokens on
+    rank r): every message is sized by the block that travels - the receive buffer of a step by the block that arrives,
+    the gradient buffer by the block it belongs to (reference: the ``shapes`` argument of ringattn_context_parallel,
+    mindspeed/core/context_parallel/ring_context_parallel/ring_context_parallel.py:422-426, 995-1028, 1104-1178)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, group, ranks, group_overlap, scale, shapes):
+        cp = len(ranks)
+        rank = ranks.index(dist.get_rank())
+        if q.shape[0] != shapes[rank] or k.shape[0] != shapes[rank]:
+            raise ValueError(f"rank {rank} holds {q.shape[0]} tokens, shapes says {shapes[rank]}")
+        ring = RingP2P(ranks, group, group_overlap)
+        same, dk = k.shape == v.shape, k.shape[-1]
+        seq_dim = 1 if same else 0
+        kv = _pack_kv(k, v)
+
+        def like(block):
+            shp = list(kv.shape)
+            shp[seq_dim] = shapes[block]
+            return shp
+        out = lse = None
+        blocks = []
+        for i in range(cp):
+            nxt = None
+            if i < cp - 1:
+                nxt = kv.new_empty(like((rank - i - 1) % cp))
+                ring.async_send_recv(kv, nxt)
+            kk, vv = _unpack_kv(kv, dk, same)
+            o, l, c = A.attn_fwd_block(q, kk, vv, False, scale)
+            out, lse = (o.contiguous(), l.contiguous()) if out is None else A.merge_lse(out, lse, o, l)
+            blocks.append(c)
+            if i < cp - 1:
+                ring.wait()
+                kv = nxt
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.meta = (group, ranks, group_overlap, scale, blocks, list(shapes))
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        group, ranks, group_overlap, scale, blocks, shapes = ctx.meta
+        q, k, v, out, lse = ctx.saved_tensors
+        cp = len(ranks)
+        rank = ranks.index(dist.get_rank())
+        same, dk = k.shape == v.shape, k.shape[-1]
+        seq_dim = 1 if same else 0
+        dout = dout.contiguous()
+        kv_ring, dkv_ring = RingP2P(ranks, group, group_overlap), RingP2P(ranks, group, group_overlap)
+        kv = _pack_kv(k, v)
+
+        def like(block, ref):
+            shp = list(ref.shape)
+            shp[seq_dim] = shapes[block]
+            return shp
+        dq = torch.zeros_like(q, dtype=torch.float32)
+        dkv_recv = None
+        for i in range(cp):
+            nxt = None
+            if i < cp - 1:
+                nxt = kv.new_empty(like((rank - i - 1) % cp, kv))
+                kv_ring.async_send_recv(kv, nxt)
+            kk, vv = _unpack_kv(kv, dk, same)
+            gq, gk, gv = A.attn_bwd_block(dout, q, kk, vv, out, lse, False, scale, blocks[i])
+            dq += gq.float()
+            blk = _pack_grads(gk, gv, same)
+            if i > 0:
+                dkv_ring.wait()
+                blk = dkv_recv + blk                      # what earlier holders of this block accumulated
+            # the gradient travels with its block; after the last step it arrives at the block's origin.  What arrives here
+            # next belongs to the block this rank holds in the next step (its own block after the last one)
+            dkv_recv = blk.new_empty(like((rank - i - 1) % cp, blk))
+            dkv_ring.async_send_recv(blk, dkv_recv)
+            if i < cp - 1:
+                kv_ring.wait()
+                kv = nxt
+        dkv_ring.wait()
+        if same:
+            gk_home, gv_home = dkv_recv[0], dkv_recv[1]
+        else:
+            gk_home, gv_home = dkv_recv[..., :dk], dkv_recv[..., dk:]
+        return dq.to(q.dtype), gk_home.to(k.dtype), gv_home.to(v.dtype), None, None, None, None, None
+
+
 def ring_attention(q, k, v, config=None, causal=True, softmax_scale=None, layer_number=1, group=None, ranks=None,
-                   group_overlap=None):
-    """q [s_local, b, nq, d], k/v [s_local, b, nkv, d] where s_local holds chunks (r, 2cp-1-r)."""
+                   group_overlap=None, shapes=None):
+    """q [s_local, b, nq, d], k/v [s_local, b, nkv, d] where s_local holds chunks (r, 2cp-1-r).
+    ``shapes``: tokens per rank when the slices differ in length (contiguous slices, no causal mask)."""
     if group is None:
         group = ps.get_context_parallel_group()
         ranks = ps.get_context_parallel_global_ranks()
         group_overlap = ps.get_context_parallel_group_for_send_recv_overlap()
+    if shapes is not None and len(set(shapes)) > 1:
+        if causal:
+            raise NotImplementedError("ring attention over slices of different lengths is implemented without a causal mask")
+        return _RingAttentionUnaligned.apply(q.contiguous(), k.contiguous(), v.contiguous(), group, list(ranks), group_overlap,
+                                             softmax_scale, list(shapes))
     policy = getattr(config, "context_parallel_kv_cache_policy", None) if config is not None else None
     interval = getattr(config, "context_parallel_cache_interval", 0) if config is not None else 0
     cache = policy in ("full", "half") and (interval == 0 or (layer_number - 1) % (interval + 1) == 0)

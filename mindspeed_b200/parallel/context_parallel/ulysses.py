@@ -58,9 +58,79 @@ def heads_to_seq(x, group):
     return t.reshape(s // p, b, p * nl, d)
 
 
-def ulysses_attention(q, k, v, config, group, causal=True, softmax_scale=None, layer_number=1, inner=None):
+# ---- sequence lengths that the group size does not divide -------------------------------------------------------------
+class GatherSizeCalculator:
+    """Tells ``ulysses_attention`` the length of the full sequence when the ranks hold slices of different lengths;
+    ``calculate()`` returns that length or None (None = every rank holds the same number of tokens)."""
+
+    def calculate(self, *args, **kwargs):
+        raise NotImplementedError
+
+
+class DefaultGatherSizeCalculator(GatherSizeCalculator):
+    def calculate(self, *args, **kwargs):
+        return None
+
+
+class DynamicGatherSizeCalculator(GatherSizeCalculator):
+    """Length of the current batch's sequence, read from its attention mask (last axis) or given directly."""
+
+    def calculate(self, *args, **kwargs):
+        mask = kwargs.get("attention_mask", args[0] if args else None)
+        if mask is None:
+            return None
+        return int(mask) if isinstance(mask, int) else int(mask.shape[-1])
+
+
+def split_lengths(total: int, p: int):
+    """How ``total`` tokens are laid out over ``p`` ranks when ``p`` does not divide it: the first ``total % p`` ranks hold
+    one token more."""
+    base, extra = divmod(total, p)
+    return [base + (1 if r < extra else 0) for r in range(p)]
+
+
+def seq_to_heads_unaligned(x, group, lengths):
+    """[s_r, b, n, d] with s_r = lengths[rank] -> [sum(lengths), b, n/p, d]: the all-to-all receives ``lengths[j]`` rows from
+    rank j (reference: the gather-size path of ulysses_context_parallel.py:127-221)."""
+    p = dist.get_world_size(group)
+    sl, b, n, d = x.shape
+    r = dist.get_rank(group)
+    if sl != lengths[r]:
+        raise ValueError(f"rank {r} holds {sl} tokens, the layout says {lengths[r]}")
+    t = x.reshape(sl, b, p, n // p, d).permute(2, 0, 1, 3, 4).contiguous().reshape(p * sl, b, n // p, d)
+    return M.all_to_all(group, t, list(lengths), [sl] * p)
+
+
+def heads_to_seq_unaligned(x, group, lengths):
+    """[sum(lengths), b, n/p, d] -> [lengths[rank], b, n, d]"""
+    p = dist.get_world_size(group)
+    s, b, nl, d = x.shape
+    r = dist.get_rank(group)
+    mine = lengths[r]
+    t = M.all_to_all(group, x.contiguous(), [mine] * p, list(lengths))          # [p * mine, b, n/p, d] by head group
+    return t.reshape(p, mine, b, nl, d).permute(1, 2, 0, 3, 4).reshape(mine, b, p * nl, d)
+
+
+def ulysses_attention(q, k, v, config, group, causal=True, softmax_scale=None, layer_number=1, inner=None,
+                      gather_size_calculator: GatherSizeCalculator = None, **calc_kwargs):
     p = dist.get_world_size(group)
     nkv = k.shape[2]
+    total = gather_size_calculator.calculate(**calc_kwargs) if gather_size_calculator is not None else None
+    if total is not None and p > 1 and (total % p != 0 or q.shape[0] * p != total):
+        # ranks hold slices of different lengths: all-to-alls with per-rank row counts
+        lengths = split_lengths(total, p)
+        if nkv < p:
+            rep = p // nkv
+            k, v = k.repeat_interleave(rep, dim=2), v.repeat_interleave(rep, dim=2)
+        qh, kh, vh = (seq_to_heads_unaligned(t, group, lengths) for t in (q, k, v))
+        if inner is not None:
+            o = inner(qh, kh, vh)
+        else:
+            want = getattr(config, "attention_backend", "auto") if config is not None else "library"
+            backend = "library" if want == "library" else (
+                "sm100" if (config is not None and config.optimization_level >= 1 and q.is_cuda) else None)
+            o = A.flash_attention(qh, kh, vh, causal=causal, softmax_scale=softmax_scale, backend=backend)
+        return heads_to_seq_unaligned(o, group, lengths)
     if nkv < p and bool(getattr(config, "use_ulysses_allgather_kv", False)) and p % nkv == 0:
         # --use-ulysses-allgather-kv: fewer KV heads than ranks.  Instead of repeating the KV heads up to the group size
         # and sending the copies through the all-to-all, gather K and V along the sequence (gradient: reduce-scatter) and

@@ -189,3 +189,70 @@ def test_double_ring_schedule_is_consistent():
             assert sch[home][0][cp - 1] == r                               # my block's gradient comes home from its last holder
     with pytest.raises(ValueError):
         ring_schedule(6, 0, 4)
+
+
+def _unaligned_ulysses(rank, world, total):
+    import torch.distributed as dist
+    from mindspeed_b200.ops.attention import attention_ref
+    from mindspeed_b200.parallel.context_parallel import ulysses as U
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    g = torch.Generator().manual_seed(0)
+    b, n, d = 2, 4, 8
+    q, k, v = (torch.randn(total, b, n, d, generator=g) for _ in range(3))
+    lens = U.split_lengths(total, world)
+    lo = sum(lens[:rank])
+    sl = slice(lo, lo + lens[rank])
+    ql, kl, vl = (t[sl].clone().requires_grad_(True) for t in (q, k, v))
+    out = U.ulysses_attention(ql, kl, vl, None, dist.group.WORLD, causal=True,
+                              inner=lambda a, b_, c: attention_ref(a, b_, c, causal=True),
+                              gather_size_calculator=U.DynamicGatherSizeCalculator(), attention_mask=total)
+    qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
+    ref = attention_ref(qf, kf, vf, causal=True)
+    w = torch.randn(total, b, n, d, generator=g)
+    (out * w[sl]).sum().backward()
+    (ref * w).sum().backward()
+    # gradients of K / V on this rank's slice collect contributions of every rank's queries through the all-to-alls
+    ok = torch.allclose(out, ref[sl], atol=1e-5) and torch.allclose(ql.grad, qf.grad[sl], atol=1e-5) \
+        and torch.allclose(kl.grad, kf.grad[sl], atol=1e-5) and torch.allclose(vl.grad, vf.grad[sl], atol=1e-5)
+    dist.destroy_process_group()
+    return ok, lens
+
+
+def test_ulysses_with_a_sequence_length_the_group_does_not_divide():
+    from mindspeed_b200.parallel.context_parallel.ulysses import DefaultGatherSizeCalculator, DynamicGatherSizeCalculator, split_lengths
+    assert split_lengths(10, 4) == [3, 3, 2, 2] and split_lengths(8, 4) == [2, 2, 2, 2]
+    assert DefaultGatherSizeCalculator().calculate() is None
+    assert DynamicGatherSizeCalculator().calculate(attention_mask=torch.zeros(1, 1, 7, 7)) == 7
+    res = run_distributed(_unaligned_ulysses, 2, 13)
+    assert all(ok for ok, _ in res) and res[0][1] == [7, 6]
+    res = run_distributed(_unaligned_ulysses, 4, 10)
+    assert all(ok for ok, _ in res)
+
+
+def _unaligned_ring(rank, world, lens):
+    import torch.distributed as dist
+    from mindspeed_b200.ops.attention import attention_ref
+    from mindspeed_b200.parallel.context_parallel.ring import ring_attention
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    g = torch.Generator().manual_seed(0)
+    total, b, n, d = sum(lens), 2, 2, 8
+    q, k = torch.randn(total, b, n, d, generator=g), torch.randn(total, b, n, d, generator=g)
+    v = torch.randn(total, b, n, d, generator=g)
+    lo = sum(lens[:rank])
+    sl = slice(lo, lo + lens[rank])
+    ql, kl, vl = (t[sl].clone().requires_grad_(True) for t in (q, k, v))
+    out = ring_attention(ql, kl, vl, None, causal=False, group=dist.group.WORLD, ranks=list(range(world)), shapes=lens)
+    qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
+    ref = attention_ref(qf, kf, vf, causal=False)
+    w = torch.randn(total, b, n, d, generator=g)
+    (out * w[sl]).sum().backward()
+    (ref * w).sum().backward()
+    ok = torch.allclose(out, ref[sl], atol=1e-5) and torch.allclose(ql.grad, qf.grad[sl], atol=1e-5) \
+        and torch.allclose(kl.grad, kf.grad[sl], atol=1e-5) and torch.allclose(vl.grad, vf.grad[sl], atol=1e-5)
+    dist.destroy_process_group()
+    return ok
+
+
+@pytest.mark.parametrize("lens", [[5, 3], [5, 3, 4], [2, 6, 1, 4]])
+def test_ring_attention_over_slices_of_different_lengths(lens):
+    assert all(run_distributed(_unaligned_ring, len(lens), lens))
