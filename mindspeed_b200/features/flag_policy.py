@@ -28,8 +28,6 @@ NO_EFFECT: Dict[str, str] = {
     "attention-mask-on-cpu": "the causal mask is generated inside the attention kernels, no mask tensor is built",
     "square-alibi-mask": "shape of the ALiBi bias tensor on the unfused path; the bias here is evaluated from the head slopes block by block, no bias tensor of either shape exists",
     "fill-neg-inf": "mask fill value of the unfused softmax path; masked scores are -inf in every kernel here",
-    "te-comparison-with-bf16": "debug comparison hook of the reference's TE shim",
-    "te-comparison-with-cpu": "debug comparison hook of the reference's TE shim",
     "te-gmm-mode": "grouped-GEMM backend choice of the reference's TE shim; one grouped kernel here",
     "no-use-gmm-fp8": "grouped-GEMM backend choice of the reference's TE shim; fp8 experts follow --fp8-format",
     "fp8-reuse-quantized-weight": "quantised weights are always cached across micro-batches (models/te_compat.py)",

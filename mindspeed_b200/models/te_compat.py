@@ -210,14 +210,52 @@ class _FakeQuantLinearFn(torch.autograd.Function):
         return dx, dw, None, None
 
 
+class OnlineComparison:
+    """``--te-comparison-with-bf16`` / ``--te-comparison-with-cpu``: every low-precision linear is also computed in the
+    unquantised working precision on the device, or in fp32 on the host, and the relative error of the fp8 result
+    (``|y_fp8 - y_ref|_F / |y_ref|_F``) is recorded; an error above ``limit`` stops the run with the offending layer's shape.
+    reference: the online comparison of the reference's low-precision modules (``--te-comparison-with-cpu/-bf16``,
+    mindspeed/features_manager/megatron_basic/transformer_engine_basic.py)."""
+    mode: Optional[str] = None           # None | "bf16" | "cpu"
+    limit: float = 0.25
+    records: List[dict] = []
+
+    @classmethod
+    def configure(cls, with_bf16: bool = False, with_cpu: bool = False, limit: float = 0.25):
+        cls.mode = "cpu" if with_cpu else ("bf16" if with_bf16 else None)
+        cls.limit, cls.records = limit, []
+
+    @classmethod
+    def check(cls, x, w, y):
+        with torch.no_grad():
+            if cls.mode == "cpu":
+                ref = torch.matmul(x.detach().float().cpu(), w.detach().float().cpu().t())
+                got = y.detach().float().cpu()
+            else:
+                ref = torch.matmul(x.detach(), w.detach().t()).float()
+                got = y.detach().float()
+            err = float((got - ref).norm() / ref.norm().clamp_min(1e-30))
+        rec = {"shape": (tuple(x.shape), tuple(w.shape)), "reference": cls.mode, "rel_err": err}
+        cls.records.append(rec)
+        if len(cls.records) > 4096:
+            del cls.records[:2048]
+        if not (err <= cls.limit):
+            raise RuntimeError(f"low-precision linear x{tuple(x.shape)} @ w{tuple(w.shape)}^T deviates from the {cls.mode} "
+                               f"reference by {err:.4f} (limit {cls.limit})")
+
+
 def fp8_linear(x, w, module=None, recipe: Optional[Recipe] = None):
     """Local (un-sharded) fp8 linear under ``recipe`` (default: the active autocast recipe)."""
     recipe = recipe or _FP8State.recipe
     state = module._fp8_state if module is not None else None
     if isinstance(recipe, BlockwiseScaling) and x.shape[-1] % 128 == 0 and w.shape[0] % 128 == 0:
         cache = module._fp8_wcache if module is not None else None
-        return fp8_blockwise_linear(x, w, cache, recipe.dtype_for("grads"))
-    return _FakeQuantLinearFn.apply(x, w, recipe, state)
+        y = fp8_blockwise_linear(x, w, cache, recipe.dtype_for("grads"))
+    else:
+        y = _FakeQuantLinearFn.apply(x, w, recipe, state)
+    if OnlineComparison.mode is not None:
+        OnlineComparison.check(x, w, y)
+    return y
 
 
 class _Fp8Mixin:

@@ -185,6 +185,9 @@ def setup_model_and_optimizer(model_provider_func, no_wd_decay_cond=None, scale_
     if args.swap_attention:
         from ..memory.swap_attention import install_swap_attention
         install_swap_attention(model, args)
+    if getattr(args, "te_comparison_with_bf16", False) or getattr(args, "te_comparison_with_cpu", False):
+        from ..models.te_compat import OnlineComparison
+        OnlineComparison.configure(with_bf16=args.te_comparison_with_bf16, with_cpu=args.te_comparison_with_cpu)
     if getattr(args, "qat_scheme", None):
         from ..qat import QATConfig, apply_qat
         qcfg = QATConfig(scheme=args.qat_scheme.upper(), weight_group=getattr(args, "qat_quant_block_size", 128))

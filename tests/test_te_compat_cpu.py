@@ -97,3 +97,27 @@ def test_layernorm_linear_grouped_linear_and_quantize_linears():
     z = net(torch.randn(4, 256))
     z.sum().backward()
     assert net[0].weight.grad is not None
+
+
+def test_online_comparison_records_errors_and_stops_on_a_bad_result():
+    import torch
+    from mindspeed_b200.models import te_compat as TE
+    torch.manual_seed(0)
+    lin = TE.Fp8Linear(torch.nn.Linear(64, 32, bias=False), TE.MXFP8Scaling())
+    x = torch.randn(16, 64)
+    try:
+        for with_cpu in (False, True):
+            TE.OnlineComparison.configure(with_bf16=not with_cpu, with_cpu=with_cpu)
+            lin(x)
+            rec = TE.OnlineComparison.records[-1]
+            assert rec["reference"] == ("cpu" if with_cpu else "bf16") and 1e-4 < rec["rel_err"] < 0.1
+            assert rec["shape"] == ((16, 64), (32, 64))
+        TE.OnlineComparison.configure(with_bf16=True, limit=1e-6)       # fp8 cannot meet this: the run stops
+        import pytest
+        with pytest.raises(RuntimeError, match="deviates from the bf16 reference"):
+            lin(x)
+    finally:
+        TE.OnlineComparison.configure()
+    assert TE.OnlineComparison.mode is None
+    lin(x)
+    assert TE.OnlineComparison.records == []
