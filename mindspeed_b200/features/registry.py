@@ -172,6 +172,16 @@ class LegacySpellingsFeature(Feature):
             args.layerzero = True
         if args.yarn_scaling_factor != 1.0 and getattr(args, "rope_scaling_factor", 1.0) == 1.0:
             args.rope_scaling_factor = args.yarn_scaling_factor
+        args.micro_batch_sizes = None
+        if args.optimized_mbs_list and args.optimized_mbs_mode:
+            import ast
+            v = args.optimized_mbs_list
+            sizes = list(ast.literal_eval(v if v.strip().startswith("[") else f"[{v}]")) if isinstance(v, str) else list(v)
+            if not sizes or any((not isinstance(b, int)) or b < 1 for b in sizes):
+                raise AssertionError("--optimized-mbs-list is a list of positive micro-batch sizes, e.g. '[2,1,1]'")
+            args.optimized_mbs_list = sizes
+            args.micro_batch_sizes = sizes
+            args.micro_batch_size = max(sizes)       # what buffers and memory estimates are sized for
         if getattr(args, "expert_interval", 1) > 1:
             if getattr(args, "moe_model_type", "megatron_moe") != "deepspeed_moe":
                 raise AssertionError("--expert-interval belongs to --moe-model-type deepspeed_moe; use --moe-layer-freq otherwise")
@@ -183,6 +193,16 @@ class LegacySpellingsFeature(Feature):
             raise AssertionError("--moe-adaptive-recompute-activation needs a MoE model (--num-experts)")
         if getattr(args, "moe_adaptive_recompute_activation_scale", 2.0) <= 0:
             raise AssertionError("--moe-adaptive-recompute-activation-scale must be positive")
+        if getattr(args, "micro_batch_sizes", None):
+            if sum(args.micro_batch_sizes) * args.data_parallel_size != args.global_batch_size:
+                raise AssertionError(f"--optimized-mbs-list {args.micro_batch_sizes} sums to {sum(args.micro_batch_sizes)} samples per "
+                                     f"data-parallel rank; the global batch {args.global_batch_size} over {args.data_parallel_size} "
+                                     "data-parallel ranks needs " + str(args.global_batch_size // args.data_parallel_size))
+            for other in ("reset_attention_mask", "use_multiparameter_pipeline_model_parallel"):
+                if getattr(args, other, False):
+                    raise AssertionError(f"--optimized-mbs-list is not combined with --{other.replace('_', '-')}")
+            if getattr(args, "schedules_method", None) in ("dualpipev", "dualpipe", "chimera"):
+                raise AssertionError("--optimized-mbs-list works with the 1F1B and interleaved schedules")
         if not (0.0 <= args.save_memory_ratio < 1.0):
             raise AssertionError("--save-memory-ratio is a fraction in [0, 1)")
 

@@ -93,8 +93,14 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
     gspecs = [sp for sp in specs if sp[1].is_floating_point]
     dev = next(model[0].parameters()).device
 
+    mb_sizes = getattr(config, "micro_batch_sizes", None)       # --optimized-mbs-list: the batch axis differs per micro-batch
+
     def specs_of(m):
-        return specs if m.kind == "act" else gspecs
+        sp = specs if m.kind == "act" else gspecs
+        if mb_sizes and not multi:
+            b = mb_sizes[m.mb % len(mb_sizes)]
+            sp = [((sh[0], b) + tuple(sh[2:]), dt) for sh, dt in sp]
+        return sp
 
     def unwrap(payload):
         return payload if multi else payload[0]
@@ -134,7 +140,7 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
     grad_pool: List[torch.Tensor] = []
 
     def new_bufs(m):
-        if m.kind == "grad" and grad_pool and not multi:
+        if m.kind == "grad" and grad_pool and not multi and not mb_sizes:
             return [grad_pool.pop()]
         return [torch.empty(sh, dtype=dt, device=dev) for sh, dt in specs_of(m)]
 

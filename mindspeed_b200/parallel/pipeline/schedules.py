@@ -98,14 +98,18 @@ def forward_step(forward_step_func, data_iterator, model, num_microbatches, inpu
     if ps.is_pipeline_last_stage():
         if not collect_non_loss_data:
             outputs = loss_func(output_tensor)
+            # micro-batches of different sizes (--optimized-mbs-list) weigh in by their share of the step's samples
+            sizes = getattr(config, "micro_batch_sizes", None)
+            mb = _CURRENT.get("mb") if current_microbatch is None else current_microbatch
+            share = (sizes[mb % len(sizes)] / sum(sizes)) if sizes and mb is not None else 1.0 / num_microbatches
             if len(outputs) == 3:
                 output_tensor, num_tokens, loss_reduced = outputs
                 if not config.calculate_per_token_loss:
                     output_tensor = output_tensor / num_tokens.clamp(min=1)
-                    output_tensor = output_tensor / num_microbatches
+                    output_tensor = output_tensor * share
             else:
                 output_tensor, loss_reduced = outputs
-                output_tensor = output_tensor / num_microbatches
+                output_tensor = output_tensor * share
             forward_data_store.append(loss_reduced)
         else:
             forward_data_store.append(loss_func(output_tensor, non_loss_data=True))
@@ -282,7 +286,8 @@ def forward_backward_pipelining_without_interleaving(*, forward_step_func, data_
                                                      seq_length, micro_batch_size, decoder_seq_length=None,
                                                      forward_only=False, collect_non_loss_data=False, first_val_step=None):
     """Non-interleaved 1F1B: warm-up forwards, steady 1F1B, cool-down backwards."""
-    if is_multi_parameter(_cfg(model)) or (getattr(_cfg(model), "moe_fb_overlap", False) and not forward_only):
+    if is_multi_parameter(_cfg(model)) or (getattr(_cfg(model), "moe_fb_overlap", False) and not forward_only) \
+            or getattr(_cfg(model), "micro_batch_sizes", None):
         # list-valued stage interfaces and forward/backward overlap are handled by the plan executor (same 1F1B order, as data)
         from .executor import run_plan
         from .interleaved import _plan

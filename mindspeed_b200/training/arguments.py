@@ -257,8 +257,9 @@ def _core_validate(args):
         raise AssertionError(f"world size {args.world_size} is not divisible by tp*pp*cp = {mp}")
     args.data_parallel_size = args.world_size // mp
     if args.global_batch_size is None:
-        args.global_batch_size = args.micro_batch_size * args.data_parallel_size
-    if args.global_batch_size % (args.micro_batch_size * args.data_parallel_size) != 0:
+        per_rank = sum(args.micro_batch_sizes) if getattr(args, "micro_batch_sizes", None) else args.micro_batch_size
+        args.global_batch_size = per_rank * args.data_parallel_size
+    if not getattr(args, "micro_batch_sizes", None) and args.global_batch_size % (args.micro_batch_size * args.data_parallel_size) != 0:
         raise AssertionError("global batch size must be divisible by micro batch size * data parallel size")
     if args.num_layers is None or args.hidden_size is None or args.num_attention_heads is None:
         raise AssertionError("--num-layers, --hidden-size and --num-attention-heads are required")

@@ -29,19 +29,25 @@ class SyntheticGPTDataset(torch.utils.data.Dataset):
 class BatchIterator:
     """Yields micro-batches for this data-parallel rank in global-sample order."""
 
-    def __init__(self, dataset, micro_batch_size, dp_rank, dp_size, start=0, pin=False, device=None):
+    def __init__(self, dataset, micro_batch_size, dp_rank, dp_size, start=0, pin=False, device=None, micro_batch_sizes=None):
         self.ds, self.mbs, self.r, self.n = dataset, micro_batch_size, dp_rank, dp_size
         self.cursor, self.pin, self.device = start, pin, device
+        # --optimized-mbs-list: the micro-batches of a step have these sizes, in this order, step after step
+        self.sizes, self._k = (list(micro_batch_sizes) if micro_batch_sizes else None), 0
 
     def __iter__(self):
         return self
 
     def __next__(self):
         items = []
-        for i in range(self.mbs):
-            idx = (self.cursor + self.r * self.mbs + i) % len(self.ds)
+        mbs = self.mbs
+        if self.sizes:
+            mbs = self.sizes[self._k % len(self.sizes)]
+            self._k += 1
+        for i in range(mbs):
+            idx = (self.cursor + self.r * mbs + i) % len(self.ds)
             items.append(self.ds[idx])
-        self.cursor += self.mbs * self.n
+        self.cursor += mbs * self.n
         batch = {k: torch.stack([it[k] for it in items]) for k in items[0]}
         if self.pin and torch.cuda.is_available():
             batch = {k: v.pin_memory() for k, v in batch.items()}

@@ -19,7 +19,18 @@ def get_args():
 
 def get_num_microbatches():
     a = get_args()
+    sizes = get_micro_batch_sizes()
+    if sizes:
+        return len(sizes)
     return a.global_batch_size // (a.micro_batch_size * a.data_parallel_size)
+
+
+def get_micro_batch_sizes():
+    """``--optimized-mbs-list``: the batch size of every micro-batch of a step (their sum times the data-parallel size is the
+    global batch), or None when all micro-batches have ``--micro-batch-size`` samples."""
+    a = get_args()
+    sizes = getattr(a, "optimized_mbs_list", None)
+    return list(sizes) if sizes and getattr(a, "optimized_mbs_mode", True) else None
 
 
 class _Timer:

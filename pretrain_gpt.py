@@ -64,10 +64,10 @@ def train_valid_test_datasets_provider(args):
         if train is None:
             raise ValueError("--split leaves no documents for training")
         return BatchIterator(train, args.micro_batch_size, ps.get_data_parallel_rank(), ps.get_data_parallel_world_size(),
-                             start=args.iteration * args.global_batch_size)
+                             start=args.iteration * args.global_batch_size, micro_batch_sizes=getattr(args, "micro_batch_sizes", None))
     ds = SyntheticGPTDataset(args.padded_vocab_size, args.seq_length, 1 << 20, seed=args.seed)
     return BatchIterator(ds, args.micro_batch_size, ps.get_data_parallel_rank(), ps.get_data_parallel_world_size(),
-                         start=args.iteration * args.global_batch_size)
+                         start=args.iteration * args.global_batch_size, micro_batch_sizes=getattr(args, "micro_batch_sizes", None))
 
 
 if __name__ == "__main__":

@@ -42,8 +42,10 @@ def test_older_spellings_are_rewritten(monkeypatch, tmp_path):
     cfgf.write_text("no_such_argument: 1\n")
     with pytest.raises(AssertionError, match="unknown argument"):
         _args(["--additional-config", str(cfgf)], 1, monkeypatch)
-    with pytest.raises(NotImplementedError, match="optimized-mbs-list"):
-        _args(["--optimized-mbs-list", "[2,1,1]"], 1, monkeypatch)
+    a = _args(["--optimized-mbs-list", "[2,1,1]"], 1, monkeypatch)
+    assert a.micro_batch_sizes == [2, 1, 1] and a.global_batch_size == 4 and a.micro_batch_size == 2
+    with pytest.raises(NotImplementedError, match="pp-schedule-list"):
+        _args(["--pp-schedule-list", "[[0,1],[1,0]]"], 1, monkeypatch)
     with pytest.raises(AssertionError, match="use-nanopipe"):
         _args(["--use-nanopipe"], 1, monkeypatch)
 
@@ -132,3 +134,39 @@ def test_dense_bias_flag_adds_the_projection_bias():
     cfg2.add_dense_bias = True
     assert SelfAttention(cfg2).linear_proj.bias is not None and SelfAttention(cfg2).linear_qkv.bias is None
     ps.destroy_model_parallel()
+
+
+def _train_mbs(rank, world, extra):
+    import io
+    from contextlib import redirect_stdout
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import pretrain_gpt as pg
+    from test_pipeline_cpu import BASE as TB, _canonical_init
+    from mindspeed_b200.training import initialize_megatron, setup_model_and_optimizer, train_step
+    args = initialize_megatron(args_list=list(TB) + list(extra))
+    model, opt, sched = setup_model_and_optimizer(pg.model_provider)
+    _canonical_init(model)
+    if hasattr(opt, "reload_model_params"):
+        opt.reload_model_params()
+    it = pg.train_valid_test_datasets_provider(args)
+    out = []
+    with redirect_stdout(io.StringIO()):
+        for _ in range(2):
+            ld, *_ = train_step(pg.forward_step, [it] * len(model) if len(model) > 1 else it, model, opt, sched)
+            out.append(float(ld["lm loss"]) if "lm loss" in ld else None)
+    return out
+
+
+def test_micro_batches_of_different_sizes_give_the_same_step():
+    """--optimized-mbs-list: 8 samples per step as micro-batches of 3 + 1 + 2 + 2 equal eight micro-batches of one sample,
+    without pipeline parallelism and across two stages (messages sized per micro-batch)."""
+    from dist_utils import run_distributed
+    ref = run_distributed(_train_mbs, 1, [])[0]
+    got = run_distributed(_train_mbs, 1, ["--optimized-mbs-list", "[3,1,2,2]"])[0]
+    assert got == pytest.approx(ref, abs=2e-5), (ref, got)
+    pp = run_distributed(_train_mbs, 2, ["--pipeline-model-parallel-size", "2", "--optimized-mbs-list", "3,1,2,2"])
+    have = [r for r in pp if r[0] is not None][0]
+    assert have == pytest.approx(ref, abs=2e-4), (ref, have)
+    from mindspeed_b200.training.arguments import parse_args, validate_args
+    with pytest.raises(AssertionError, match="sums to"):
+        validate_args(parse_args(args_list=BASE + ["--global-batch-size", "8", "--optimized-mbs-list", "[3,1]"]))
