@@ -101,15 +101,15 @@ def forward_step(forward_step_func, data_iterator, model, num_microbatches, inpu
             # micro-batches of different sizes (--optimized-mbs-list) weigh in by their share of the step's samples
             sizes = getattr(config, "micro_batch_sizes", None)
             mb = _CURRENT.get("mb") if current_microbatch is None else current_microbatch
-            share = (sizes[mb % len(sizes)] / sum(sizes)) if sizes and mb is not None else 1.0 / num_microbatches
+            share = (sizes[mb % len(sizes)] / sum(sizes)) if sizes and mb is not None else None
             if len(outputs) == 3:
                 output_tensor, num_tokens, loss_reduced = outputs
                 if not config.calculate_per_token_loss:
                     output_tensor = output_tensor / num_tokens.clamp(min=1)
-                    output_tensor = output_tensor * share
+                    output_tensor = output_tensor / num_microbatches if share is None else output_tensor * share
             else:
                 output_tensor, loss_reduced = outputs
-                output_tensor = output_tensor * share
+                output_tensor = output_tensor / num_microbatches if share is None else output_tensor * share
             forward_data_store.append(loss_reduced)
         else:
             forward_data_store.append(loss_func(output_tensor, non_loss_data=True))
