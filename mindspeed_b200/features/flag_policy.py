@@ -79,7 +79,6 @@ NO_EFFECT: Dict[str, str] = {
 
 UNSUPPORTED: Dict[str, str] = {
     "ampipe-tp-sp-comm-overlap": "option of --ampipe-degree, for which the reference ships no forward path any more",
-    "pp-schedule-list": "stored forward / backward order of --automated-pipeline-perf; schedules here are generated by parallel/pipeline/plan.py from --schedules-method and the virtual-pipeline flags",
     "ampipe-degree": "attention-MoE micro-pipelining: the reference registers and validates the flag (mindspeed/arguments.py:336-340, 803-820) but ships no forward path for it any more; here --moe-fb-overlap and --use-pipe-experts cover the overlap of MoE communication with compute",
 }
 

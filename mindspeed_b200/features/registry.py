@@ -182,6 +182,19 @@ class LegacySpellingsFeature(Feature):
             args.optimized_mbs_list = sizes
             args.micro_batch_sizes = sizes
             args.micro_batch_size = max(sizes)       # what buffers and memory estimates are sized for
+        args.pp_schedule = None
+        if args.pp_schedule_list:
+            import ast
+            import json
+            v = args.pp_schedule_list
+            if isinstance(v, str):
+                try:
+                    v = json.loads(v)
+                except ValueError:
+                    v = ast.literal_eval(v)
+            if not isinstance(v, dict) or not all(isinstance(x, (list, tuple)) for x in v.values()):
+                raise AssertionError('--pp-schedule-list is a mapping like {"stage0": ["F1", "F2", "B1", "B2"], "stage1": [...]}')
+            args.pp_schedule_list = args.pp_schedule = {k: list(x) for k, x in v.items()}
         if getattr(args, "expert_interval", 1) > 1:
             if getattr(args, "moe_model_type", "megatron_moe") != "deepspeed_moe":
                 raise AssertionError("--expert-interval belongs to --moe-model-type deepspeed_moe; use --moe-layer-freq otherwise")
@@ -203,6 +216,18 @@ class LegacySpellingsFeature(Feature):
                     raise AssertionError(f"--optimized-mbs-list is not combined with --{other.replace('_', '-')}")
             if getattr(args, "schedules_method", None) in ("dualpipev", "dualpipe", "chimera"):
                 raise AssertionError("--optimized-mbs-list works with the 1F1B and interleaved schedules")
+        if getattr(args, "pp_schedule", None):
+            if args.pipeline_model_parallel_size < 2 or getattr(args, "num_layers_per_virtual_pipeline_stage", None) \
+                    or getattr(args, "schedules_method", None) in ("dualpipev", "dualpipe", "chimera"):
+                raise AssertionError("--pp-schedule-list orders the steps of the non-interleaved pipeline: it needs pipeline "
+                                     "parallelism without virtual stages and without --schedules-method")
+            from ..parallel.pipeline.plan import plan_from_stage_lists
+            n_mb = len(args.micro_batch_sizes) if getattr(args, "micro_batch_sizes", None) else \
+                args.global_batch_size // (args.micro_batch_size * args.data_parallel_size)
+            try:
+                plan_from_stage_lists(args.pipeline_model_parallel_size, n_mb, args.pp_schedule)
+            except (ValueError, RuntimeError) as e:
+                raise AssertionError(f"--pp-schedule-list: {e}")
         if not (0.0 <= args.save_memory_ratio < 1.0):
             raise AssertionError("--save-memory-ratio is a fraction in [0, 1)")
 

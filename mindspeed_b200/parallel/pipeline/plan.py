@@ -479,6 +479,35 @@ def validate(plan: Plan) -> None:
                     assert b < seen[((pipe, s - 1), "B", mb)]
 
 
+def plan_from_stage_lists(pp: int, n_mb: int, stages: Dict[str, List[str]]) -> Plan:
+    """A stored schedule of the non-interleaved pipeline: ``{"stage0": ["F1", "F2", "B1", ...], "stage1": [...]}`` - per
+    pipeline rank the order of its forward (F) and backward (B) steps with 1-based micro-batch numbers, the form
+    ``--pp-schedule-list`` carries (reference: mindspeed/core/pipeline_parallel/flexible_schedules.py:265-305, 431-446).
+    The lists are checked (every micro-batch once per kind, backward after forward) and turned into a slot table; an order
+    in which two ranks wait for each other is reported instead of being run."""
+    orders: List[List[Op]] = []
+    for r in range(pp):
+        key = f"stage{r}"
+        if key not in stages:
+            raise ValueError(f"--pp-schedule-list has no entry {key!r} (pipeline size {pp})")
+        ops, seen = [], set()
+        for tag in stages[key]:
+            kind, num = tag[:1].upper(), tag[1:]
+            if kind not in ("F", "B") or not num.isdigit() or not (1 <= int(num) <= n_mb):
+                raise ValueError(f"{key}: {tag!r} is not F<k> or B<k> with 1 <= k <= {n_mb}")
+            mb = int(num) - 1
+            if (kind, mb) in seen or (kind == "B" and ("F", mb) not in seen):
+                raise ValueError(f"{key}: {tag!r} is repeated or comes before its forward")
+            seen.add((kind, mb))
+            ops.append(Op(kind, 0, mb))
+        if len(seen) != 2 * n_mb:
+            raise ValueError(f"{key}: {len(seen)} steps listed, {2 * n_mb} expected (one F and one B per micro-batch)")
+        orders.append(ops)
+    plan = assign_slots(placement_1f1b(pp), orders, n_mb)
+    validate(plan)
+    return plan
+
+
 def insert_recompute(orders: List[List[Op]], mode: str = "bubble") -> List[List[Op]]:
     """Scheduler-placed recompute (RiPipe): the forward of (chunk, mb) drops its activations and an ``R`` op rebuilds
     them before the backward.

@@ -139,6 +139,9 @@ def _set_aux_loss_scale(config, num_microbatches, like):
         DSAIndexerLossScaler.set_loss_scale(scale)
 
 
+_STORED_PLANS: dict = {}
+
+
 def is_multi_parameter(config) -> bool:
     return bool(getattr(config, "use_multiparameter_pipeline_model_parallel", False)) and \
         bool(getattr(config, "pipeline_tensor_shapes", None))
@@ -286,6 +289,17 @@ def forward_backward_pipelining_without_interleaving(*, forward_step_func, data_
                                                      seq_length, micro_batch_size, decoder_seq_length=None,
                                                      forward_only=False, collect_non_loss_data=False, first_val_step=None):
     """Non-interleaved 1F1B: warm-up forwards, steady 1F1B, cool-down backwards."""
+    stored = getattr(_cfg(model), "pp_schedule", None)
+    if stored and not forward_only:
+        # --pp-schedule-list: the order of forward and backward steps per rank is given; run it as a plan
+        from .executor import run_plan
+        from .plan import plan_from_stage_lists
+        key = (ps.get_pipeline_model_parallel_world_size(), num_microbatches, id(stored))
+        if key not in _STORED_PLANS:
+            _STORED_PLANS[key] = plan_from_stage_lists(key[0], num_microbatches, stored)
+        return run_plan(_STORED_PLANS[key], forward_step_func=forward_step_func, data_iterator=data_iterator, model=model,
+                        num_microbatches=num_microbatches, seq_length=seq_length, micro_batch_size=micro_batch_size,
+                        forward_only=forward_only, collect_non_loss_data=collect_non_loss_data)
     if is_multi_parameter(_cfg(model)) or (getattr(_cfg(model), "moe_fb_overlap", False) and not forward_only) \
             or getattr(_cfg(model), "micro_batch_sizes", None):
         # list-valued stage interfaces and forward/backward overlap are handled by the plan executor (same 1F1B order, as data)

@@ -44,8 +44,8 @@ def test_older_spellings_are_rewritten(monkeypatch, tmp_path):
         _args(["--additional-config", str(cfgf)], 1, monkeypatch)
     a = _args(["--optimized-mbs-list", "[2,1,1]"], 1, monkeypatch)
     assert a.micro_batch_sizes == [2, 1, 1] and a.global_batch_size == 4 and a.micro_batch_size == 2
-    with pytest.raises(NotImplementedError, match="pp-schedule-list"):
-        _args(["--pp-schedule-list", "[[0,1],[1,0]]"], 1, monkeypatch)
+    with pytest.raises(NotImplementedError, match="ampipe"):
+        _args(["--ampipe-degree", "2"], 1, monkeypatch)
     with pytest.raises(AssertionError, match="use-nanopipe"):
         _args(["--use-nanopipe"], 1, monkeypatch)
 
@@ -154,6 +154,9 @@ def _train_mbs(rank, world, extra):
         for _ in range(2):
             ld, *_ = train_step(pg.forward_step, [it] * len(model) if len(model) > 1 else it, model, opt, sched)
             out.append(float(ld["lm loss"]) if "lm loss" in ld else None)
+    from mindspeed_b200.parallel.pipeline import schedules as S
+    if S._STORED_PLANS:
+        out.append("stored plan")
     return out
 
 
@@ -170,3 +173,28 @@ def test_micro_batches_of_different_sizes_give_the_same_step():
     from mindspeed_b200.training.arguments import parse_args, validate_args
     with pytest.raises(AssertionError, match="sums to"):
         validate_args(parse_args(args_list=BASE + ["--global-batch-size", "8", "--optimized-mbs-list", "[3,1]"]))
+
+
+def test_stored_pipeline_schedule_runs_as_given():
+    """--pp-schedule-list: an all-forward-then-all-backward order (not the 1F1B default) gives the same step; an order in
+    which the two ranks wait for each other is refused at start-up."""
+    import json
+    from dist_utils import run_distributed
+    from mindspeed_b200.parallel.pipeline.plan import plan_from_stage_lists
+    n = 8
+    gpipe = {f"stage{r}": [f"F{i}" for i in range(1, n + 1)] + [f"B{i}" for i in range(1, n + 1)] for r in range(2)}
+    plan = plan_from_stage_lists(2, n, gpipe)
+    assert [o.kind for slot in plan.table[1] for o in slot][:n] == ["F"] * n
+    ref = run_distributed(_train_mbs, 1, [])[0]
+    got = [r for r in run_distributed(_train_mbs, 2, ["--pipeline-model-parallel-size", "2", "--pp-schedule-list", json.dumps(gpipe)])
+           if r[0] is not None][0]
+    assert got[-1] == "stored plan" and got[:-1] == pytest.approx(ref, abs=2e-4), (ref, got)
+    bad = {"stage0": ["F1", "B1"] + [t for i in range(2, n + 1) for t in (f"F{i}", f"B{i}")],
+           "stage1": [f"F{i}" for i in range(n, 0, -1)] + [f"B{i}" for i in range(1, n + 1)]}
+    with pytest.raises(RuntimeError, match="deadlocks"):
+        plan_from_stage_lists(2, n, bad)
+    with pytest.raises(ValueError, match="expected"):
+        plan_from_stage_lists(2, n, {"stage0": ["F1", "B1"], "stage1": ["F1", "B1"]})
+    with pytest.raises(ValueError, match="before its forward"):
+        plan_from_stage_lists(2, 1, {"stage0": ["B1", "F1"], "stage1": ["F1", "B1"]})
+
