@@ -56,6 +56,7 @@ NO_EFFECT: Dict[str, str] = {
     "img-w": "read by vision-language model definitions built on this package (parallel/multimodal), not by the GPT entry point",
     "patch-dim": "read by vision-language model definitions built on this package (parallel/multimodal), not by the GPT entry point",
     "mbs-idx": "index used by the reference's profiling launcher while it tries the entries of a micro-batch size list; the list itself is --optimized-mbs-list",
+    "ampipe-tp-sp-comm-overlap": "the tensor-parallel communication of the attention output projection is already fused with its GEMM (--use-ascend-mc2 / level 2); --ampipe-degree pipelines what follows it",
     "adaptive-cp-only-reschedule": "adaptive CP here always keeps the sequence order and only schedules the exchanges",
     "adaptive-cp-without-coarse": "the mask is coarsened to context-parallel rank granularity for scheduling only; nothing else uses the coarse form",
     "gemm-gradient-accumulation-fusion": "weight gradients always accumulate into main_grad inside the GEMM epilogue",
@@ -78,8 +79,6 @@ NO_EFFECT: Dict[str, str] = {
 }
 
 UNSUPPORTED: Dict[str, str] = {
-    "ampipe-tp-sp-comm-overlap": "option of --ampipe-degree, for which the reference ships no forward path any more",
-    "ampipe-degree": "attention-MoE micro-pipelining: the reference registers and validates the flag (mindspeed/arguments.py:336-340, 803-820) but ships no forward path for it any more; here --moe-fb-overlap and --use-pipe-experts cover the overlap of MoE communication with compute",
 }
 
 

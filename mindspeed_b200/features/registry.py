@@ -202,6 +202,18 @@ class LegacySpellingsFeature(Feature):
             args.moe_layer_freq = str([1 if (i + 1) % n == 0 else 0 for i in range(args.num_layers)])
 
     def validate_args(self, args):
+        if getattr(args, "ampipe_degree", 1) > 1:
+            if not args.num_experts or getattr(args, "moe_model_type", "megatron_moe") != "deepspeed_moe":
+                raise AssertionError("--ampipe-degree pipelines the DeepSpeed-style MoE behind the attention: it needs --num-experts "
+                                     "and --moe-model-type deepspeed_moe")
+            local = args.seq_length // max(1, getattr(args, "context_parallel_size", 1))
+            if getattr(args, "sequence_parallel", False):
+                local //= args.tensor_model_parallel_size
+            if local % args.ampipe_degree != 0:
+                raise AssertionError("the sequence length per rank must be divisible by --ampipe-degree")
+            for other in ("use_nanopipe", "recompute_in_bubble", "recompute_in_advance", "adaptive_recompute_device_swap", "moe_fb_overlap"):
+                if getattr(args, other, False):
+                    raise AssertionError(f"--ampipe-degree is not combined with --{other.replace('_', '-')}")
         if getattr(args, "moe_adaptive_recompute_activation", False) and not args.num_experts:
             raise AssertionError("--moe-adaptive-recompute-activation needs a MoE model (--num-experts)")
         if getattr(args, "moe_adaptive_recompute_activation_scale", 2.0) <= 0:

@@ -126,9 +126,11 @@ class TransformerLayer(nn.Module):
         if is_moe is None:
             is_moe = _is_moe_layer(config, self.layer_number)
         self.is_moe = is_moe
+        self.ampipe, self._ampipe_streams = 1, None      # > 1 only with the DeepSpeed-style MoE (set below)
         if is_moe and getattr(config, "moe_model_type", "megatron_moe") == "deepspeed_moe":
             from ..legacy_moe.adapter import LegacyMoEBlock
             self.mlp = LegacyMoEBlock(config, layer_number=self.layer_number)
+            self.ampipe = int(getattr(config, "ampipe_degree", 1) or 1)
         elif is_moe:
             from ..parallel.moe.moe_layer import MoELayer
             self.mlp = MoELayer(config, layer_number=self.layer_number)
@@ -165,6 +167,43 @@ class TransformerLayer(nn.Module):
                 return self._forward(hidden_states, attention_mask, rotary_pos_emb, packed_seq_params, **kwargs)
         return self._forward(hidden_states, attention_mask, rotary_pos_emb, packed_seq_params, **kwargs)
 
+    def _ampipe_tail(self, attn_out, attn_bias, residual):
+        """``--ampipe-degree d``: everything behind the attention - residual add, norm, the DeepSpeed-style MoE, residual add -
+        runs on d slices of the sequence, slice after slice, each MoE on one of two side streams: while slice i's tokens are
+        exchanged and run through their experts, slice i + 1 is already normalised, gated and dispatched, so all-to-alls of
+        one slice overlap expert GEMMs of the other.  Every slice is routed on its own (capacity per slice).
+        reference: the ampipe option of the DeepSpeed-style MoE (mindspeed/arguments.py:336-340, 803-820; mindspeed/moe/utils.py:73-102
+        slice index helpers)."""
+        d = self.ampipe
+        s = attn_out.shape[0]
+        if s % d != 0:
+            raise ValueError(f"--ampipe-degree {d} must divide the local sequence length {s}")
+        use_streams = attn_out.is_cuda
+        if use_streams and self._ampipe_streams is None:
+            self._ampipe_streams = (torch.cuda.Stream(), torch.cuda.Stream())
+        main = torch.cuda.current_stream() if use_streams else None
+        outs = []
+        for i, (a, r) in enumerate(zip(attn_out.chunk(d, dim=0), residual.chunk(d, dim=0))):
+            h = _bda(a, attn_bias, r, self.hidden_dropout, self.training)
+            x = self.pre_mlp_layernorm(h)
+            if use_streams:
+                side = self._ampipe_streams[i % 2]
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    m, mb = self.mlp(x)
+                    o = _bda(m, mb, x if self.config.apply_residual_connection_post_layernorm else h, self.hidden_dropout, self.training)
+                x.record_stream(side)                 # made on the main stream, read on the side stream ...
+                h.record_stream(side)
+                o.record_stream(main)                 # ... and the other way round
+            else:
+                m, mb = self.mlp(x)
+                o = _bda(m, mb, x if self.config.apply_residual_connection_post_layernorm else h, self.hidden_dropout, self.training)
+            outs.append(o)
+        if use_streams:
+            for side in self._ampipe_streams:
+                main.wait_stream(side)
+        return torch.cat(outs, dim=0)
+
     def _forward(self, hidden_states, attention_mask=None, rotary_pos_emb=None, packed_seq_params=None, **kwargs):
         residual = hidden_states
         if self.recompute_norm and self.training and hidden_states.requires_grad:
@@ -189,6 +228,8 @@ class TransformerLayer(nn.Module):
                                                       packed_seq_params=packed_seq_params)
         if self.config.apply_residual_connection_post_layernorm:
             residual = ln
+        if self.ampipe > 1:
+            return self._ampipe_tail(attn_out, attn_bias, residual), None
         ln2 = None
         if (attn_bias is None and not (self.hidden_dropout > 0.0 and self.training) and not self.recompute_norm
                 and not self.recompute_mlp_block and not self.config.apply_residual_connection_post_layernorm and hasattr(self.pre_mlp_layernorm, "forward_add")):

@@ -59,7 +59,14 @@ def test_unsupported_flag_stops_and_no_effect_flag_is_announced(capsys):
     from mindspeed_b200.training.arguments import parse_args, validate_args
     base = ["--num-layers", "2", "--hidden-size", "64", "--num-attention-heads", "4", "--seq-length", "32",
             "--micro-batch-size", "1", "--vocab-size", "128"]
-    with pytest.raises(NotImplementedError, match="ampipe-degree"):
-        validate_args(parse_args(args_list=base + ["--ampipe-degree", "2"]))
+    # every registered flag is implemented or listed as having no effect; the refusal mechanism itself is kept and checked
+    from mindspeed_b200.features import flag_policy
+    assert flag_policy.UNSUPPORTED == {}
+    flag_policy.UNSUPPORTED["log-params-norm"] = "example entry"
+    try:
+        with pytest.raises(NotImplementedError, match="log-params-norm"):
+            validate_args(parse_args(args_list=base + ["--log-params-norm"]))
+    finally:
+        flag_policy.UNSUPPORTED.clear()
     validate_args(parse_args(args_list=base + ["--jit-compile"]))
     assert "--jit-compile has no effect here" in capsys.readouterr().out

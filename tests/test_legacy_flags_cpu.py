@@ -44,7 +44,7 @@ def test_older_spellings_are_rewritten(monkeypatch, tmp_path):
         _args(["--additional-config", str(cfgf)], 1, monkeypatch)
     a = _args(["--optimized-mbs-list", "[2,1,1]"], 1, monkeypatch)
     assert a.micro_batch_sizes == [2, 1, 1] and a.global_batch_size == 4 and a.micro_batch_size == 2
-    with pytest.raises(NotImplementedError, match="ampipe"):
+    with pytest.raises(AssertionError, match="deepspeed_moe"):
         _args(["--ampipe-degree", "2"], 1, monkeypatch)
     with pytest.raises(AssertionError, match="use-nanopipe"):
         _args(["--use-nanopipe"], 1, monkeypatch)

@@ -126,3 +126,35 @@ def test_deepspeed_style_moe_trains_and_pipelined_experts_change_nothing(tmp_pat
     assert plain[-1] < plain[0] - 0.1, plain
     for a, b in zip(plain, piped):
         assert abs(a - b) < 1e-5 * max(1.0, abs(a)), (plain, piped)
+
+
+def test_ampipe_pipelines_the_moe_over_sequence_slices(tmp_path):
+    """--ampipe-degree 2: residual add, norm and the DeepSpeed-style MoE behind the attention run on two sequence slices.
+    With --moe-no-drop every slice routes as the whole sequence would, so the training run is the same."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from dist_utils import run_distributed
+    from test_gpt_dataset_cpu import _corpus
+    prefix = str(tmp_path / "c")
+    _corpus(prefix, n_docs=60, vocab=100)
+    plain = run_distributed(_train_legacy, 2, prefix, ["--moe-aux-loss-coeff", "0.0", "--train-iters", "3"])[0]
+    sliced = run_distributed(_train_legacy, 2, prefix, ["--moe-aux-loss-coeff", "0.0", "--train-iters", "3", "--ampipe-degree", "2"])[0]
+    assert len(plain) == 3
+    for a, b in zip(plain, sliced):
+        assert abs(a - b) < 2e-5 * max(1.0, abs(a)), (plain, sliced)
+    # the slices were in fact used
+    from mindspeed_b200.config import TransformerConfig
+    import torch
+    cfg = TransformerConfig(num_layers=1, hidden_size=32, num_attention_heads=4, use_cpu_initialization=True, optimization_level=0)
+    cfg.ampipe_degree = 2
+    from mindspeed_b200.models.transformer import TransformerLayer
+    import torch.distributed as dist
+    from mindspeed_b200.parallel import parallel_state as ps
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", "29881")
+    if not dist.is_initialized():
+        dist.init_process_group("gloo", rank=0, world_size=1)
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(1, 1)
+    assert TransformerLayer(cfg, 1).ampipe == 1                      # a dense layer ignores the option
+    ps.destroy_model_parallel()
