@@ -8,7 +8,7 @@ reference: mindspeed/tokenizer/tokenizer.py:24-63 (PretrainedFromHF), mindspeed/
 """
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import Dict, List, Optional
 
 
 def _pad_vocab(n: int, divisible_by: int, tp: int) -> int:
