@@ -167,6 +167,16 @@ def _train(rank, world, extra, bidirectional):
     return out
 
 
+_REF = {}
+
+
+def _reference_losses(model_flags):
+    """The one-rank run every pipeline layout is compared with (computed once per model shape)."""
+    if model_flags not in _REF:
+        _REF[model_flags] = run_distributed(_train, 1, list(model_flags), False)[0]
+    return _REF[model_flags]
+
+
 @pytest.mark.parametrize("world,extra,bidir", [
     (2, ["--pipeline-model-parallel-size", "2"], False),
     (2, ["--pipeline-model-parallel-size", "2", "--num-layers-per-virtual-pipeline-stage", "1"], False),
@@ -197,7 +207,7 @@ def _train(rank, world, extra, bidirectional):
 def test_pipeline_matches_no_pipeline(world, extra, bidir):
     # flags that change the model itself also apply to the one-rank oracle
     model_flags = [extra[i + j] for i, x in enumerate(extra) if x in ("--vocab-size", "--num-layers") for j in (0, 1)]
-    ref = run_distributed(_train, 1, model_flags, False)[0]
+    ref = _reference_losses(tuple(model_flags))
     res = run_distributed(_train, world, extra, bidir)
     have = [r for r in res if r[0] is not None]
     # bidirectional schedules compute half of the micro-batches' losses at each end of the pipeline

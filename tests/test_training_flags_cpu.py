@@ -18,7 +18,8 @@ from test_pipeline_cpu import _train  # noqa: E402
     (["--qat-scheme", "w8a16"], False),
 ])
 def test_flag_runs_and_matches_plain_training(extra, exact):
-    ref = run_distributed(_train, 1, [], False)[0]
+    from test_pipeline_cpu import _reference_losses
+    ref = _reference_losses(())
     got = run_distributed(_train, 1, extra, False)[0]
     for a, b in zip(ref, got):
         tol = 2e-4 if exact else 2e-2
