@@ -218,6 +218,18 @@ def _core_args(p: argparse.ArgumentParser):
     g.add_argument("--dist-ckpt-optim-sharding-type", type=str, default="fully_sharded_bucket_space",
                    choices=["fully_sharded_bucket_space", "dp_zero_gather_scatter", "fully_sharded_model_space"])
     g.add_argument("--tensorboard-dir", type=str, default=None)
+    g.add_argument("--tensorboard-log-interval", type=int, default=1, help="write scalars every this many iterations")
+    g.add_argument("--tensorboard-queue-size", type=int, default=1000)
+    g.add_argument("--log-timers-to-tensorboard", action="store_true")
+    g.add_argument("--log-memory-to-tensorboard", action="store_true")
+    g.add_argument("--log-world-size-to-tensorboard", action="store_true")
+    g.add_argument("--log-validation-ppl-to-tensorboard", action="store_true")
+    g.add_argument("--no-log-learnig-rate-to-tensorboard", "--no-log-learning-rate-to-tensorboard", action="store_false",
+                   dest="log_learning_rate_to_tensorboard")
+    g.add_argument("--no-log-loss-scale-to-tensorboard", action="store_false", dest="log_loss_scale_to_tensorboard")
+    g.add_argument("--wandb-project", type=str, default="", help="also send the scalars to Weights & Biases (when the package exists)")
+    g.add_argument("--wandb-exp-name", type=str, default="")
+    g.add_argument("--wandb-save-dir", type=str, default="")
     g.add_argument("--log-throughput", action="store_true")
     g.add_argument("--num-workers", type=int, default=0)
     g.add_argument("--reset-position-ids", action="store_true")

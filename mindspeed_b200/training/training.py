@@ -342,25 +342,38 @@ class ScalarWriter:
     """--tensorboard-dir: scalars go to a TensorBoard event file when the tensorboard package is importable, and always to
     ``scalars.jsonl`` in the same directory (one {"step", "tag", "value"} object per line)."""
 
-    def __init__(self, log_dir):
+    def __init__(self, log_dir, queue_size=1000, wandb_project="", wandb_name="", wandb_dir="", config=None):
         os.makedirs(log_dir, exist_ok=True)
         self.f = open(os.path.join(log_dir, "scalars.jsonl"), "a")
         try:
             from torch.utils.tensorboard import SummaryWriter
-            self.tb = SummaryWriter(log_dir=log_dir)
+            self.tb = SummaryWriter(log_dir=log_dir, max_queue=queue_size)
         except Exception:
             self.tb = None
+        self.wandb = None
+        if wandb_project:                                  # --wandb-project: a third sink, when the package is installed
+            try:
+                import wandb
+                wandb.init(project=wandb_project, name=wandb_name or None, dir=wandb_dir or log_dir, config=config or {})
+                self.wandb = wandb
+            except Exception:
+                print_rank_last("note: --wandb-project given but the wandb package is not usable here; scalars go to "
+                                f"{log_dir} only")
 
     def add_scalar(self, tag, value, step):
         self.f.write(json.dumps({"step": int(step), "tag": tag, "value": float(value)}) + "\n")
         self.f.flush()
         if self.tb is not None:
             self.tb.add_scalar(tag, float(value), int(step))
+        if self.wandb is not None:
+            self.wandb.log({tag: float(value)}, step=int(step))
 
     def close(self):
         self.f.close()
         if self.tb is not None:
             self.tb.close()
+        if self.wandb is not None:
+            self.wandb.finish()
 
 
 def evaluate(forward_step_func, data_iterator, model, eval_iters):
@@ -441,7 +454,13 @@ def train(forward_step_func, model, optimizer, opt_param_scheduler, train_data_i
         prof = build_profiler(args)
         prof.__enter__()
     history = []
-    writer = ScalarWriter(args.tensorboard_dir) if (args.tensorboard_dir and args.rank == args.world_size - 1) else None
+    writer = None
+    if args.tensorboard_dir and args.rank == args.world_size - 1:
+        writer = ScalarWriter(args.tensorboard_dir, getattr(args, "tensorboard_queue_size", 1000), getattr(args, "wandb_project", ""),
+                              getattr(args, "wandb_exp_name", ""), getattr(args, "wandb_save_dir", ""),
+                              {k: v for k, v in vars(args).items() if isinstance(v, (int, float, str, bool))})
+        if getattr(args, "log_world_size_to_tensorboard", False):
+            writer.add_scalar("world-size", args.world_size, iteration)
     routers = _moe_routers(model) if (getattr(args, "print_expert_load", False) or getattr(args, "enable_expert_placement", False)) else []
     planners = {}
     while iteration < args.train_iters:
@@ -480,11 +499,22 @@ def train(forward_step_func, model, optimizer, opt_param_scheduler, train_data_i
                             if x != 0:
                                 loss_dict[f"{name} layer {i + 1}"] = x
             training_log(loss_dict, iteration, elapsed, grad_norm, skipped, optimizer.param_groups[0]["lr"])
-            if writer is not None:
+            if writer is not None and iteration % max(1, getattr(args, "tensorboard_log_interval", 1)) == 0:
                 for k, v in loss_dict.items():
                     writer.add_scalar(k, float(v), iteration)
-                writer.add_scalar("learning-rate", optimizer.param_groups[0]["lr"], iteration)
-                writer.add_scalar("iteration-time", elapsed, iteration)
+                if getattr(args, "log_learning_rate_to_tensorboard", True):
+                    writer.add_scalar("learning-rate", optimizer.param_groups[0]["lr"], iteration)
+                if getattr(args, "log_loss_scale_to_tensorboard", True) and hasattr(optimizer, "get_loss_scale"):
+                    writer.add_scalar("loss-scale", float(optimizer.get_loss_scale()), iteration)
+                if getattr(args, "log_timers_to_tensorboard", False):
+                    writer.add_scalar("iteration-time", elapsed, iteration)
+                    writer.add_scalar("tokens-per-second", args.global_batch_size * args.seq_length / elapsed, iteration)
+                else:
+                    writer.add_scalar("iteration-time", elapsed, iteration)
+                if getattr(args, "log_memory_to_tensorboard", False) and torch.cuda.is_available():
+                    writer.add_scalar("mem-allocated-bytes", torch.cuda.memory_allocated(), iteration)
+                    writer.add_scalar("mem-max-allocated-bytes", torch.cuda.max_memory_allocated(), iteration)
+                    writer.add_scalar("mem-reserved-bytes", torch.cuda.memory_reserved(), iteration)
                 if grad_norm is not None:
                     writer.add_scalar("grad-norm", float(grad_norm), iteration)
         if routers and (iteration % args.log_interval == 0 or
@@ -496,6 +526,8 @@ def train(forward_step_func, model, optimizer, opt_param_scheduler, train_data_i
             if writer is not None:
                 for k, v in ev.items():
                     writer.add_scalar(f"{k} validation", v, iteration)
+                    if getattr(args, "log_validation_ppl_to_tensorboard", False) and "loss" in k:
+                        writer.add_scalar(f"{k} validation ppl", math.exp(min(20.0, v)), iteration)
         history.append({k: float(v) for k, v in loss_dict.items()})
         if args.save and args.save_interval and iteration % args.save_interval == 0:
             from ..checkpointing import save_checkpoint

@@ -37,6 +37,25 @@ def test_eval_loop_and_scalar_file():
         assert max(r["step"] for r in rows) == 4
 
 
+def test_scalar_sinks_follow_the_logging_flags():
+    with tempfile.TemporaryDirectory() as d:
+        _, out = run_distributed(_train_with, 1, ["--train-iters", "4", "--eval-interval", "4", "--eval-iters", "1", "--tensorboard-dir", d,
+                                                  "--tensorboard-log-interval", "2", "--log-world-size-to-tensorboard",
+                                                  "--log-validation-ppl-to-tensorboard", "--log-timers-to-tensorboard",
+                                                  "--no-log-learning-rate-to-tensorboard", "--wandb-project", "unit-test"])[0]
+        rows = [json.loads(l) for l in open(os.path.join(d, "scalars.jsonl"))]
+        tags = {r["tag"] for r in rows}
+        assert {"world-size", "lm loss", "tokens-per-second", "lm loss validation ppl"} <= tags and "learning-rate" not in tags
+        assert sorted({r["step"] for r in rows if r["tag"] == "lm loss"}) == [2, 4]          # every second iteration
+        ppl = next(r["value"] for r in rows if r["tag"] == "lm loss validation ppl")
+        val = next(r["value"] for r in rows if r["tag"] == "lm loss validation")
+        assert ppl == pytest.approx(__import__("math").exp(val), rel=1e-6)
+        try:
+            import wandb  # noqa: F401
+        except ImportError:
+            assert "wandb package is not usable" in out
+
+
 def test_lr_warmup_fraction_sets_warmup_steps():
     from mindspeed_b200.training.training import OptimizerParamScheduler
 
