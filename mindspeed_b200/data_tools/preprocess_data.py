@@ -27,6 +27,17 @@ def main(argv=None) -> int:
     ap.add_argument("--pad-to-multiple-of", type=int, default=1,
                     help="pretrain handlers: pad every document to a multiple of this many tokens")
     ap.add_argument("--train-on-inputs", action="store_true", help="instruction handlers: loss on the prompt tokens too")
+    ap.add_argument("--append-eod", action="store_true", help="accepted for script compatibility: the end-of-document token is "
+                    "appended unless --no-append-eod is given")
+    ap.add_argument("--keep-newlines", action="store_true", help="--split-sentences: sentences keep their line breaks")
+    ap.add_argument("--vocab-file", default=None, help="GPT2BPETokenizer: vocab.json")
+    ap.add_argument("--merge-file", default=None, help="GPT2BPETokenizer: merges.txt")
+    ap.add_argument("--tokenizer-not-use-fast", action="store_true")
+    ap.add_argument("--make-vocab-size-divisible-by", type=int, default=128)
+    ap.add_argument("--pad-vocab-size-to", type=int, default=None)
+    ap.add_argument("--workers", type=int, default=1, help="accepted; records are tokenised in this process")
+    ap.add_argument("--log-interval", type=int, default=100)
+    ap.add_argument("--dataset-impl", default="mmap", choices=["mmap", "lazy", "cached"], help="accepted; the files are memory-mapped")
     a = ap.parse_args(argv)
     a.padded_vocab_size = 1          # not needed here; stops build_tokenizer from touching parallel sizes
     tok = build_tokenizer(a)

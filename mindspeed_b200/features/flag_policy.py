@@ -57,6 +57,9 @@ NO_EFFECT: Dict[str, str] = {
     "patch-dim": "read by vision-language model definitions built on this package (parallel/multimodal), not by the GPT entry point",
     "mbs-idx": "index used by the reference's profiling launcher while it tries the entries of a micro-batch size list; the list itself is --optimized-mbs-list",
     "ampipe-tp-sp-comm-overlap": "the tensor-parallel communication of the attention output projection is already fused with its GEMM (--use-ascend-mc2 / level 2); --ampipe-degree pipelines what follows it",
+    "moe-hierarchical-alltoallv": "two-level all-to-all for fabrics where the ranks inside a node are closer than the ones across; inside one NVSwitch domain every peer is one hop away and the exchange is flat (peer-memory dispatch at level 2)",
+    "no-create-attention-mask-in-dataloader": "the data path never builds attention masks; the kernels generate the causal mask",
+    "overlap-param-gather-with-optimizer-step": "parameter all-gathers start bucket by bucket right after the update (--overlap-param-gather); there is no separate staging to overlap",
     "adaptive-cp-only-reschedule": "adaptive CP here always keeps the sequence order and only schedules the exchanges",
     "adaptive-cp-without-coarse": "the mask is coarsened to context-parallel rank granularity for scheduling only; nothing else uses the coarse form",
     "gemm-gradient-accumulation-fusion": "weight gradients always accumulate into main_grad inside the GEMM epilogue",

@@ -61,6 +61,9 @@ def _core_args(p: argparse.ArgumentParser):
     g = p.add_argument_group("moe")
     g.add_argument("--num-experts", type=int, default=None)
     g.add_argument("--moe-router-topk", type=int, default=2)
+    g.add_argument("--moe-hierarchical-alltoallv", action="store_true")
+    g.add_argument("--no-create-attention-mask-in-dataloader", action="store_false", dest="create_attention_mask_in_dataloader")
+    g.add_argument("--overlap-param-gather-with-optimizer-step", action="store_true")
     g.add_argument("--moe-router-dtype", type=str, default=None, choices=[None, "fp32", "fp64"],
                    help="precision of the router's logits, softmax and top-k (fp32 when unset)")
     g.add_argument("--seq-aux", action="store_true", help="the same as --moe-router-load-balancing-type seq_aux_loss")
