@@ -80,10 +80,11 @@ class GeneralPretrainHandler(BaseHandler):
     ``vocab_size`` (one past the vocabulary, dropped from the loss by the training data path) so that its length, end-of-
     document token included, is a multiple - the layout context parallelism wants for packed documents."""
 
-    def __init__(self, tokenizer, text_key: str = "text", split_sentences: bool = False, pad_to_multiple_of: int = 1, **kw):
+    def __init__(self, tokenizer, text_key: str = "text", split_sentences: bool = False, pad_to_multiple_of: int = 1,
+                 keep_newlines: bool = False, **kw):
         super().__init__(tokenizer, **kw)
         self.text_keys = [k for k in str(text_key).split(",") if k]
-        self.split_sentences, self.pad = split_sentences, max(1, int(pad_to_multiple_of))
+        self.split_sentences, self.pad, self.keep_newlines = split_sentences, max(1, int(pad_to_multiple_of)), keep_newlines
 
     def text(self, record) -> Optional[str]:
         parts = [record.get(k) for k in self.text_keys]
@@ -94,7 +95,7 @@ class GeneralPretrainHandler(BaseHandler):
         text = self.text(record)
         if not text:
             return None
-        sentences = split_sentences(text) if self.split_sentences else [text]
+        sentences = split_sentences(text, self.keep_newlines) if self.split_sentences else [text]
         parts = [list(self.tok.tokenize(s)) for s in sentences if s]
         parts = [p for p in parts if p]
         if not parts:

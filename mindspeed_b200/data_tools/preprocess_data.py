@@ -45,7 +45,7 @@ def main(argv=None) -> int:
     from .data_handler import HANDLERS, GeneralInstructionHandler, GeneralPretrainHandler
     cls = HANDLERS.get(a.handler_name)
     if cls is not None and issubclass(cls, GeneralPretrainHandler):
-        kw.update(split_sentences=a.split_sentences, pad_to_multiple_of=a.pad_to_multiple_of)
+        kw.update(split_sentences=a.split_sentences, pad_to_multiple_of=a.pad_to_multiple_of, keep_newlines=a.keep_newlines)
         if cls is GeneralPretrainHandler:
             kw["text_key"] = a.json_key
     if cls is not None and issubclass(cls, GeneralInstructionHandler):
