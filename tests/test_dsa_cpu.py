@@ -108,7 +108,7 @@ def single_rank():
     from mindspeed_b200.parallel import parallel_state as ps
     import torch.distributed as dist
     import os
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", "29877")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", str(__import__("dist_utils")._free_port()))
     if not dist.is_initialized():
         dist.init_process_group("gloo", rank=0, world_size=1)
     ps.destroy_model_parallel()

@@ -122,7 +122,7 @@ def test_dense_bias_flag_adds_the_projection_bias():
     from mindspeed_b200.models.attention import SelfAttention
     from mindspeed_b200.parallel import parallel_state as ps
     import torch.distributed as dist
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", "29878")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", str(__import__("dist_utils")._free_port()))
     if not dist.is_initialized():
         dist.init_process_group("gloo", rank=0, world_size=1)
     ps.destroy_model_parallel()

@@ -145,7 +145,7 @@ def test_router_dtype_and_seq_aux(monkeypatch):
     from mindspeed_b200.parallel import parallel_state as ps
     from mindspeed_b200.parallel.moe.router import TopKRouter
     import torch.distributed as dist
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", "29879")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", str(__import__("dist_utils")._free_port()))
     if not dist.is_initialized():
         dist.init_process_group("gloo", rank=0, world_size=1)
     ps.destroy_model_parallel()

@@ -151,7 +151,7 @@ def test_ampipe_pipelines_the_moe_over_sequence_slices(tmp_path):
     from mindspeed_b200.models.transformer import TransformerLayer
     import torch.distributed as dist
     from mindspeed_b200.parallel import parallel_state as ps
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", "29881")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", str(__import__("dist_utils")._free_port()))
     if not dist.is_initialized():
         dist.init_process_group("gloo", rank=0, world_size=1)
     ps.destroy_model_parallel()
