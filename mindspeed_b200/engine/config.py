@@ -67,6 +67,7 @@ class ParallelEngineConfig:
     tensor_parallel_size: int = 1
     expert_parallel_size: int = 1
     fully_shard_parallel_size: Optional[int] = None      # None: world / tp
+    ulysses_parallel_size: int = 1                       # sequence slices per data-parallel group (engine/context_parallel.py)
     tp_plan: TPPlanConfig = dataclasses.field(default_factory=TPPlanConfig)
     ep_plan: EPPlanConfig = dataclasses.field(default_factory=EPPlanConfig)
     fsdp_plan: FSDPPlanConfig = dataclasses.field(default_factory=FSDPPlanConfig)
@@ -85,6 +86,9 @@ class ParallelEngineConfig:
         fs = self.fully_shard_parallel_size or dp
         if dp % fs != 0:
             raise ValueError(f"fully_shard_parallel_size {fs} must divide world / tp = {dp}")
+        cp = self.ulysses_parallel_size
+        if cp < 1 or dp % cp != 0:
+            raise ValueError(f"ulysses_parallel_size {cp} must divide world / tp = {dp}")
         for pat, kind in self.tp_plan.rules.items():
             if kind not in ("colwise", "rowwise", "vocab"):
                 raise ValueError(f"tp plan rule {pat!r}: unknown style {kind!r}")

@@ -60,6 +60,18 @@ class MindSpeedParallelEngine(nn.Module):
                     g = dist.new_group(sub) if ep > 1 else None
                     if rank in sub:
                         self.ep_group = g
+        # Ulysses context parallelism: runs of ``ulysses_parallel_size`` consecutive data-parallel indices hold slices of one
+        # sequence; they stay data-parallel for gradients (every rank sees different tokens)
+        self.cp_group = None
+        cp = config.ulysses_parallel_size
+        if world > 1 and cp > 1:
+            for t in range(tp):
+                ranks = list(range(t, world, tp))
+                for i in range(0, dp, cp):
+                    sub = ranks[i:i + cp]
+                    g = dist.new_group(sub)
+                    if rank in sub:
+                        self.cp_group = g
         self.stats = {}
         if config.quantization is not None:
             from .quantization import convert_linears
@@ -121,7 +133,18 @@ class MindSpeedParallelEngine(nn.Module):
         return n
 
     def forward(self, *a, **kw):
+        if self.cp_group is not None:
+            from .context_parallel import ulysses_attention_patch
+            with ulysses_attention_patch(self.cp_group):
+                return self.model(*a, **kw)
         return self.model(*a, **kw)
+
+    def shard_sequence(self, x, dim: int = 1):
+        """This rank's slice of a full-sequence input (tokens, labels, position ids) under Ulysses context parallelism."""
+        if self.cp_group is None:
+            return x
+        from .context_parallel import shard_sequence
+        return shard_sequence(x, self.cp_group, dim)
 
     def loss(self, hidden: torch.Tensor, lm_head_weight: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100):
         """LM loss from final hidden states; chunked when ``loss_chunk_size`` is set."""
