@@ -23,6 +23,7 @@ class EPPlanConfig:
 @dataclasses.dataclass
 class FSDPPlanConfig:
     wrap: List[str] = dataclasses.field(default_factory=list)
+    ignored_modules: List[str] = dataclasses.field(default_factory=list)      # kept whole on every rank, gradients all-reduced
     shard_size: Optional[int] = None
     zero1_over_replicas: bool = False
     param_dtype: Optional[str] = None

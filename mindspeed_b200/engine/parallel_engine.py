@@ -95,7 +95,7 @@ class MindSpeedParallelEngine(nn.Module):
                                  param_dtype=config.fsdp_plan.param_dtype)
                 self.expert_fsdp = FullyShardedDataParallel(model, eplan, shard_group=self._edp_group(world, tp, dp, ep, rank) or "local",
                                                             replica_group=None, grad_scale=1.0 / ep, root_unit=False)
-            plan = FSDPPlan(wrap=tuple(config.fsdp_plan.wrap), shard_size=fs, zero1_over_replicas=config.fsdp_plan.zero1_over_replicas,
+            plan = FSDPPlan(wrap=tuple(config.fsdp_plan.wrap), ignore=tuple(config.fsdp_plan.ignored_modules), shard_size=fs, zero1_over_replicas=config.fsdp_plan.zero1_over_replicas,
                             param_dtype=config.fsdp_plan.param_dtype, reduce_dtype=config.fsdp_plan.reduce_dtype)
             self.model = FullyShardedDataParallel(model, plan, dp_group_ranks=self.dp_ranks,
                                                   all_dp_rank_lists=[list(range(t, world, tp)) for t in range(tp)])

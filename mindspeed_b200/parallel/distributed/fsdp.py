@@ -37,6 +37,8 @@ from ...utils.patterns import match as _match
 class FSDPPlan:
     """Which modules to shard and how.  ``wrap`` holds class names or glob patterns over qualified module names."""
     wrap: Sequence[str] = ("TransformerLayer",)
+    ignore: Sequence[str] = ()                # modules (class names / patterns) whose parameters stay whole on every rank:
+    #                                           not sharded, gradients averaged over the data-parallel ranks after backward
     shard_size: Optional[int] = None          # ranks per shard group (None: the whole data-parallel group)
     zero1_over_replicas: bool = False         # LayerZeRO: optimizer state also split over the replica group
     reshard_after_forward: bool = True
@@ -331,6 +333,14 @@ class FullyShardedDataParallel(nn.Module):
             shard_group, replica_group = build_groups(ranks, self.plan.shard_size, all_dp_rank_lists)
         self.shard_group, self.replica_group = shard_group, replica_group
         self.units: List[ShardedUnit] = []
+        self.ignored: List[nn.Parameter] = []
+        self._dp_ranks = dp_group_ranks
+        for name, sub in module.named_modules():
+            if name and any(sub.__class__.__name__ == pat or _match(name, pat) for pat in self.plan.ignore):
+                for p in sub.parameters():
+                    if not getattr(p, "_fsdp_owned", False):
+                        p._fsdp_owned = True               # keeps every unit from taking it
+                        self.ignored.append(p)
         for name, sub in module.named_modules():
             if sub is module:
                 continue
@@ -369,10 +379,22 @@ class FullyShardedDataParallel(nn.Module):
         return self.module.set_input_tensor(t)
 
     def optimizer_params(self) -> List[nn.Parameter]:
-        return [u.opt_param for u in self.units]
+        return [u.opt_param for u in self.units] + [p for p in self.ignored if p.requires_grad]
+
+    def _sync_ignored(self):
+        """Average the gradients of the unsharded (``plan.ignore``) parameters over shard and replica group."""
+        for group in (self.shard_group, self.replica_group):
+            n = M._ws(group)
+            if n > 1:
+                for p in self.ignored:
+                    if p.grad is not None:
+                        dist.all_reduce(p.grad, group=group)
+                        p.grad /= n
 
     def finish_grad_sync(self):
         """Reduce units whose backward never fired completely (unused parameters)."""
+        if self.ignored:
+            self._sync_ignored()
         for u in self.units:
             if not u._reduced and (u._pending_grads > 0 or any(p.grad is not None for p in u.params)):
                 u.reduce_grads()
@@ -384,6 +406,8 @@ class FullyShardedDataParallel(nn.Module):
     def zero_grad(self, set_to_none: bool = True):
         for u in self.units:
             u.opt_param.grad = None
+        for p in self.ignored:
+            p.grad = None
 
     def post_step(self):
         for u in self.units:
@@ -397,6 +421,9 @@ class FullyShardedDataParallel(nn.Module):
             for p, t in zip(u.params, u.full_parameters()):
                 if id(p) in names:
                     out[names[id(p)]] = t
+        for p in self.ignored:                         # whole on every rank already
+            if id(p) in names:
+                out[names[id(p)]] = p.detach().clone()
         return out
 
     def post_load(self):
@@ -489,6 +516,9 @@ class ShardedAdamW:
     def __init__(self, wrappers: Sequence[FullyShardedDataParallel], lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
                  clip_grad: float = 0.0):
         self.wrappers = list(wrappers)
+        if any(w.ignored for w in self.wrappers):
+            raise NotImplementedError("FSDP plan 'ignore' keeps parameters outside the flat shards this optimizer updates; use it "
+                                      "with an optimizer built over optimizer_params() (the engine), not with the training loop")
         self.param_groups = [dict(lr=lr, weight_decay=weight_decay, betas=betas, eps=eps, step=0)]
         self.clip_grad = clip_grad
         self.state = []

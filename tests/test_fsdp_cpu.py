@@ -59,15 +59,17 @@ def _reference(world, steps):
     return losses, {k: v.detach().clone() for k, v in net.state_dict().items()}
 
 
-def _rank(rank, world, steps, shard_size, zero1):
+def _rank(rank, world, steps, shard_size, zero1, ignore=()):
     import torch.distributed as dist
     from mindspeed_b200.parallel.distributed.fsdp import FSDPPlan, fully_shard
     dist.init_process_group("gloo", rank=rank, world_size=world)
     torch.manual_seed(0)
     net = Net()
-    plan = FSDPPlan(wrap=["Block"], shard_size=shard_size, zero1_over_replicas=zero1)
+    plan = FSDPPlan(wrap=["Block"], shard_size=shard_size, zero1_over_replicas=zero1, ignore=tuple(ignore))
     model = fully_shard(net, plan)
     assert len(model.units) == 4                       # three blocks + root
+    if ignore:
+        assert len(model.ignored) == 2 and all(p.numel() > 0 for p in model.ignored)       # out.weight, out.bias stay whole
     ms = model.memory_summary()
     assert ms["param_shard_bytes"] * (shard_size or world) >= ms["unsharded_bytes"]
     opt = torch.optim.AdamW(model.optimizer_params(), lr=1e-2, weight_decay=0.01)
@@ -102,6 +104,18 @@ def test_sharded_training_matches_reference(world, shard_size, zero1):
             if k == "unused":
                 continue
             assert torch.allclose(torch.as_tensor(sd[k]), v, atol=2e-5, rtol=1e-4), k
+
+
+def test_ignored_modules_stay_whole_and_train_the_same():
+    """``FSDPPlan.ignore``: the output layer is not sharded; its gradients are averaged over the ranks instead."""
+    steps = 3
+    ref_losses, ref_sd = _reference(2, steps)
+    for losses, sd in run_distributed(_rank, 2, steps, None, False, ["out"]):
+        for a, b in zip(losses, ref_losses):
+            assert abs(a - b) < 1e-5 * max(1.0, abs(b)), (losses, ref_losses)
+        for k in ("out.weight", "out.bias", "inp.weight", "blocks.1.fc.weight"):
+            if k in ref_sd:
+                assert torch.allclose(torch.as_tensor(sd[k]), ref_sd[k], atol=2e-5, rtol=1e-4), k
 
 
 def test_plan_from_dict_and_yaml(tmp_path):
