@@ -298,6 +298,8 @@ class TransformerConfig(ModelParallelConfig):
 class MLATransformerConfig(TransformerConfig):
     """Multi-head latent attention (DeepSeek-V2/V3)."""
     multi_latent_attention: bool = True
+    recompute_mla_up_proj: bool = False       # rebuild the q / kv up-projection outputs in backward
+    mla_swap_core_attn_out: bool = False      # tensors the core attention saves wait in pinned host memory
     q_lora_rank: Optional[int] = 512
     kv_lora_rank: int = 512
     qk_head_dim: int = 128

@@ -60,6 +60,9 @@ NO_EFFECT: Dict[str, str] = {
     "moe-hierarchical-alltoallv": "two-level all-to-all for fabrics where the ranks inside a node are closer than the ones across; inside one NVSwitch domain every peer is one hop away and the exchange is flat (peer-memory dispatch at level 2)",
     "no-create-attention-mask-in-dataloader": "the data path never builds attention masks; the kernels generate the causal mask",
     "overlap-param-gather-with-optimizer-step": "parameter all-gathers start bucket by bucket right after the update (--overlap-param-gather); there is no separate staging to overlap",
+    "mla-mm-split": "whether the latent up-projection runs as one GEMM or as separate no-position / rotary and key / value GEMMs; here it is one GEMM per projection whose output is split by views",
+    "mla-up-proj-tp-overlap": "tensor-parallel communication of the projections is fused with their GEMMs at level 2 (--use-ascend-mc2)",
+    "mtp-mem-efficient-logits": "the multi-token-prediction heads compute their loss with the vocabulary-parallel cross-entropy kernels on the 16-bit logits; no fp32 copy of the logits is kept",
     "adaptive-cp-only-reschedule": "adaptive CP here always keeps the sequence order and only schedules the exchanges",
     "adaptive-cp-without-coarse": "the mask is coarsened to context-parallel rank granularity for scheduling only; nothing else uses the coarse form",
     "gemm-gradient-accumulation-fusion": "weight gradients always accumulate into main_grad inside the GEMM epilogue",

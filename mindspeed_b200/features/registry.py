@@ -553,6 +553,11 @@ class MLAFeature(Feature):
         add_arg(g, "--v-head-dim", type=int, default=128)
         add_arg(g, "--qk-rope-head-dim", "--qk-pos-emb-head-dim", dest="qk_rope_head_dim", type=int, default=64)
         add_arg(g, "--qk-nope-head-dim", "--qk-head-dim", dest="qk_nope_head_dim", type=int, default=128)
+        add_arg(g, "--recompute-mla-up-proj", action="store_true", help="rebuild the q / kv up-projection outputs in backward")
+        add_arg(g, "--mla-swap-core-attn-out", action="store_true", help="tensors the MLA core attention saves wait in host memory")
+        add_arg(g, "--mla-mm-split", action="store_true")
+        add_arg(g, "--mla-up-proj-tp-overlap", action="store_true")
+        add_arg(g, "--mtp-mem-efficient-logits", action="store_true")
         add_arg(g, "--rope-scaling-type", type=str, default=None, choices=[None, "yarn"])
         add_arg(g, "--rope-scaling-factor", "--rotary-scaling-factor", dest="rope_scaling_factor", type=float, default=1.0)
         add_arg(g, "--rope-scaling-original-max-position-embeddings", type=int, default=4096)

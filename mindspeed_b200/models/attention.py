@@ -242,12 +242,20 @@ class MLASelfAttention(nn.Module):
         cfg = self.config
         x = hidden_states
         sp = cfg.sequence_parallel and ps.get_tensor_model_parallel_world_size() > 1
+        # --recompute-mla-up-proj: the up-projections' outputs (the widest activations of the layer) are rebuilt in backward
+        re_up = bool(getattr(cfg, "recompute_mla_up_proj", False)) and self.training and torch.is_grad_enabled()
+
+        def up(lin, t):
+            if re_up and t.requires_grad:
+                from torch.utils.checkpoint import checkpoint
+                return checkpoint(lambda z: lin(z)[0], t, use_reentrant=False)
+            return lin(t)[0]
         if cfg.q_lora_rank is None:
             qc = x
             q, _ = self.linear_q_proj(x)
         else:
             qc = self.q_layernorm(self.linear_q_down_proj(x))
-            q, _ = self.linear_q_up_proj(qc)
+            q = up(self.linear_q_up_proj, qc)
         s, b = q.shape[0], q.shape[1]
         q = q.view(s, b, self.n, self.q_head_dim)
         kvc = self.linear_kv_down_proj(x)
@@ -257,7 +265,7 @@ class MLASelfAttention(nn.Module):
         kv_lat = self.kv_layernorm(kv_lat.contiguous())
         if not self.dsa:                            # the sparse path applies the up-projection weight itself
             kv_in = M.scatter_to_sequence_parallel_region(kv_lat) if sp else kv_lat
-            kv, _ = self.linear_kv_up_proj(kv_in)
+            kv = up(self.linear_kv_up_proj, kv_in)
             kv = kv.view(s, b, self.n, self.qk_nope + self.v_dim)
             k_nope, v = kv.split([self.qk_nope, self.v_dim], dim=-1)
         q_nope, q_pe = q.split([self.qk_nope, self.qk_rope], dim=-1)
@@ -276,7 +284,14 @@ class MLASelfAttention(nn.Module):
             ctx = dsa_attention(self, xf, qcf, qf, kv_lat, k_pe, rotary_pos_emb)
             return self.linear_proj(ctx)
         kf = torch.cat((k_nope, k_pe.expand(s, b, self.n, self.qk_rope)), dim=-1)
-        ctx = self.core_attention(qf, kf, v.contiguous(), attention_mask, packed_seq_params)
+        if getattr(cfg, "mla_swap_core_attn_out", False) and self.training and torch.is_grad_enabled() and qf.is_cuda:
+            # --mla-swap-core-attn-out: what the attention keeps for backward (q, k, v, output, softmax statistics) waits in
+            # pinned host memory
+            from ..memory.host_offload import OffloadSaved
+            with OffloadSaved():
+                ctx = self.core_attention(qf, kf, v.contiguous(), attention_mask, packed_seq_params)
+        else:
+            ctx = self.core_attention(qf, kf, v.contiguous(), attention_mask, packed_seq_params)
         return self.linear_proj(ctx)
 
 

@@ -170,6 +170,24 @@ def test_indexer_learns_the_attention_distribution(single_rank):
     assert losses[-1] < 0.5 * losses[0]
 
 
+def test_recomputed_up_projections_change_nothing(single_rank):
+    from mindspeed_b200.models.attention import MLASelfAttention
+    S, B = 12, 2
+    rope = _rope(S, 8)
+    a = MLASelfAttention(_mla_config(experimental_attention_variant=None))
+    b = MLASelfAttention(_mla_config(experimental_attention_variant=None, recompute_mla_up_proj=True))
+    b.load_state_dict(a.state_dict())
+    x1 = torch.randn(S, B, 64, requires_grad=True)
+    x2 = x1.detach().clone().requires_grad_(True)
+    y1, _ = a(x1, rotary_pos_emb=rope)
+    y2, _ = b(x2, rotary_pos_emb=rope)
+    assert torch.allclose(y1, y2, atol=1e-6)
+    y1.pow(2).sum().backward(); y2.pow(2).sum().backward()
+    assert torch.allclose(x1.grad, x2.grad, atol=1e-6)
+    for (n, p), (_, q) in zip(a.named_parameters(), b.named_parameters()):
+        assert torch.allclose(p.grad, q.grad, atol=1e-5), n
+
+
 def test_flags_validate():
     from mindspeed_b200.training.arguments import parse_args, validate_args
     base = ["--num-layers", "2", "--hidden-size", "64", "--num-attention-heads", "4", "--seq-length", "32",
