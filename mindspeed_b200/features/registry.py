@@ -820,8 +820,8 @@ class MoEFeature(Feature):
                     getattr(args, "use_multiparameter_pipeline_model_parallel", False)):
                 raise AssertionError("--moe-fb-overlap with pipeline parallelism runs on the 1F1B, interleaved and DualPipeV "
                                      "schedules, without scheduler-placed recompute or list-valued stage interfaces")
-            if getattr(args, "recompute_granularity", None) == "full" or getattr(args, "noop_layers", None):
-                raise AssertionError("--moe-fb-overlap keeps the staged layer graphs: no full recompute, no no-op layers")
+            if getattr(args, "recompute_granularity", None) == "full":
+                raise AssertionError("--moe-fb-overlap keeps the staged layer graphs: no full recompute")
         if args.moe_alltoall_mc2 and getattr(args, "use_ascend_mc2", False) and ne:
             pass
         if args.moe_tp_extend_ep and ne and ne % (getattr(args, "tensor_model_parallel_size", 1) *

@@ -287,7 +287,7 @@ class BlockOverlap:
     """
 
     def __init__(self, layers: Sequence):
-        self.staged = [StagedMoELayer(l) for l in layers]
+        self.staged = [StagedMoELayer(l) for l in layers if hasattr(l, "mlp")]     # no-op layers are identities: left out
         self.streams: Optional[_Streams] = None
         self.prev = None          # (graphs, block input, output leaf) of the micro-batch whose backward is pending
 
@@ -348,7 +348,7 @@ class StagedBlockState:
     interleaved schedule) and dualpipev/dualpipev_schedules.py:310-346 (overlap phase)."""
 
     def __init__(self, layers: Sequence):
-        self.staged = [StagedMoELayer(l) for l in layers]
+        self.staged = [StagedMoELayer(l) for l in layers if hasattr(l, "mlp")]     # no-op layers are identities: left out
         self.streams: Optional[_Streams] = None
         self.records = {}
 

@@ -91,7 +91,10 @@ def run_plan(plan: Plan, *, forward_step_func, data_iterator, model, num_microba
     specs = S.get_tensor_specs(seq_length=seq_length, micro_batch_size=micro_batch_size, config=config)
     multi = S.is_multi_parameter(config)
     gspecs = [sp for sp in specs if sp[1].is_floating_point]
-    dev = next(model[0].parameters()).device
+    # a chunk may hold no parameters at all (only no-op layers): take the device from any chunk that has some
+    dev = next((p.device for m in model for p in m.parameters()),
+               torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() and dist.get_backend() != "gloo"
+               else torch.device("cpu"))
 
     mb_sizes = getattr(config, "micro_batch_sizes", None)       # --optimized-mbs-list: the batch axis differs per micro-batch
 

@@ -414,10 +414,15 @@ def check_kernel_status():
     G.check_status()
 
 
+def _model_device(model) -> torch.device:
+    """Device of the model's parameters (a chunk made of no-op layers only has none: any other chunk answers)."""
+    return next((p.device for m in model for p in m.parameters()), torch.device("cpu"))
+
+
 def calc_params_l2_norm(model) -> float:
     """L2 norm of all parameters of the job: tensor-parallel duplicates and shared embeddings counted once, summed over
     the model-parallel group (and the expert-parallel ranks for expert weights)."""
-    dense = torch.zeros(1, dtype=torch.float32, device=next(model[0].parameters()).device)
+    dense = torch.zeros(1, dtype=torch.float32, device=_model_device(model))
     expert = torch.zeros_like(dense)
     tp_rank = ps.get_tensor_model_parallel_rank()
     for chunk in model:
@@ -471,7 +476,7 @@ def train(forward_step_func, model, optimizer, opt_param_scheduler, train_data_i
         if getattr(args, "manual_gc", False) and args.manual_gc_interval and iteration % args.manual_gc_interval == 0:
             import gc
             gc.collect()                     # every rank at the same step: no rank stalls the others at a random moment
-        if torch.cuda.is_available() and next(model[0].parameters()).is_cuda:
+        if torch.cuda.is_available() and _model_device(model).type == "cuda":
             torch.cuda.synchronize()
         check_kernel_status()
         elapsed = time.time() - t0
@@ -489,7 +494,7 @@ def train(forward_step_func, model, optimizer, opt_param_scheduler, train_data_i
                 calls = get_num_microbatches() * min(args.log_interval, iteration)
                 tracker = ps.get_moe_layer_wise_logging_tracker()
                 if "load_balancing_loss" not in tracker:         # a stage without MoE layers still joins the reduction
-                    dev = next(model[0].parameters()).device
+                    dev = _model_device(model)
                     tracker["load_balancing_loss"] = {"values": torch.zeros(args.num_layers, device=dev)}
                 for name, per_layer in reduce_moe_metrics(tracker, calls).items():
                     n_moe = max(1, int((per_layer != 0).sum()))

@@ -38,7 +38,10 @@ def loss_func(loss_mask, output_tensor):
 
 
 def forward_step(data_iterator, model):
-    dev = next(model.parameters()).device
+    dev = next((p.device for p in model.parameters()), None)
+    if dev is None:           # a pipeline chunk made of no-op layers only holds no parameters
+        on_gpu = torch.cuda.is_available() and torch.distributed.is_initialized() and torch.distributed.get_backend() != "gloo"
+        dev = torch.device("cuda", torch.cuda.current_device()) if on_gpu else torch.device("cpu")
     tokens, labels, loss_mask, attention_mask, position_ids, packed = get_batch(data_iterator, dev, return_packed=True)
     args = get_args()
     if getattr(args, "qad_enable", False):

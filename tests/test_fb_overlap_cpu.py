@@ -133,7 +133,9 @@ def _train_pp(rank, world, extra):
     return [h.get("lm loss") for h in hist]
 
 
-@pytest.mark.parametrize("schedule", [[], ["--num-layers-per-virtual-pipeline-stage", "1"], ["--schedules-method", "dualpipev"]])
+@pytest.mark.parametrize("schedule", [[], ["--num-layers-per-virtual-pipeline-stage", "1"], ["--schedules-method", "dualpipev"],
+                                      # a no-op layer (identity, used to balance stages) inside the overlapped chunks
+                                      ["--schedules-method", "dualpipev", "--noop-layers", "1"]])
 def test_pipeline_schedules_with_fb_overlap_match_plain(schedule):
     """Pipeline 2 x expert parallel 2 on four ranks: with ``--moe-fb-overlap`` the schedules put an F and a B of different
     micro-batches into one slot and interleave them stage by stage; the losses are those of the unpaired schedule."""
