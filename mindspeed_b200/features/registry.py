@@ -655,7 +655,12 @@ class PipelineMiscFeature(Feature):
             if getattr(args, "schedules_method", None):
                 raise AssertionError("recompute scheduling applies to the 1F1B and interleaved schedules only")
             if getattr(args, "recompute_granularity", None):
-                raise AssertionError("scheduler-placed recompute replaces --recompute-granularity; do not set both")
+                # launch scripts give the schedule flag on top of --recompute-granularity full: the scheduler then places the
+                # recompute of every layer it covers, so the in-backward recompute is switched off
+                from ..utils.logging import print_rank_0
+                print_rank_0("note: scheduler-placed recompute (--recompute-in-bubble / --recompute-in-advance) takes the place of "
+                             "--recompute-granularity / --recompute-method / --recompute-num-layers")
+                args.recompute_granularity, args.recompute_method, args.recompute_num_layers = None, None, None
         if isinstance(args.noop_layers, str):
             args.noop_layers = sorted({int(x) for x in args.noop_layers.split(",") if x != ""})
         if isinstance(args.pipeline_num_transformer_layers, str):

@@ -266,6 +266,28 @@ def parse_args(extra_args_provider=None, ignore_unknown_args=False, args_list=No
     return args
 
 
+def _layer_pattern(text: str):
+    """``--moe-layer-freq``: an integer N (every N-th layer) or a list expression such as ``([0]*3+[1]*1)*4`` - lists of
+    integers joined by ``+`` and repeated by ``*``.  Evaluated from the syntax tree: nothing but those forms is accepted."""
+    import ast
+
+    def ev(n):
+        if isinstance(n, ast.Expression):
+            return ev(n.body)
+        if isinstance(n, ast.Constant) and isinstance(n.value, int):
+            return n.value
+        if isinstance(n, (ast.List, ast.Tuple)):
+            return [ev(e) for e in n.elts]
+        if isinstance(n, ast.BinOp) and isinstance(n.op, (ast.Add, ast.Mult)):
+            a, b = ev(n.left), ev(n.right)
+            if isinstance(n.op, ast.Add) and isinstance(a, list) and isinstance(b, list):
+                return a + b
+            if isinstance(n.op, ast.Mult) and (isinstance(a, list) != isinstance(b, list) or (isinstance(a, int) and isinstance(b, int))):
+                return a * b
+        raise AssertionError(f"--moe-layer-freq: cannot read {text!r} (an integer, or integer lists combined with + and *)")
+    return ev(ast.parse(text.strip(), mode="eval"))
+
+
 def _core_validate(args):
     mp = args.tensor_model_parallel_size * args.pipeline_model_parallel_size * args.context_parallel_size
     if args.world_size % mp != 0:
@@ -310,6 +332,7 @@ def _core_validate(args):
         args.weight_decay = args.start_weight_decay
     if args.use_torch_fsdp2 or (args.use_custom_fsdp and args.data_parallel_sharding_strategy == "optim_grads_params"):
         args.layerzero = True                                        # parameters, gradients and optimizer state sharded
+        args.use_distributed_optimizer = False                       # ... which includes what the distributed optimizer shards
     elif args.use_custom_fsdp and args.data_parallel_sharding_strategy in ("optim", "optim_grads"):
         args.use_distributed_optimizer = True                        # optimizer state (and reduce-scattered gradients) sharded
     if args.manual_gc and args.manual_gc_interval < 0:
@@ -345,9 +368,7 @@ def _core_validate(args):
         vpp = args.num_virtual_stages_per_pipeline_rank
     args.virtual_pipeline_model_parallel_size = vpp
     if isinstance(args.moe_layer_freq, str):
-        import ast
-        v = ast.literal_eval(args.moe_layer_freq)
-        args.moe_layer_freq = v
+        args.moe_layer_freq = _layer_pattern(args.moe_layer_freq)
     if args.num_experts is not None and args.expert_model_parallel_size > 1:
         if args.num_experts % args.expert_model_parallel_size != 0:
             raise AssertionError("num_experts must be divisible by expert parallel size")

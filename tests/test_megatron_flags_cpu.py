@@ -207,3 +207,31 @@ position_embedding_type: rope
     cfg = core_transformer_config_from_args(a)
     assert cfg.layernorm_epsilon == 0.00002 and cfg.layernorm_zero_centered_gamma and cfg.gated_linear_unit
     assert cfg.num_query_groups == 4 and cfg.sequence_parallel and not cfg.add_bias_linear and cfg.num_moe_experts is None
+
+
+def test_launch_script_combinations_validate(monkeypatch):
+    """Combinations the reference's own launch scripts use."""
+    monkeypatch.setenv("WORLD_SIZE", "8")
+    from mindspeed_b200.training.arguments import _layer_pattern, parse_args, validate_args
+    base = ["--num-layers", "4", "--hidden-size", "64", "--num-attention-heads", "4", "--seq-length", "32",
+            "--micro-batch-size", "1", "--vocab-size", "128"]
+    assert _layer_pattern("([0]*1+[1]*3)") == [0, 1, 1, 1] and _layer_pattern("2") == 2
+    with pytest.raises(AssertionError):
+        _layer_pattern("__import__('os').getcwd()")
+    a = validate_args(parse_args(args_list=base + ["--num-experts", "4", "--moe-layer-freq", "([0]*1+[1]*3)"]))
+    assert a.moe_layer_freq == [0, 1, 1, 1]
+    # data-parallel sharding of everything given together with the distributed optimizer
+    a = validate_args(parse_args(args_list=base + ["--use-custom-fsdp", "--data-parallel-sharding-strategy", "optim_grads_params",
+                                                   "--use-distributed-optimizer"]))
+    assert a.layerzero and not a.use_distributed_optimizer
+    # scheduler-placed recompute on top of full recompute flags: the scheduler takes over
+    a = validate_args(parse_args(args_list=base + ["--pipeline-model-parallel-size", "2", "--recompute-in-advance",
+                                                   "--recompute-granularity", "full", "--recompute-method", "block",
+                                                   "--recompute-num-layers", "2"]))
+    assert a.recompute_in_advance and a.recompute_granularity is None
+    # forward/backward overlap of the DualPipeV schedule with a no-op layer
+    a = validate_args(parse_args(args_list=base + ["--pipeline-model-parallel-size", "2", "--expert-model-parallel-size", "4",
+                                                   "--num-experts", "8", "--moe-grouped-gemm", "--moe-token-dispatcher-type", "alltoall",
+                                                   "--schedules-method", "dualpipev", "--moe-fb-overlap", "--noop-layers", "3",
+                                                   "--global-batch-size", "16"]))
+    assert a.moe_fb_overlap and a.noop_layers == [3]
